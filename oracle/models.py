@@ -1,0 +1,254 @@
+"""CPU oracle, part 1: the five benchmark models as plain PyTorch modules.
+
+TEST INFRASTRUCTURE ONLY. Nothing on the product path may import this package;
+it is the checker for the CUDA path (tests, the smoke check and the CPU
+baseline leg of the benchmark).
+
+Why PyTorch CPU eager is the oracle: the reference pins every compiled result
+to PyTorch CPU eager with ``torch.allclose(rtol=1e-5, atol=1e-5)``
+(llcompiler/test_models/utility.py:18-28, used by every script under
+test/python/ops/).  Its own CPU lowering needs LLVM/MLIR/StableHLO sources
+that are not vendored, so it cannot be built offline; the eager result the
+reference compares itself against is therefore the ground truth here too.
+
+Parity status: pinned (through the reference's own pin) for the ops the
+reference tests under test/python/ops; "parity unpinned" for LayerNorm, GELU,
+embedding, softmax-as-one-op, global average pool and every bf16 path, because
+the reference has no working path for them (include/llcompiler/Dialect/LLH/IR/
+LLHOps.td:337-339, 454-463, 519-526 declare some of them without a lowering).
+
+All models are built after ``torch.manual_seed(0)``; inputs come from
+``torch.Generator().manual_seed(1)``.
+"""
+from __future__ import annotations
+
+import math
+from dataclasses import dataclass
+from typing import Callable, List, Tuple
+
+import torch
+import torch.nn as nn
+import torch.nn.functional as F
+
+
+# --------------------------------------------------------------------------
+# cfg1: 2-layer MLP (the reference's Linear test family,
+# llcompiler/test_models/ops/linear.py, scaled to 784-512-10 with biases)
+# --------------------------------------------------------------------------
+class MLP(nn.Module):
+    def __init__(self, d_in: int = 784, d_hidden: int = 512, d_out: int = 10):
+        super().__init__()
+        self.fc1 = nn.Linear(d_in, d_hidden)
+        self.fc2 = nn.Linear(d_hidden, d_out)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        return self.fc2(torch.relu(self.fc1(x)))
+
+
+# --------------------------------------------------------------------------
+# cfg3: one pre-LayerNorm transformer encoder layer; attention written with
+# explicit matmul / softmax so that it decomposes to the bmm, amax, sub, exp,
+# sum, div chain the reference's importer understands
+# (llcompiler/compiler/torch_compile_config.py:12-28 lists aten._softmax as
+# decomposed; llcompiler/test_models/models/multi_head_attention.py is the
+# reference's own attention test model).
+# --------------------------------------------------------------------------
+class SelfAttention(nn.Module):
+    def __init__(self, d_model: int, n_heads: int):
+        super().__init__()
+        self.h = n_heads
+        self.dh = d_model // n_heads
+        self.q = nn.Linear(d_model, d_model)
+        self.k = nn.Linear(d_model, d_model)
+        self.v = nn.Linear(d_model, d_model)
+        self.o = nn.Linear(d_model, d_model)
+
+    def forward(self, x: torch.Tensor, add_mask: torch.Tensor | None = None) -> torch.Tensor:
+        b, s, d = x.shape
+        q = self.q(x).view(b, s, self.h, self.dh).permute(0, 2, 1, 3)
+        k = self.k(x).view(b, s, self.h, self.dh).permute(0, 2, 1, 3)
+        v = self.v(x).view(b, s, self.h, self.dh).permute(0, 2, 1, 3)
+        scores = torch.matmul(q, k.transpose(-1, -2)) / math.sqrt(self.dh)
+        if add_mask is not None:
+            scores = scores + add_mask
+        p = torch.softmax(scores, dim=-1)
+        ctx = torch.matmul(p, v).permute(0, 2, 1, 3).reshape(b, s, d)
+        return self.o(ctx)
+
+
+class PreLNEncoderLayer(nn.Module):
+    def __init__(self, d_model: int = 768, n_heads: int = 12, d_ff: int = 3072):
+        super().__init__()
+        self.ln1 = nn.LayerNorm(d_model)
+        self.attn = SelfAttention(d_model, n_heads)
+        self.ln2 = nn.LayerNorm(d_model)
+        self.ff1 = nn.Linear(d_model, d_ff)
+        self.ff2 = nn.Linear(d_ff, d_model)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        x = x + self.attn(self.ln1(x))
+        x = x + self.ff2(F.gelu(self.ff1(self.ln2(x))))
+        return x
+
+
+# --------------------------------------------------------------------------
+# cfg5: BERT-base-shaped encoder (post-LayerNorm), token + learned position
+# embeddings, LayerNorm after the embedding sum, additive attention mask
+# built from the 0/1 mask input.
+# --------------------------------------------------------------------------
+class PostLNEncoderLayer(nn.Module):
+    def __init__(self, d_model: int, n_heads: int, d_ff: int):
+        super().__init__()
+        self.attn = SelfAttention(d_model, n_heads)
+        self.ln1 = nn.LayerNorm(d_model, eps=1e-12)
+        self.ff1 = nn.Linear(d_model, d_ff)
+        self.ff2 = nn.Linear(d_ff, d_model)
+        self.ln2 = nn.LayerNorm(d_model, eps=1e-12)
+
+    def forward(self, x: torch.Tensor, add_mask: torch.Tensor) -> torch.Tensor:
+        x = self.ln1(x + self.attn(x, add_mask))
+        x = self.ln2(x + self.ff2(F.gelu(self.ff1(x))))
+        return x
+
+
+class BertEncoder(nn.Module):
+    def __init__(self, n_layers: int = 12, d_model: int = 768, n_heads: int = 12,
+                 d_ff: int = 3072, vocab: int = 30522, max_pos: int = 512):
+        super().__init__()
+        self.tok = nn.Embedding(vocab, d_model)
+        self.pos = nn.Embedding(max_pos, d_model)
+        self.ln = nn.LayerNorm(d_model, eps=1e-12)
+        self.layers = nn.ModuleList(
+            [PostLNEncoderLayer(d_model, n_heads, d_ff) for _ in range(n_layers)])
+        self.register_buffer("pos_ids", torch.arange(max_pos), persistent=False)
+
+    def forward(self, ids: torch.Tensor, mask: torch.Tensor) -> torch.Tensor:
+        s = ids.shape[1]
+        x = self.tok(ids) + self.pos(self.pos_ids[:s])
+        x = self.ln(x)
+        add_mask = (1.0 - mask.to(x.dtype))[:, None, None, :] * -10000.0
+        for layer in self.layers:
+            x = layer(x, add_mask)
+        return x
+
+
+# --------------------------------------------------------------------------
+# initialisers named in the benchmark configurations
+# --------------------------------------------------------------------------
+def _init_xavier(m: nn.Module) -> None:
+    for mod in m.modules():
+        if isinstance(mod, nn.Linear):
+            nn.init.xavier_uniform_(mod.weight)
+            nn.init.zeros_(mod.bias)
+
+
+def _init_bert(m: nn.Module) -> None:
+    for mod in m.modules():
+        if isinstance(mod, nn.Linear):
+            nn.init.normal_(mod.weight, 0.0, 0.02)
+            nn.init.zeros_(mod.bias)
+        elif isinstance(mod, nn.Embedding):
+            nn.init.normal_(mod.weight, 0.0, 0.02)
+
+
+def _resnet(kind: str) -> nn.Module:
+    # torchvision's constructor already applies kaiming_normal_(fan_out, relu)
+    # to every conv and gamma=1 / beta=0 to every BatchNorm; running stats start
+    # at mean=0, var=1 (llcompiler/test_models/models/resnet.py:18-39 wraps the
+    # same torchvision family).
+    import torchvision
+    net = getattr(torchvision.models, kind)(weights=None)
+    return net
+
+
+@dataclass
+class Config:
+    name: str
+    build: Callable[[], nn.Module]
+    make_inputs: Callable[..., Tuple[torch.Tensor, ...]]
+    dtype: str          # arithmetic type of the CUDA path
+    rtol: float         # relative tolerance stated by the benchmark definition
+    batch: int
+    dynamic: bool
+    flops_per_sample: float
+
+
+def _gen() -> torch.Generator:
+    return torch.Generator().manual_seed(1)
+
+
+def _mlp_inputs(batch: int = 64):
+    return (torch.randn(batch, 784, generator=_gen()),)
+
+
+def _img_inputs(batch: int):
+    return (torch.randn(batch, 3, 224, 224, generator=_gen()),)
+
+
+def _enc_inputs(batch: int = 8, seq: int = 128):
+    return (torch.randn(batch, seq, 768, generator=_gen()),)
+
+
+def _bert_inputs(batch: int = 256, seq: int = 384):
+    ids = torch.randint(0, 30522, (batch, seq), generator=_gen(), dtype=torch.int64)
+    return (ids, torch.ones(batch, seq, dtype=torch.int64))
+
+
+def build_model(name: str, **kw) -> nn.Module:
+    """Seeded construction of one of the benchmark models, eval mode, fp32."""
+    torch.manual_seed(0)
+    if name == "mlp":
+        m = MLP()
+    elif name == "resnet18":
+        m = _resnet("resnet18")
+    elif name == "resnet50":
+        m = _resnet("resnet50")
+    elif name == "encoder":
+        m = PreLNEncoderLayer()
+        _init_xavier(m)
+    elif name == "bert":
+        m = BertEncoder(**kw)
+        _init_bert(m)
+    else:
+        raise KeyError(name)
+    return m.eval()
+
+
+CONFIGS = {
+    "mlp": Config("mlp", lambda: build_model("mlp"), _mlp_inputs, "f32", 1e-4, 64, True,
+                  5.2036e7 / 64),
+    "resnet18": Config("resnet18", lambda: build_model("resnet18"),
+                       lambda batch=32: _img_inputs(batch), "f32", 1e-4, 32, False, 3.628e9),
+    "encoder": Config("encoder", lambda: build_model("encoder"), _enc_inputs, "tf32", 2e-2, 8,
+                      True, 1.4898e10 / 8),
+    "resnet50": Config("resnet50", lambda: build_model("resnet50"),
+                       lambda batch=256: _img_inputs(batch), "bf16", 2e-2, 256, False, 8.178e9),
+    "bert": Config("bert", lambda: build_model("bert"), _bert_inputs, "bf16", 2e-2, 256, False,
+                   1.809e13 / 256),
+}
+
+
+def round_to_bf16_(m: nn.Module) -> nn.Module:
+    """Round every floating parameter/buffer to bf16 and back, in place.
+
+    The bf16 configurations are judged against the fp32 eager result computed
+    on bf16-rounded parameters and inputs, so that the comparison measures the
+    arithmetic of the CUDA path and not the storage rounding.
+    """
+    with torch.no_grad():
+        for t in list(m.parameters()) + list(m.buffers()):
+            if t.is_floating_point():
+                t.copy_(t.to(torch.bfloat16).to(t.dtype))
+    return m
+
+
+def max_rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
+    """Largest |got-want| divided by the largest |want| (one scale per tensor).
+
+    A single scale per tensor is the relative error that survives values that
+    are legitimately near zero (post-ReLU activations, logits around 0).
+    """
+    got = got.detach().double().cpu()
+    want = want.detach().double().cpu()
+    denom = want.abs().max().clamp_min(1e-30)
+    return float((got - want).abs().max() / denom)
