@@ -1,0 +1,83 @@
+"""ctypes view of the C ABI in include/llc_runtime.h and include/llc_cuda.h.
+
+The product path goes through the ``llcompiler_`` extension module; this thin
+layer exists for the tests (which must call kernels through the C ABI) and for
+tools that only need the compile side.  It never falls back to anything: a
+missing library is an ImportError with the build command in it.
+"""
+from __future__ import annotations
+
+import ctypes
+from ctypes import POINTER, Structure, byref, c_char_p, c_int, c_int32, c_int64, c_size_t, c_void_p
+from pathlib import Path
+from typing import Optional, Sequence
+
+LIB_PATH = Path(__file__).resolve().parent / "lib" / "libllc_cuda.so"
+
+
+class LlcTensor(Structure):
+    _fields_ = [("data", c_void_p), ("dtype", c_int32), ("device", c_int32), ("rank", c_int32),
+                ("sizes", POINTER(c_int64)), ("strides", POINTER(c_int64))]
+
+
+class LlcOptions(Structure):
+    _fields_ = [(n, c_char_p) for n in ("mode", "target", "pipeline", "global_layout", "log_root",
+                                        "log_level", "cpu", "mtriple", "precision")]
+
+
+_lib: Optional[ctypes.CDLL] = None
+
+
+def lib() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not LIB_PATH.exists():
+            raise ImportError(f"{LIB_PATH} is missing; build it with `python -m llcompiler_b200.build`")
+        _lib = ctypes.CDLL(str(LIB_PATH))
+        _lib.llc_last_error.restype = c_char_p
+        _lib.llc_version.restype = c_char_p
+        _lib.llc_compile.argtypes = [c_char_p, POINTER(LlcOptions), c_char_p, c_size_t]
+        _lib.llc_run_pass.argtypes = [c_char_p, c_char_p, POINTER(LlcOptions), POINTER(c_char_p)]
+    return _lib
+
+
+class LlcError(RuntimeError):
+    def __init__(self, code: int, message: str):
+        super().__init__(f"[llc status {code}] {message}")
+        self.code = code
+
+
+def check(code: int) -> None:
+    if code != 0:
+        raise LlcError(code, lib().llc_last_error().decode("utf-8", "replace"))
+
+
+def make_options(**kw) -> LlcOptions:
+    o = LlcOptions()
+    for k, v in kw.items():
+        if v is not None:
+            setattr(o, k, str(v).encode())
+    return o
+
+
+def run_pass(text: str, pass_name: str, **options) -> str:
+    out = c_char_p()
+    o = make_options(**options)
+    check(lib().llc_run_pass(text.encode(), pass_name.encode(), byref(o), byref(out)))
+    return out.value.decode()
+
+
+def compile_text(text: str, **options) -> str:
+    buf = ctypes.create_string_buffer(1024)
+    o = make_options(**options)
+    check(lib().llc_compile(text.encode(), byref(o), buf, len(buf)))
+    return buf.value.decode()
+
+
+def tensor_desc(ptr: int, dtype_code: int, device: int, sizes: Sequence[int], strides: Sequence[int]):
+    """Returns (LlcTensor, keepalive) for caller-owned memory."""
+    n = len(sizes)
+    s = (c_int64 * max(n, 1))(*sizes)
+    st = (c_int64 * max(n, 1))(*strides)
+    t = LlcTensor(c_void_p(ptr), dtype_code, device, n, ctypes.cast(s, POINTER(c_int64)), ctypes.cast(st, POINTER(c_int64)))
+    return t, (s, st)

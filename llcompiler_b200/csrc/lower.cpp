@@ -1,0 +1,1250 @@
+// The GPU pipeline: LLH module -> kernel plan.
+//
+// This replaces everything the reference does below the LLH level
+// (src/Pipeline/TransformPipeline.cpp:100-226: LLH -> StableHLO -> linalg ->
+// affine -> LLVM).  Ops are visited in program order.  Every tensor value is
+// one of: a strided view onto a buffer, a lazy elementwise expression tree, the
+// not-yet-emitted result of a GEMM/conv call that can still absorb elementwise
+// consumers into its epilogue, or a reshape that could not be expressed on
+// strides.  Data movement ops (reshape, transpose, broadcast_to, slice,
+// extract) only rewrite strides; layout changes (the reference's
+// transform-layout pass, src/Dialect/LLH/Transforms/TransformLayout.cpp:141-198)
+// fall out of the same mechanism because an NHWC buffer is an NCHW-shaped view
+// with permuted strides.  Shapes are symbolic expressions following the
+// reference's inference rules (src/Dialect/LLH/IR/LLHinfersymbolShape.cpp:
+// 114-212 broadcast/reduce, :257-292 and :640-672 conv/pool, :531-585 matmul).
+#include <cmath>
+#include <cstring>
+#include <functional>
+#include <set>
+#include <sstream>
+
+#include "plan.h"
+
+namespace llc {
+namespace {
+
+[[noreturn]] void fail(const std::string& m) { throw std::runtime_error("llc compile: " + m); }
+
+struct ENode {
+  enum Kind { Leaf, Const, Op } kind = Const;
+  std::string op;
+  int a = -1, b = -1, c = -1;
+  View leaf;
+  bool leafConst = false;
+  double cst = 0;
+};
+
+struct TV {
+  enum Kind { None, Scalar, ViewK, Lazy, Pending, Deferred } kind = None;
+  Expr scalar;                 // Scalar (i64)
+  double fscalar = 0; bool isFloatScalar = false;
+  DType dtype = DType::F32;
+  std::vector<Expr> shape;
+  View view;                   // ViewK / Pending (logical view onto the result buffer) / Deferred (source)
+  int root = -1;               // Lazy
+  int pending = -1;            // Pending
+  bool isConst = false;        // computable at load time
+};
+
+struct PendingK {
+  Step step;
+  int buf = -1;
+  View nativeOut;
+  int chanDim = -1;            // channel dim in nativeOut
+  int stage = 0;               // 0 affine, 1 residual added, 2 activation applied
+  int scaleRoot = -1, shiftRoot = -1;
+  bool hasRes = false; View res;
+  std::string act = "none";
+  bool emitted = false;
+};
+
+std::vector<int64_t> intArray(const Op* op, const char* name, std::vector<int64_t> dflt = {}) {
+  const Attr* a = op->attr(name);
+  if (!a) return dflt;
+  if (a->kind == Attr::IntArray) return a->ints;
+  if (a->kind == Attr::Dense) return a->ints;
+  if (a->kind == Attr::Array) { std::vector<int64_t> o; for (auto& e : a->elems) o.push_back(e.i); return o; }
+  fail(std::string("attribute '") + name + "' of " + op->name + " is not an integer array");
+}
+
+Expr numelOf(const std::vector<Expr>& shape) { Expr n(1); for (auto& d : shape) n = n * d; return n; }
+
+std::vector<Expr> rowMajor(const std::vector<Expr>& shape) {
+  std::vector<Expr> st(shape.size());
+  Expr acc(1);
+  for (int i = (int)shape.size() - 1; i >= 0; --i) { st[i] = acc; acc = acc * shape[i]; }
+  return st;
+}
+
+bool isContiguous(const View& v) {
+  Expr acc(1);
+  for (int i = (int)v.rank() - 1; i >= 0; --i) {
+    if (v.shape[i].isConst(1)) continue;
+    if (v.strides[i] != acc) return false;
+    acc = acc * v.shape[i];
+  }
+  return true;
+}
+
+// Finds the dim order (outermost first) in which `v` is dense, if it is a permuted-contiguous view.
+bool denseOrder(const View& v, std::vector<int>& order) {
+  size_t r = v.rank();
+  std::vector<bool> used(r, false);
+  std::vector<int> inner;  // innermost first
+  Expr acc(1);
+  for (size_t n = 0; n < r; ++n) {
+    int pick = -1;
+    for (size_t d = 0; d < r; ++d) if (!used[d] && !v.shape[d].isConst(1) && v.strides[d] == acc) { pick = (int)d; break; }
+    if (pick < 0) { for (size_t d = 0; d < r; ++d) if (!used[d] && v.shape[d].isConst(1)) { pick = (int)d; break; } }
+    if (pick < 0) return false;
+    used[pick] = true; inner.push_back(pick); acc = acc * v.shape[pick];
+  }
+  order.assign(inner.rbegin(), inner.rend());
+  return true;
+}
+
+// Re-expresses `v` with a new shape without moving data, when the strides allow it.
+bool reshapeView(const View& v, const std::vector<Expr>& newShape, View& out) {
+  out = v; out.shape = newShape; out.strides.assign(newShape.size(), Expr(0));
+  // maximal mergeable chunks of the old view (size-1 dims dropped)
+  struct Chunk { Expr numel, base; };
+  std::vector<Chunk> chunks;
+  for (size_t d = 0; d < v.rank(); ++d) {
+    if (v.shape[d].isConst(1)) continue;
+    if (!chunks.empty() && chunks.back().base == v.strides[d] * v.shape[d]) { chunks.back().numel = chunks.back().numel * v.shape[d]; chunks.back().base = v.strides[d]; }
+    else chunks.push_back({v.shape[d], v.strides[d]});
+  }
+  size_t c = 0; Expr acc(1); std::vector<size_t> group;
+  auto flush = [&](const Chunk& ch) {
+    Expr st = ch.base;
+    for (int k = (int)group.size() - 1; k >= 0; --k) { out.strides[group[k]] = st; st = st * newShape[group[k]]; }
+    group.clear(); acc = Expr(1);
+  };
+  for (size_t d = 0; d < newShape.size(); ++d) {
+    if (newShape[d].isConst(1)) { out.strides[d] = Expr(0); continue; }
+    if (c >= chunks.size()) return false;
+    group.push_back(d); acc = acc * newShape[d];
+    if (acc == chunks[c].numel) { flush(chunks[c]); ++c; }
+  }
+  if (!group.empty() || c != chunks.size()) return false;
+  // size-1 dims get the stride a contiguous tensor would have (harmless, keeps isContiguous true)
+  Expr run(1);
+  for (int d = (int)newShape.size() - 1; d >= 0; --d) { if (newShape[d].isConst(1)) out.strides[d] = run; else run = out.strides[d] * newShape[d]; }
+  return true;
+}
+
+View broadcastView(const View& v, const std::vector<Expr>& shape, const std::vector<int64_t>& castDims) {
+  View o = v; o.shape = shape; o.strides.assign(shape.size(), Expr(0));
+  for (size_t i = 0; i < v.rank(); ++i) {
+    int64_t d = castDims[i];
+    if (d < 0 || d >= (int64_t)shape.size()) fail("broadcast dim out of range");
+    if (v.shape[i] == shape[d]) o.strides[d] = v.shape[i].isConst(1) ? Expr(0) : v.strides[i];
+    else if (v.shape[i].isConst(1)) o.strides[d] = Expr(0);
+    else fail("cannot broadcast extent " + v.shape[i].str() + " to " + shape[d].str());
+  }
+  return o;
+}
+
+std::string fmtDouble(double v) { char b[64]; snprintf(b, sizeof b, "%.9g", v); return b; }
+
+// ---------------------------------------------------------------------------------------------
+struct Lowering {
+  Module& m;
+  const CompileOptionsData& opts;
+  Plan plan;
+  std::vector<ENode> nodes;
+  std::vector<PendingK> pend;
+  std::map<Value*, TV> tvs;
+  std::map<std::string, int> constVecCache;
+
+  Lowering(Module& mod, const CompileOptionsData& o) : m(mod), opts(o) {}
+
+  // ---- buffers
+  int newBuffer(DType dt, const Expr& numel, BufferDecl::Kind kind) {
+    BufferDecl b; b.dtype = dt; b.numel = numel; b.kind = kind;
+    plan.buffers.push_back(b);
+    return (int)plan.buffers.size() - 1;
+  }
+  View freshView(DType dt, const std::vector<Expr>& shape, bool isConst, const std::vector<Expr>* strides = nullptr) {
+    Expr n = numelOf(shape);
+    View v; v.dtype = dt; v.shape = shape; v.strides = strides ? *strides : rowMajor(shape);
+    v.buf = newBuffer(dt, n, (isConst && n.isConst()) ? BufferDecl::Const : BufferDecl::Temp);
+    return v;
+  }
+  bool bufIsConst(int buf) const { auto k = plan.buffers[buf].kind; return k == BufferDecl::Weight || k == BufferDecl::Const; }
+
+  // ---- lazy trees
+  int leafNode(const View& v) { ENode n; n.kind = ENode::Leaf; n.leaf = v; n.leafConst = bufIsConst(v.buf); nodes.push_back(n); return (int)nodes.size() - 1; }
+  int constNode(double c) { ENode n; n.kind = ENode::Const; n.cst = c; nodes.push_back(n); return (int)nodes.size() - 1; }
+  int opNode(const std::string& op, int a, int b = -1, int c = -1) { ENode n; n.kind = ENode::Op; n.op = op; n.a = a; n.b = b; n.c = c; nodes.push_back(n); return (int)nodes.size() - 1; }
+  bool treeIsConst(int root) {
+    const ENode& n = nodes[root];
+    if (n.kind == ENode::Leaf) return n.leafConst;
+    if (n.kind == ENode::Const) return true;
+    return treeIsConst(n.a) && (n.b < 0 || treeIsConst(n.b)) && (n.c < 0 || treeIsConst(n.c));
+  }
+  int mapLeaves(int root, const std::function<bool(const View&, View&)>& f, std::map<int, int>& memo, bool& ok) {
+    auto it = memo.find(root);
+    if (it != memo.end()) return it->second;
+    ENode n = nodes[root];
+    int res;
+    if (n.kind == ENode::Leaf) { View nv; if (!f(n.leaf, nv)) { ok = false; nv = n.leaf; } ENode c = n; c.leaf = nv; nodes.push_back(c); res = (int)nodes.size() - 1; }
+    else if (n.kind == ENode::Const) res = root;
+    else {
+      int a = mapLeaves(n.a, f, memo, ok), b = n.b >= 0 ? mapLeaves(n.b, f, memo, ok) : -1, c = n.c >= 0 ? mapLeaves(n.c, f, memo, ok) : -1;
+      ENode o = n; o.a = a; o.b = b; o.c = c; nodes.push_back(o); res = (int)nodes.size() - 1;
+    }
+    memo[root] = res;
+    return res;
+  }
+  bool splatValue(const TV& t, double& v) const {
+    if (t.kind != TV::Lazy) return false;
+    if (nodes[t.root].kind != ENode::Const) return false;
+    v = nodes[t.root].cst; return true;
+  }
+
+  // ---- eltwise emission
+  void emitEltwise(int root, const View& out, bool init) {
+    Step s; s.kernel = "eltwise"; s.init = init;
+    s.views.emplace_back("out", out);
+    std::vector<std::string> leafKeys;
+    std::map<int, int> reg;  // node -> register
+    std::vector<std::string> prog;
+    std::function<int(int)> walk = [&](int id) -> int {
+      auto it = reg.find(id);
+      if (it != reg.end()) return it->second;
+      const ENode n = nodes[id];
+      std::string ins;
+      if (n.kind == ENode::Leaf) {
+        std::string key = n.leaf.str();
+        size_t k = 0;
+        for (; k < leafKeys.size(); ++k) if (leafKeys[k] == key) break;
+        if (k == leafKeys.size()) { leafKeys.push_back(key); s.views.emplace_back("in" + std::to_string(k), n.leaf); }
+        ins = "ld" + std::to_string(k);
+      } else if (n.kind == ENode::Const) {
+        ins = "#" + fmtDouble(n.cst);
+      } else {
+        int a = walk(n.a), b = n.b >= 0 ? walk(n.b) : -1, c = n.c >= 0 ? walk(n.c) : -1;
+        ins = n.op + "," + std::to_string(a);
+        if (b >= 0) ins += "," + std::to_string(b);
+        if (c >= 0) ins += "," + std::to_string(c);
+      }
+      prog.push_back(ins);
+      reg[id] = (int)prog.size() - 1;
+      return reg[id];
+    };
+    walk(root);
+    std::string p;
+    for (size_t i = 0; i < prog.size(); ++i) p += (i ? ";" : "") + prog[i];
+    s.params.emplace_back("prog", p);
+    if (leafKeys.size() > 8) fail("elementwise fusion produced more than 8 inputs");
+    if (prog.size() > 48) fail("elementwise fusion produced more than 48 instructions");
+    plan.steps.push_back(s);
+  }
+
+  // Materialises a lazy tree.  The result layout follows the first dense, non-broadcast leaf so that
+  // NHWC data stays NHWC.
+  View materializeTree(int root, DType dt, const std::vector<Expr>& shape, const std::vector<Expr>* wantStrides = nullptr, int intoBuf = -1) {
+    bool isC = treeIsConst(root) && numelOf(shape).isConst();
+    std::vector<Expr> strides = rowMajor(shape);
+    if (wantStrides) strides = *wantStrides;
+    else {
+      std::function<bool(int)> findLeaf = [&](int id) -> bool {
+        const ENode& n = nodes[id];
+        if (n.kind == ENode::Leaf) {
+          std::vector<int> order;
+          bool nz = true; for (auto& st : n.leaf.strides) if (st.isConst(0)) nz = false;
+          for (size_t d = 0; d < n.leaf.rank(); ++d) if (n.leaf.shape[d].isConst(1)) nz = nz;  // size-1 dims are fine
+          if (n.leaf.shape == shape && denseOrder(n.leaf, order)) {
+            bool bcast = false;
+            for (size_t d = 0; d < shape.size(); ++d) if (!shape[d].isConst(1) && n.leaf.strides[d].isConst(0)) bcast = true;
+            if (!bcast) { Expr acc(1); for (int k = (int)order.size() - 1; k >= 0; --k) { strides[order[k]] = acc; acc = acc * shape[order[k]]; } return true; }
+          }
+          return false;
+        }
+        if (n.kind == ENode::Const) return false;
+        return findLeaf(n.a) || (n.b >= 0 && findLeaf(n.b)) || (n.c >= 0 && findLeaf(n.c));
+      };
+      if (intoBuf < 0) findLeaf(root);
+    }
+    View out;
+    if (intoBuf >= 0) { out.buf = intoBuf; out.dtype = dt; out.shape = shape; out.strides = strides; }
+    else out = freshView(dt, shape, isC, &strides);
+    emitEltwise(root, out, isC && intoBuf < 0);
+    return out;
+  }
+
+  // ---- pending producers
+  void emitPending(int id) {
+    PendingK& p = pend[id];
+    if (p.emitted) return;
+    p.emitted = true;
+    Step s = p.step;
+    s.views.emplace_back("out", p.nativeOut);
+    double alpha = 1.0;
+    Expr C = p.nativeOut.shape[p.chanDim];
+    auto vec = [&](int root, const char* name) {
+      const ENode& rn = nodes[root];
+      if (rn.kind == ENode::Leaf && rn.leaf.dtype == DType::F32 && rn.leaf.strides[0].isConst(1)) { s.views.emplace_back(name, rn.leaf); return; }
+      View v = materializeTree(root, DType::F32, {C});
+      s.views.emplace_back(name, v);
+    };
+    if (p.scaleRoot >= 0) {
+      if (nodes[p.scaleRoot].kind == ENode::Const) alpha = nodes[p.scaleRoot].cst;
+      else vec(p.scaleRoot, "scale");
+    }
+    if (p.shiftRoot >= 0) {
+      if (!(nodes[p.shiftRoot].kind == ENode::Const && nodes[p.shiftRoot].cst == 0.0)) {
+        int root = p.shiftRoot;
+        vec(root, "shift");   // a constant shift still becomes a per-channel vector
+      }
+    }
+    if (p.hasRes) s.views.emplace_back("res", p.res);
+    s.params.emplace_back("alpha", fmtDouble(alpha));
+    s.params.emplace_back("act", p.act);
+    plan.steps.push_back(s);
+  }
+
+  // ---- TV access
+  TV& raw(Value* v) {
+    auto it = tvs.find(v);
+    if (it == tvs.end()) fail("value " + v->name + " used before definition");
+    return it->second;
+  }
+  void settle(TV& t) { if (t.kind == TV::Pending && pend[t.pending].emitted) { t.kind = TV::ViewK; } }
+
+  // Forces a value into a strided view (emitting whatever produces it).
+  void toView(TV& t) {
+    settle(t);
+    if (t.kind == TV::ViewK) return;
+    if (t.kind == TV::Pending) { emitPending(t.pending); t.kind = TV::ViewK; return; }
+    if (t.kind == TV::Lazy) {
+      View v = materializeTree(t.root, t.dtype, t.shape);
+      t.isConst = bufIsConst(v.buf);
+      t.view = v; t.kind = TV::ViewK; return;
+    }
+    if (t.kind == TV::Deferred) {
+      // copy the strided source into a dense row-major buffer, then the reshape is free
+      std::vector<Expr> rm = rowMajor(t.view.shape);
+      View dense = materializeTree(leafNode(t.view), t.dtype, t.view.shape, &rm);
+      View r;
+      if (!reshapeView(dense, t.shape, r)) fail("internal: reshape of a dense buffer failed");
+      t.view = r; t.kind = TV::ViewK; t.isConst = bufIsConst(r.buf); return;
+    }
+    fail("expected a tensor value");
+  }
+  TV& get(Value* v) {
+    TV& t = raw(v);
+    settle(t);
+    // a value with several consumers is computed once
+    if (v->users.size() > 1 && (t.kind == TV::Pending || (t.kind == TV::Lazy && nodes[t.root].kind != ENode::Const && !isCheap(t.root))))
+      toView(t);
+    return t;
+  }
+  bool isCheap(int root) {  // leaf or constant: re-reading is free
+    return nodes[root].kind != ENode::Op;
+  }
+  View viewOf(Value* v) { TV& t = get(v); toView(t); return t.view; }
+  // A float->float convert_to is only a change of storage type: consumers that read any float
+  // type take the view underneath it instead of a converted copy.
+  bool isLeafOnly(const TV& t) const { return t.kind == TV::Lazy && nodes[t.root].kind == ENode::Leaf && isFloat(nodes[t.root].leaf.dtype) && isFloat(t.dtype); }
+  View leafOrView(Value* v) {
+    TV& t = get(v);
+    if (isLeafOnly(t)) return nodes[t.root].leaf;
+    toView(t); return t.view;
+  }
+  View contiguousLeafOrView(Value* v) {
+    TV& t = get(v);
+    if (isLeafOnly(t) && isContiguous(nodes[t.root].leaf)) return nodes[t.root].leaf;
+    return contiguousViewOf(v);
+  }
+  // If the only consumer of `res` converts it to another float type, produce that type directly.
+  DType resultDtype(Value* res) {
+    DType dt = res->type.elt;
+    if (res->users.size() == 1 && res->users[0]->name == "llh.convert_to" && isFloat(dt)) {
+      DType to = res->users[0]->results[0]->type.elt;
+      if (isFloat(to)) return to;
+    }
+    return dt;
+  }
+  View contiguousViewOf(Value* v) {
+    TV& t = get(v); toView(t);
+    if (isContiguous(t.view)) return t.view;
+    std::vector<Expr> rm = rowMajor(t.shape);
+    View d = materializeTree(leafNode(t.view), t.dtype, t.shape, &rm);
+    t.view = d; t.isConst = bufIsConst(d.buf);
+    return d;
+  }
+  View viewWithStrides(Value* v, const std::vector<Expr>& want) {
+    TV& t = get(v);
+    if (t.kind == TV::Lazy && nodes[t.root].kind == ENode::Op) {   // compute straight into the wanted layout
+      View d = materializeTree(t.root, t.dtype, t.shape, &want);
+      t.kind = TV::ViewK; t.view = d; t.isConst = bufIsConst(d.buf);
+      return d;
+    }
+    toView(t);
+    bool same = true;
+    for (size_t d = 0; d < want.size(); ++d) if (!t.shape[d].isConst(1) && t.view.strides[d] != want[d]) same = false;
+    if (same) return t.view;
+    View d = materializeTree(leafNode(t.view), t.dtype, t.shape, &want);
+    t.view = d; t.isConst = bufIsConst(d.buf);
+    return d;
+  }
+  Expr scalarOf(Value* v) {
+    TV& t = raw(v);
+    if (t.kind != TV::Scalar || t.isFloatScalar) fail("expected an integer scalar for " + v->name);
+    return t.scalar;
+  }
+
+  TV makeView(const View& v, bool isConst) { TV t; t.kind = TV::ViewK; t.view = v; t.shape = v.shape; t.dtype = v.dtype; t.isConst = isConst; return t; }
+  TV makeLazy(int root, DType dt, const std::vector<Expr>& shape) { TV t; t.kind = TV::Lazy; t.root = root; t.dtype = dt; t.shape = shape; t.isConst = treeIsConst(root); return t; }
+
+  // node for an operand inside an elementwise op, broadcast (numpy style) to `shape`
+  int operandNode(TV& t, const std::vector<Expr>& shape) {
+    if (t.kind == TV::Scalar) {
+      if (t.isFloatScalar) return constNode(t.fscalar);
+      if (t.scalar.isConst()) return constNode((double)t.scalar.constant());
+      fail("symbolic scalar used as a tensor operand");
+    }
+    if (t.kind != TV::Lazy) toView(t);
+    std::vector<int64_t> cast;
+    size_t off = shape.size() - t.shape.size();
+    for (size_t i = 0; i < t.shape.size(); ++i) cast.push_back((int64_t)(off + i));
+    if (t.kind == TV::ViewK) return leafNode(broadcastView(t.view, shape, cast));
+    if (t.shape == shape) return t.root;
+    std::map<int, int> memo; bool ok = true;
+    return mapLeaves(t.root, [&](const View& l, View& o) { o = broadcastView(l, shape, cast); return true; }, memo, ok);
+  }
+
+  std::vector<Expr> broadcastShapes(const std::vector<Expr>& a, const std::vector<Expr>& b) {
+    size_t r = std::max(a.size(), b.size());
+    std::vector<Expr> o(r);
+    for (size_t i = 0; i < r; ++i) {
+      const Expr* x = i + a.size() >= r ? &a[i + a.size() - r] : nullptr;
+      const Expr* y = i + b.size() >= r ? &b[i + b.size() - r] : nullptr;
+      if (!x) o[i] = *y; else if (!y) o[i] = *x;
+      else if (x->isConst(1)) o[i] = *y; else if (y->isConst(1)) o[i] = *x;
+      else if (*x == *y) o[i] = *x;
+      else o[i] = *x;   // symbolically different names for the same extent: trust the producer
+    }
+    return o;
+  }
+
+  // ---- epilogue absorption
+  // Restricts a tensor operand that only varies along `dim` of `shape` to a 1-D tree over that dim.
+  bool channelTree(TV& x, const std::vector<Expr>& shape, int dim, int& rootOut) {
+    if (x.kind == TV::Pending || x.kind == TV::Deferred || x.kind == TV::Scalar) return false;
+    if (x.kind == TV::ViewK && !x.isConst) return false;
+    if (x.kind == TV::Lazy && !treeIsConst(x.root)) return false;
+    int root = operandNode(x, shape);
+    std::map<int, int> memo; bool ok = true;
+    rootOut = mapLeaves(root, [&](const View& l, View& o) {
+      for (size_t d = 0; d < l.rank(); ++d) if ((int)d != dim && !l.strides[d].isConst(0) && !l.shape[d].isConst(1)) return false;
+      o = l; o.shape = {shape[dim]}; o.strides = {l.strides[dim]};
+      return true;
+    }, memo, ok);
+    return ok;
+  }
+
+  // Tries to fold `op(P, other)` into pending P's epilogue.  `pIsLhs` tells which side P is on.
+  bool absorb(const std::string& op, Value* pv, Value* ov, bool pIsLhs, Value* result) {
+    TV& pt = raw(pv);
+    settle(pt);
+    if (pt.kind != TV::Pending || pv->users.size() != 1) return false;
+    PendingK& P = pend[pt.pending];
+    // channel dim of the current logical view: unit stride, extent = channel count
+    Expr C = P.nativeOut.shape[P.chanDim];
+    int cd = -1;
+    for (size_t d = 0; d < pt.view.rank(); ++d) if (pt.view.strides[d].isConst(1) && pt.view.shape[d] == C) cd = (int)d;
+    auto finish = [&]() {
+      TV r = pt;
+      DType to = result->type.elt;
+      if (to != DType::None && isFloat(to) && to != r.dtype) { r.dtype = to; r.view.dtype = to; P.nativeOut.dtype = to; plan.buffers[P.buf].dtype = to; }
+      tvs[result] = r; return true;
+    };
+    if (!ov) {  // unary activation
+      if (P.stage == 2) return false;
+      if (op == "relu" || op == "gelu") { P.act = op; P.stage = 2; return finish(); }
+      return false;
+    }
+    TV& ot = get(ov);
+    if (broadcastShapes(pt.shape, ot.shape) != pt.shape) return false;
+    double sv;
+    bool isSplat = splatValue(ot, sv);
+    if (op == "max" && isSplat && sv == 0.0 && P.stage < 2) { P.act = "relu"; P.stage = 2; return finish(); }
+    if (P.stage == 0 && cd >= 0) {
+      int vroot = -1;
+      bool isVec = isSplat ? (vroot = constNode(sv), true) : channelTree(ot, pt.shape, cd, vroot);
+      if (isVec) {
+        if (op == "mul" || (op == "div" && pIsLhs)) {
+          P.scaleRoot = P.scaleRoot < 0 ? (op == "mul" ? vroot : opNode("div", constNode(1.0), vroot)) : opNode(op, P.scaleRoot, vroot);
+          if (P.shiftRoot >= 0) P.shiftRoot = opNode(op, P.shiftRoot, vroot);
+          foldConst(P.scaleRoot);
+          return finish();
+        }
+        if (op == "add" || (op == "sub" && pIsLhs)) {
+          P.shiftRoot = P.shiftRoot < 0 ? (op == "add" ? vroot : opNode("neg", vroot)) : opNode(op, P.shiftRoot, vroot);
+          return finish();
+        }
+        return false;
+      }
+    }
+    if (op == "add" && P.stage <= 0 + 0 && !P.hasRes) {
+      // residual: another run-time tensor of the same shape
+      if (ot.kind == TV::Lazy && nodes[ot.root].kind == ENode::Const) return false;
+      if (ot.kind == TV::Pending && ot.pending == pt.pending) return false;
+      View ov2;
+      if (isLeafOnly(ot)) ov2 = nodes[ot.root].leaf; else { toView(ot); ov2 = ot.view; }
+      std::vector<int64_t> cast; size_t off = pt.shape.size() - ot.shape.size();
+      for (size_t i = 0; i < ot.shape.size(); ++i) cast.push_back((int64_t)(off + i));
+      View r = broadcastView(ov2, pt.shape, cast);
+      bool sameLayout = true;
+      for (size_t d = 0; d < r.rank(); ++d) if (!r.shape[d].isConst(1) && r.strides[d] != pt.view.strides[d]) sameLayout = false;
+      bool isNative = pt.view.shape == P.nativeOut.shape && pt.view.strides == P.nativeOut.strides;
+      if (sameLayout) { View nr = P.nativeOut; nr.buf = r.buf; nr.offset = r.offset; nr.dtype = r.dtype; P.res = nr; }
+      else if (isNative && P.step.kernel == "gemm") P.res = r;
+      else return false;
+      P.hasRes = true; P.stage = 1;
+      return finish();
+    }
+    return false;
+  }
+  void foldConst(int& root) {
+    ENode& n = nodes[root];
+    if (n.kind == ENode::Op && n.b >= 0 && nodes[n.a].kind == ENode::Const && nodes[n.b].kind == ENode::Const) {
+      double a = nodes[n.a].cst, b = nodes[n.b].cst, r;
+      if (n.op == "mul") r = a * b; else if (n.op == "div") r = a / b; else if (n.op == "add") r = a + b; else if (n.op == "sub") r = a - b; else return;
+      root = constNode(r);
+    }
+  }
+
+  // ---- generic elementwise op
+  void eltwise(Op* op, const std::string& name) {
+    Value* res = op->results[0];
+    size_t n = op->operands.size();
+    DType outDt = res->type.elt;
+    if (n == 1 && absorb(name, op->operands[0], nullptr, true, res)) return;
+    if (n == 2) {
+      if (absorb(name, op->operands[0], op->operands[1], true, res)) return;
+      if ((name == "add" || name == "mul" || name == "max") && absorb(name, op->operands[1], op->operands[0], false, res)) return;
+    }
+    std::vector<TV*> ts;
+    std::vector<Expr> shape;
+    for (Value* v : op->operands) { TV& t = get(v); ts.push_back(&t); if (t.kind != TV::Scalar) shape = shape.empty() ? t.shape : broadcastShapes(shape, t.shape); }
+    if (shape.empty()) fail("elementwise op without tensor operands: " + op->name);
+    // identities: x*1, x/1, x+0, x-0
+    if (n == 2) {
+      double sv;
+      if (splatValue(*ts[1], sv) && ts[0]->shape == shape && ((sv == 1.0 && (name == "mul" || name == "div")) || (sv == 0.0 && (name == "add" || name == "sub"))) && ts[0]->dtype == outDt) { TV c = *ts[0]; tvs[res] = c; return; }
+      if (splatValue(*ts[0], sv) && ts[1]->shape == shape && ((sv == 1.0 && name == "mul") || (sv == 0.0 && name == "add")) && ts[1]->dtype == outDt) { TV c = *ts[1]; tvs[res] = c; return; }
+    }
+    std::vector<int> ids;
+    for (TV* t : ts) ids.push_back(operandNode(*t, shape));
+    int root = opNode(name, ids[0], n > 1 ? ids[1] : -1, n > 2 ? ids[2] : -1);
+    if (n == 2) foldConst(root);
+    tvs[res] = makeLazy(root, outDt, shape);
+  }
+
+  // ---- GEMM
+  View to4d(const View& v) {  // [.., M, K] -> [b0, b1, M, K]
+    View o = v;
+    while (o.rank() < 4) { o.shape.insert(o.shape.begin(), Expr(1)); o.strides.insert(o.strides.begin(), Expr(0)); }
+    return o;
+  }
+  std::string gemmPrecision(DType dt) {
+    if (dt == DType::BF16 || dt == DType::F16) return "bf16";
+    if (opts.precision == "tf32" || opts.precision == "tf32x3" || opts.precision == "fp32") return opts.precision;
+    return "fp32";
+  }
+  View gemmOperand(Value* v, bool isB, std::vector<Expr>* split) {
+    TV& t = get(v);
+    settle(t);
+    // reshape(rank-4 strided) that only merges the two leading dims: use the rank-4 strides directly
+    if (t.kind == TV::Deferred && t.view.rank() == 4 && t.shape.size() == 3 && t.shape[1] == t.view.shape[2] && t.shape[2] == t.view.shape[3]) {
+      const View& s = t.view;
+      bool unitInner = s.strides[3].isConst(1) || s.strides[2].isConst(1);
+      if (unitInner && (isB || s.strides[3].isConst(1))) { if (split) *split = {s.shape[0], s.shape[1]}; return s; }
+    }
+    View x;
+    if (isLeafOnly(t)) x = nodes[t.root].leaf; else { toView(t); x = t.view; }
+    size_t r = x.rank();
+    bool ok = isB ? (x.strides[r - 1].isConst(1) || x.strides[r - 2].isConst(1)) : x.strides[r - 1].isConst(1);
+    if (x.shape[r - 1].isConst(1) && !isB) ok = true;
+    if (!ok) { std::vector<Expr> rm = rowMajor(x.shape); x = materializeTree(leafNode(x), x.dtype, x.shape, &rm); }
+    return x;
+  }
+  void gemm(Op* op, bool batched) {
+    std::vector<Expr> splitA, splitB;
+    View a = gemmOperand(op->operands[0], false, &splitA);
+    View b = gemmOperand(op->operands[1], true, &splitB);
+    std::vector<Expr> split = !splitA.empty() ? splitA : splitB;
+    auto lift = [&](View v) -> View {
+      if (v.rank() == 4) return v;
+      if (v.rank() == 3 && !split.empty()) {   // [b, r, c] -> [b0, b1, r, c]
+        View o = v; o.shape = {split[0], split[1], v.shape[1], v.shape[2]};
+        o.strides = {v.strides[0] * split[1], v.strides[0], v.strides[1], v.strides[2]};
+        return o;
+      }
+      return to4d(v);
+    };
+    if (a.dtype != b.dtype) {   // mixed storage types: bring both to the wider one
+      DType wide = (a.dtype == DType::F32 || b.dtype == DType::F32) ? DType::F32 : a.dtype;
+      auto conv = [&](View& v) { if (v.dtype != wide) { v = materializeTree(leafNode(v), wide, v.shape); } };
+      conv(a); conv(b);
+    }
+    a = lift(a); b = lift(b);
+    Expr M = a.shape[2], K = a.shape[3], N = b.shape[3];
+    DType dt = op->results[0]->type.elt;
+    PendingK P;
+    P.step.kernel = "gemm";
+    P.step.views.emplace_back("a", a);
+    P.step.views.emplace_back("b", b);
+    P.step.params.emplace_back("prec", gemmPrecision(a.dtype));
+    std::vector<Expr> nshape = {a.shape[0], a.shape[1], M, N};
+    if (a.shape[0].isConst(1) && !b.shape[0].isConst(1)) nshape[0] = b.shape[0];
+    if (a.shape[1].isConst(1) && !b.shape[1].isConst(1)) nshape[1] = b.shape[1];
+    P.nativeOut = freshView(dt, nshape, false);
+    P.buf = P.nativeOut.buf;
+    P.chanDim = 3;
+    pend.push_back(P);
+    TV t; t.kind = TV::Pending; t.pending = (int)pend.size() - 1; t.dtype = dt;
+    t.shape = batched ? std::vector<Expr>{nshape[0] * nshape[1], M, N} : std::vector<Expr>{M, N};
+    t.view = P.nativeOut; t.view.shape = t.shape; t.view.strides = rowMajor(t.shape);
+    (void)K;
+    tvs[op->results[0]] = t;
+  }
+
+  // ---- conv / pool
+  std::vector<Expr> nhwcStrides(const std::vector<Expr>& s) {  // logical [N,C,H,W] over an NHWC buffer
+    return {s[2] * s[3] * s[1], Expr(1), s[3] * s[1], s[1]};
+  }
+  Expr windowOut(const Expr& in, int64_t padLo, int64_t padHi, int64_t dil, int64_t k, int64_t stride, bool ceil = false) {
+    // LLHinfersymbolShape.cpp:257-292: (in + pad_l + pad_h - dil*(k-1) - 1) / stride + 1
+    Expr num = in + Expr(padLo + padHi - dil * (k - 1) - 1);
+    return (ceil ? num.ceildiv(Expr(stride)) : num.floordiv(Expr(stride))) + Expr(1);
+  }
+  void conv(Op* op, bool hasBias) {
+    Value* xv = op->operands[0];
+    TV& xt = get(xv);
+    if (xt.shape.size() != 4) fail("llh.conv expects rank-4 input");
+    auto stride = intArray(op, "stride", {1, 1}), pad = intArray(op, "pad", {0, 0, 0, 0}), dil = intArray(op, "dilation", {1, 1});
+    const Attr* g = op->attr("group");
+    if (g && g->i != 1) fail("grouped convolution is not supported by the CUDA pipeline");
+    const Attr* lay = op->attr("layout");
+    if (lay && lay->s != "NCHW") fail("llh.conv: only NCHW-typed modules are accepted (the NHWC layout is chosen internally)");
+    View x = viewWithStrides(xv, nhwcStrides(xt.shape));
+    TV& wt = get(op->operands[1]); toView(wt);
+    if (wt.shape.size() != 4) fail("llh.conv expects rank-4 weight");
+    // weight [F,C,KH,KW] -> dense [F,KH,KW,C]
+    View wperm = wt.view;
+    wperm.shape = {wt.view.shape[0], wt.view.shape[2], wt.view.shape[3], wt.view.shape[1]};
+    wperm.strides = {wt.view.strides[0], wt.view.strides[2], wt.view.strides[3], wt.view.strides[1]};
+    std::string key = "wperm:" + wperm.str();
+    View w;
+    if (constVecCache.count(key)) { w = wperm; w.buf = constVecCache[key]; w.offset = Expr(0); w.strides = rowMajor(wperm.shape); }
+    else { std::vector<Expr> rm = rowMajor(wperm.shape); w = materializeTree(leafNode(wperm), wperm.dtype, wperm.shape, &rm); constVecCache[key] = w.buf; }
+    Expr N = xt.shape[0], H = xt.shape[2], W = xt.shape[3], F = wt.shape[0];
+    int64_t KH = wt.shape[2].constant(), KW = wt.shape[3].constant();
+    if (!wt.shape[2].isConst() || !wt.shape[3].isConst()) fail("symbolic kernel extent");
+    // pad attr order: (top, left, bottom, right) as written by the importer (fx_op_translate/conv.py:48-57)
+    Expr OH = windowOut(H, pad[0], pad[2], dil[0], KH, stride[0]);
+    Expr OW = windowOut(W, pad[1], pad[3], dil[1], KW, stride[1]);
+    std::vector<Expr> oshape = {N, F, OH, OW};
+    DType dt = op->results[0]->type.elt;
+    PendingK P;
+    P.step.kernel = "conv";
+    P.step.views.emplace_back("x", x);
+    P.step.views.emplace_back("w", w);
+    auto arr = [](const std::vector<int64_t>& v) { std::string o; for (size_t i = 0; i < v.size(); ++i) o += (i ? "," : "") + std::to_string(v[i]); return o; };
+    P.step.params.emplace_back("stride", arr(stride));
+    P.step.params.emplace_back("pad", arr(pad));
+    P.step.params.emplace_back("dil", arr(dil));
+    P.step.params.emplace_back("prec", gemmPrecision(x.dtype));
+    std::vector<Expr> ost = nhwcStrides(oshape);
+    P.nativeOut = freshView(dt, oshape, false, &ost);
+    P.buf = P.nativeOut.buf;
+    P.chanDim = 1;
+    if (hasBias) {
+      TV& bt = get(op->operands[2]); toView(bt);
+      P.shiftRoot = leafNode(bt.view);
+    }
+    pend.push_back(P);
+    TV t; t.kind = TV::Pending; t.pending = (int)pend.size() - 1; t.dtype = dt; t.shape = oshape; t.view = P.nativeOut;
+    tvs[op->results[0]] = t;
+  }
+  void maxPool(Op* op) {
+    Value* xv = op->operands[0];
+    TV& xt = get(xv);
+    if (xt.shape.size() != 4) fail("llh.max_pool expects rank-4 input");
+    auto stride = intArray(op, "stride", {1, 1}), pad = intArray(op, "pad", {0, 0, 0, 0}), dil = intArray(op, "dilation", {1, 1}), k = intArray(op, "kernel_shape");
+    const Attr* cm = op->attr("ceil_mode");
+    bool ceil = cm && cm->i;
+    View x = viewWithStrides(xv, nhwcStrides(xt.shape));
+    std::vector<Expr> oshape = {xt.shape[0], xt.shape[1], windowOut(xt.shape[2], pad[0], pad[2], dil[0], k[0], stride[0], ceil),
+                                windowOut(xt.shape[3], pad[1], pad[3], dil[1], k[1], stride[1], ceil)};
+    std::vector<Expr> ost = nhwcStrides(oshape);
+    DType odt = resultDtype(op->results[0]);
+    View out = freshView(odt, oshape, false, &ost);
+    Step s; s.kernel = "maxpool";
+    s.views.emplace_back("x", x); s.views.emplace_back("out", out);
+    auto arr = [](const std::vector<int64_t>& v) { std::string o; for (size_t i = 0; i < v.size(); ++i) o += (i ? "," : "") + std::to_string(v[i]); return o; };
+    s.params.emplace_back("kernel", arr(k)); s.params.emplace_back("stride", arr(stride));
+    s.params.emplace_back("pad", arr(pad)); s.params.emplace_back("dil", arr(dil));
+    plan.steps.push_back(s);
+    tvs[op->results[0]] = makeView(out, false);
+  }
+
+  // ---- reductions
+  // x viewed as [outer, R, inner]; out [outer, inner]
+  View emitReduce(const View& x3, const std::string& kind, DType dt, bool isConst) {
+    View out = freshView(dt, {x3.shape[0], x3.shape[2]}, isConst);
+    Step s; s.kernel = "reduce"; s.init = plan.buffers[out.buf].kind == BufferDecl::Const;
+    s.views.emplace_back("x", x3); s.views.emplace_back("out", out);
+    s.params.emplace_back("op", kind);
+    plan.steps.push_back(s);
+    return out;
+  }
+  void reduce(Op* op, const std::string& kind) {
+    Value* xv = op->operands[0];
+    TV& xt = get(xv);
+    size_t r = xt.shape.size();
+    std::vector<int64_t> axes = intArray(op, "axis");
+    if (axes.empty()) { const Attr* a = op->attr("axis"); if (a && a->kind == Attr::Int) axes = {a->i}; }
+    for (auto& a : axes) if (a < 0) a += (int64_t)r;
+    std::sort(axes.begin(), axes.end());
+    std::set<int64_t> ax(axes.begin(), axes.end());
+    std::vector<Expr> kept;
+    for (size_t d = 0; d < r; ++d) if (!ax.count((int64_t)d)) kept.push_back(xt.shape[d]);
+    if (kept.empty()) kept.push_back(Expr(1));
+    toView(xt);
+    View x = xt.view;
+    // permute reduced axes to a block: (kept-before..., reduced..., kept-after...) when they are adjacent, else move them last
+    bool adjacent = true;
+    for (size_t i = 1; i < axes.size(); ++i) if (axes[i] != axes[i - 1] + 1) adjacent = false;
+    View x3;
+    bool done = false;
+    if (adjacent) {
+      Expr outer(1), R(1), inner(1);
+      for (size_t d = 0; d < r; ++d) { if ((int64_t)d < axes.front()) outer = outer * xt.shape[d]; else if ((int64_t)d > axes.back()) inner = inner * xt.shape[d]; else R = R * xt.shape[d]; }
+      done = reshapeView(x, {outer, R, inner}, x3);
+      if (!done) {
+        // NHWC-style views: try (kept..., reduced...) order on strides
+        View perm = x; perm.shape.clear(); perm.strides.clear();
+        for (size_t d = 0; d < r; ++d) if (!ax.count((int64_t)d)) { perm.shape.push_back(x.shape[d]); perm.strides.push_back(x.strides[d]); }
+        size_t nk = perm.shape.size();
+        for (auto a : axes) { perm.shape.push_back(x.shape[a]); perm.strides.push_back(x.strides[a]); }
+        // find any dim order in which the view is dense with the reduced dims forming one block
+        std::vector<int> order;
+        if (denseOrder(perm, order)) {
+          // positions of reduced dims in the dense order must be adjacent
+          std::vector<int> pos;
+          for (size_t k = 0; k < order.size(); ++k) if ((size_t)order[k] >= nk) pos.push_back((int)k);
+          bool blk = true; for (size_t i = 1; i < pos.size(); ++i) if (pos[i] != pos[i - 1] + 1) blk = false;
+          bool keptOrdered = true; int last = -1;
+          for (size_t k = 0; k < order.size(); ++k) if ((size_t)order[k] < nk) { if (order[k] < last) keptOrdered = false; last = order[k]; }
+          if (blk && keptOrdered && !pos.empty()) {
+            Expr o2(1), R2(1), i2(1);
+            for (size_t k = 0; k < order.size(); ++k) { const Expr& e = perm.shape[order[k]]; if ((int)k < pos.front()) o2 = o2 * e; else if ((int)k > pos.back()) i2 = i2 * e; else R2 = R2 * e; }
+            x3 = x; x3.shape = {o2, R2, i2}; x3.strides = {R2 * i2, i2, Expr(1)};
+            done = true;
+          }
+        }
+      }
+    }
+    if (!done) {
+      View perm = x; perm.shape.clear(); perm.strides.clear();
+      for (size_t d = 0; d < r; ++d) if (!ax.count((int64_t)d)) { perm.shape.push_back(x.shape[d]); perm.strides.push_back(x.strides[d]); }
+      Expr R(1);
+      for (auto a : axes) { perm.shape.push_back(x.shape[a]); perm.strides.push_back(x.strides[a]); R = R * x.shape[a]; }
+      std::vector<Expr> rm = rowMajor(perm.shape);
+      View dense = materializeTree(leafNode(perm), x.dtype, perm.shape, &rm);
+      if (!reshapeView(dense, {numelOf(kept), R, Expr(1)}, x3)) fail("internal: reduce reshape");
+    }
+    View out = emitReduce(x3, kind, op->results[0]->type.elt, xt.isConst);
+    View o2;
+    if (!reshapeView(out, kept, o2)) fail("internal: reduce result reshape");
+    tvs[op->results[0]] = makeView(o2, bufIsConst(o2.buf));
+  }
+  void adaptiveAvgPool(Op* op) {
+    auto os = intArray(op, "out_size");
+    if (os.size() != 2 || os[0] != 1 || os[1] != 1) fail("llh.adaptive_average_pool: only out_size [1,1] is supported");
+    Value* xv = op->operands[0];
+    TV& xt = get(xv); toView(xt);
+    View x = xt.view, x3;
+    Expr N = xt.shape[0], C = xt.shape[1], HW = xt.shape[2] * xt.shape[3];
+    std::vector<Expr> nh = nhwcStrides(xt.shape);
+    bool isNhwc = true;
+    for (int d = 0; d < 4; ++d) if (!xt.shape[d].isConst(1) && x.strides[d] != nh[d]) isNhwc = false;
+    View res;
+    if (isNhwc) {
+      x3 = x; x3.shape = {N, HW, C}; x3.strides = {HW * C, C, Expr(1)};
+      View out = emitReduce(x3, "mean", op->results[0]->type.elt, false);   // [N, C]
+      res = out; res.shape = {N, C, Expr(1), Expr(1)}; res.strides = {C, Expr(1), Expr(1), Expr(1)};
+    } else {
+      View xc = contiguousViewOf(xv);
+      x3 = xc; x3.shape = {N * C, HW, Expr(1)}; x3.strides = {HW, Expr(1), Expr(1)};
+      View out = emitReduce(x3, "mean", op->results[0]->type.elt, false);
+      res = out; res.shape = {N, C, Expr(1), Expr(1)}; res.strides = {C, Expr(1), Expr(1), Expr(1)};
+    }
+    tvs[op->results[0]] = makeView(res, false);
+  }
+
+  void softmax(Op* op) {
+    Value* xv = op->operands[0];
+    TV& xt = get(xv);
+    size_t r = xt.shape.size();
+    const Attr* a = op->attr("axis");
+    int64_t axis = a ? a->i : (int64_t)r - 1;
+    if (axis < 0) axis += (int64_t)r;
+    if (axis != (int64_t)r - 1) fail("llh.softmax: only the last axis is supported");
+    View x = contiguousLeafOrView(xv);
+    Expr rows(1); for (size_t d = 0; d + 1 < r; ++d) rows = rows * xt.shape[d];
+    View x2 = x; x2.shape = {rows, xt.shape[r - 1]}; x2.strides = {xt.shape[r - 1], Expr(1)};
+    View out = freshView(resultDtype(op->results[0]), xt.shape, false);
+    View o2 = out; o2.shape = x2.shape; o2.strides = x2.strides;
+    Step s; s.kernel = "softmax"; s.views.emplace_back("x", x2); s.views.emplace_back("out", o2);
+    plan.steps.push_back(s);
+    tvs[op->results[0]] = makeView(out, false);
+  }
+  void layerNorm(Op* op) {
+    Value* xv = op->operands[0];
+    TV& xt = get(xv);
+    size_t r = xt.shape.size();
+    const Attr* a = op->attr("axis");
+    int64_t axis = a ? a->i : (int64_t)r - 1;
+    if (axis < 0) axis += (int64_t)r;
+    const Attr* e = op->attr("epsilon");
+    View x = contiguousLeafOrView(xv);
+    Expr rows(1), D(1);
+    for (size_t d = 0; d < r; ++d) { if ((int64_t)d < axis) rows = rows * xt.shape[d]; else D = D * xt.shape[d]; }
+    View x2 = x; x2.shape = {rows, D}; x2.strides = {D, Expr(1)};
+    View g = contiguousViewOf(op->operands[1]), b = contiguousViewOf(op->operands[2]);
+    g.shape = {D}; g.strides = {Expr(1)}; b.shape = {D}; b.strides = {Expr(1)};
+    View out = freshView(resultDtype(op->results[0]), xt.shape, false);
+    View o2 = out; o2.shape = x2.shape; o2.strides = x2.strides;
+    Step s; s.kernel = "layernorm";
+    s.views.emplace_back("x", x2); s.views.emplace_back("gamma", g); s.views.emplace_back("beta", b); s.views.emplace_back("out", o2);
+    s.params.emplace_back("eps", fmtDouble(e ? e->f : 1e-5));
+    plan.steps.push_back(s);
+    tvs[op->results[0]] = makeView(out, false);
+  }
+  void embedding(Op* op) {
+    View table = contiguousViewOf(op->operands[0]);
+    View ids = contiguousViewOf(op->operands[1]);
+    TV& it = raw(op->operands[1]);
+    if (table.rank() != 2) fail("llh.embedding expects a rank-2 table");
+    std::vector<Expr> oshape = it.shape; oshape.push_back(table.shape[1]);
+    Expr rows = numelOf(it.shape);
+    View idf = ids; idf.shape = {rows}; idf.strides = {Expr(1)};
+    View out = freshView(resultDtype(op->results[0]), oshape, false);
+    View o2 = out; o2.shape = {rows, table.shape[1]}; o2.strides = {table.shape[1], Expr(1)};
+    Step s; s.kernel = "gather";
+    s.views.emplace_back("table", table); s.views.emplace_back("ids", idf); s.views.emplace_back("out", o2);
+    plan.steps.push_back(s);
+    tvs[op->results[0]] = makeView(out, false);
+  }
+  void batchNormInference(Op* op) {
+    // y = (x - mean) * gamma / sqrt(var + eps) + beta (src/Dialect/LLH/Transforms/DecomposeOps.cpp:125-144),
+    // restated as a per-channel scale/shift computed once at load: scale = gamma / sqrt(var + eps),
+    // shift = beta - mean * scale.
+    const Attr* e = op->attr("epsilon");
+    const Attr* fi = op->attr("feature_index");
+    int64_t f = fi ? fi->i : 1;
+    double eps = e ? e->f : 1e-5;
+    Value* xv = op->operands[0];
+    TV& xt = get(xv);
+    std::vector<View> p;
+    for (int i = 1; i <= 4; ++i) { TV& t = get(op->operands[i]); toView(t); View v = t.view; if (v.rank() != 1) fail("batch_norm parameters must be rank 1"); p.push_back(v); }
+    int gamma = leafNode(p[0]), beta = leafNode(p[1]), mean = leafNode(p[2]), var = leafNode(p[3]);
+    int scale = opNode("div", gamma, opNode("sqrt", opNode("add", var, constNode(eps))));
+    int shift = opNode("sub", beta, opNode("mul", mean, scale));
+    settle(xt);
+    if (xt.kind == TV::Pending && xv->users.size() == 1) {
+      PendingK& P = pend[xt.pending];
+      int cd = -1;
+      for (size_t d = 0; d < xt.view.rank(); ++d) if (xt.view.strides[d].isConst(1) && xt.view.shape[d] == P.nativeOut.shape[P.chanDim]) cd = (int)d;
+      if (P.stage == 0 && cd == f) {
+        P.shiftRoot = P.shiftRoot < 0 ? shift : opNode("add", opNode("mul", P.shiftRoot, scale), shift);
+        P.scaleRoot = P.scaleRoot < 0 ? scale : opNode("mul", P.scaleRoot, scale);
+        TV r = xt; r.dtype = op->results[0]->type.elt; tvs[op->results[0]] = r;
+        return;
+      }
+    }
+    // general case: one fused elementwise pass with the vectors broadcast along feature_index
+    std::vector<Expr> shape = xt.shape;
+    // the vectors are materialised once (load time), then broadcast
+    View sv = materializeTree(scale, DType::F32, {shape[f]}), hv = materializeTree(shift, DType::F32, {shape[f]});
+    int xn = operandNode(xt, shape);
+    int sn = leafNode(broadcastView(sv, shape, {f})), hn = leafNode(broadcastView(hv, shape, {f}));
+    tvs[op->results[0]] = makeLazy(opNode("add", opNode("mul", xn, sn), hn), op->results[0]->type.elt, shape);
+  }
+
+  // ---- data movement
+  void reshapeTo(Op* op, const std::vector<Expr>& target) {
+    Value* xv = op->operands[0];
+    TV& xt = get(xv);
+    std::vector<Expr> shape = target;
+    // one -1 extent is inferred (LLHCanonicalize.cpp reshape handling)
+    int neg = -1; Expr known(1);
+    for (size_t d = 0; d < shape.size(); ++d) { if (shape[d].isConst(-1)) neg = (int)d; else known = known * shape[d]; }
+    if (neg >= 0) shape[neg] = numelOf(xt.shape).floordiv(known);
+    TV r; r.dtype = op->results[0]->type.elt == DType::None ? xt.dtype : xt.dtype; r.shape = shape; r.isConst = xt.isConst;
+    settle(xt);
+    if (xt.kind == TV::Lazy) {
+      std::map<int, int> memo; bool ok = true;
+      int root = mapLeaves(xt.root, [&](const View& l, View& o) { return reshapeView(l, shape, o); }, memo, ok);
+      if (ok) { tvs[op->results[0]] = makeLazy(root, xt.dtype, shape); return; }
+      toView(xt);
+    }
+    if (xt.kind == TV::Deferred) toView(xt);
+    View nv;
+    if (reshapeView(xt.view, shape, nv)) {
+      r.kind = xt.kind; r.view = nv; r.pending = xt.pending;
+      tvs[op->results[0]] = r; return;
+    }
+    if (xt.kind == TV::Pending) toView(xt);
+    r.kind = TV::Deferred; r.view = xt.view;
+    tvs[op->results[0]] = r;
+  }
+  void transpose(Op* op) {
+    Value* xv = op->operands[0];
+    TV& xt = get(xv);
+    std::vector<int64_t> perms = intArray(op, "perms");
+    if (perms.size() != xt.shape.size()) fail("llh.transpose: perms rank mismatch");
+    auto permute = [&](const View& v) { View o = v; for (size_t i = 0; i < perms.size(); ++i) { o.shape[i] = v.shape[perms[i]]; o.strides[i] = v.strides[perms[i]]; } return o; };
+    settle(xt);
+    if (xt.kind == TV::Deferred) toView(xt);
+    std::vector<Expr> shape(perms.size());
+    for (size_t i = 0; i < perms.size(); ++i) shape[i] = xt.shape[perms[i]];
+    if (xt.kind == TV::Lazy) {
+      std::map<int, int> memo; bool ok = true;
+      int root = mapLeaves(xt.root, [&](const View& l, View& o) { o = permute(l); return true; }, memo, ok);
+      tvs[op->results[0]] = makeLazy(root, xt.dtype, shape); return;
+    }
+    TV r = xt; r.shape = shape; r.view = permute(xt.view);
+    tvs[op->results[0]] = r;
+  }
+  void broadcastTo(Op* op) {
+    Value* xv = op->operands[0];
+    TV& xt = get(xv);
+    std::vector<Expr> shape;
+    for (size_t i = 1; i < op->operands.size(); ++i) shape.push_back(scalarOf(op->operands[i]));
+    std::vector<int64_t> cast = intArray(op, "cast_dims");
+    if (cast.empty()) for (size_t i = 0; i < xt.shape.size(); ++i) cast.push_back((int64_t)(shape.size() - xt.shape.size() + i));
+    settle(xt);
+    // dims that are already the target extent keep the producer's name for them
+    for (size_t i = 0; i < xt.shape.size(); ++i) if (!xt.shape[i].isConst(1)) shape[cast[i]] = xt.shape[i];
+    if (xt.kind == TV::Lazy) {
+      std::map<int, int> memo; bool ok = true;
+      int root = mapLeaves(xt.root, [&](const View& l, View& o) { o = broadcastView(l, shape, cast); return true; }, memo, ok);
+      tvs[op->results[0]] = makeLazy(root, xt.dtype, shape); return;
+    }
+    if (xt.kind == TV::Pending && xt.shape.size() == shape.size()) {   // identity broadcast keeps the producer open
+      bool same = true; for (size_t i = 0; i < shape.size(); ++i) if (cast[i] != (int64_t)i || xt.shape[i] != shape[i]) same = false;
+      if (same) { TV r = xt; tvs[op->results[0]] = r; return; }
+    }
+    if (xt.kind == TV::Deferred && xt.shape.size() == shape.size()) {
+      bool same = true; for (size_t i = 0; i < shape.size(); ++i) if (cast[i] != (int64_t)i || xt.shape[i] != shape[i]) same = false;
+      if (same) { TV r = xt; tvs[op->results[0]] = r; return; }
+    }
+    toView(xt);
+    tvs[op->results[0]] = makeView(broadcastView(xt.view, shape, cast), xt.isConst);
+  }
+  void strideSlice(Op* op) {
+    Value* xv = op->operands[0];
+    View x = viewOf(xv);
+    size_t r = x.rank();
+    if (op->operands.size() != 1 + 3 * r) fail("llh.stride_slice: expects starts, ends and strides for every dim");
+    View o = x;
+    for (size_t d = 0; d < r; ++d) {
+      Expr st = scalarOf(op->operands[1 + d]), en = scalarOf(op->operands[1 + r + d]), sp = scalarOf(op->operands[1 + 2 * r + d]);
+      if (en.isConst() && en.constant() >= (int64_t)1 << 62) en = x.shape[d];
+      if (st.isConst() && st.constant() < 0) st = st + x.shape[d];
+      if (en.isConst() && en.constant() < 0) en = en + x.shape[d];
+      o.offset = o.offset + st * x.strides[d];
+      o.shape[d] = (en - st).ceildiv(sp);
+      o.strides[d] = x.strides[d] * sp;
+    }
+    tvs[op->results[0]] = makeView(o, raw(xv).isConst);
+  }
+  void extract(Op* op) {
+    View x = viewOf(op->operands[0]);
+    Expr idx = scalarOf(op->operands[1]);
+    if (idx.isConst() && idx.constant() < 0) idx = idx + x.shape[0];
+    View o = x;
+    o.offset = o.offset + idx * x.strides[0];
+    o.shape.erase(o.shape.begin()); o.strides.erase(o.strides.begin());
+    if (o.shape.empty()) { o.shape.push_back(Expr(1)); o.strides.push_back(Expr(1)); }
+    tvs[op->results[0]] = makeView(o, raw(op->operands[0]).isConst);
+  }
+
+  // ---- constants / arguments
+  void constant(Op* op) {
+    const Attr* a = op->attr("value");
+    if (!a) fail("llh.constant without value");
+    Value* res = op->results[0];
+    if (a->kind == Attr::Int || a->kind == Attr::Bool) {
+      TV t; t.kind = TV::Scalar; t.scalar = Expr(a->i); t.dtype = DType::I64; t.isConst = true; tvs[res] = t; return;
+    }
+    if (a->kind == Attr::Float) { TV t; t.kind = TV::Scalar; t.isFloatScalar = true; t.fscalar = a->f; t.dtype = DType::F32; t.isConst = true; tvs[res] = t; return; }
+    if (a->kind != Attr::Dense) fail("unsupported llh.constant value");
+    std::vector<Expr> shape;
+    for (auto d : a->type.dims) shape.push_back(Expr(d));
+    if (shape.empty()) shape.push_back(Expr(1));
+    bool isF = isFloat(a->type.elt);
+    size_t n = isF ? a->floats.size() : a->ints.size();
+    if (n == 1) { tvs[res] = makeLazy(constNode(isF ? a->floats[0] : (double)a->ints[0]), a->type.elt, shape); return; }
+    View v = freshView(a->type.elt, shape, true);
+    plan.buffers[v.buf].kind = BufferDecl::Const;
+    for (size_t k = 0; k < n; ++k) plan.buffers[v.buf].values.push_back(isF ? a->floats[k] : (double)a->ints[k]);
+    tvs[res] = makeView(v, true);
+  }
+  void weight(Op* op) {
+    const Attr* f = op->attr("weight_file");
+    if (!f) fail("llh.weight without weight_file");
+    const Type& t = op->results[0]->type;
+    std::vector<Expr> shape;
+    for (auto d : t.dims) { if (d == kDynamic) fail("llh.weight with a dynamic extent"); shape.push_back(Expr(d)); }
+    if (shape.empty()) shape.push_back(Expr(1));
+    View v = freshView(t.elt, shape, true);
+    plan.buffers[v.buf].kind = BufferDecl::Weight;
+    plan.buffers[v.buf].file = f->s;
+    tvs[op->results[0]] = makeView(v, true);
+  }
+  void scalarBinary(Op* op, const std::string& name) {
+    Expr a = scalarOf(op->operands[0]), b = scalarOf(op->operands[1]);
+    TV t; t.kind = TV::Scalar; t.dtype = DType::I64; t.isConst = true;
+    if (name == "add") t.scalar = a + b; else if (name == "sub") t.scalar = a - b; else if (name == "mul") t.scalar = a * b;
+    else if (name == "div") t.scalar = a.floordiv(b); else fail("unsupported scalar op llh." + name);
+    tvs[op->results[0]] = t;
+  }
+
+  void bindArguments(Func& f) {
+    int symArgs = 0, tensorArgs = 0, fresh = 0;
+    std::set<std::string> seen;
+    for (size_t i = 0; i < f.args.size(); ++i) {
+      Value* a = f.args[i];
+      const AttrList& attrs = i < f.argAttrs.size() ? f.argAttrs[i] : AttrList();
+      if (a->type.kind == Type::Scalar) {
+        const Attr* s = findAttr(attrs, "func.symbol_int");
+        std::string name = s ? s->s : "s" + std::to_string(fresh++);
+        TV t; t.kind = TV::Scalar; t.dtype = DType::I64;
+        if (name.size() > 1 && name[0] == 'c' && std::isdigit((unsigned char)name[1])) t.scalar = Expr(std::stoll(name.substr(1)));
+        else { t.scalar = Expr::sym(name); SymbolBinding b; b.name = name; b.symbolArg = symArgs; plan.symbols.push_back(b); }
+        ++symArgs;
+        tvs[a] = t;
+        continue;
+      }
+      if (!a->type.isTensor()) fail("unsupported argument type");
+      std::vector<Expr> shape;
+      for (size_t d = 0; d < a->type.dims.size(); ++d) {
+        const Attr* s = findAttr(attrs, "func.input_symbol_" + std::to_string(d));
+        std::string name = s ? s->s : "";
+        if (a->type.dims[d] != kDynamic) { shape.push_back(Expr(a->type.dims[d])); continue; }
+        if (name.empty()) name = "s" + std::to_string(fresh++);
+        if (name[0] == 'c' && name.size() > 1 && std::isdigit((unsigned char)name[1])) { shape.push_back(Expr(std::stoll(name.substr(1)))); continue; }
+        // a torch symbol expression such as "2*s0" cannot name an input extent; plain names only
+        shape.push_back(Expr::sym(name));
+        SymbolBinding b; b.name = name; b.input = tensorArgs; b.dim = (int)d; plan.symbols.push_back(b);
+      }
+      if (shape.empty()) shape.push_back(Expr(1));
+      View v; v.dtype = a->type.elt; v.shape = shape; v.strides = rowMajor(shape);
+      v.buf = newBuffer(a->type.elt, numelOf(shape), BufferDecl::Input);
+      plan.buffers[v.buf].index = tensorArgs;
+      IoDecl io; io.buf = v.buf; io.dtype = a->type.elt; io.shape = shape;
+      plan.inputs.push_back(io);
+      ++tensorArgs;
+      tvs[a] = makeView(v, false);
+    }
+    plan.numSymbolArgs = symArgs;
+  }
+
+  void finishOutputs(Op* ret) {
+    std::set<int> taken;
+    for (size_t k = 0; k < ret->operands.size(); ++k) {
+      Value* v = ret->operands[k];
+      TV& t = raw(v);
+      settle(t);
+      if (t.kind == TV::Scalar) fail("returning scalars is not supported");
+      IoDecl io; io.dtype = t.dtype; io.shape = t.shape;
+      std::vector<Expr> rm = rowMajor(t.shape);
+      bool direct = false;
+      if (t.kind == TV::Pending && v->users.size() == 1 && isContiguous(t.view) && t.view.offset.isConst(0) && !taken.count(t.view.buf)) {
+        plan.buffers[t.view.buf].kind = BufferDecl::Output; plan.buffers[t.view.buf].index = (int)k;
+        emitPending(t.pending); settle(t);
+        io.buf = t.view.buf; direct = true;
+      } else if (t.kind == TV::Lazy && nodes[t.root].kind != ENode::Leaf) {
+        int buf = newBuffer(t.dtype, numelOf(t.shape), BufferDecl::Output);
+        plan.buffers[buf].index = (int)k;
+        materializeTree(t.root, t.dtype, t.shape, &rm, buf);
+        io.buf = buf; direct = true;
+      }
+      if (!direct) {
+        toView(t);
+        const BufferDecl& b = plan.buffers[t.view.buf];
+        if (b.kind == BufferDecl::Temp && isContiguous(t.view) && t.view.offset.isConst(0) && b.numel == numelOf(t.shape) && !taken.count(t.view.buf)) {
+          plan.buffers[t.view.buf].kind = BufferDecl::Output; plan.buffers[t.view.buf].index = (int)k;
+          io.buf = t.view.buf;
+        } else {
+          int buf = newBuffer(t.dtype, numelOf(t.shape), BufferDecl::Output);
+          plan.buffers[buf].index = (int)k;
+          materializeTree(leafNode(t.view), t.dtype, t.shape, &rm, buf);
+          io.buf = buf;
+        }
+      }
+      taken.insert(io.buf);
+      plan.outputs.push_back(io);
+    }
+  }
+
+  void run() {
+    Func* f = m.entrance();
+    if (!f) fail("module has no function");
+    m.recomputeUsers();
+    bindArguments(*f);
+    static const std::set<std::string> binary = {"add", "sub", "mul", "div", "max", "min", "pow"};
+    static const std::set<std::string> unary = {"relu", "abs", "sqrt", "rsqrt", "exp", "gelu", "tanh", "erf", "sigmoid", "neg"};
+    for (Op* op : f->ops) {
+      if (op->erased) continue;
+      const std::string& n = op->name;
+      if (n == "func.return") { finishOutputs(op); continue; }
+      if (n.compare(0, 4, "llh.") != 0) fail("operation '" + n + "' is not part of the LLH surface");
+      std::string s = n.substr(4);
+      if (s == "constant") constant(op);
+      else if (s == "weight") weight(op);
+      else if (s == "torch_symbolic_int" || s == "symbolic_int") {
+        const Attr* a = op->attr("sym_name");
+        if (!a) fail("symbolic int without sym_name");
+        if (op->results.empty()) continue;
+        TV t; t.kind = TV::Scalar; t.dtype = DType::I64;
+        t.scalar = (a->s.size() > 1 && a->s[0] == 'c' && std::isdigit((unsigned char)a->s[1])) ? Expr(std::stoll(a->s.substr(1))) : Expr::sym(a->s);
+        tvs[op->results[0]] = t;
+      }
+      else if (s == "dim") {
+        TV& x = raw(op->operands[0]);
+        Expr d = scalarOf(op->operands[1]);
+        if (!d.isConst()) fail("llh.dim with a symbolic index");
+        int64_t k = d.constant(); if (k < 0) k += (int64_t)x.shape.size();
+        if (k < 0 || k >= (int64_t)x.shape.size()) fail("llh.dim index out of range");
+        TV t; t.kind = TV::Scalar; t.dtype = DType::I64; t.scalar = x.shape[k]; tvs[op->results[0]] = t;
+      }
+      else if (binary.count(s)) {
+        if (op->results[0]->type.kind == Type::Scalar) scalarBinary(op, s); else eltwise(op, s);
+      }
+      else if (unary.count(s)) eltwise(op, s);
+      else if (s == "where") eltwise(op, "where");
+      else if (s == "compare") {
+        const Attr* k = op->attr("kind");
+        std::string kind = k ? k->s : "EQ";
+        for (auto& c : kind) c = (char)std::tolower((unsigned char)c);
+        eltwise(op, kind);
+      }
+      else if (s == "convert_to") {
+        TV& x = get(op->operands[0]);
+        if (x.kind == TV::Scalar) { tvs[op->results[0]] = x; continue; }
+        DType to = op->results[0]->type.elt;
+        if (to == x.dtype) { TV c = x; tvs[op->results[0]] = c; continue; }
+        if (isFloat(to) && isFloat(x.dtype)) {
+          // float -> float: arithmetic is fp32 everywhere, only the storage type of whatever is
+          // materialised next changes, so the conversion does not break a fusion
+          settle(x);
+          if (x.kind == TV::Pending && op->operands[0]->users.size() == 1) {
+            PendingK& P = pend[x.pending];
+            P.nativeOut.dtype = to; plan.buffers[P.buf].dtype = to;
+            TV r = x; r.dtype = to; r.view.dtype = to; tvs[op->results[0]] = r; continue;
+          }
+          if (x.kind == TV::Lazy) { TV r = x; r.dtype = to; tvs[op->results[0]] = r; continue; }
+          toView(x);
+          tvs[op->results[0]] = makeLazy(leafNode(x.view), to, x.shape); continue;
+        }
+        int node = operandNode(x, x.shape);
+        tvs[op->results[0]] = makeLazy(opNode(isFloat(to) ? "cast" : "trunc", node), to, x.shape);
+      }
+      else if (s == "scalar_cast") {
+        TV& x = raw(op->operands[0]);
+        if (x.kind != TV::Scalar) fail("llh.scalar_cast expects a scalar");
+        if (op->results[0]->type.isTensor()) {
+          if (!x.isFloatScalar && !x.scalar.isConst()) fail("llh.scalar_cast of a symbolic value to a tensor is not supported");
+          tvs[op->results[0]] = makeLazy(constNode(x.isFloatScalar ? x.fscalar : (double)x.scalar.constant()), op->results[0]->type.elt, {Expr(1)});
+        } else { TV c = x; tvs[op->results[0]] = c; }
+      }
+      else if (s == "matmul") gemm(op, false);
+      else if (s == "batch_matmul") gemm(op, true);
+      else if (s == "conv") conv(op, false);
+      else if (s == "conv_bias") conv(op, true);
+      else if (s == "batch_norm_inference") batchNormInference(op);
+      else if (s == "max_pool") maxPool(op);
+      else if (s == "adaptive_average_pool") adaptiveAvgPool(op);
+      else if (s == "reduce_sum") reduce(op, "sum");
+      else if (s == "reduce_max") reduce(op, "max");
+      else if (s == "reduce_min") reduce(op, "min");
+      else if (s == "reduce_mean") reduce(op, "mean");
+      else if (s == "softmax") softmax(op);
+      else if (s == "layer_norm") layerNorm(op);
+      else if (s == "embedding") embedding(op);
+      else if (s == "reshape") { std::vector<Expr> t; for (size_t i = 1; i < op->operands.size(); ++i) t.push_back(scalarOf(op->operands[i])); reshapeTo(op, t); }
+      else if (s == "flatten") {
+        TV& x = raw(op->operands[0]);
+        int64_t d = scalarOf(op->operands[1]).constant(); if (d < 0) d += (int64_t)x.shape.size();
+        Expr lo(1), hi(1);
+        for (size_t i = 0; i < x.shape.size(); ++i) { if ((int64_t)i < d) lo = lo * x.shape[i]; else hi = hi * x.shape[i]; }
+        reshapeTo(op, d == 0 ? std::vector<Expr>{hi} : std::vector<Expr>{lo, hi});
+      }
+      else if (s == "transpose") transpose(op);
+      else if (s == "broadcast_to" || s == "expand") broadcastTo(op);
+      else if (s == "stride_slice") strideSlice(op);
+      else if (s == "extract") extract(op);
+      else if (s == "symbolic_bind" || s == "encoding_bind" || s == "symbol_bind" || s == "print" || s == "aot" ||
+               s == "symbol_relation" || s == "symbol_relation_map" || s == "symbol_binary_relation") continue;
+      else if (s == "drop") { TV c = get(op->operands[0]); tvs[op->results[0]] = c; }   // inference: identity
+      else fail("no CUDA lowering for '" + n + "'");
+    }
+    plan.options["precision"] = opts.precision;
+    plan.options["mode"] = opts.mode;
+    plan.options["target"] = opts.target;
+  }
+};
+
+}  // namespace
+
+Plan lowerToPlan(Module& m, const CompileOptionsData& opts) {
+  runOperationLegalization(m);
+  runRemoveRedundantOps(m);
+  runFuseSoftmax(m);
+  Lowering L(m, opts);
+  L.run();
+  return L.plan;
+}
+
+}  // namespace llc
+
+namespace llc {
+// infer-symbol-shape: runs the same shape rules as the lowering and writes the result back
+// as static extents plus #llh.encoding<shapes = ...> on every tensor type
+// (the reference pass: src/Dialect/LLH/SymbolInfer/InferSymbolShape.cpp:61-175).  Constant
+// extents are named c<value>, input symbols keep their names, derived extents are printed as
+// expressions where the reference would mint a fresh symbol plus a relation.
+void runInferSymbolShape(Module& m) {
+  runOperationLegalization(m);
+  CompileOptionsData opts;
+  Lowering L(m, opts);
+  L.run();
+  for (auto& kv : L.tvs) {
+    Value* v = kv.first;
+    const TV& t = kv.second;
+    if (!v->type.isTensor() || t.kind == TV::None || t.kind == TV::Scalar) continue;
+    v->type.unranked = false;
+    v->type.dims.clear(); v->type.encoding.clear();
+    for (auto& e : t.shape) {
+      v->type.dims.push_back(e.isConst() ? e.constant() : kDynamic);
+      v->type.encoding.push_back(e.isConst() ? "c" + std::to_string(e.constant()) : e.str());
+    }
+  }
+  Func* f = m.entrance();
+  if (f) {
+    f->resultTypes.clear();
+    for (Op* op : f->ops) if (op->name == "func.return") for (Value* v : op->operands) f->resultTypes.push_back(v->type);
+  }
+}
+}  // namespace llc

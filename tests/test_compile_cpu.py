@@ -1,0 +1,55 @@
+"""Compiler-only checks that need no GPU: importer -> llc_compile -> kernel plan, with the
+plan executed by the CPU oracle interpreter and compared with eager PyTorch (the reference's
+own parity pin, llcompiler/test_models/utility.py:18-28)."""
+import pytest
+import torch
+
+from helpers import InterpreterCompiler, compile_with
+from oracle.models import build_model, max_rel_err
+
+
+def _run(model, inputs, dynamic=False, precision="auto"):
+    comp = InterpreterCompiler(precision=precision)
+    with torch.no_grad():
+        want = model(*inputs)
+        got = compile_with(comp, model, dynamic)(*inputs)
+    return comp, got, want
+
+
+def test_mlp_dynamic_batch():
+    m = build_model("mlp")
+    comp, got, want = _run(m, (torch.randn(64, 784),), dynamic=True)
+    assert max_rel_err(got, want) < 1e-5
+    plan = comp.compiled[0].engine.text
+    assert plan.count("step gemm") == 2 and "step eltwise" not in plan      # bias+relu fused
+    # the same plan serves another batch size (symbolic batch)
+    x = torch.randn(7, 784)
+    with torch.no_grad():
+        got7 = comp.compiled[0].engine.run(7, x)[0]
+        assert max_rel_err(got7, m(x)) < 1e-5
+
+
+def test_resnet18_fuses_to_conv_steps():
+    m = build_model("resnet18")
+    comp, got, want = _run(m, (torch.randn(2, 3, 64, 64),))
+    assert max_rel_err(got, want) < 1e-4
+    plan = comp.compiled[0].engine.text
+    assert plan.count("step conv") == 20 and plan.count("step maxpool") == 1
+    assert plan.count("step eltwise") == 1      # only the NCHW->NHWC input re-layout
+
+
+def test_encoder_layer_dynamic_seq():
+    m = build_model("encoder")
+    comp, got, want = _run(m, (torch.randn(2, 16, 768),), dynamic=True)
+    assert max_rel_err(got, want) < 1e-4
+    plan = comp.compiled[0].engine.text
+    assert plan.count("step softmax") == 1 and plan.count("step layernorm") == 2
+
+
+def test_bert_two_layers():
+    m = build_model("bert", n_layers=2)
+    ids = torch.randint(0, 30522, (2, 16))
+    mask = torch.ones(2, 16, dtype=torch.int64)
+    mask[1, 10:] = 0
+    comp, got, want = _run(m, (ids, mask))
+    assert max_rel_err(got, want) < 1e-4
