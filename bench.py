@@ -1,0 +1,294 @@
+#!/usr/bin/env python
+"""Benchmark of the compiled-model inference path.
+
+  python bench.py --gpus N --steps K --warmup W [--config resnet18] [--impl reference]
+
+A step is one forward of the configured model over one batch of seeded synthetic input.  At
+N > 1 (one rank per GPU, launched with torch.distributed.run) every rank runs its own batch
+shard with replicated weights and the outputs are all-gathered over NCCL inside the timed step
+(weak scaling: the per-GPU batch is fixed).  The line printed by rank 0 carries:
+  value      samples/s with inputs resident in HBM, device-timed with CUDA events, max over ranks
+  e2e        the same metric through Torch_ExecutionEngine.run with pinned HOST tensors, the
+             host->device and device->host copies inside the timed region
+  roofline   the dominant kernel (convolution / GEMM): algorithmic FLOPs / event-timed duration
+  cpu_baseline  the CPU oracle (PyTorch CPU eager fp32, what the reference pins itself to) on a
+             bounded sample of the same workload, on this box's host cores
+`--impl reference` times that CPU path alone with all host threads.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+if ROOT not in sys.path:
+    sys.path.insert(0, ROOT)
+
+import torch  # noqa: E402
+
+WORKLOADS = {
+    # name: (oracle config, per-GPU batch, extra make_inputs kwargs, dtype label, precision option)
+    "mlp": ("mlp", 64, {}, "f32", "auto"),
+    "resnet18": ("resnet18", 32, {}, "f32", "auto"),
+    "encoder128": ("encoder", 8, {"seq": 128}, "f32", "auto"),
+    "encoder512": ("encoder", 8, {"seq": 512}, "f32", "auto"),
+    "resnet50": ("resnet50", 256, {}, "bf16", "auto"),
+    "bert": ("bert", 256, {}, "bf16", "auto"),
+}
+DESCRIPTION = {
+    "resnet18": "ResNet-18 fp32 NCHW [32,3,224,224] (configs[1])",
+    "mlp": "MLP 784-512-10 fp32 B=64 (configs[0])",
+    "encoder128": "pre-LN encoder layer d768 h12 [8,128,768] (configs[2], S=128)",
+    "encoder512": "pre-LN encoder layer d768 h12 [8,512,768] (configs[2], S=512)",
+    "resnet50": "ResNet-50 bf16 [256,3,224,224] (configs[3])",
+    "bert": "BERT-base x12 bf16 ids[256,384] (configs[4])",
+}
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        p = json.load(open(path))
+        return {"hbm_gbs": p["hbm_gbs"], "tflops": p["bf16_tflops"], "tflops_sustained": p.get("bf16_tflops_sustained"), "source": "measured"}
+    return {"hbm_gbs": 6650.0, "tflops": 1590.0, "tflops_sustained": 1400.0, "source": "fallback"}
+
+
+class ClockSampler:
+    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.index, self.samples, self.proc = index, [], None
+
+    def __enter__(self):
+        q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={q}", "--format=csv,noheader,nounits", "-lms", "200"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            self.thread = threading.Thread(target=self._read, daemon=True)
+            self.thread.start()
+        except OSError:
+            self.proc = None
+        return self
+
+    def _read(self):
+        for line in self.proc.stdout:
+            f = [x.strip() for x in line.split(",")]
+            if len(f) >= 6 and f[0].isdigit():
+                self.samples.append(f)
+
+    def __exit__(self, *a):
+        if self.proc:
+            time.sleep(0.25)
+            self.proc.terminate()
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+
+    def summary(self):
+        if not self.samples:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["unsampled"]}
+        mhz = sorted(int(s[0]) for s in self.samples)
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        reasons = [n for i, n in enumerate(names) if any(s[2 + i].lower().startswith("active") for s in self.samples)]
+        return {"sm_mhz": mhz[len(mhz) // 2], "sm_max_mhz": int(self.samples[0][1]), "reasons": reasons}
+
+
+def build_workload(name: str, batch: int, kw: dict):
+    from oracle.models import CONFIGS, build_model
+    cfg = CONFIGS[name]
+    model = build_model(name)
+    inputs = cfg.make_inputs(batch=batch, **kw)
+    return cfg, model, inputs
+
+
+def cpu_oracle_rate(model, inputs, batch: int, budget_s: float, threads: int, sample_batch: int):
+    """samples/s of PyTorch CPU eager fp32 on a bounded sample of the workload."""
+    torch.set_num_threads(threads)
+    sub = tuple(i[:sample_batch] for i in inputs)
+    with torch.no_grad():
+        model(*sub)
+        t0 = time.perf_counter()
+        n = 0
+        while True:
+            model(*sub)
+            n += 1
+            dt = time.perf_counter() - t0
+            if dt > budget_s or n >= 50:
+                break
+    return sample_batch * n / dt, n, dt
+
+
+def run_reference(args, rank: int, world: int):
+    if rank != 0:
+        return
+    oname, batch, kw, dtype, _ = WORKLOADS[args.config]
+    cfg, model, inputs = build_workload(oname, batch, kw)
+    threads = os.cpu_count() or 1
+    sample_batch = min(batch, 8 if oname in ("resnet50", "bert") else batch)
+    if oname == "bert":
+        sample_batch = 2
+    torch.set_num_threads(threads)
+    sub = tuple(i[:sample_batch] for i in inputs)
+    times = []
+    with torch.no_grad():
+        for _ in range(max(args.warmup, 1)):
+            model(*sub)
+        for _ in range(args.steps):
+            t0 = time.perf_counter()
+            model(*sub)
+            times.append(time.perf_counter() - t0)
+    total = sum(times)
+    value = sample_batch * args.steps / total
+    sample = f"{args.steps} forwards of a {sample_batch}-sample slice of the batch, PyTorch CPU eager fp32 (the reference's own parity pin; its CPU lowering cannot be built offline)"
+    line = {
+        "impl": "reference", "metric": "inferences_per_sec", "value": value, "unit": "samples/s", "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps * (batch / sample_batch),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": {"workload": DESCRIPTION[args.config], "per_gpu_batch": batch},
+        "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours")
+    ap.add_argument("--config", default="resnet18", choices=sorted(WORKLOADS))
+    ap.add_argument("--cpu-budget", type=float, default=15.0)
+    ap.add_argument("--precision", default=None)
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    args.warmup = max(args.warmup, 3)
+
+    from __graft_entry__ import build
+    if rank == 0:
+        build()
+    import torch.distributed as dist
+    if world > 1:
+        torch.cuda.set_device(local)
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.barrier()
+    else:
+        torch.cuda.set_device(0)
+    from llcompiler_b200.compiler import LLCompiler
+
+    oname, batch, kw, dtype, prec = WORKLOADS[args.config]
+    prec = args.precision or prec
+    cfg, model, inputs = build_workload(oname, batch, kw)
+    dev = torch.device("cuda", local if world > 1 else 0)
+    gmodel = model.to(torch.bfloat16) if dtype == "bf16" else model
+    import copy
+    gmodel = copy.deepcopy(gmodel).to(dev)
+    cast = (lambda t: t.to(torch.bfloat16)) if dtype == "bf16" else (lambda t: t)
+    host_inputs = tuple((cast(i) if i.is_floating_point() else i).contiguous().pin_memory() for i in inputs)
+    dev_inputs = tuple(i.to(dev) for i in host_inputs)
+
+    comp = LLCompiler(precision=prec, device=dev.index)
+    torch._dynamo.reset()
+    fn = torch.compile(gmodel, backend=comp, dynamic=False, fullgraph=True)
+    with torch.no_grad():
+        out = fn(*dev_inputs)
+    torch.cuda.synchronize()
+    eng = comp.compiled[0].engine
+    launches_per_step = eng.executor.last_launch_count()
+
+    gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=dev) if world > 1 else None
+    flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
+
+    def step():
+        o = eng.run(*dev_inputs)[0]
+        if world > 1:
+            dist.all_gather_into_tensor(gathered, o)
+        return o
+
+    for _ in range(args.warmup):
+        step()
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    starts = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    ends = [torch.cuda.Event(enable_timing=True) for _ in range(args.steps)]
+    with ClockSampler(dev.index) as clocks:
+        torch.cuda.synchronize()
+        for i in range(args.steps):
+            flush.zero_()                       # evict L2 between timed iterations (outside the timed span)
+            starts[i].record()
+            step()
+            ends[i].record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        total_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
+        # end to end: pinned host inputs, host outputs, copies inside the timed region
+        for _ in range(2):
+            eng.run(*host_inputs)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for _ in range(args.steps):
+            o_host = eng.run(*host_inputs)[0]
+        torch.cuda.synchronize()
+        e2e_s = time.perf_counter() - t0
+    t = torch.tensor([total_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    total_ms, e2e_ms = float(t[0]), float(t[1])
+
+    # dominant kernel: event-timed per kernel family over a profiled pass (events around every launch)
+    prof = eng.profile(*dev_inputs, reps=5)
+    roof = None
+    pk = peaks()
+    if prof:
+        top = max(prof, key=lambda r: r["ms"])
+        if top["flops"] > 0 and top["kernel"] in ("conv", "gemm"):
+            achieved = top["flops"] / (top["ms"] * 1e-3) / 1e12
+            roof = {"bound": "tensor", "kernel": top["kernel"], "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
+                    "frac": achieved / pk["tflops"], "traffic": None, "peak_source": pk["source"], "launches": top["launches"],
+                    "share_of_step": top["ms"] / max(sum(r["ms"] for r in prof), 1e-9)}
+        else:
+            achieved = top["bytes"] / (top["ms"] * 1e-3) / 1e9
+            roof = {"bound": "hbm", "kernel": top["kernel"], "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
+                    "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"], "launches": top["launches"],
+                    "share_of_step": top["ms"] / max(sum(r["ms"] for r in prof), 1e-9)}
+
+    if rank == 0:
+        cpu_val, cpu_n, cpu_dt = cpu_oracle_rate(model, inputs, batch, args.cpu_budget, os.cpu_count() or 1,
+                                                 2 if oname == "bert" else (8 if oname == "resnet50" else batch))
+        h2d = sum(i.numel() * i.element_size() for i in host_inputs)
+        d2h = out.numel() * out.element_size()
+        line = {
+            "metric": "inferences_per_sec", "value": batch * world * args.steps / (total_ms * 1e-3), "unit": "samples/s",
+            "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
+            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": {"workload": DESCRIPTION[args.config], "per_gpu_batch": batch, "parallelism": f"batch-sharded x{world}",
+                       "l2": "flushed between timed iterations (256 MB write)", "precision": prec},
+            "clocks": clocks.summary(),
+            "e2e": {"value": batch * world * args.steps / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "gpu_launches": int(launches_per_step * args.steps),
+            "roofline": roof,
+            "cpu_baseline": {"value": cpu_val, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "port",
+                             "sample": f"{cpu_n} forwards in {cpu_dt:.1f} s, PyTorch CPU eager fp32 (CPU oracle)"},
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

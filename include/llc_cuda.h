@@ -1,0 +1,110 @@
+/* C ABI of the sm_100a kernel library ("ops/cuda", the sibling of the reference's empty
+ * ops/cpu/ops.h).  One entry point per kernel family; each is the CUDA replacement for
+ * the code the reference generates for the named LLH ops.  Pointers are device pointers,
+ * extents and strides are in elements, `stream` is a cudaStream_t (NULL = legacy default
+ * stream).  Every function returns 0 or an LlcStatus (llc_runtime.h) and records a message
+ * readable with llc_last_error().  Nothing here allocates device memory.
+ */
+#ifndef LLC_CUDA_H_
+#define LLC_CUDA_H_
+
+#include <stdint.h>
+
+#include "llc_runtime.h"
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef enum LlcAct { LLC_ACT_NONE = 0, LLC_ACT_RELU = 1, LLC_ACT_GELU = 2 } LlcAct;
+typedef enum LlcPrecision { LLC_PREC_FP32 = 0, LLC_PREC_TF32 = 1, LLC_PREC_TF32X3 = 2, LLC_PREC_BF16 = 3 } LlcPrecision;
+
+/* out[b0,b1,m,n] = act(alpha * scale[n] * sum_k A[b0,b1,m,k] * B[b0,b1,k,n] + shift[n] + res[b0,b1,m,n])
+ * Replaces llh.matmul / llh.batch_matmul (-> stablehlo.dot / dot_general,
+ * src/Conversion/LLHToHLO/LLHToHLO.cpp:363-382, :485) together with the elementwise ops that
+ * follow it in the graph (bias add, ReLU = max(x,0) LLHPreprocessingForHLO.cpp:76-101, residual).
+ * A must have unit stride along k.  B has unit stride along k (b_sk == 1, weights stored [n][k])
+ * or along n (b_sn == 1).  scale/shift/res may be NULL.  Accumulation is fp32. */
+typedef struct LlcGemmParams {
+  const void* a; const void* b; void* out;
+  const float* scale; const float* shift; const void* res;
+  int32_t in_dtype;    /* LLC_FLOAT32 or LLC_BFLOAT16, both operands */
+  int32_t out_dtype;   /* LLC_FLOAT32 or LLC_BFLOAT16 */
+  int32_t res_dtype;
+  int32_t precision;   /* LlcPrecision; LLC_PREC_FP32 = FMA path */
+  int64_t m, n, k, b0, b1;
+  int64_t a_s0, a_s1, a_sm;            /* strides of A: batch0, batch1, row (k stride is 1) */
+  int64_t b_s0, b_s1, b_sk, b_sn;
+  int64_t o_s0, o_s1, o_sm;            /* n stride is 1 */
+  int64_t r_s0, r_s1, r_sm, r_sn;
+  float alpha;
+  int32_t act;         /* LlcAct */
+} LlcGemmParams;
+int llc_cuda_gemm(const LlcGemmParams* p, void* stream);
+
+/* NHWC implicit-GEMM convolution with the same epilogue; replaces llh.conv
+ * (-> stablehlo.convolution, LLHToHLO.cpp:214-270), the decomposed batch-norm inference that
+ * follows it (src/Dialect/LLH/Transforms/DecomposeOps.cpp:125-144, folded to scale/shift),
+ * the residual add and the ReLU.  x is [N,H,W,C], w is [F,KH,KW,C], out and res are [N,OH,OW,F]. */
+typedef struct LlcConvParams {
+  const void* x; const void* w; void* out;
+  const float* scale; const float* shift; const void* res;
+  int32_t in_dtype, out_dtype, res_dtype, precision;
+  int64_t n, h, w_in, c, f, kh, kw, oh, ow;
+  int32_t stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+  float alpha;
+  int32_t act;
+} LlcConvParams;
+int llc_cuda_conv2d(const LlcConvParams* p, void* stream);
+
+/* NHWC max pooling; replaces llh.max_pool (-> stablehlo.reduce_window, LLHToHLO.cpp:295-339).
+ * Padding taps are skipped (equivalent to a -inf initial value; the reference initialises
+ * with 0, :313-314). */
+typedef struct LlcPoolParams {
+  const void* x; void* out;
+  int32_t in_dtype, out_dtype;
+  int64_t n, h, w, c, oh, ow;
+  int32_t kh, kw, stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
+} LlcPoolParams;
+int llc_cuda_maxpool2d(const LlcPoolParams* p, void* stream);
+
+/* out[o,i] = reduce_r x[o,r,i]; x dense [outer,R,inner].  op: 0 sum, 1 max, 2 min, 3 mean.
+ * Replaces llh.reduce_sum/max/min (-> stablehlo.reduce, LLHToHLO.cpp:81-171) and the global
+ * average pool (llh.adaptive_average_pool, declared without a lowering, LLHOps.td:337-339). */
+int llc_cuda_reduce(const void* x, void* out, int32_t in_dtype, int32_t out_dtype, int64_t outer,
+                    int64_t r, int64_t inner, int32_t op, void* stream);
+
+/* Row softmax over dense [rows, len]; replaces the amax/sub/exp/sum/div chain of the
+ * reference's decomposition (llcompiler/compiler/torch_compile_config.py:24). */
+int llc_cuda_softmax(const void* x, void* out, int32_t in_dtype, int32_t out_dtype, int64_t rows,
+                     int64_t len, void* stream);
+
+/* Row LayerNorm over dense [rows, d] with fp32 statistics; llh.layer_norm is declared by the
+ * reference (LLHOps.td:454-463) without a lowering. */
+int llc_cuda_layernorm(const void* x, const void* gamma, const void* beta, void* out, int32_t in_dtype,
+                       int32_t param_dtype, int32_t out_dtype, int64_t rows, int64_t d, float eps, void* stream);
+
+/* out[r,:] = table[ids[r],:]; ids are int64.  Rows with an id outside [0, vocab) are written
+ * as zeros and counted in *bad_ids when bad_ids is not NULL (a device int32). */
+int llc_cuda_gather(const void* table, const int64_t* ids, void* out, int32_t table_dtype, int32_t out_dtype,
+                    int64_t rows, int64_t d, int64_t vocab, int32_t* bad_ids, void* stream);
+
+/* Fused elementwise chain: one coalesced pass that evaluates a small register program per
+ * output element.  Replaces chains of llh.add/sub/mul/div/max/min/abs/sqrt/exp/where/compare/
+ * convert_to/broadcast_to (-> stablehlo elementwise ops, LLHToHLO.cpp:479-490) and strided
+ * copies (llh.transpose -> stablehlo.transpose).  `prog` is ';'-separated instructions, the
+ * i-th defines register i: "ld<k>" loads input k, "#<v>" is a constant, "<op>,<a>[,<b>[,<c>]]"
+ * applies an op to earlier registers.  All arithmetic is fp32.  Up to 8 inputs, rank <= 6. */
+typedef struct LlcEltwiseOperand { const void* data; int32_t dtype; int64_t strides[6]; } LlcEltwiseOperand;
+typedef struct LlcEltwiseParams {
+  void* out; int32_t out_dtype; int32_t rank;
+  int64_t shape[6]; int64_t out_strides[6];
+  int32_t n_in; LlcEltwiseOperand in[8];
+  const char* prog;
+} LlcEltwiseParams;
+int llc_cuda_eltwise(const LlcEltwiseParams* p, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* LLC_CUDA_H_ */

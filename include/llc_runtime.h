@@ -102,6 +102,14 @@ int llc_output_shape(LlcExec* exec, const int64_t* symbols, int n_symbols, const
 int llc_run(LlcExec* exec, const int64_t* symbols, int n_symbols, const LlcTensor* inputs, int n_inputs,
             LlcTensor* outputs, int n_outputs, void* stream);
 
+/* Same arguments as llc_run; runs the plan `reps` times (after one warm-up pass) with CUDA events
+ * around every kernel and writes a text report: one "step <i> <kernel> <ms> <flops> <bytes>" line per
+ * plan step and one "kernel <name> <launches> <ms> <flops> <bytes>" line per kernel family (ms and
+ * work per run; flops and bytes are the algorithmic figures).  The reference's only timing aid is a
+ * wall-clock decorator (llcompiler/utility/utility.py:6-15). */
+int llc_profile(LlcExec* exec, const int64_t* symbols, int n_symbols, const LlcTensor* inputs, int n_inputs,
+                LlcTensor* outputs, int n_outputs, int reps, void* stream, char* report, size_t report_len);
+
 /* Number of kernels the last llc_run on this handle launched, and arena bytes in use. */
 int64_t llc_last_launch_count(const LlcExec* exec);
 int64_t llc_arena_bytes(const LlcExec* exec);

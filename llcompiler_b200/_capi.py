@@ -81,3 +81,51 @@ def tensor_desc(ptr: int, dtype_code: int, device: int, sizes: Sequence[int], st
     st = (c_int64 * max(n, 1))(*strides)
     t = LlcTensor(c_void_p(ptr), dtype_code, device, n, ctypes.cast(s, POINTER(c_int64)), ctypes.cast(st, POINTER(c_int64)))
     return t, (s, st)
+
+
+# ---- kernel library (include/llc_cuda.h) -----------------------------------------------
+from ctypes import c_float  # noqa: E402
+
+LLC_DTYPE = {"int8": 0, "int16": 1, "int32": 2, "int64": 3, "float32": 4, "float64": 5, "bool": 6,
+             "float16": 7, "bfloat16": 8}
+ACT = {"none": 0, "relu": 1, "gelu": 2}
+PREC = {"fp32": 0, "tf32": 1, "tf32x3": 2, "bf16": 3}
+
+
+class LlcGemmParams(Structure):
+    _fields_ = [("a", c_void_p), ("b", c_void_p), ("out", c_void_p), ("scale", c_void_p), ("shift", c_void_p),
+                ("res", c_void_p), ("in_dtype", c_int32), ("out_dtype", c_int32), ("res_dtype", c_int32),
+                ("precision", c_int32)] + [(n, c_int64) for n in (
+                    "m", "n", "k", "b0", "b1", "a_s0", "a_s1", "a_sm", "b_s0", "b_s1", "b_sk", "b_sn",
+                    "o_s0", "o_s1", "o_sm", "r_s0", "r_s1", "r_sm", "r_sn")] + [("alpha", c_float), ("act", c_int32)]
+
+
+class LlcConvParams(Structure):
+    _fields_ = [("x", c_void_p), ("w", c_void_p), ("out", c_void_p), ("scale", c_void_p), ("shift", c_void_p),
+                ("res", c_void_p), ("in_dtype", c_int32), ("out_dtype", c_int32), ("res_dtype", c_int32),
+                ("precision", c_int32)] + [(n, c_int64) for n in ("n", "h", "w_in", "c", "f", "kh", "kw", "oh", "ow")] + \
+               [(n, c_int32) for n in ("stride_h", "stride_w", "pad_h", "pad_w", "dil_h", "dil_w")] + \
+               [("alpha", c_float), ("act", c_int32)]
+
+
+class LlcPoolParams(Structure):
+    _fields_ = [("x", c_void_p), ("out", c_void_p), ("in_dtype", c_int32), ("out_dtype", c_int32)] + \
+               [(n, c_int64) for n in ("n", "h", "w", "c", "oh", "ow")] + \
+               [(n, c_int32) for n in ("kh", "kw", "stride_h", "stride_w", "pad_h", "pad_w", "dil_h", "dil_w")]
+
+
+class LlcEltwiseOperand(Structure):
+    _fields_ = [("data", c_void_p), ("dtype", c_int32), ("strides", c_int64 * 6)]
+
+
+class LlcEltwiseParams(Structure):
+    _fields_ = [("out", c_void_p), ("out_dtype", c_int32), ("rank", c_int32), ("shape", c_int64 * 6),
+                ("out_strides", c_int64 * 6), ("n_in", c_int32), ("inputs", LlcEltwiseOperand * 8), ("prog", c_char_p)]
+
+
+EXPORTED_SYMBOLS = [
+    "llc_compile", "llc_run_pass", "llc_load", "llc_num_inputs", "llc_num_outputs", "llc_num_symbols",
+    "llc_output_shape", "llc_run", "llc_profile", "llc_last_launch_count", "llc_arena_bytes", "llc_free", "llc_last_error",
+    "llc_version", "llc_cuda_gemm", "llc_cuda_conv2d", "llc_cuda_maxpool2d", "llc_cuda_reduce",
+    "llc_cuda_softmax", "llc_cuda_layernorm", "llc_cuda_gather", "llc_cuda_eltwise",
+]

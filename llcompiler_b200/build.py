@@ -26,7 +26,7 @@ INCLUDE = ROOT.parent / "include"
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 ARCH = ["-gencode", "arch=compute_100a,code=sm_100a"]
 CXX_FLAGS = ["-O3", "-std=c++17", "-fPIC", "-Wall", "-Wno-unused-function", f"-I{INCLUDE}", f"-I{CSRC}"]
-NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "--use_fast_math", "-Xcompiler", "-fPIC", f"-I{INCLUDE}", f"-I{CSRC}",
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", f"-I{INCLUDE}", f"-I{CSRC}",
               "--expt-relaxed-constexpr", "-Xptxas", "-v"] + ARCH
 
 
@@ -34,11 +34,26 @@ def _headers() -> List[Path]:
     return list(CSRC.rglob("*.h")) + list(CSRC.rglob("*.cuh")) + list(INCLUDE.glob("*.h"))
 
 
-def _stale(target: Path, deps: List[Path]) -> bool:
-    if not target.exists():
+def _digest(deps: List[Path], extra: str = "") -> str:
+    import hashlib
+    h = hashlib.sha1(extra.encode())
+    for d in sorted(deps):
+        h.update(d.name.encode())
+        h.update(d.read_bytes())
+    return h.hexdigest()
+
+
+def _stale(target: Path, deps: List[Path], extra: str = "") -> bool:
+    """A target is rebuilt when the content of its inputs changed (a content stamp, not mtimes:
+    a copied tree keeps the built objects valid)."""
+    stamp = target.with_name(target.name + ".stamp")
+    if not target.exists() or not stamp.exists():
         return True
-    t = target.stat().st_mtime
-    return any(d.stat().st_mtime > t for d in deps)
+    return stamp.read_text() != _digest(deps, extra)
+
+
+def _mark(target: Path, deps: List[Path], extra: str = "") -> None:
+    target.with_name(target.name + ".stamp").write_text(_digest(deps, extra))
 
 
 def _compile_one(src: Path, obj: Path, verbose: bool) -> str:
@@ -61,16 +76,19 @@ def build_library(verbose: bool = False, force: bool = False) -> Path:
     hdrs = _headers()
     jobs = []
     objs = []
+    flags = " ".join(NVCC_FLAGS + CXX_FLAGS)
     for s in srcs:
         o = OBJ_DIR / (s.relative_to(CSRC).as_posix().replace("/", "_") + ".o")
         objs.append(o)
-        if force or _stale(o, [s] + hdrs):
+        if force or _stale(o, [s] + hdrs, flags):
             jobs.append((s, o))
     if jobs:
         with ThreadPoolExecutor(max_workers=min(8, os.cpu_count() or 2)) as ex:
             for log in ex.map(lambda j: _compile_one(j[0], j[1], verbose), jobs):
                 if verbose:
                     print(log)
+        for s, o in jobs:
+            _mark(o, [s] + hdrs, flags)
     if jobs or not LIB.exists():
         cmd = [NVCC, "-shared", "-o", str(LIB)] + [str(o) for o in objs] + ARCH + ["-lcudart_static", "-ldl", "-lpthread", "-lrt"]
         r = subprocess.run(cmd, capture_output=True, text=True)
@@ -87,13 +105,15 @@ def build_pybind(force: bool = False) -> Path:
     import pybind11
     src = CSRC / "pybind" / "entrance.cpp"
     out = pybind_module_path()
-    if force or _stale(out, [src, LIB] + _headers()):
+    deps = [src] + _headers()
+    if force or _stale(out, deps) or out.stat().st_mtime < LIB.stat().st_mtime - 1e9:
         cmd = ["g++", "-O2", "-std=c++17", "-fPIC", "-shared", f"-I{pybind11.get_include()}",
                f"-I{sysconfig.get_paths()['include']}", f"-I{INCLUDE}", str(src), "-o", str(out),
                f"-L{LIB_DIR}", "-lllc_cuda", f"-Wl,-rpath,{LIB_DIR}", "-Wl,-rpath,$ORIGIN/llcompiler_b200/lib"]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
             raise RuntimeError("building the llcompiler_ module failed:\n" + r.stdout + r.stderr)
+        _mark(out, deps)
     return out
 
 

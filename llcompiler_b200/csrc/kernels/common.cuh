@@ -1,0 +1,115 @@
+// Shared device helpers for the sm_100a kernel library.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#include <string>
+
+#include "../../../include/llc_cuda.h"
+#include "../capi_common.h"
+
+namespace llc {
+
+constexpr int kNumSMs = 148;   // B200: 2 dies x 74 SMs
+
+inline int cudaFail(cudaError_t e, const char* what) {
+  return setError(LLC_ERR_CUDA, std::string("llc cuda: ") + what + ": " + cudaGetErrorString(e));
+}
+#define LLC_CUDA_CHECK(expr)                                   \
+  do {                                                         \
+    cudaError_t e__ = (expr);                                  \
+    if (e__ != cudaSuccess) return llc::cudaFail(e__, #expr);  \
+  } while (0)
+#define LLC_LAUNCH_CHECK(name)                                     \
+  do {                                                             \
+    cudaError_t e__ = cudaGetLastError();                          \
+    if (e__ != cudaSuccess) return llc::cudaFail(e__, name);       \
+  } while (0)
+
+inline int dtypeBytes(int32_t dt) {
+  switch (dt) {
+    case LLC_INT8: case LLC_INT1: return 1;
+    case LLC_INT16: case LLC_FLOAT16: case LLC_BFLOAT16: return 2;
+    case LLC_INT32: case LLC_FLOAT32: return 4;
+    default: return 8;
+  }
+}
+inline bool isFloatOut(int32_t dt) { return dt == LLC_FLOAT32 || dt == LLC_BFLOAT16 || dt == LLC_FLOAT16 || dt == LLC_FLOAT64; }
+
+// ---- scalar load/store with a run-time element type (uniform per launch) -------------------
+__device__ __forceinline__ float loadAs(const void* p, int64_t i, int dt) {
+  switch (dt) {
+    case LLC_FLOAT32: return reinterpret_cast<const float*>(p)[i];
+    case LLC_BFLOAT16: return __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(p)[i]);
+    case LLC_FLOAT16: return __half2float(reinterpret_cast<const __half*>(p)[i]);
+    case LLC_INT64: return (float)reinterpret_cast<const long long*>(p)[i];
+    case LLC_INT32: return (float)reinterpret_cast<const int*>(p)[i];
+    case LLC_INT16: return (float)reinterpret_cast<const short*>(p)[i];
+    case LLC_INT8: return (float)reinterpret_cast<const signed char*>(p)[i];
+    case LLC_INT1: return reinterpret_cast<const unsigned char*>(p)[i] ? 1.f : 0.f;
+    case LLC_FLOAT64: return (float)reinterpret_cast<const double*>(p)[i];
+  }
+  return 0.f;
+}
+__device__ __forceinline__ void storeAs(void* p, int64_t i, int dt, float v) {
+  switch (dt) {
+    case LLC_FLOAT32: reinterpret_cast<float*>(p)[i] = v; break;
+    case LLC_BFLOAT16: reinterpret_cast<__nv_bfloat16*>(p)[i] = __float2bfloat16_rn(v); break;
+    case LLC_FLOAT16: reinterpret_cast<__half*>(p)[i] = __float2half_rn(v); break;
+    case LLC_INT64: reinterpret_cast<long long*>(p)[i] = (long long)v; break;
+    case LLC_INT32: reinterpret_cast<int*>(p)[i] = (int)v; break;
+    case LLC_INT16: reinterpret_cast<short*>(p)[i] = (short)v; break;
+    case LLC_INT8: reinterpret_cast<signed char*>(p)[i] = (signed char)v; break;
+    case LLC_INT1: reinterpret_cast<unsigned char*>(p)[i] = v != 0.f ? 1 : 0; break;
+    case LLC_FLOAT64: reinterpret_cast<double*>(p)[i] = (double)v; break;
+  }
+}
+
+// ---- 4-wide vector access for the two storage types the hot kernels use --------------------
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+  static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+  static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<__nv_bfloat16> {
+  static __device__ __forceinline__ float4 load(const __nv_bfloat16* p) {
+    uint2 raw = *reinterpret_cast<const uint2*>(p);
+    __nv_bfloat162 lo = *reinterpret_cast<__nv_bfloat162*>(&raw.x), hi = *reinterpret_cast<__nv_bfloat162*>(&raw.y);
+    float2 a = __bfloat1622float2(lo), b = __bfloat1622float2(hi);
+    return make_float4(a.x, a.y, b.x, b.y);
+  }
+  static __device__ __forceinline__ void store(__nv_bfloat16* p, float4 v) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(v.x, v.y), hi = __floats2bfloat162_rn(v.z, v.w);
+    uint2 raw; raw.x = *reinterpret_cast<unsigned*>(&lo); raw.y = *reinterpret_cast<unsigned*>(&hi);
+    *reinterpret_cast<uint2*>(p) = raw;
+  }
+};
+template <typename T> __device__ __forceinline__ float toFloat(T v);
+template <> __device__ __forceinline__ float toFloat<float>(float v) { return v; }
+template <> __device__ __forceinline__ float toFloat<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+
+__device__ __forceinline__ float geluErf(float x) { return 0.5f * x * (1.f + erff(x * 0.70710678118654752f)); }
+__device__ __forceinline__ float applyAct(float v, int act) {
+  if (act == LLC_ACT_RELU) return fmaxf(v, 0.f);
+  if (act == LLC_ACT_GELU) return geluErf(v);
+  return v;
+}
+
+__device__ __forceinline__ float warpSum(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+  return v;
+}
+__device__ __forceinline__ float warpMax(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+__device__ __forceinline__ float warpMin(float v) {
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) v = fminf(v, __shfl_xor_sync(0xffffffffu, v, o));
+  return v;
+}
+
+}  // namespace llc

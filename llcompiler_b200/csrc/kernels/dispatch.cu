@@ -1,0 +1,35 @@
+// Entry points of the contraction kernels: argument checks and the choice between the
+// tensor-core path and the FMA path.
+#include "common.cuh"
+
+namespace llc {
+int igemmSimtGemm(const LlcGemmParams* p, cudaStream_t st);
+int igemmSimtConv(const LlcConvParams* p, cudaStream_t st);
+}  // namespace llc
+
+using namespace llc;
+
+static bool floatIo(int32_t dt) { return dt == LLC_FLOAT32 || dt == LLC_BFLOAT16; }
+
+extern "C" int llc_cuda_gemm(const LlcGemmParams* p, void* stream) {
+  if (!p) return setError(LLC_ERR_ARGUMENT, "llc argument: gemm null parameter block");
+  if (p->m < 0 || p->n < 0 || p->k < 0 || p->b0 < 0 || p->b1 < 0) return setError(LLC_ERR_ARGUMENT, "llc argument: gemm negative extent");
+  if (p->m == 0 || p->n == 0 || p->b0 == 0 || p->b1 == 0) return LLC_OK;
+  if (!p->a || !p->b || !p->out) return setError(LLC_ERR_ARGUMENT, "llc argument: gemm null operand");
+  if (!floatIo(p->in_dtype) || !floatIo(p->out_dtype) || (p->res && !floatIo(p->res_dtype)))
+    return setError(LLC_ERR_UNSUPPORTED, "llc argument: gemm operands must be f32 or bf16");
+  return igemmSimtGemm(p, (cudaStream_t)stream);
+}
+
+extern "C" int llc_cuda_conv2d(const LlcConvParams* p, void* stream) {
+  if (!p) return setError(LLC_ERR_ARGUMENT, "llc argument: conv null parameter block");
+  if (p->n < 0 || p->oh < 0 || p->ow < 0 || p->f < 0) return setError(LLC_ERR_ARGUMENT, "llc argument: conv negative extent");
+  if (p->n == 0 || p->oh == 0 || p->ow == 0 || p->f == 0) return LLC_OK;
+  if (!p->x || !p->w || !p->out) return setError(LLC_ERR_ARGUMENT, "llc argument: conv null operand");
+  if (p->stride_h <= 0 || p->stride_w <= 0 || p->dil_h <= 0 || p->dil_w <= 0 || p->kh <= 0 || p->kw <= 0 || p->c <= 0)
+    return setError(LLC_ERR_ARGUMENT, "llc argument: conv stride, dilation, kernel and channel extents must be positive");
+  if (!floatIo(p->in_dtype) || !floatIo(p->out_dtype) || (p->res && !floatIo(p->res_dtype)))
+    return setError(LLC_ERR_UNSUPPORTED, "llc argument: conv operands must be f32 or bf16");
+  if (p->h * p->w_in * p->c >= (1LL << 31) || p->kh * p->kw * p->c >= (1LL << 31)) return setError(LLC_ERR_UNSUPPORTED, "llc argument: conv image or filter too large");
+  return igemmSimtConv(p, (cudaStream_t)stream);
+}

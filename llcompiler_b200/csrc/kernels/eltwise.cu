@@ -1,0 +1,335 @@
+// Fused elementwise chains, strided copies, max pooling and embedding gather: the HBM-bound
+// data-movement kernels.  Algorithmic bytes per call: every input element once + every output
+// element once at storage width.
+#include <cstdlib>
+#include <cstring>
+#include <algorithm>
+#include <vector>
+
+#include "common.cuh"
+
+namespace llc {
+namespace {
+
+constexpr int kMaxInstr = 48;
+constexpr int kMaxRank = 6;
+constexpr int kMaxIn = 8;
+
+enum EltOp : int {
+  E_LD = 0, E_IMM, E_ADD, E_SUB, E_MUL, E_DIV, E_MAX, E_MIN, E_POW, E_RELU, E_ABS, E_SQRT, E_RSQRT, E_EXP, E_GELU, E_TANH,
+  E_ERF, E_SIGMOID, E_NEG, E_CAST, E_TRUNC, E_WHERE, E_EQ, E_NE, E_GE, E_GT, E_LE, E_LT
+};
+
+struct EltProgram {
+  int n;
+  unsigned char op[kMaxInstr], a[kMaxInstr], b[kMaxInstr], c[kMaxInstr];
+  float imm[kMaxInstr];
+};
+
+struct EltArgs {
+  void* out; int odt; int rank; int nin;
+  long long shape[kMaxRank], ostr[kMaxRank];
+  const void* in[kMaxIn]; int idt[kMaxIn]; long long istr[kMaxIn][kMaxRank];
+  long long total;      // number of output elements
+  int innerVec;         // elements handled per thread along the innermost dim (1 or 4)
+  EltProgram prog;
+};
+
+__device__ __forceinline__ float evalOp(int op, float x, float y, float z, float imm) {
+  switch (op) {
+    case E_IMM: return imm;
+    case E_ADD: return x + y;
+    case E_SUB: return x - y;
+    case E_MUL: return x * y;
+    case E_DIV: return x / y;
+    case E_MAX: return fmaxf(x, y);
+    case E_MIN: return fminf(x, y);
+    case E_POW: return powf(x, y);
+    case E_RELU: return fmaxf(x, 0.f);
+    case E_ABS: return fabsf(x);
+    case E_SQRT: return sqrtf(x);
+    case E_RSQRT: return rsqrtf(x);
+    case E_EXP: return expf(x);
+    case E_GELU: return geluErf(x);
+    case E_TANH: return tanhf(x);
+    case E_ERF: return erff(x);
+    case E_SIGMOID: return 1.f / (1.f + expf(-x));
+    case E_NEG: return -x;
+    case E_CAST: return x;
+    case E_TRUNC: return truncf(x);
+    case E_WHERE: return x != 0.f ? y : z;
+    case E_EQ: return x == y ? 1.f : 0.f;
+    case E_NE: return x != y ? 1.f : 0.f;
+    case E_GE: return x >= y ? 1.f : 0.f;
+    case E_GT: return x > y ? 1.f : 0.f;
+    case E_LE: return x <= y ? 1.f : 0.f;
+    case E_LT: return x < y ? 1.f : 0.f;
+  }
+  return 0.f;
+}
+
+// One thread produces V consecutive elements of the innermost (unit output stride) dim.
+template <int V>
+__global__ void __launch_bounds__(256) eltwise_kernel(const __grid_constant__ EltArgs p) {
+  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long first = t * V;
+  if (first >= p.total) return;
+  // decompose the linear index over the (collapsed) shape, innermost last
+  long long rem = first, oOff = 0, iOff[kMaxIn];
+#pragma unroll
+  for (int k = 0; k < kMaxIn; ++k) iOff[k] = 0;
+  for (int d = p.rank - 1; d >= 0; --d) {
+    long long c = rem % p.shape[d]; rem /= p.shape[d];
+    oOff += c * p.ostr[d];
+    for (int k = 0; k < p.nin; ++k) iOff[k] += c * p.istr[k][d];
+  }
+  const int last = p.rank - 1;
+  float regs[kMaxInstr][V];
+  for (int i = 0; i < p.prog.n; ++i) {
+    const int op = p.prog.op[i];
+    if (op == E_LD) {
+      const int k = p.prog.a[i];
+#pragma unroll
+      for (int v = 0; v < V; ++v) regs[i][v] = loadAs(p.in[k], iOff[k] + v * p.istr[k][last], p.idt[k]);
+    } else {
+      const int a = p.prog.a[i], b = p.prog.b[i], c = p.prog.c[i];
+#pragma unroll
+      for (int v = 0; v < V; ++v) regs[i][v] = evalOp(op, regs[a][v], regs[b][v], regs[c][v], p.prog.imm[i]);
+    }
+  }
+  const int r = p.prog.n - 1;
+#pragma unroll
+  for (int v = 0; v < V; ++v) storeAs(p.out, oOff + v * p.ostr[last], p.odt, regs[r][v]);
+}
+
+// Fast path: everything dense (or broadcast) along the innermost dim, f32/bf16 storage, 16-byte
+// aligned: 128-bit loads and stores, four elements per thread.
+struct VecIo {
+  static __device__ __forceinline__ float4 load(const void* p, long long off, int dt, long long stride) {
+    if (stride == 0) { float v = loadAs(p, off, dt); return make_float4(v, v, v, v); }
+    if (dt == LLC_FLOAT32) return Vec4<float>::load(reinterpret_cast<const float*>(p) + off);
+    return Vec4<__nv_bfloat16>::load(reinterpret_cast<const __nv_bfloat16*>(p) + off);
+  }
+  static __device__ __forceinline__ void store(void* p, long long off, int dt, float4 v) {
+    if (dt == LLC_FLOAT32) Vec4<float>::store(reinterpret_cast<float*>(p) + off, v);
+    else Vec4<__nv_bfloat16>::store(reinterpret_cast<__nv_bfloat16*>(p) + off, v);
+  }
+};
+__global__ void __launch_bounds__(256) eltwise_vec_kernel(const __grid_constant__ EltArgs p) {
+  long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long first = t * 4;
+  if (first >= p.total) return;
+  long long rem = first, oOff = 0, iOff[kMaxIn];
+#pragma unroll
+  for (int k = 0; k < kMaxIn; ++k) iOff[k] = 0;
+  for (int d = p.rank - 1; d >= 0; --d) {
+    long long c = rem % p.shape[d]; rem /= p.shape[d];
+    oOff += c * p.ostr[d];
+    for (int k = 0; k < p.nin; ++k) iOff[k] += c * p.istr[k][d];
+  }
+  const int last = p.rank - 1;
+  float regs[kMaxInstr][4];
+  for (int i = 0; i < p.prog.n; ++i) {
+    const int op = p.prog.op[i];
+    if (op == E_LD) {
+      const int k = p.prog.a[i];
+      float4 v = VecIo::load(p.in[k], iOff[k], p.idt[k], p.istr[k][last]);
+      regs[i][0] = v.x; regs[i][1] = v.y; regs[i][2] = v.z; regs[i][3] = v.w;
+    } else {
+      const int a = p.prog.a[i], b = p.prog.b[i], c = p.prog.c[i];
+#pragma unroll
+      for (int v = 0; v < 4; ++v) regs[i][v] = evalOp(op, regs[a][v], regs[b][v], regs[c][v], p.prog.imm[i]);
+    }
+  }
+  const int r = p.prog.n - 1;
+  VecIo::store(p.out, oOff, p.odt, make_float4(regs[r][0], regs[r][1], regs[r][2], regs[r][3]));
+}
+
+int parseProgram(const char* text, EltProgram& prog, int nin) {
+  static const struct { const char* name; int op; int arity; } table[] = {
+      {"add", E_ADD, 2}, {"sub", E_SUB, 2}, {"mul", E_MUL, 2}, {"div", E_DIV, 2}, {"max", E_MAX, 2}, {"min", E_MIN, 2}, {"pow", E_POW, 2},
+      {"relu", E_RELU, 1}, {"abs", E_ABS, 1}, {"sqrt", E_SQRT, 1}, {"rsqrt", E_RSQRT, 1}, {"exp", E_EXP, 1}, {"gelu", E_GELU, 1},
+      {"tanh", E_TANH, 1}, {"erf", E_ERF, 1}, {"sigmoid", E_SIGMOID, 1}, {"neg", E_NEG, 1}, {"cast", E_CAST, 1}, {"trunc", E_TRUNC, 1},
+      {"where", E_WHERE, 3}, {"eq", E_EQ, 2}, {"ne", E_NE, 2}, {"ge", E_GE, 2}, {"gt", E_GT, 2}, {"le", E_LE, 2}, {"lt", E_LT, 2}};
+  prog.n = 0;
+  std::string s = text ? text : "";
+  size_t pos = 0;
+  while (pos <= s.size()) {
+    size_t end = s.find(';', pos);
+    if (end == std::string::npos) end = s.size();
+    std::string ins = s.substr(pos, end - pos);
+    pos = end + 1;
+    if (ins.empty()) { if (end == s.size()) break; continue; }
+    if (prog.n >= kMaxInstr) return setError(LLC_ERR_ARGUMENT, "llc argument: elementwise program longer than 48 instructions");
+    int i = prog.n++;
+    prog.a[i] = prog.b[i] = prog.c[i] = 0; prog.imm[i] = 0.f;
+    if (ins.compare(0, 2, "ld") == 0) {
+      int k = atoi(ins.c_str() + 2);
+      if (k < 0 || k >= nin) return setError(LLC_ERR_ARGUMENT, "llc argument: elementwise program loads a missing input");
+      prog.op[i] = E_LD; prog.a[i] = (unsigned char)k;
+    } else if (ins[0] == '#') {
+      prog.op[i] = E_IMM; prog.imm[i] = strtof(ins.c_str() + 1, nullptr);
+    } else {
+      std::vector<std::string> f; size_t q = 0;
+      while (q <= ins.size()) { size_t e = ins.find(',', q); if (e == std::string::npos) e = ins.size(); f.push_back(ins.substr(q, e - q)); q = e + 1; }
+      int found = -1;
+      for (size_t k = 0; k < sizeof(table) / sizeof(table[0]); ++k) if (f[0] == table[k].name) found = (int)k;
+      if (found < 0) return setError(LLC_ERR_ARGUMENT, "llc argument: unknown elementwise op '" + f[0] + "'");
+      if ((int)f.size() - 1 != table[found].arity) return setError(LLC_ERR_ARGUMENT, "llc argument: wrong operand count for '" + f[0] + "'");
+      prog.op[i] = (unsigned char)table[found].op;
+      unsigned char* dst[3] = {&prog.a[i], &prog.b[i], &prog.c[i]};
+      for (int k = 0; k < table[found].arity; ++k) {
+        int r = atoi(f[k + 1].c_str());
+        if (r < 0 || r >= i) return setError(LLC_ERR_ARGUMENT, "llc argument: elementwise program reads an undefined register");
+        *dst[k] = (unsigned char)r;
+      }
+    }
+  }
+  if (prog.n == 0) return setError(LLC_ERR_ARGUMENT, "llc argument: empty elementwise program");
+  return LLC_OK;
+}
+
+// ---- max pooling (NHWC) -------------------------------------------------------------------------
+template <typename T, int V>
+__global__ void __launch_bounds__(256) maxpool_nhwc_kernel(const T* __restrict__ x, T* __restrict__ out, LlcPoolParams p) {
+  const long long cv = p.c / V;
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  long long total = p.n * p.oh * p.ow * cv;
+  if (idx >= total) return;
+  int c = (int)(idx % cv) * V; long long t = idx / cv;
+  int ow = (int)(t % p.ow); t /= p.ow; int oh = (int)(t % p.oh); long long n = t / p.oh;
+  float m[V];
+#pragma unroll
+  for (int v = 0; v < V; ++v) m[v] = -INFINITY;
+  for (int r = 0; r < p.kh; ++r) {
+    int ih = oh * p.stride_h - p.pad_h + r * p.dil_h;
+    if (ih < 0 || ih >= p.h) continue;
+    for (int s = 0; s < p.kw; ++s) {
+      int iw = ow * p.stride_w - p.pad_w + s * p.dil_w;
+      if (iw < 0 || iw >= p.w) continue;
+      const T* src = x + ((n * p.h + ih) * p.w + iw) * p.c + c;
+      if (V == 4) { float4 q = Vec4<T>::load(src); m[0] = fmaxf(m[0], q.x); m[1] = fmaxf(m[1], q.y); m[2] = fmaxf(m[2], q.z); m[3] = fmaxf(m[3], q.w); }
+      else m[0] = fmaxf(m[0], toFloat<T>(src[0]));
+    }
+  }
+  T* dst = out + ((n * p.oh + oh) * p.ow + ow) * p.c + c;
+  if (V == 4) Vec4<T>::store(dst, make_float4(m[0], m[1], m[2], m[3]));
+  else storeAs(dst, 0, sizeof(T) == 4 ? LLC_FLOAT32 : LLC_BFLOAT16, m[0]);
+}
+
+// ---- gather --------------------------------------------------------------------------------------
+__global__ void __launch_bounds__(256) gather_rows_kernel(const void* table, const long long* ids, void* out, int tdt, int odt, long long rows, long long d,
+                                                          long long vocab, int* bad, int fastCopy) {
+  long long row = (long long)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int lane = threadIdx.x & 31;
+  long long id = ids[row];
+  bool ok = id >= 0 && id < vocab;
+  if (!ok && lane == 0 && bad) atomicAdd(bad, 1);
+  if (ok && fastCopy) {
+    // same storage type: copy 16 bytes at a time
+    const int eb = tdt == LLC_FLOAT32 ? 4 : 2;
+    const uint4* src = reinterpret_cast<const uint4*>(reinterpret_cast<const char*>(table) + id * d * eb);
+    uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<char*>(out) + row * d * eb);
+    long long n16 = d * eb / 16;
+    for (long long i = lane; i < n16; i += 32) dst[i] = src[i];
+    return;
+  }
+  for (long long c = lane; c < d; c += 32) storeAs(out, row * d + c, odt, ok ? loadAs(table, id * d + c, tdt) : 0.f);
+}
+
+}  // namespace
+}  // namespace llc
+
+using namespace llc;
+
+extern "C" int llc_cuda_eltwise(const LlcEltwiseParams* q, void* stream) {
+  if (!q || !q->out) return setError(LLC_ERR_ARGUMENT, "llc argument: eltwise null pointer");
+  if (q->rank < 1 || q->rank > kMaxRank) return setError(LLC_ERR_ARGUMENT, "llc argument: eltwise rank must be 1..6");
+  if (q->n_in < 0 || q->n_in > kMaxIn) return setError(LLC_ERR_ARGUMENT, "llc argument: eltwise takes at most 8 inputs");
+  EltArgs a{};
+  int rc = parseProgram(q->prog, a.prog, q->n_in);
+  if (rc) return rc;
+  a.out = q->out; a.odt = q->out_dtype; a.nin = q->n_in;
+  for (int k = 0; k < q->n_in; ++k) { a.in[k] = q->in[k].data; a.idt[k] = q->in[k].dtype; if (!a.in[k]) return setError(LLC_ERR_ARGUMENT, "llc argument: eltwise null input"); }
+  // order dims by output stride (outermost first), drop unit dims, merge dims that are dense in every operand
+  std::vector<int> dims;
+  long long total = 1;
+  for (int d = 0; d < q->rank; ++d) { if (q->shape[d] < 0) return setError(LLC_ERR_ARGUMENT, "llc argument: negative extent"); total *= q->shape[d]; if (q->shape[d] != 1) dims.push_back(d); }
+  if (total == 0) return LLC_OK;
+  std::stable_sort(dims.begin(), dims.end(), [&](int x, int y) { return q->out_strides[x] > q->out_strides[y]; });
+  int r = 0;
+  for (int d : dims) {
+    bool merge = r > 0;
+    if (merge) {
+      if (a.ostr[r - 1] != q->shape[d] * q->out_strides[d]) merge = false;
+      for (int k = 0; k < q->n_in && merge; ++k) if (a.istr[k][r - 1] != q->shape[d] * q->in[k].strides[d]) merge = false;
+    }
+    if (merge) {
+      a.shape[r - 1] *= q->shape[d]; a.ostr[r - 1] = q->out_strides[d];
+      for (int k = 0; k < q->n_in; ++k) a.istr[k][r - 1] = q->in[k].strides[d];
+    } else {
+      a.shape[r] = q->shape[d]; a.ostr[r] = q->out_strides[d];
+      for (int k = 0; k < q->n_in; ++k) a.istr[k][r] = q->in[k].strides[d];
+      ++r;
+    }
+  }
+  if (r == 0) { a.shape[0] = 1; a.ostr[0] = 1; for (int k = 0; k < q->n_in; ++k) a.istr[k][0] = 0; r = 1; }
+  a.rank = r; a.total = total;
+  cudaStream_t st = (cudaStream_t)stream;
+  const long long inner = a.shape[r - 1];
+  auto isVecType = [](int dt) { return dt == LLC_FLOAT32 || dt == LLC_BFLOAT16; };
+  auto alignedFor = [](const void* p, int dt) { return (reinterpret_cast<uintptr_t>(p) % (dt == LLC_FLOAT32 ? 16 : 8)) == 0; };
+  bool vec = inner % 4 == 0 && a.ostr[r - 1] == 1 && isVecType(a.odt) && alignedFor(a.out, a.odt);
+  for (int d = 0; d + 1 < r && vec; ++d) if (a.ostr[d] % 4) vec = false;
+  for (int k = 0; k < a.nin && vec; ++k) {
+    long long s = a.istr[k][r - 1];
+    if (s == 0) continue;
+    if (s != 1 || !isVecType(a.idt[k]) || !alignedFor(a.in[k], a.idt[k])) vec = false;
+    for (int d = 0; d + 1 < r && vec; ++d) if (a.istr[k][d] % 4) vec = false;
+  }
+  if (vec) {
+    long long threads = total / 4;
+    eltwise_vec_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(a);
+    LLC_LAUNCH_CHECK("eltwise_vec_kernel");
+  } else if (inner % 4 == 0) {
+    long long threads = total / 4;
+    eltwise_kernel<4><<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(a);
+    LLC_LAUNCH_CHECK("eltwise_kernel<4>");
+  } else {
+    eltwise_kernel<1><<<(unsigned)((total + 255) / 256), 256, 0, st>>>(a);
+    LLC_LAUNCH_CHECK("eltwise_kernel<1>");
+  }
+  return LLC_OK;
+}
+
+extern "C" int llc_cuda_maxpool2d(const LlcPoolParams* p, void* stream) {
+  if (!p || !p->x || !p->out) return setError(LLC_ERR_ARGUMENT, "llc argument: maxpool null pointer");
+  if (p->in_dtype != p->out_dtype) return setError(LLC_ERR_ARGUMENT, "llc argument: maxpool input and output types differ");
+  long long total = p->n * p->oh * p->ow * p->c;
+  if (total <= 0) return LLC_OK;
+  cudaStream_t st = (cudaStream_t)stream;
+  bool v4 = p->c % 4 == 0 && (reinterpret_cast<uintptr_t>(p->x) % 16) == 0 && (reinterpret_cast<uintptr_t>(p->out) % 16) == 0;
+  long long threads = v4 ? total / 4 : total;
+  unsigned blocks = (unsigned)((threads + 255) / 256);
+  if (p->in_dtype == LLC_FLOAT32) {
+    if (v4) maxpool_nhwc_kernel<float, 4><<<blocks, 256, 0, st>>>((const float*)p->x, (float*)p->out, *p);
+    else maxpool_nhwc_kernel<float, 1><<<blocks, 256, 0, st>>>((const float*)p->x, (float*)p->out, *p);
+  } else if (p->in_dtype == LLC_BFLOAT16) {
+    if (v4) maxpool_nhwc_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
+    else maxpool_nhwc_kernel<__nv_bfloat16, 1><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
+  } else return setError(LLC_ERR_UNSUPPORTED, "llc argument: maxpool type must be f32 or bf16");
+  LLC_LAUNCH_CHECK("maxpool_nhwc_kernel");
+  return LLC_OK;
+}
+
+extern "C" int llc_cuda_gather(const void* table, const int64_t* ids, void* out, int32_t tdt, int32_t odt, int64_t rows, int64_t d, int64_t vocab,
+                               int32_t* bad, void* stream) {
+  if (rows <= 0 || d <= 0) return LLC_OK;
+  if (!table || !ids || !out) return setError(LLC_ERR_ARGUMENT, "llc argument: gather null pointer");
+  int fast = tdt == odt && d % 8 == 0 && (tdt == LLC_BFLOAT16 || tdt == LLC_FLOAT32) && (reinterpret_cast<uintptr_t>(table) % 16) == 0 &&
+             (reinterpret_cast<uintptr_t>(out) % 16) == 0;
+  gather_rows_kernel<<<(unsigned)((rows + 7) / 8), 256, 0, (cudaStream_t)stream>>>(table, (const long long*)ids, out, tdt, odt, rows, d, vocab, bad, fast);
+  LLC_LAUNCH_CHECK("gather_rows_kernel");
+  return LLC_OK;
+}

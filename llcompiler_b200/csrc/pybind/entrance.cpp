@@ -1,0 +1,162 @@
+// pybind11 module `llcompiler_`: the reference's Python-facing native module
+// (src/Pybind/Entrance.cpp:69-120) re-bound onto the C ABI of llc_runtime.h.  Same submodules
+// (tensor, compiler, executor), same class and method names, same argument order.  A non-zero
+// status from the C ABI becomes a Python RuntimeError (the reference logs and carries on,
+// include/llcompiler/Support/Logger.h:126-134).
+#include <pybind11/pybind11.h>
+#include <pybind11/stl.h>
+
+#include <cstring>
+#include <stdexcept>
+#include <string>
+#include <vector>
+
+#include "llc_runtime.h"
+
+namespace py = pybind11;
+
+namespace {
+
+void check(int rc) { if (rc != LLC_OK) throw std::runtime_error(std::string("[llc status ") + std::to_string(rc) + "] " + llc_last_error()); }
+
+// llc::compiler::Tensor (include/llcompiler/Compiler/Tensor.h:35-48) plus a device ordinal.
+struct Tensor {
+  uintptr_t data = 0, base = 0;
+  int type = LLC_FLOAT32;
+  int64_t offset = 0;
+  std::vector<int64_t> size, stride;
+  int device = -1;
+  Tensor() {}
+  Tensor(uintptr_t data_ptr, uintptr_t base_ptr, int type_, int64_t offset_, std::vector<int64_t> size_, std::vector<int64_t> stride_, int device_ = -1)
+      : data(data_ptr), base(base_ptr), type(type_), offset(offset_), size(std::move(size_)), stride(std::move(stride_)), device(device_) {}
+  LlcTensor desc() const { return LlcTensor{reinterpret_cast<void*>(data), type, device, (int32_t)size.size(), size.data(), stride.data()}; }
+  void print() const {
+    std::string s = "Tensor(data=" + std::to_string(data) + ", type=" + std::to_string(type) + ", device=" + std::to_string(device) + ", size=[";
+    for (size_t i = 0; i < size.size(); ++i) s += (i ? "," : "") + std::to_string(size[i]);
+    py::print(s + "])");
+  }
+};
+
+// llc::compiler::CompileOptions (include/llcompiler/Compiler/CompileOption.h:39-71)
+struct CompileOptions {
+  std::string mode = "inference", target = "sm_100a", pipeline = "cuda", global_layout = "NCHW", log_root, log_level = "debug", cpu, mtriple, precision = "auto";
+  bool mlir_passes = false, llvm_passes = false;
+  LlcOptions c() const { return LlcOptions{mode.c_str(), target.c_str(), pipeline.c_str(), global_layout.c_str(), log_root.c_str(), log_level.c_str(), cpu.c_str(), mtriple.c_str(), precision.c_str()}; }
+};
+
+struct Compiler {
+  std::string compile_mlir_to_shared_lib(const std::string& text, const CompileOptions& o) {
+    char path[1024];
+    LlcOptions c = o.c();
+    check(llc_compile(text.c_str(), &c, path, sizeof path));
+    return path;
+  }
+  std::string run_pass(const std::string& text, const std::string& pass, const CompileOptions& o) {
+    const char* out = nullptr;
+    LlcOptions c = o.c();
+    check(llc_run_pass(text.c_str(), pass.c_str(), &c, &out));
+    return out;
+  }
+};
+
+// llc::compiler::Execution (src/Compiler/Execution.cpp:10-66)
+struct Execution {
+  LlcExec* exec = nullptr;
+  ~Execution() { if (exec) llc_free(exec); }
+  void load(const std::string& path, int device) {
+    if (exec) throw std::runtime_error("Execution.load may be called once per object");
+    check(llc_load(path.c_str(), device, &exec));
+  }
+  void need() const { if (!exec) throw std::runtime_error("Execution.load has not been called"); }
+  void run_impl(const std::vector<int64_t>& symbols, std::vector<Tensor*>& in, std::vector<Tensor*>& out, uintptr_t stream) {
+    need();
+    std::vector<LlcTensor> ci, co;
+    for (auto* t : in) ci.push_back(t->desc());
+    for (auto* t : out) co.push_back(t->desc());
+    int rc;
+    {
+      py::gil_scoped_release release;
+      rc = llc_run(exec, symbols.data(), (int)symbols.size(), ci.data(), (int)ci.size(), co.data(), (int)co.size(), reinterpret_cast<void*>(stream));
+    }
+    check(rc);
+  }
+  void run(std::vector<Tensor*> in, std::vector<Tensor*> out, uintptr_t stream) { run_impl({}, in, out, stream); }
+  void run_with_symbols(std::vector<int64_t> symbols, std::vector<Tensor*> in, std::vector<Tensor*> out, uintptr_t stream) { run_impl(symbols, in, out, stream); }
+  std::vector<std::pair<std::vector<int64_t>, int>> output_shapes(std::vector<int64_t> symbols, std::vector<Tensor*> in) {
+    need();
+    std::vector<LlcTensor> ci;
+    for (auto* t : in) ci.push_back(t->desc());
+    std::vector<std::pair<std::vector<int64_t>, int>> res;
+    for (int k = 0; k < llc_num_outputs(exec); ++k) {
+      int64_t sizes[8]; int32_t rank = 0, dtype = 0;
+      check(llc_output_shape(exec, symbols.data(), (int)symbols.size(), ci.data(), (int)ci.size(), k, sizes, &rank, &dtype));
+      res.emplace_back(std::vector<int64_t>(sizes, sizes + rank), dtype);
+    }
+    return res;
+  }
+  std::string profile(std::vector<int64_t> symbols, std::vector<Tensor*> in, std::vector<Tensor*> out, int reps, uintptr_t stream) {
+    need();
+    std::vector<LlcTensor> ci, co;
+    for (auto* t : in) ci.push_back(t->desc());
+    for (auto* t : out) co.push_back(t->desc());
+    std::string report(1 << 20, '\0');
+    check(llc_profile(exec, symbols.data(), (int)symbols.size(), ci.data(), (int)ci.size(), co.data(), (int)co.size(), reps,
+                      reinterpret_cast<void*>(stream), &report[0], report.size()));
+    report.resize(strlen(report.c_str()));
+    return report;
+  }
+  int num_inputs() const { need(); return llc_num_inputs(exec); }
+  int num_outputs() const { need(); return llc_num_outputs(exec); }
+  int num_symbols() const { need(); return llc_num_symbols(exec); }
+  int64_t last_launch_count() const { need(); return llc_last_launch_count(exec); }
+  int64_t arena_bytes() const { need(); return llc_arena_bytes(exec); }
+};
+
+}  // namespace
+
+PYBIND11_MODULE(llcompiler_, m) {
+  m.doc() = "B200 execution backend with the llcompiler_ module surface";
+  auto tensor = m.def_submodule("tensor");
+  py::class_<Tensor>(tensor, "Tensor")
+      .def(py::init<>())
+      .def(py::init<uintptr_t, uintptr_t, int, int64_t, std::vector<int64_t>, std::vector<int64_t>, int>(), py::arg("data_ptr"), py::arg("base_ptr"),
+           py::arg("type"), py::arg("offset"), py::arg("size"), py::arg("stride"), py::arg("device") = -1)
+      .def_readwrite("data", &Tensor::data).def_readwrite("base", &Tensor::base).def_readwrite("offset", &Tensor::offset)
+      .def_readwrite("size", &Tensor::size).def_readwrite("stride", &Tensor::stride).def_readwrite("type", &Tensor::type)
+      .def_readwrite("device", &Tensor::device)
+      .def("print", &Tensor::print);
+  tensor.attr("INT8") = (int)LLC_INT8; tensor.attr("INT16") = (int)LLC_INT16; tensor.attr("INT32") = (int)LLC_INT32;
+  tensor.attr("INT64") = (int)LLC_INT64; tensor.attr("FLOAT32") = (int)LLC_FLOAT32; tensor.attr("DOUBL64") = (int)LLC_FLOAT64;
+  tensor.attr("INT1") = (int)LLC_INT1; tensor.attr("FLOAT16") = (int)LLC_FLOAT16; tensor.attr("BFLOAT16") = (int)LLC_BFLOAT16;
+
+  auto compiler = m.def_submodule("compiler");
+  py::class_<Compiler>(compiler, "Compiler")
+      .def(py::init<>())
+      .def("compile_mlir_to_shared_lib", &Compiler::compile_mlir_to_shared_lib)
+      .def("run_pass", &Compiler::run_pass);
+  py::class_<CompileOptions>(compiler, "CompileOptions")
+      .def(py::init<>())
+      .def("set_log_root", [](CompileOptions& o, const std::string& v) { o.log_root = v; })
+      .def("set_mode", [](CompileOptions& o, const std::string& v) { o.mode = v; })
+      .def("set_target", [](CompileOptions& o, const std::string& v) { o.target = v; })
+      .def("set_log_level", [](CompileOptions& o, const std::string& v) { o.log_level = v; })
+      .def("set_pipeline", [](CompileOptions& o, const std::string& v) { o.pipeline = v; })
+      .def("set_global_layout", [](CompileOptions& o, const std::string& v) { o.global_layout = v; })
+      .def("set_cpu", [](CompileOptions& o, const std::string& v) { o.cpu = v; })
+      .def("set_mtriple", [](CompileOptions& o, const std::string& v) { o.mtriple = v; })
+      .def("set_precision", [](CompileOptions& o, const std::string& v) { o.precision = v; })
+      .def("display_llvm_passes", [](CompileOptions& o, bool v) { o.llvm_passes = v; })
+      .def("display_mlir_passes", [](CompileOptions& o, bool v) { o.mlir_passes = v; });
+
+  auto executor = m.def_submodule("executor");
+  py::class_<Execution>(executor, "Execution")
+      .def(py::init<>())
+      .def("load", &Execution::load, py::arg("path"), py::arg("device") = 0)
+      .def("run", &Execution::run, py::arg("inputs"), py::arg("outs"), py::arg("stream") = 0)
+      .def("run_with_symbols", &Execution::run_with_symbols, py::arg("symbols"), py::arg("inputs"), py::arg("outs"), py::arg("stream") = 0)
+      .def("output_shapes", &Execution::output_shapes)
+      .def("profile", &Execution::profile, py::arg("symbols"), py::arg("inputs"), py::arg("outs"), py::arg("reps") = 5, py::arg("stream") = 0)
+      .def("num_inputs", &Execution::num_inputs).def("num_outputs", &Execution::num_outputs).def("num_symbols", &Execution::num_symbols)
+      .def("last_launch_count", &Execution::last_launch_count).def("arena_bytes", &Execution::arena_bytes);
+  m.def("version", []() { return std::string(llc_version()); });
+}

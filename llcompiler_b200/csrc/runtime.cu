@@ -1,0 +1,545 @@
+// The executor: loads a kernel plan, owns weights and the activation arena, binds shape
+// symbols per call and launches the plan's kernels on a CUDA stream.
+//
+// Stands in for llc::compiler::Execution (src/Compiler/Execution.cpp:10-66), which dlopens the
+// compiled object and calls its main(void**).  The reference's generated code mallocs and frees
+// every intermediate on every call (memref_include.mlir:4-23); here all intermediates live in one
+// arena whose layout is computed once per symbol binding from the plan's symbolic sizes by
+// lifetime-based first-fit packing, and reused by every later call with that binding.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdio>
+#include <cstring>
+#include <fstream>
+#include <map>
+#include <memory>
+#include <sstream>
+
+#include "../../include/llc_cuda.h"
+#include "../../include/llc_runtime.h"
+#include "capi_common.h"
+#include "plan.h"
+
+namespace llc {
+
+int igemmSimtGemm(const LlcGemmParams* p, cudaStream_t st);
+int igemmSimtConv(const LlcConvParams* p, cudaStream_t st);
+
+namespace {
+
+[[noreturn]] void failArg(const std::string& m) { throw std::runtime_error("llc argument: " + m); }
+[[noreturn]] void failIo(const std::string& m) { throw std::runtime_error("llc io: " + m); }
+void cudaOk(cudaError_t e, const char* what) { if (e != cudaSuccess) throw std::runtime_error(std::string("llc cuda: ") + what + ": " + cudaGetErrorString(e)); }
+
+int toLlcDType(DType t) {
+  switch (t) {
+    case DType::F32: return LLC_FLOAT32; case DType::BF16: return LLC_BFLOAT16; case DType::F16: return LLC_FLOAT16;
+    case DType::F64: return LLC_FLOAT64; case DType::I64: case DType::Index: return LLC_INT64; case DType::I32: return LLC_INT32;
+    case DType::I16: return LLC_INT16; case DType::I8: return LLC_INT8; case DType::I1: return LLC_INT1; default: return -1;
+  }
+}
+size_t align256(size_t v) { return (v + 255) & ~size_t(255); }
+
+uint16_t f32ToBf16(float f) { uint32_t u; memcpy(&u, &f, 4); if ((u & 0x7fffffff) > 0x7f800000) return 0x7fc0; u += 0x7fff + ((u >> 16) & 1); return (uint16_t)(u >> 16); }
+
+// .npy reader for the files llh.weight names (format v1/v2, little endian, C order); the
+// reference's reader is src/Dialect/LLH/Transforms/LoadWeight.cpp:58-103.
+std::vector<char> readNpy(const std::string& path, DType want, size_t numel) {
+  std::ifstream f(path, std::ios::binary);
+  if (!f) failIo("cannot open weight file " + path);
+  char magic[10];
+  f.read(magic, 10);
+  if (!f || memcmp(magic, "\x93NUMPY", 6) != 0) failIo(path + " is not an .npy file");
+  size_t hlen = (unsigned char)magic[8] | ((unsigned char)magic[9] << 8);
+  if (magic[6] >= 2) { char more[2]; f.read(more, 2); hlen |= ((size_t)(unsigned char)more[0] << 16) | ((size_t)(unsigned char)more[1] << 24); }
+  std::string header(hlen, ' ');
+  f.read(&header[0], (std::streamsize)hlen);
+  auto field = [&](const std::string& key) { size_t p = header.find("'" + key + "'"); if (p == std::string::npos) failIo(path + ": header lacks " + key); return header.substr(header.find(':', p) + 1); };
+  std::string descr = field("descr");
+  size_t q1 = descr.find('\''), q2 = descr.find('\'', q1 + 1);
+  descr = descr.substr(q1 + 1, q2 - q1 - 1);
+  if (field("fortran_order").find("True") < 8) failIo(path + ": fortran_order arrays are not supported");
+  if (descr[0] == '>') failIo(path + ": big-endian arrays are not supported");
+  std::string code = descr.substr(1);
+  size_t srcSize = std::stoul(code.substr(1));
+  std::vector<char> raw(numel * srcSize);
+  f.read(raw.data(), (std::streamsize)raw.size());
+  if ((size_t)f.gcount() != raw.size()) failIo(path + ": holds fewer than " + std::to_string(numel) + " elements");
+  size_t dstSize = (size_t)dtypeSize(want);
+  auto same = [&](const char* c) { return code == c; };
+  bool direct = (want == DType::F32 && same("f4")) || (want == DType::BF16 && (same("u2") || same("i2"))) || (want == DType::F16 && same("f2")) ||
+                (want == DType::I64 && same("i8")) || (want == DType::I32 && same("i4")) || (want == DType::I1 && same("b1")) ||
+                (want == DType::F64 && same("f8")) || (want == DType::I8 && (same("i1") || same("u1"))) || (want == DType::I16 && same("i2"));
+  if (direct) return raw;
+  std::vector<char> out(numel * dstSize);
+  for (size_t i = 0; i < numel; ++i) {
+    double v;
+    if (same("f4")) { float x; memcpy(&x, &raw[i * 4], 4); v = x; }
+    else if (same("f8")) { memcpy(&v, &raw[i * 8], 8); }
+    else if (same("i8")) { int64_t x; memcpy(&x, &raw[i * 8], 8); v = (double)x; }
+    else if (same("i4")) { int32_t x; memcpy(&x, &raw[i * 4], 4); v = x; }
+    else failIo(path + ": cannot convert dtype " + descr + " to " + dtypeName(want));
+    if (want == DType::F32) { float x = (float)v; memcpy(&out[i * 4], &x, 4); }
+    else if (want == DType::BF16) { uint16_t x = f32ToBf16((float)v); memcpy(&out[i * 2], &x, 2); }
+    else if (want == DType::I64) { int64_t x = (int64_t)v; memcpy(&out[i * 8], &x, 8); }
+    else failIo(path + ": cannot convert dtype " + descr + " to " + dtypeName(want));
+  }
+  return out;
+}
+
+struct RView { int buf; long long off; int rank; long long shape[6], strides[6]; int dtype; };
+
+struct RStep {
+  const Step* step;
+  std::vector<std::pair<std::string, RView>> views;
+  const RView* view(const char* n) const { for (auto& v : views) if (v.first == n) return &v.second; return nullptr; }
+};
+
+struct Binding {
+  std::map<std::string, int64_t> env;
+  std::vector<size_t> bufBytes, arenaOffset;   // per buffer
+  size_t arenaBytes = 0;
+  std::vector<RStep> steps;
+  std::vector<std::vector<int64_t>> inShapes, outShapes;
+};
+
+std::vector<int64_t> ints(const std::string& s) {
+  std::vector<int64_t> o; std::stringstream ss(s); std::string t;
+  while (std::getline(ss, t, ',')) o.push_back(std::stoll(t));
+  return o;
+}
+
+}  // namespace
+}  // namespace llc
+
+using namespace llc;
+
+struct LlcExec {
+  Plan plan;
+  int device = 0;
+  char* staticPool = nullptr;                 // weights + load-time constants
+  std::vector<size_t> staticOffset;           // per buffer (weights/consts)
+  char* arena = nullptr; size_t arenaCap = 0;
+  char* stageIn = nullptr; size_t stageInCap = 0;
+  char* stageOut = nullptr; size_t stageOutCap = 0;
+  int* badIds = nullptr;
+  std::map<std::vector<int64_t>, std::unique_ptr<Binding>> bindings;
+  int64_t lastLaunches = 0;
+  std::vector<char*> base;                    // per-buffer device base pointers for the current call
+
+  ~LlcExec() {
+    cudaSetDevice(device);
+    if (staticPool) cudaFree(staticPool);
+    if (arena) cudaFree(arena);
+    if (stageIn) cudaFree(stageIn);
+    if (stageOut) cudaFree(stageOut);
+    if (badIds) cudaFree(badIds);
+  }
+
+  RView resolve(const View& v, const std::map<std::string, int64_t>& env) const {
+    RView r{};
+    r.buf = v.buf; r.off = EvalExpr::eval(v.offset.str(), env); r.rank = (int)v.rank(); r.dtype = toLlcDType(v.dtype);
+    if (r.rank > 6) failArg("view rank above 6");
+    for (int d = 0; d < r.rank; ++d) { r.shape[d] = EvalExpr::eval(v.shape[d].str(), env); r.strides[d] = EvalExpr::eval(v.strides[d].str(), env); }
+    return r;
+  }
+  void* ptr(const RView& v) const { return base[v.buf] + v.off * dtypeSize(plan.buffers[v.buf].dtype); }
+
+  int launch(const RStep& rs, cudaStream_t st);
+  Binding& bind(const int64_t* symbols, int nsym, const LlcTensor* in, int nin);
+  void runSteps(const std::vector<RStep>& steps, cudaStream_t st);
+};
+
+// One kernel call of the plan.
+int LlcExec::launch(const RStep& rs, cudaStream_t st) {
+  const Step& s = *rs.step;
+  auto need = [&](const char* n) -> const RView& { const RView* v = rs.view(n); if (!v) throw std::runtime_error(std::string("llc internal: step '") + s.kernel + "' lacks operand " + n); return *v; };
+  auto actOf = [&]() { std::string a = s.param("act", "none"); return a == "relu" ? LLC_ACT_RELU : a == "gelu" ? LLC_ACT_GELU : LLC_ACT_NONE; };
+  auto precOf = [&]() { std::string p = s.param("prec", "fp32"); return p == "tf32" ? LLC_PREC_TF32 : p == "tf32x3" ? LLC_PREC_TF32X3 : p == "bf16" ? LLC_PREC_BF16 : LLC_PREC_FP32; };
+  if (s.kernel == "gemm") {
+    const RView &a = need("a"), &b = need("b"), &o = need("out");
+    LlcGemmParams p{};
+    p.a = ptr(a); p.b = ptr(b); p.out = ptr(o);
+    p.in_dtype = a.dtype; p.out_dtype = o.dtype; p.precision = precOf();
+    p.b0 = o.shape[0]; p.b1 = o.shape[1]; p.m = o.shape[2]; p.n = o.shape[3]; p.k = a.shape[3];
+    p.a_s0 = a.strides[0]; p.a_s1 = a.strides[1]; p.a_sm = a.strides[2];
+    p.b_s0 = b.strides[0]; p.b_s1 = b.strides[1]; p.b_sk = b.strides[2]; p.b_sn = b.strides[3];
+    if (b.shape[2] == 1 && p.b_sn != 1) p.b_sk = 1;   // k == 1: either operand order is unit-stride
+    p.o_s0 = o.strides[0]; p.o_s1 = o.strides[1]; p.o_sm = o.strides[2];
+    if (a.shape[3] != 1 && a.strides[3] != 1) failArg("gemm A operand must have unit stride along k");
+    if (o.strides[3] != 1 && o.shape[3] != 1) failArg("gemm output must have unit stride along n");
+    if (const RView* v = rs.view("scale")) p.scale = (const float*)ptr(*v);
+    if (const RView* v = rs.view("shift")) p.shift = (const float*)ptr(*v);
+    if (const RView* v = rs.view("res")) { p.res = ptr(*v); p.res_dtype = v->dtype; p.r_s0 = v->strides[0]; p.r_s1 = v->strides[1]; p.r_sm = v->strides[2]; p.r_sn = v->strides[3]; }
+    p.alpha = std::stof(s.param("alpha", "1")); p.act = actOf();
+    return llc_cuda_gemm(&p, st);
+  }
+  if (s.kernel == "conv") {
+    const RView &x = need("x"), &w = need("w"), &o = need("out");
+    LlcConvParams p{};
+    p.x = ptr(x); p.w = ptr(w); p.out = ptr(o);
+    p.in_dtype = x.dtype; p.out_dtype = o.dtype; p.precision = precOf();
+    p.n = x.shape[0]; p.c = x.shape[1]; p.h = x.shape[2]; p.w_in = x.shape[3];
+    p.f = w.shape[0]; p.kh = w.shape[1]; p.kw = w.shape[2]; p.oh = o.shape[2]; p.ow = o.shape[3];
+    auto st2 = ints(s.param("stride", "1,1")), pd = ints(s.param("pad", "0,0,0,0")), dl = ints(s.param("dil", "1,1"));
+    p.stride_h = (int)st2[0]; p.stride_w = (int)st2[1]; p.pad_h = (int)pd[0]; p.pad_w = (int)pd[1]; p.dil_h = (int)dl[0]; p.dil_w = (int)dl[1];
+    if (const RView* v = rs.view("scale")) p.scale = (const float*)ptr(*v);
+    if (const RView* v = rs.view("shift")) p.shift = (const float*)ptr(*v);
+    if (const RView* v = rs.view("res")) { p.res = ptr(*v); p.res_dtype = v->dtype; }
+    p.alpha = std::stof(s.param("alpha", "1")); p.act = actOf();
+    return llc_cuda_conv2d(&p, st);
+  }
+  if (s.kernel == "maxpool") {
+    const RView &x = need("x"), &o = need("out");
+    LlcPoolParams p{};
+    p.x = ptr(x); p.out = ptr(o); p.in_dtype = x.dtype; p.out_dtype = o.dtype;
+    p.n = x.shape[0]; p.c = x.shape[1]; p.h = x.shape[2]; p.w = x.shape[3]; p.oh = o.shape[2]; p.ow = o.shape[3];
+    auto k = ints(s.param("kernel")), st2 = ints(s.param("stride", "1,1")), pd = ints(s.param("pad", "0,0,0,0")), dl = ints(s.param("dil", "1,1"));
+    p.kh = (int)k[0]; p.kw = (int)k[1]; p.stride_h = (int)st2[0]; p.stride_w = (int)st2[1]; p.pad_h = (int)pd[0]; p.pad_w = (int)pd[1]; p.dil_h = (int)dl[0]; p.dil_w = (int)dl[1];
+    return llc_cuda_maxpool2d(&p, st);
+  }
+  if (s.kernel == "reduce") {
+    const RView &x = need("x"), &o = need("out");
+    std::string op = s.param("op", "sum");
+    int code = op == "max" ? 1 : op == "min" ? 2 : op == "mean" ? 3 : 0;
+    return llc_cuda_reduce(ptr(x), ptr(o), x.dtype, o.dtype, x.shape[0], x.shape[1], x.shape[2], code, st);
+  }
+  if (s.kernel == "softmax") {
+    const RView &x = need("x"), &o = need("out");
+    return llc_cuda_softmax(ptr(x), ptr(o), x.dtype, o.dtype, x.shape[0], x.shape[1], st);
+  }
+  if (s.kernel == "layernorm") {
+    const RView &x = need("x"), &g = need("gamma"), &b = need("beta"), &o = need("out");
+    if (g.dtype != b.dtype) failArg("layernorm scale and bias types differ");
+    return llc_cuda_layernorm(ptr(x), ptr(g), ptr(b), ptr(o), x.dtype, g.dtype, o.dtype, x.shape[0], x.shape[1], std::stof(s.param("eps", "1e-5")), st);
+  }
+  if (s.kernel == "gather") {
+    const RView &t = need("table"), &ids = need("ids"), &o = need("out");
+    if (ids.dtype != LLC_INT64) failArg("gather indices must be int64");
+    return llc_cuda_gather(ptr(t), (const int64_t*)ptr(ids), ptr(o), t.dtype, o.dtype, o.shape[0], o.shape[1], t.shape[0], badIds, st);
+  }
+  if (s.kernel == "eltwise") {
+    const RView& o = need("out");
+    LlcEltwiseParams p{};
+    p.out = ptr(o); p.out_dtype = o.dtype; p.rank = o.rank;
+    for (int d = 0; d < o.rank; ++d) { p.shape[d] = o.shape[d]; p.out_strides[d] = o.strides[d]; }
+    std::string prog = s.param("prog");
+    p.prog = prog.c_str();
+    for (int k = 0; k < 8; ++k) {
+      const RView* v = rs.view(("in" + std::to_string(k)).c_str());
+      if (!v) break;
+      p.in[k].data = ptr(*v); p.in[k].dtype = v->dtype;
+      for (int d = 0; d < v->rank; ++d) p.in[k].strides[d] = v->strides[d];
+      p.n_in = k + 1;
+    }
+    return llc_cuda_eltwise(&p, st);
+  }
+  throw std::runtime_error("llc internal: unknown kernel '" + s.kernel + "' in plan");
+}
+
+void LlcExec::runSteps(const std::vector<RStep>& steps, cudaStream_t st) {
+  for (auto& rs : steps) {
+    int rc = launch(rs, st);
+    if (rc != LLC_OK) throw std::runtime_error(std::string(llc_last_error()));
+    ++lastLaunches;
+  }
+}
+
+Binding& LlcExec::bind(const int64_t* symbols, int nsym, const LlcTensor* in, int nin) {
+  if (nin != (int)plan.inputs.size()) failArg("expected " + std::to_string(plan.inputs.size()) + " input tensors, got " + std::to_string(nin));
+  if (nsym != plan.numSymbolArgs && nsym != 0) failArg("expected " + std::to_string(plan.numSymbolArgs) + " symbol values, got " + std::to_string(nsym));
+  std::map<std::string, int64_t> env;
+  for (auto& sb : plan.symbols) {
+    int64_t v;
+    if (sb.symbolArg >= 0) { if (nsym == 0) continue; v = symbols[sb.symbolArg]; }
+    else {
+      if (sb.input >= nin || sb.dim >= in[sb.input].rank) failArg("input " + std::to_string(sb.input) + " has too few dims for symbol " + sb.name);
+      v = in[sb.input].sizes[sb.dim];
+    }
+    auto it = env.find(sb.name);
+    if (it == env.end()) env[sb.name] = v;
+    else if (it->second != v) failArg("shape symbol " + sb.name + " bound to both " + std::to_string(it->second) + " and " + std::to_string(v));
+  }
+  std::vector<int64_t> key;
+  for (auto& kv : env) key.push_back(kv.second);
+  auto it = bindings.find(key);
+  if (it != bindings.end()) return *it->second;
+
+  std::unique_ptr<Binding> b(new Binding());
+  b->env = env;
+  size_t nb = plan.buffers.size();
+  b->bufBytes.assign(nb, 0); b->arenaOffset.assign(nb, 0);
+  for (size_t i = 0; i < nb; ++i) {
+    int64_t n = EvalExpr::eval(plan.buffers[i].numel.str(), env);
+    if (n < 0) failArg("negative buffer extent for the given symbols");
+    b->bufBytes[i] = (size_t)n * dtypeSize(plan.buffers[i].dtype);
+  }
+  for (auto& io : plan.inputs) { std::vector<int64_t> s; for (auto& e : io.shape) s.push_back(EvalExpr::eval(e.str(), env)); b->inShapes.push_back(s); }
+  for (auto& io : plan.outputs) { std::vector<int64_t> s; for (auto& e : io.shape) s.push_back(EvalExpr::eval(e.str(), env)); b->outShapes.push_back(s); }
+  // resolve run steps and buffer lifetimes
+  std::vector<int> firstUse(nb, -1), lastUse(nb, -1);
+  for (auto& s : plan.steps) {
+    if (s.init) continue;
+    RStep rs; rs.step = &s;
+    for (auto& v : s.views) {
+      rs.views.emplace_back(v.first, resolve(v.second, env));
+      int id = v.second.buf, idx = (int)b->steps.size();
+      if (firstUse[id] < 0) firstUse[id] = idx;
+      lastUse[id] = idx;
+    }
+    b->steps.push_back(std::move(rs));
+  }
+  // first-fit packing of temporaries by lifetime
+  std::vector<int> temps;
+  for (size_t i = 0; i < nb; ++i) if (plan.buffers[i].kind == BufferDecl::Temp && firstUse[i] >= 0) temps.push_back((int)i);
+  std::sort(temps.begin(), temps.end(), [&](int x, int y) { return firstUse[x] != firstUse[y] ? firstUse[x] < firstUse[y] : b->bufBytes[x] > b->bufBytes[y]; });
+  std::vector<int> placed;
+  for (int t : temps) {
+    size_t size = align256(std::max<size_t>(b->bufBytes[t], 1));
+    std::vector<std::pair<size_t, size_t>> busy;
+    for (int c : placed) if (!(lastUse[c] < firstUse[t] || lastUse[t] < firstUse[c])) busy.emplace_back(b->arenaOffset[c], align256(std::max<size_t>(b->bufBytes[c], 1)));
+    std::sort(busy.begin(), busy.end());
+    size_t off = 0;
+    for (auto& iv : busy) { if (off + size <= iv.first) break; off = std::max(off, iv.first + iv.second); }
+    b->arenaOffset[t] = off;
+    b->arenaBytes = std::max(b->arenaBytes, off + size);
+    placed.push_back(t);
+  }
+  Binding& ref = *b;
+  bindings[key] = std::move(b);
+  return ref;
+}
+
+static bool isDenseRowMajor(const LlcTensor& t) {
+  int64_t acc = 1;
+  for (int d = t.rank - 1; d >= 0; --d) { if (t.sizes[d] != 1 && t.strides && t.strides[d] != acc) return false; acc *= t.sizes[d]; }
+  return true;
+}
+
+extern "C" int llc_load(const char* path, int device, LlcExec** out) {
+  if (!path || !out) return setError(LLC_ERR_ARGUMENT, "null argument");
+  std::unique_ptr<LlcExec> ex(new LlcExec());
+  try {
+    std::ifstream f(path);
+    if (!f) failIo(std::string("cannot open plan ") + path);
+    std::stringstream ss; ss << f.rdbuf();
+    ex->plan = parsePlan(ss.str());
+    int count = 0;
+    cudaError_t e = cudaGetDeviceCount(&count);
+    if (e != cudaSuccess || count == 0) throw std::runtime_error("llc cuda: no CUDA device is available (the B200 backend has no CPU fallback)");
+    if (device < 0 || device >= count) failArg("device ordinal " + std::to_string(device) + " out of range");
+    ex->device = device;
+    cudaOk(cudaSetDevice(device), "cudaSetDevice");
+    size_t nb = ex->plan.buffers.size();
+    ex->staticOffset.assign(nb, 0);
+    ex->base.assign(nb, nullptr);
+    size_t total = 0;
+    std::map<std::string, int64_t> empty;
+    std::vector<size_t> bytes(nb, 0);
+    for (size_t i = 0; i < nb; ++i) {
+      auto& b = ex->plan.buffers[i];
+      if (b.kind != BufferDecl::Weight && b.kind != BufferDecl::Const) continue;
+      bytes[i] = (size_t)EvalExpr::eval(b.numel.str(), empty) * dtypeSize(b.dtype);
+      ex->staticOffset[i] = total; total += align256(std::max<size_t>(bytes[i], 1));
+    }
+    cudaOk(cudaMalloc(&ex->staticPool, std::max<size_t>(total, 256)), "cudaMalloc(weights)");
+    cudaOk(cudaMalloc(&ex->badIds, sizeof(int)), "cudaMalloc(status)");
+    cudaOk(cudaMemset(ex->badIds, 0, sizeof(int)), "cudaMemset(status)");
+    for (size_t i = 0; i < nb; ++i) {
+      auto& b = ex->plan.buffers[i];
+      if (b.kind != BufferDecl::Weight && b.kind != BufferDecl::Const) continue;
+      ex->base[i] = ex->staticPool + ex->staticOffset[i];
+      size_t n = bytes[i] / dtypeSize(b.dtype);
+      if (b.kind == BufferDecl::Weight) {
+        std::vector<char> host = readNpy(b.file, b.dtype, n);
+        cudaOk(cudaMemcpy(ex->base[i], host.data(), bytes[i], cudaMemcpyHostToDevice), "cudaMemcpy(weight)");
+      } else if (!b.values.empty()) {
+        if (b.values.size() != n) failArg("constant buffer value count mismatch");
+        std::vector<char> host(bytes[i]);
+        for (size_t k = 0; k < n; ++k) {
+          double v = b.values[k];
+          switch (b.dtype) {
+            case DType::F32: { float x = (float)v; memcpy(&host[k * 4], &x, 4); break; }
+            case DType::BF16: { uint16_t x = f32ToBf16((float)v); memcpy(&host[k * 2], &x, 2); break; }
+            case DType::I64: { int64_t x = (int64_t)v; memcpy(&host[k * 8], &x, 8); break; }
+            case DType::I32: { int32_t x = (int32_t)v; memcpy(&host[k * 4], &x, 4); break; }
+            case DType::I1: case DType::I8: { host[k] = (char)(int)v; break; }
+            default: failArg("unsupported constant element type");
+          }
+        }
+        cudaOk(cudaMemcpy(ex->base[i], host.data(), bytes[i], cudaMemcpyHostToDevice), "cudaMemcpy(constant)");
+      }
+    }
+    // load-time kernels: weight re-layout, folded batch-norm vectors
+    std::vector<RStep> init;
+    for (auto& s : ex->plan.steps) {
+      if (!s.init) continue;
+      RStep rs; rs.step = &s;
+      for (auto& v : s.views) rs.views.emplace_back(v.first, ex->resolve(v.second, empty));
+      init.push_back(std::move(rs));
+    }
+    ex->runSteps(init, 0);
+    cudaOk(cudaDeviceSynchronize(), "load-time kernels");
+    ex->lastLaunches = 0;
+    *out = ex.release();
+    return LLC_OK;
+  } catch (const std::exception& e) { return setError(statusFor(e), e.what()); }
+}
+
+extern "C" int llc_num_inputs(const LlcExec* e) { return e ? (int)e->plan.inputs.size() : -1; }
+extern "C" int llc_num_outputs(const LlcExec* e) { return e ? (int)e->plan.outputs.size() : -1; }
+extern "C" int llc_num_symbols(const LlcExec* e) { return e ? e->plan.numSymbolArgs : -1; }
+extern "C" int64_t llc_last_launch_count(const LlcExec* e) { return e ? e->lastLaunches : -1; }
+extern "C" int64_t llc_arena_bytes(const LlcExec* e) { return e ? (int64_t)e->arenaCap : -1; }
+extern "C" void llc_free(LlcExec* e) { delete e; }
+
+extern "C" int llc_output_shape(LlcExec* ex, const int64_t* symbols, int nsym, const LlcTensor* in, int nin, int index, int64_t* sizes, int32_t* rank, int32_t* dtype) {
+  if (!ex || !sizes || !rank) return setError(LLC_ERR_ARGUMENT, "null argument");
+  try {
+    Binding& b = ex->bind(symbols, nsym, in, nin);
+    if (index < 0 || index >= (int)b.outShapes.size()) failArg("output index out of range");
+    auto& s = b.outShapes[index];
+    if (s.size() > 8) failArg("output rank above 8");
+    *rank = (int32_t)s.size();
+    for (size_t d = 0; d < s.size(); ++d) sizes[d] = s[d];
+    if (dtype) *dtype = toLlcDType(ex->plan.outputs[index].dtype);
+    return LLC_OK;
+  } catch (const std::exception& e) { return setError(statusFor(e), e.what()); }
+}
+
+// Binds symbols, sizes the arena, points every input/output buffer at caller memory (staging host
+// tensors through the device) and returns the binding to launch.
+static Binding& prepareCall(LlcExec* ex, const int64_t* symbols, int nsym, const LlcTensor* in, int nin, LlcTensor* outs, int nout, cudaStream_t st, bool& anyHostOut) {
+  cudaOk(cudaSetDevice(ex->device), "cudaSetDevice");
+  Binding& b = ex->bind(symbols, nsym, in, nin);
+  if (nout != (int)ex->plan.outputs.size()) failArg("expected " + std::to_string(ex->plan.outputs.size()) + " output tensors, got " + std::to_string(nout));
+  if (b.arenaBytes > ex->arenaCap) {
+    cudaOk(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+    if (ex->arena) cudaOk(cudaFree(ex->arena), "cudaFree(arena)");
+    ex->arena = nullptr; ex->arenaCap = 0;
+    cudaOk(cudaMalloc(&ex->arena, b.arenaBytes), "cudaMalloc(arena)");
+    ex->arenaCap = b.arenaBytes;
+  }
+  size_t nb = ex->plan.buffers.size();
+  for (size_t i = 0; i < nb; ++i) if (ex->plan.buffers[i].kind == BufferDecl::Temp) ex->base[i] = ex->arena + b.arenaOffset[i];
+  // inputs: device tensors are used in place, host tensors are staged
+  auto check = [&](const LlcTensor& t, const IoDecl& io, const std::vector<int64_t>& shape, const char* what, int k) {
+    if (t.dtype != toLlcDType(io.dtype)) failArg(std::string(what) + " " + std::to_string(k) + " has element type code " + std::to_string(t.dtype) + ", the plan expects " + dtypeName(io.dtype));
+    if (t.rank != (int)shape.size() && !(t.rank == 0 && shape.size() == 1 && shape[0] == 1)) failArg(std::string(what) + " " + std::to_string(k) + " has rank " + std::to_string(t.rank) + ", expected " + std::to_string(shape.size()));
+    for (int d = 0; d < t.rank; ++d) if (t.sizes[d] != shape[d]) failArg(std::string(what) + " " + std::to_string(k) + " dim " + std::to_string(d) + " is " + std::to_string(t.sizes[d]) + ", expected " + std::to_string(shape[d]));
+    if (!isDenseRowMajor(t)) failArg(std::string(what) + " " + std::to_string(k) + " must be contiguous");
+    int64_t n = 1; for (auto s : shape) n *= s;
+    if (!t.data && n) failArg(std::string(what) + " " + std::to_string(k) + " has a null data pointer");
+    if (t.device >= 0 && t.device != ex->device) failArg(std::string(what) + " " + std::to_string(k) + " lives on device " + std::to_string(t.device) + ", the plan is loaded on " + std::to_string(ex->device));
+  };
+  size_t needIn = 0, needOut = 0;
+  for (int k = 0; k < nin; ++k) { check(in[k], ex->plan.inputs[k], b.inShapes[k], "input", k); if (in[k].device < 0) needIn += align256(b.bufBytes[ex->plan.inputs[k].buf]); }
+  for (int k = 0; k < nout; ++k) { check(outs[k], ex->plan.outputs[k], b.outShapes[k], "output", k); if (outs[k].device < 0) needOut += align256(b.bufBytes[ex->plan.outputs[k].buf]); }
+  auto grow = [&](char*& p, size_t& cap, size_t need) {
+    if (need <= cap) return;
+    cudaOk(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+    if (p) cudaOk(cudaFree(p), "cudaFree(staging)");
+    p = nullptr; cap = 0;
+    cudaOk(cudaMalloc(&p, need), "cudaMalloc(staging)");
+    cap = need;
+  };
+  grow(ex->stageIn, ex->stageInCap, needIn);
+  grow(ex->stageOut, ex->stageOutCap, needOut);
+  size_t offIn = 0, offOut = 0;
+  for (int k = 0; k < nin; ++k) {
+    int buf = ex->plan.inputs[k].buf;
+    if (in[k].device >= 0) ex->base[buf] = (char*)in[k].data;
+    else {
+      ex->base[buf] = ex->stageIn + offIn;
+      if (b.bufBytes[buf]) cudaOk(cudaMemcpyAsync(ex->base[buf], in[k].data, b.bufBytes[buf], cudaMemcpyHostToDevice, st), "cudaMemcpyAsync(H2D)");
+      offIn += align256(b.bufBytes[buf]);
+    }
+  }
+  anyHostOut = false;
+  for (int k = 0; k < nout; ++k) {
+    int buf = ex->plan.outputs[k].buf;
+    if (outs[k].device >= 0) ex->base[buf] = (char*)outs[k].data;
+    else { ex->base[buf] = ex->stageOut + offOut; offOut += align256(b.bufBytes[buf]); anyHostOut = true; }
+  }
+  return b;
+}
+
+static void finishCall(LlcExec* ex, Binding& b, LlcTensor* outs, int nout, cudaStream_t st, bool anyHostOut) {
+  if (!anyHostOut) return;
+  for (int k = 0; k < nout; ++k) {
+    int buf = ex->plan.outputs[k].buf;
+    if (outs[k].device < 0 && b.bufBytes[buf]) cudaOk(cudaMemcpyAsync(outs[k].data, ex->base[buf], b.bufBytes[buf], cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(D2H)");
+  }
+  cudaOk(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+}
+
+extern "C" int llc_run(LlcExec* ex, const int64_t* symbols, int nsym, const LlcTensor* in, int nin, LlcTensor* outs, int nout, void* stream) {
+  if (!ex || (nin > 0 && !in) || (nout > 0 && !outs)) return setError(LLC_ERR_ARGUMENT, "null argument");
+  try {
+    cudaStream_t st = (cudaStream_t)stream;
+    bool anyHostOut = false;
+    Binding& b = prepareCall(ex, symbols, nsym, in, nin, outs, nout, st, anyHostOut);
+    ex->lastLaunches = 0;
+    ex->runSteps(b.steps, st);
+    finishCall(ex, b, outs, nout, st, anyHostOut);
+    return LLC_OK;
+  } catch (const std::exception& e) { return setError(statusFor(e), e.what()); }
+}
+
+// Algorithmic work of one step: FLOPs of the contraction, bytes = every operand element once.
+static void stepWork(const RStep& rs, double& flops, double& bytes) {
+  flops = 0; bytes = 0;
+  for (auto& v : rs.views) {
+    double n = 1;
+    for (int d = 0; d < v.second.rank; ++d) if (v.second.strides[d] != 0 || v.second.shape[d] == 1) n *= (double)v.second.shape[d];
+    int eb = v.second.dtype == LLC_FLOAT32 || v.second.dtype == LLC_INT32 ? 4 : v.second.dtype == LLC_BFLOAT16 || v.second.dtype == LLC_FLOAT16 || v.second.dtype == LLC_INT16 ? 2
+           : v.second.dtype == LLC_INT64 || v.second.dtype == LLC_FLOAT64 ? 8 : 1;
+    bytes += n * eb;
+  }
+  const std::string& k = rs.step->kernel;
+  if (k == "gemm") { const RView* a = rs.view("a"); const RView* o = rs.view("out"); flops = 2.0 * o->shape[0] * o->shape[1] * o->shape[2] * o->shape[3] * a->shape[3]; }
+  if (k == "conv") { const RView* w = rs.view("w"); const RView* o = rs.view("out"); flops = 2.0 * o->shape[0] * o->shape[2] * o->shape[3] * w->shape[0] * w->shape[1] * w->shape[2] * w->shape[3]; }
+}
+
+extern "C" int llc_profile(LlcExec* ex, const int64_t* symbols, int nsym, const LlcTensor* in, int nin, LlcTensor* outs, int nout, int reps, void* stream,
+                           char* report, size_t reportLen) {
+  if (!ex || !report || reps <= 0) return setError(LLC_ERR_ARGUMENT, "null argument");
+  try {
+    cudaStream_t st = (cudaStream_t)stream;
+    bool anyHostOut = false;
+    Binding& b = prepareCall(ex, symbols, nsym, in, nin, outs, nout, st, anyHostOut);
+    size_t n = b.steps.size();
+    std::vector<cudaEvent_t> ev(2 * n);
+    for (auto& e : ev) cudaOk(cudaEventCreate(&e), "cudaEventCreate");
+    std::vector<double> ms(n, 0.0);
+    for (int r = 0; r < reps + 1; ++r) {   // the first pass is a warm-up
+      for (size_t i = 0; i < n; ++i) {
+        cudaOk(cudaEventRecord(ev[2 * i], st), "cudaEventRecord");
+        int rc = ex->launch(b.steps[i], st);
+        if (rc != LLC_OK) throw std::runtime_error(std::string(llc_last_error()));
+        cudaOk(cudaEventRecord(ev[2 * i + 1], st), "cudaEventRecord");
+      }
+      cudaOk(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+      if (r == 0) continue;
+      for (size_t i = 0; i < n; ++i) { float t = 0; cudaOk(cudaEventElapsedTime(&t, ev[2 * i], ev[2 * i + 1]), "cudaEventElapsedTime"); ms[i] += t; }
+    }
+    for (auto& e : ev) cudaEventDestroy(e);
+    finishCall(ex, b, outs, nout, st, anyHostOut);
+    struct Agg { int launches = 0; double ms = 0, flops = 0, bytes = 0; };
+    std::map<std::string, Agg> agg;
+    std::ostringstream o;
+    o.precision(9);
+    for (size_t i = 0; i < n; ++i) {
+      double f, by; stepWork(b.steps[i], f, by);
+      Agg& a = agg[b.steps[i].step->kernel];
+      a.launches += 1; a.ms += ms[i] / reps; a.flops += f; a.bytes += by;
+      o << "step " << i << " " << b.steps[i].step->kernel << " " << ms[i] / reps << " " << f << " " << by << "\n";
+    }
+    for (auto& kv : agg) o << "kernel " << kv.first << " " << kv.second.launches << " " << kv.second.ms << " " << kv.second.flops << " " << kv.second.bytes << "\n";
+    std::string text = o.str();
+    if (text.size() + 1 > reportLen) text.resize(reportLen ? reportLen - 1 : 0);
+    memcpy(report, text.c_str(), text.size() + 1);
+    return LLC_OK;
+  } catch (const std::exception& e) { return setError(statusFor(e), e.what()); }
+}

@@ -1,0 +1,3 @@
+from .engine import ExecutionEngine, Torch_ExecutionEngine
+
+__all__ = ["ExecutionEngine", "Torch_ExecutionEngine"]

@@ -1,0 +1,113 @@
+"""End-to-end parity on the GPU: the benchmark models go through
+torch.compile(backend=LLCompiler) -> importer -> llcompiler_.Compiler -> Execution, and the
+result is compared with the CPU oracle (PyTorch CPU fp32 eager on the same seeded model and
+inputs).  Tolerances are the ones the benchmark definition states: 1e-4 relative for fp32
+paths, 2e-2 relative for bf16 paths (against the fp32 oracle on bf16-rounded parameters)."""
+import copy
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+from helpers import compile_with  # noqa: E402
+from llcompiler_b200.compiler import LLCompiler  # noqa: E402
+from oracle.models import CONFIGS, build_model, max_rel_err, round_to_bf16_  # noqa: E402
+
+
+def _gpu_run(model, inputs, dynamic=False, precision="auto", device_inputs=True):
+    comp = LLCompiler(precision=precision)
+    if device_inputs:
+        model = copy.deepcopy(model).cuda()
+    fn = compile_with(comp, model, dynamic)
+    args = [i.cuda() if device_inputs else i for i in inputs]
+    with torch.no_grad():
+        out = fn(*args)
+    torch.cuda.synchronize()
+    return comp, fn, out
+
+
+def test_mlp_symbolic_batch_device_and_host_tensors():
+    m = build_model("mlp")
+    x = CONFIGS["mlp"].make_inputs()[0]
+    with torch.no_grad():
+        want = m(x)
+    comp, fn, out = _gpu_run(m, (x,), dynamic=True)
+    assert out.is_cuda and max_rel_err(out, want) < 1e-4
+    eng = comp.compiled[0].engine
+    assert eng.executor.last_launch_count() == 2          # two fused GEMM launches, nothing else
+    for b in (1, 7, 65, 1024):                             # same plan, other batch sizes
+        xb = torch.randn(b, 784, generator=torch.Generator().manual_seed(b))
+        with torch.no_grad():
+            got = eng.run(b, xb.cuda())[0]
+            assert max_rel_err(got, m(xb)) < 1e-4
+    # host tensors in, host tensors out (the reference's calling convention)
+    with torch.no_grad():
+        got = eng.run(64, x)[0]
+    assert not got.is_cuda and max_rel_err(got, want) < 1e-4
+
+
+def test_resnet18_fp32():
+    m = build_model("resnet18")
+    x = CONFIGS["resnet18"].make_inputs(batch=8)[0]
+    with torch.no_grad():
+        want = m(x)
+    comp, fn, out = _gpu_run(m, (x,))
+    assert max_rel_err(out, want) < 1e-4
+    assert comp.compiled[0].engine.executor.last_launch_count() == 24
+
+
+@pytest.mark.parametrize("seq", [128, 512])
+def test_encoder_layer_symbolic_seq(seq):
+    m = build_model("encoder")
+    x = CONFIGS["encoder"].make_inputs(batch=8, seq=seq)[0]
+    with torch.no_grad():
+        want = m(x)
+    comp, fn, out = _gpu_run(m, (x,), dynamic=True)
+    assert max_rel_err(out, want) < 1e-4                  # fp32 FMA path; the TF32 path states 2e-2
+
+
+def test_resnet50_bf16():
+    m = round_to_bf16_(build_model("resnet50"))
+    x = CONFIGS["resnet50"].make_inputs(batch=4)[0].to(torch.bfloat16)
+    with torch.no_grad():
+        want = m(x.float())
+    mb = build_model("resnet50").to(torch.bfloat16)
+    comp, fn, out = _gpu_run(mb, (x,))
+    assert out.dtype == torch.bfloat16
+    assert max_rel_err(out.float(), want) < 2e-2
+
+
+def test_bert_bf16_two_layers_with_mask():
+    m = round_to_bf16_(build_model("bert", n_layers=2))
+    ids, mask = CONFIGS["bert"].make_inputs(batch=4, seq=384)
+    mask = mask.clone()
+    mask[1, 300:] = 0
+    with torch.no_grad():
+        want = m(ids, mask)
+    mb = build_model("bert", n_layers=2).to(torch.bfloat16)
+    comp, fn, out = _gpu_run(mb, (ids, mask))
+    assert max_rel_err(out.float(), want) < 2e-2
+
+
+def test_bert_fp32_two_layers():
+    m = build_model("bert", n_layers=2)
+    ids, mask = CONFIGS["bert"].make_inputs(batch=2, seq=64)
+    with torch.no_grad():
+        want = m(ids, mask)
+    comp, fn, out = _gpu_run(m, (ids, mask))
+    assert max_rel_err(out, want) < 1e-4
+
+
+def test_wrong_inputs_raise():
+    m = build_model("mlp")
+    x = torch.randn(4, 784)
+    comp, fn, out = _gpu_run(m, (x,), dynamic=True)
+    eng = comp.compiled[0].engine
+    with pytest.raises(RuntimeError):
+        eng.run(4, torch.randn(4, 783).cuda())             # wrong static extent
+    with pytest.raises(RuntimeError):
+        eng.run(5, torch.randn(4, 784).cuda())             # symbol value contradicts the tensor
+    with pytest.raises(RuntimeError):
+        eng.run(4, torch.randn(4, 784, dtype=torch.float64).cuda())
+    assert max_rel_err(eng.run(4, x.cuda())[0], m(x)) < 1e-4   # the handle stays usable
