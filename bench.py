@@ -192,9 +192,11 @@ def main():
     prec = args.precision or prec
     cfg, model, inputs = build_workload(oname, batch, kw)
     dev = torch.device("cuda", local if world > 1 else 0)
-    gmodel = model.to(torch.bfloat16) if dtype == "bf16" else model
     import copy
-    gmodel = copy.deepcopy(gmodel).to(dev)
+    gmodel = copy.deepcopy(model)
+    if dtype == "bf16":
+        gmodel = gmodel.to(torch.bfloat16)
+    gmodel = gmodel.to(dev)
     cast = (lambda t: t.to(torch.bfloat16)) if dtype == "bf16" else (lambda t: t)
     host_inputs = tuple((cast(i) if i.is_floating_point() else i).contiguous().pin_memory() for i in inputs)
     dev_inputs = tuple(i.to(dev) for i in host_inputs)

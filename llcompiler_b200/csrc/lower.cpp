@@ -245,8 +245,30 @@ struct Lowering {
 
   // Materialises a lazy tree.  The result layout follows the first dense, non-broadcast leaf so that
   // NHWC data stays NHWC.
+  std::string treeKey(int id) {
+    const ENode& n = nodes[id];
+    if (n.kind == ENode::Leaf) return "L(" + n.leaf.str() + ")";
+    if (n.kind == ENode::Const) return "#" + fmtDouble(n.cst);
+    return n.op + "(" + treeKey(n.a) + (n.b >= 0 ? "," + treeKey(n.b) : "") + (n.c >= 0 ? "," + treeKey(n.c) : "") + ")";
+  }
+  void countTree(int id, std::set<std::string>& leaves, std::set<int>& seen) {
+    if (!seen.insert(id).second) return;
+    const ENode& n = nodes[id];
+    if (n.kind == ENode::Leaf) { leaves.insert(n.leaf.str()); return; }
+    if (n.kind == ENode::Const) return;
+    countTree(n.a, leaves, seen); if (n.b >= 0) countTree(n.b, leaves, seen); if (n.c >= 0) countTree(n.c, leaves, seen);
+  }
+  std::map<std::string, View> constTreeCache;
   View materializeTree(int root, DType dt, const std::vector<Expr>& shape, const std::vector<Expr>* wantStrides = nullptr, int intoBuf = -1) {
     bool isC = treeIsConst(root) && numelOf(shape).isConst();
+    std::string ckey;
+    if (isC && intoBuf < 0) {   // load-time values are computed once, however often the graph repeats them
+      ckey = treeKey(root) + "|" + dtypeName(dt) + "|";
+      for (auto& e : shape) ckey += e.str() + ",";
+      if (wantStrides) for (auto& e : *wantStrides) ckey += e.str() + ";";
+      auto it = constTreeCache.find(ckey);
+      if (it != constTreeCache.end()) return it->second;
+    }
     std::vector<Expr> strides = rowMajor(shape);
     if (wantStrides) strides = *wantStrides;
     else {
@@ -272,6 +294,7 @@ struct Lowering {
     if (intoBuf >= 0) { out.buf = intoBuf; out.dtype = dt; out.shape = shape; out.strides = strides; }
     else out = freshView(dt, shape, isC, &strides);
     emitEltwise(root, out, isC && intoBuf < 0);
+    if (!ckey.empty()) constTreeCache[ckey] = out;
     return out;
   }
 
@@ -542,6 +565,15 @@ struct Lowering {
     std::vector<int> ids;
     for (TV* t : ts) ids.push_back(operandNode(*t, shape));
     int root = opNode(name, ids[0], n > 1 ? ids[1] : -1, n > 2 ? ids[2] : -1);
+    {   // keep fused chains within the kernel's limits (8 inputs, 48 instructions)
+      std::set<std::string> leaves; std::set<int> seen;
+      countTree(root, leaves, seen);
+      if (leaves.size() > 8 || seen.size() > 40) {
+        ids.clear();
+        for (TV* t : ts) { if (t->kind == TV::Lazy && nodes[t->root].kind == ENode::Op) toView(*t); ids.push_back(operandNode(*t, shape)); }
+        root = opNode(name, ids[0], n > 1 ? ids[1] : -1, n > 2 ? ids[2] : -1);
+      }
+    }
     if (n == 2) foldConst(root);
     tvs[res] = makeLazy(root, outDt, shape);
   }

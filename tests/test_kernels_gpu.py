@@ -180,7 +180,8 @@ def test_eltwise_programs():
                        ("ld0;#3;add,0,1;ld0;add,2,3", x + 3 + x), ("ld0;exp,0", x.exp()), ("ld0;gelu,0", F.gelu(x))]:
         G.eltwise(out, [X, Y], prog)
         exact = prog.split(";")[-1].split(",")[0] in ("add", "sub", "mul", "abs", "relu", "where")
-        assert torch.equal(out.cpu(), want) if exact else max_rel_err(out, want) < 1e-5, prog
+        err = max_rel_err(out, want)
+        assert (err == 0.0) if exact else (err < 1e-5), (prog, err)
 
 
 def test_eltwise_broadcast_and_layout_copy():
