@@ -39,8 +39,19 @@ typedef struct LlcGemmParams {
   int64_t r_s0, r_s1, r_sm, r_sn;
   float alpha;
   int32_t act;         /* LlcAct */
+  /* Optional scratch for the split-K path (few output tiles, long K): device memory, 16-byte
+   * aligned, whose first 4096 bytes are zero before the first use (the kernel leaves them zero).
+   * NULL disables split-K.  Launches that share one workspace must not overlap on the GPU. */
+  void* workspace;
+  int64_t workspace_bytes;
 } LlcGemmParams;
 int llc_cuda_gemm(const LlcGemmParams* p, void* stream);
+
+/* Health word of the tensor-core kernels.  Their waits on memory barriers are bounded; a wait that
+ * gives up records 1 (producer), 2 (issuer), 3 (operand split) or 4 (epilogue) and the launch's
+ * result is then invalid.  Returns the recorded code (0 = healthy) and clears it; -1 if the device
+ * cannot be read.  Synchronises the device.  No counterpart in the reference. */
+int llc_cuda_status(void);
 
 /* NHWC implicit-GEMM convolution with the same epilogue; replaces llh.conv
  * (-> stablehlo.convolution, LLHToHLO.cpp:214-270), the decomposed batch-norm inference that

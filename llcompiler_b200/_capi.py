@@ -97,7 +97,8 @@ class LlcGemmParams(Structure):
                 ("res", c_void_p), ("in_dtype", c_int32), ("out_dtype", c_int32), ("res_dtype", c_int32),
                 ("precision", c_int32)] + [(n, c_int64) for n in (
                     "m", "n", "k", "b0", "b1", "a_s0", "a_s1", "a_sm", "b_s0", "b_s1", "b_sk", "b_sn",
-                    "o_s0", "o_s1", "o_sm", "r_s0", "r_s1", "r_sm", "r_sn")] + [("alpha", c_float), ("act", c_int32)]
+                    "o_s0", "o_s1", "o_sm", "r_s0", "r_s1", "r_sm", "r_sn")] + [("alpha", c_float), ("act", c_int32),
+                                                                               ("workspace", c_void_p), ("workspace_bytes", c_int64)]
 
 
 class LlcConvParams(Structure):
@@ -127,5 +128,5 @@ EXPORTED_SYMBOLS = [
     "llc_compile", "llc_run_pass", "llc_load", "llc_num_inputs", "llc_num_outputs", "llc_num_symbols",
     "llc_output_shape", "llc_run", "llc_profile", "llc_last_launch_count", "llc_arena_bytes", "llc_free", "llc_last_error",
     "llc_version", "llc_cuda_gemm", "llc_cuda_conv2d", "llc_cuda_maxpool2d", "llc_cuda_reduce",
-    "llc_cuda_softmax", "llc_cuda_layernorm", "llc_cuda_gather", "llc_cuda_eltwise",
+    "llc_cuda_softmax", "llc_cuda_layernorm", "llc_cuda_gather", "llc_cuda_eltwise", "llc_cuda_status",
 ]

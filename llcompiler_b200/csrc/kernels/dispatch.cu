@@ -3,8 +3,13 @@
 #include "common.cuh"
 
 namespace llc {
-int igemmSimtGemm(const LlcGemmParams* p, cudaStream_t st);
+int igemmSimtGemm(const LlcGemmParams* p, cudaStream_t st, void* workspace, long long workspaceBytes);
 int igemmSimtConv(const LlcConvParams* p, cudaStream_t st);
+bool tcGemmSupported(const LlcGemmParams* p);
+int tcGemm(const LlcGemmParams* p, cudaStream_t st);
+bool tcConvSupported(const LlcConvParams* p);
+int tcConv(const LlcConvParams* p, cudaStream_t st);
+int tcStatus();
 }  // namespace llc
 
 using namespace llc;
@@ -18,8 +23,11 @@ extern "C" int llc_cuda_gemm(const LlcGemmParams* p, void* stream) {
   if (!p->a || !p->b || !p->out) return setError(LLC_ERR_ARGUMENT, "llc argument: gemm null operand");
   if (!floatIo(p->in_dtype) || !floatIo(p->out_dtype) || (p->res && !floatIo(p->res_dtype)))
     return setError(LLC_ERR_UNSUPPORTED, "llc argument: gemm operands must be f32 or bf16");
-  return igemmSimtGemm(p, (cudaStream_t)stream);
+  if (tcGemmSupported(p)) return tcGemm(p, (cudaStream_t)stream);
+  return igemmSimtGemm(p, (cudaStream_t)stream, p->workspace, p->workspace_bytes);
 }
+
+extern "C" int llc_cuda_status(void) { return tcStatus(); }
 
 extern "C" int llc_cuda_conv2d(const LlcConvParams* p, void* stream) {
   if (!p) return setError(LLC_ERR_ARGUMENT, "llc argument: conv null parameter block");
@@ -31,5 +39,6 @@ extern "C" int llc_cuda_conv2d(const LlcConvParams* p, void* stream) {
   if (!floatIo(p->in_dtype) || !floatIo(p->out_dtype) || (p->res && !floatIo(p->res_dtype)))
     return setError(LLC_ERR_UNSUPPORTED, "llc argument: conv operands must be f32 or bf16");
   if (p->h * p->w_in * p->c >= (1LL << 31) || p->kh * p->kw * p->c >= (1LL << 31)) return setError(LLC_ERR_UNSUPPORTED, "llc argument: conv image or filter too large");
+  if (tcConvSupported(p)) return tcConv(p, (cudaStream_t)stream);
   return igemmSimtConv(p, (cudaStream_t)stream);
 }

@@ -1,0 +1,509 @@
+// Tensor-core GEMM and implicit-GEMM convolution for sm_100a: tcgen05.mma with accumulators in
+// tensor memory, TMA-fed operands, persistent warp-specialised CTAs, fused epilogue.  Serves
+// llc_cuda_gemm / llc_cuda_conv2d for bf16 operands and for fp32 operands at precision tf32 (one
+// pass) or tf32x3 (three passes, fp32-grade accuracy).
+//
+// One CTA per SM loops over 128 x BN output tiles (BN = 64, 128 or 256).  Roles, by warp:
+//   warp 0      TMA producer: per K block waits for a free stage, arms its mbarrier with the byte
+//               count and issues the tile loads (B: BN rows x 128 bytes; dense GEMM also A: 128 rows
+//               x 128 bytes; K-major, 128-byte swizzle; rows/columns past the edge are zero-filled
+//               by TMA, which is how M, N and K tails are handled).
+//   warp 1      MMA issuer: one lane waits for the stage, issues BK/UMMA_K tcgen05.mma (fp32
+//               accumulation into one of two TMEM accumulators), commits the stage back to the
+//               producer; after the last K block commits the accumulator to the epilogue.
+//               Allocates and frees tensor memory.
+//   warps 2-9   epilogue: tcgen05.ld (32 lanes x 32 columns per warp and step; a warp owns one lane
+//               quarter and one column half), alpha*scale[n]*acc + shift[n] + res, activation,
+//               16-byte stores; releases the accumulator as soon as it is in registers so that the
+//               next tile's MMAs overlap the stores.
+//   next 4      convolution only: im2col gather of the A tile (NHWC activations) with 16-byte
+//               cp.async into the swizzled layout, zero-filling padding taps.
+//   next 4      tf32x3 only: split each landed fp32 tile into its low-order part x - tf32(x)
+//               (same swizzled position in a second buffer) and hand the stage to the issuer.
+// tf32x3: acc = A_hi*B_hi + A_lo*B_hi + A_hi*B_lo.  The tensor core reads only the upper 19 bits
+// of an fp32 operand, so A_hi is the raw tile and A_lo = A - truncate_to_tf32(A) is exact.
+//
+// Bound: tensor pipe.  Algorithmic FLOPs 2*M*N*K per batch entry; HBM bytes (M*K + N*K + M*N)
+// elements; A is re-read once per column of tiles and B once per row of tiles (L2 hits).
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace llc {
+
+__device__ int g_tcStatus = 0;   // non-zero after a bounded wait gave up: 1 producer, 2 issuer, 3 split, 4 epilogue, 5 gather
+
+namespace {
+
+using namespace tc;
+
+constexpr int BM = 128;
+constexpr int kTileKBytes = 128;          // one swizzle atom along K
+
+struct TcArgs {
+  void* out; const float* scale; const float* shift; const void* res;
+  int out_dtype, res_dtype, act; float alpha;
+  long long M, N, K;
+  long long o_s0, o_s1, o_sm, r_s0, r_s1, r_sm, r_sn;
+  int b1; int kBlocks; int vecOut;
+  int aZ0, aZ1, bZ0, bZ1;   // 1: the operand has this batch dim, 0: it is broadcast (coordinate 0)
+  int mTiles, nTiles; long long tiles;
+  // convolution (A gathered from NHWC activations)
+  const void* x; int H, W, C, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
+};
+
+template <int BN, bool X3> struct Smem {
+  static constexpr int kABytes = BM * kTileKBytes, kBBytes = BN * kTileKBytes;
+  static constexpr int kStageBytes = (kABytes + kBBytes) * (X3 ? 2 : 1);
+  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  static constexpr int kBarrierBytes = 1024;
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;   // + alignment slack
+};
+
+__device__ __forceinline__ void cpAsync16(uint32_t dst, const void* src, bool valid) {
+  const int bytes = valid ? 16 : 0;   // src-size 0: the 16 destination bytes are zero-filled
+  asm volatile("cp.async.cg.shared.global [%0], [%1], 16, %2;" ::"r"(dst), "l"(src), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
+template <int N> __device__ __forceinline__ void cpAsyncWait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+
+// KIND: 0 bf16, 1 tf32, 2 tf32x3
+template <int BN, int KIND, bool CONV>
+__global__ void __launch_bounds__((10 + (CONV ? 4 : 0) + (KIND == 2 ? 4 : 0)) * 32, 1)
+tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcArgs p) {
+  constexpr bool X3 = KIND == 2;
+  constexpr bool TF32 = KIND != 0;
+  using S = Smem<BN, X3>;
+  constexpr int kStages = S::kStages;
+  constexpr int kElemBytes = TF32 ? 4 : 2;
+  constexpr int BK = kTileKBytes / kElemBytes;          // 64 bf16 / 32 tf32
+  constexpr int UMMA_K = 32 / kElemBytes;               // 16 bf16 / 8 tf32 (32 bytes of K per instruction)
+  constexpr uint32_t kIdesc = instrDesc(TF32 ? 2 : 1, BM, BN, 0, 0);
+  constexpr int kAccCols = BN == 256 ? 512 : 2 * BN;    // two accumulators
+  constexpr int kEpiWarps = 8;
+  constexpr int kGatherWarp0 = 2 + kEpiWarps, kSplitWarp0 = kGatherWarp0 + (CONV ? 4 : 0);
+  constexpr int kFullCount = CONV ? 129 : 1;            // 128 gather threads + the TMA arm
+
+  extern __shared__ uint8_t smemRaw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
+  uint8_t* tiles = smem;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(smem + kStages * S::kStageBytes);
+  uint64_t* full = bars;                    // [kStages] operands landed
+  uint64_t* empty = bars + kStages;         // [kStages] MMAs that read the stage are done
+  uint64_t* split = bars + 2 * kStages;     // [kStages] low-order tiles written (tf32x3)
+  uint64_t* accFull = bars + 3 * kStages;   // [2] accumulator complete
+  uint64_t* accEmpty = bars + 3 * kStages + 2;  // [2] accumulator drained by the epilogue
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 4);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbarInit(&full[s], kFullCount); mbarInit(&empty[s], 1); mbarInit(&split[s], 128); }
+    for (int a = 0; a < 2; ++a) { mbarInit(&accFull[a], 1); mbarInit(&accEmpty[a], kEpiWarps); }
+    fenceBarrierInit();
+  }
+  if (warp == 1) tmemAlloc(tmemSlot, kAccCols);
+  tcFenceBefore();
+  __syncthreads();
+  tcFenceAfter();
+  const uint32_t tmemBase = *tmemSlot;
+
+  auto stageA = [&](int s) { return tiles + s * S::kStageBytes; };
+  auto stageB = [&](int s) { return tiles + s * S::kStageBytes + S::kABytes; };
+  auto stageALo = [&](int s) { return tiles + s * S::kStageBytes + S::kABytes + S::kBBytes; };
+  auto stageBLo = [&](int s) { return tiles + s * S::kStageBytes + 2 * S::kABytes + S::kBBytes; };
+  const long long tilesPerBatch = (long long)p.mTiles * p.nTiles;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- TMA producer
+    if (lane == 0) {
+      if (!CONV) prefetchTensorMap(&mapA);
+      prefetchTensorMap(&mapB);
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
+        const int z = (int)(t / tilesPerBatch); const int rem = (int)(t - z * tilesPerBatch);
+        const int tileM = rem / p.nTiles, tileN = rem - tileM * p.nTiles;
+        const int zb0 = z / p.b1, zb1 = z - zb0 * p.b1;
+        for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
+          const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
+          if (!mbarWait(&empty[s], ph ^ 1)) { atomicExch(&g_tcStatus, 1); ok = false; break; }
+          mbarExpectTx(&full[s], CONV ? S::kBBytes : S::kABytes + S::kBBytes);
+          if (!CONV) tmaLoad4d(stageA(s), &mapA, &full[s], kb * BK, tileM * BM, zb1 * p.aZ1, zb0 * p.aZ0);
+          tmaLoad4d(stageB(s), &mapB, &full[s], kb * BK, tileN * BN, zb1 * p.bZ1, zb0 * p.bZ0);
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      uint32_t it = 0, tcount = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++tcount) {
+        const int ab = tcount & 1; const uint32_t aph = (tcount >> 1) & 1;
+        if (!mbarWait(&accEmpty[ab], aph ^ 1)) { atomicExch(&g_tcStatus, 2); ok = false; break; }
+        tcFenceAfter();
+        const uint32_t acc = tmemBase + (uint32_t)(ab * (kAccCols / 2));
+        for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
+          const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
+          if (!mbarWait(X3 ? &split[s] : &full[s], ph)) { atomicExch(&g_tcStatus, 2); ok = false; break; }
+          tcFenceAfter();
+          const uint64_t dA = smemDescKMajorSw128(smemAddr(stageA(s))), dB = smemDescKMajorSw128(smemAddr(stageB(s)));
+#pragma unroll
+          for (int k = 0; k < BK / UMMA_K; ++k) {
+            const uint64_t adv = (uint64_t)((k * UMMA_K * kElemBytes) >> 4);   // 32 bytes of K per step inside the swizzle atom
+            mmaSS<TF32>(acc, dA + adv, dB + adv, kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
+          }
+          if (X3) {
+            const uint64_t dAl = smemDescKMajorSw128(smemAddr(stageALo(s))), dBl = smemDescKMajorSw128(smemAddr(stageBLo(s)));
+#pragma unroll
+            for (int k = 0; k < BK / UMMA_K; ++k) {
+              const uint64_t adv = (uint64_t)((k * UMMA_K * kElemBytes) >> 4);
+              mmaSS<TF32>(acc, dAl + adv, dB + adv, kIdesc, 1u);
+              mmaSS<TF32>(acc, dA + adv, dBl + adv, kIdesc, 1u);
+            }
+          }
+          mmaCommit(&empty[s]);
+        }
+        mmaCommit(&accFull[ab]);   // also reached after a failed wait so that the epilogue does not spin out
+      }
+    }
+  } else if (warp < 2 + kEpiWarps) {
+    // ---------------------------------------------------------------- epilogue
+    // Warp w reads TMEM lanes 32*(w%4)..+31 (a hardware rule) and the column half (w-2)/4.
+    const int q = warp & 3, half = (warp - 2) >> 2;
+    constexpr int kColsPerWarp = BN / 2;
+    char* outBase = reinterpret_cast<char*>(p.out);
+    const bool outF32 = p.out_dtype == LLC_FLOAT32;
+    uint32_t tcount = 0;
+    for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++tcount) {
+      const int z = (int)(t / tilesPerBatch); const int rem = (int)(t - z * tilesPerBatch);
+      const int tileM = rem / p.nTiles, tileN = rem - tileM * p.nTiles;
+      const int zb0 = z / p.b1, zb1 = z - zb0 * p.b1;
+      const int ab = tcount & 1; const uint32_t aph = (tcount >> 1) & 1;
+      if (!mbarWait(&accFull[ab], aph)) atomicExch(&g_tcStatus, 4);
+      tcFenceAfter();
+      const uint32_t acc = tmemBase + (uint32_t)(ab * (kAccCols / 2)) + ((uint32_t)(q * 32) << 16);
+      const long long gm = (long long)tileM * BM + q * 32 + lane;
+      const bool rowOk = gm < p.M;
+      const long long oRow = zb0 * p.o_s0 + zb1 * p.o_s1 + gm * p.o_sm;
+      const long long rRow = zb0 * p.r_s0 + zb1 * p.r_s1 + gm * p.r_sm;
+#pragma unroll 1
+      for (int c0 = half * kColsPerWarp; c0 < (half + 1) * kColsPerWarp; c0 += 32) {
+        float v[32];
+        __syncwarp();                                   // the load is warp-collective
+        tmemLoad32x32(acc + (uint32_t)c0, v);
+        if (c0 + 32 >= (half + 1) * kColsPerWarp) {     // this warp's share is in registers: hand the accumulator back
+          tcFenceBefore();
+          __syncwarp();
+          if (lane == 0) mbarArrive(&accEmpty[ab]);
+        }
+        const long long gn0 = (long long)tileN * BN + c0;
+        if (gn0 >= p.N) continue;
+        if (p.vecOut && gn0 + 32 <= p.N) {
+          // whole chunk inside the matrix: flag tests hoisted out of the element loops
+          if (p.scale) {
+            const float4* sc = reinterpret_cast<const float4*>(p.scale + gn0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { float4 s4 = __ldg(sc + j); v[4 * j] *= p.alpha * s4.x; v[4 * j + 1] *= p.alpha * s4.y; v[4 * j + 2] *= p.alpha * s4.z; v[4 * j + 3] *= p.alpha * s4.w; }
+          } else if (p.alpha != 1.f) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
+          }
+          if (p.shift) {
+            const float4* sh = reinterpret_cast<const float4*>(p.shift + gn0);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { float4 s4 = __ldg(sh + j); v[4 * j] += s4.x; v[4 * j + 1] += s4.y; v[4 * j + 2] += s4.z; v[4 * j + 3] += s4.w; }
+          }
+          if (p.res && rowOk) {
+            if (p.r_sn == 1 && p.res_dtype == LLC_BFLOAT16 && ((rRow + gn0) & 3) == 0) {
+              const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(p.res) + rRow + gn0;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { float4 r4 = Vec4<__nv_bfloat16>::load(rp + 4 * j); v[4 * j] += r4.x; v[4 * j + 1] += r4.y; v[4 * j + 2] += r4.z; v[4 * j + 3] += r4.w; }
+            } else if (p.r_sn == 1 && p.res_dtype == LLC_FLOAT32 && ((rRow + gn0) & 3) == 0) {
+              const float* rp = reinterpret_cast<const float*>(p.res) + rRow + gn0;
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { float4 r4 = Vec4<float>::load(rp + 4 * j); v[4 * j] += r4.x; v[4 * j + 1] += r4.y; v[4 * j + 2] += r4.z; v[4 * j + 3] += r4.w; }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += loadAs(p.res, rRow + (gn0 + j) * p.r_sn, p.res_dtype);
+            }
+          }
+          if (p.act == LLC_ACT_RELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
+          } else if (p.act == LLC_ACT_GELU) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] = geluErf(v[j]);
+          }
+          if (rowOk) {
+            if (outF32) {
+              float* dst = reinterpret_cast<float*>(outBase) + oRow + gn0;
+#pragma unroll
+              for (int j = 0; j < 32; j += 4) Vec4<float>::store(dst + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+            } else {
+              uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(outBase) + oRow + gn0);
+              const bool al16 = ((oRow + gn0) & 7) == 0;
+              if (al16) {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_bfloat162 a0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), a1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                  __nv_bfloat162 a2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), a3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                  uint4 pk; pk.x = *reinterpret_cast<unsigned*>(&a0); pk.y = *reinterpret_cast<unsigned*>(&a1); pk.z = *reinterpret_cast<unsigned*>(&a2); pk.w = *reinterpret_cast<unsigned*>(&a3);
+                  dst[j] = pk;
+                }
+              } else {
+                __nv_bfloat16* d2 = reinterpret_cast<__nv_bfloat16*>(outBase) + oRow + gn0;
+#pragma unroll
+                for (int j = 0; j < 32; j += 4) Vec4<__nv_bfloat16>::store(d2 + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
+              }
+            }
+          }
+        } else if (rowOk) {
+          // ragged edge: element by element
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const long long n = gn0 + j;
+            if (n < p.N) {
+              float x = v[j] * p.alpha;
+              if (p.scale) x *= __ldg(p.scale + n);
+              if (p.shift) x += __ldg(p.shift + n);
+              if (p.res) x += loadAs(p.res, rRow + n * p.r_sn, p.res_dtype);
+              storeAs(p.out, oRow + n, p.out_dtype, applyAct(x, p.act));
+            }
+          }
+        }
+      }
+    }
+  } else if (CONV && warp < kGatherWarp0 + 4) {
+    // ---------------------------------------------------------------- im2col gather of A (convolution)
+    // Thread r owns tile row r.  A 16-byte chunk never straddles a filter tap (C * element size is a
+    // multiple of 16), so each chunk is one contiguous load from x[n, ih, iw, c..] or zeros.
+    constexpr int kChunkElems = 16 / kElemBytes;
+    constexpr int kLag = kStages - 1 < 3 ? kStages - 1 : 3;   // stages in flight per thread before it signals
+    const int r = threadIdx.x - kGatherWarp0 * 32;
+    const char* X = reinterpret_cast<const char*>(p.x);
+    uint32_t it = 0, signalled = 0;
+    bool ok = true;
+    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
+      const int rem = (int)(t % tilesPerBatch);
+      const int tileM = rem / p.nTiles;
+      const long long gm = (long long)tileM * BM + r;
+      const bool rowOk = gm < p.M;
+      const long long mm = rowOk ? gm : 0;
+      const int ow = (int)(mm % p.OW); const long long t2 = mm / p.OW; const int oh = (int)(t2 % p.OH); const long long img = t2 / p.OH;
+      const int ih0 = oh * p.sh - p.ph, iw0 = ow * p.sw - p.pw;
+      const long long imgBase = img * p.H * p.W * p.C;
+      int tapR = 0, tapS = 0, cc = 0;                   // filter tap and channel of the next chunk
+      long long kk = 0;
+      for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
+        const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
+        if (!mbarWait(&empty[s], ph ^ 1)) { atomicExch(&g_tcStatus, 5); ok = false; break; }
+        const uint32_t rowAddr = smemAddr(stageA(s)) + r * 128;
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int ih = ih0 + tapR * p.dh, iw = iw0 + tapS * p.dw;
+          const bool valid = rowOk && kk < p.K && ih >= 0 && ih < p.H && iw >= 0 && iw < p.W;
+          const long long off = valid ? (imgBase + ((long long)ih * p.W + iw) * p.C + cc) * kElemBytes : 0;
+          cpAsync16(rowAddr + ((c ^ (r & 7)) << 4), X + off, valid);
+          kk += kChunkElems; cc += kChunkElems;
+          if (cc >= p.C) { cc = 0; if (++tapS == p.KW) { tapS = 0; ++tapR; } }
+        }
+        cpAsyncCommit();
+        if (it - signalled >= (uint32_t)kLag) {          // the oldest outstanding stage has landed
+          cpAsyncWait<kLag>();
+          fenceProxyAsync();
+          mbarArrive(&full[signalled % kStages]);
+          ++signalled;
+        }
+      }
+    }
+    cpAsyncWait<0>();
+    fenceProxyAsync();
+    for (; signalled < it; ++signalled) mbarArrive(&full[signalled % kStages]);
+  } else if (X3 && warp >= kSplitWarp0) {
+    // ---------------------------------------------------------------- low-order tiles (tf32x3)
+    // elementwise, so every 16-byte chunk keeps its swizzled position
+    const int et = threadIdx.x - kSplitWarp0 * 32;
+    uint32_t it = 0;
+    for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x) {
+      for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
+        const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
+        if (!mbarWait(&full[s], ph)) atomicExch(&g_tcStatus, 3);
+        const float4* srcA = reinterpret_cast<const float4*>(stageA(s)); float4* dstA = reinterpret_cast<float4*>(stageALo(s));
+        const float4* srcB = reinterpret_cast<const float4*>(stageB(s)); float4* dstB = reinterpret_cast<float4*>(stageBLo(s));
+        auto lo = [](float x) { return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); };
+#pragma unroll 4
+        for (int i = et; i < S::kABytes / 16; i += 128) { float4 v = srcA[i]; dstA[i] = make_float4(lo(v.x), lo(v.y), lo(v.z), lo(v.w)); }
+#pragma unroll 4
+        for (int i = et; i < S::kBBytes / 16; i += 128) { float4 v = srcB[i]; dstB[i] = make_float4(lo(v.x), lo(v.y), lo(v.z), lo(v.w)); }
+        fenceProxyAsync();
+        mbarArrive(&split[s]);
+      }
+    }
+  }
+  tcFenceBefore();
+  __syncthreads();
+  if (warp == 1) { tcFenceAfter(); tmemDealloc(tmemBase, kAccCols); }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn encodeTiled() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// K-major operand [b0, b1, rows, K] with unit stride along K -> 4-D tensor map, box = 128 bytes of K x boxRows rows.
+bool makeMap(CUtensorMap* map, const void* base, bool f32, long long K, long long rows, long long b1, long long b0, long long sRow, long long s1,
+             long long s0, int boxRows) {
+  EncodeTiledFn enc = encodeTiled();
+  if (!enc) return false;
+  const int eb = f32 ? 4 : 2;
+  // a broadcast batch dim (stride 0) or a unit extent becomes extent 1 with any legal stride
+  const bool has1 = b1 > 1 && s1 > 0, has0 = b0 > 1 && s0 > 0;
+  const long long dense = sRow * rows;
+  cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)(has1 ? b1 : 1), (cuuint64_t)(has0 ? b0 : 1)};
+  cuuint64_t strides[3] = {(cuuint64_t)(sRow * eb), (cuuint64_t)((has1 ? s1 : dense) * eb), (cuuint64_t)((has0 ? s0 : dense) * eb)};
+  cuuint32_t box[4] = {(cuuint32_t)(kTileKBytes / eb), (cuuint32_t)boxRows, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+int numSMs() {
+  static int n = []() { int dev = 0, v = kNumSMs; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev); return v > 0 ? v : kNumSMs; }();
+  return n;
+}
+
+template <int BN, int KIND, bool CONV>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, TcArgs a, long long batch, cudaStream_t st) {
+  using S = Smem<BN, KIND == 2>;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(tc_kernel<BN, KIND, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    if (e != cudaSuccess) return cudaFail(e, "cudaFuncSetAttribute(tc_kernel)");
+    configured = true;
+  }
+  a.mTiles = (int)((a.M + BM - 1) / BM); a.nTiles = (int)((a.N + BN - 1) / BN);
+  a.tiles = (long long)a.mTiles * a.nTiles * batch;
+  const int threads = (10 + (CONV ? 4 : 0) + (KIND == 2 ? 4 : 0)) * 32;
+  const unsigned grid = (unsigned)(a.tiles < numSMs() ? a.tiles : numSMs());
+  tc_kernel<BN, KIND, CONV><<<grid, threads, S::kTotal, st>>>(ma, mb, a);
+  LLC_LAUNCH_CHECK("tc_kernel");
+  return LLC_OK;
+}
+
+template <bool CONV>
+int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, long long batch, cudaStream_t st) {
+#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, CONV>(ma, mb, a, batch, st);
+  TC_CASE(64, 0) TC_CASE(64, 1) TC_CASE(64, 2) TC_CASE(128, 0) TC_CASE(128, 1) TC_CASE(128, 2) TC_CASE(256, 0) TC_CASE(256, 1) TC_CASE(256, 2)
+#undef TC_CASE
+  return setError(LLC_ERR_INTERNAL, "llc internal: no tensor-core kernel for this tile");
+}
+
+// Tile width: the widest tile that still gives every SM work.
+int chooseBN(long long M, long long N, long long batch) {
+  const long long mT = (M + BM - 1) / BM;
+  auto tiles = [&](long long bn) { return mT * ((N + bn - 1) / bn) * batch; };
+  if (N > 128 && tiles(256) >= numSMs()) return 256;
+  if (N > 64 && tiles(128) >= numSMs()) return 128;
+  if (N > 64 && tiles(64) < numSMs() / 2) return 128;   // tiny grids: fewer, larger tiles cost less fixed work
+  return 64;
+}
+
+}  // namespace
+
+// Whether the tensor-core kernel takes this call (otherwise the FMA kernel does).
+bool tcGemmSupported(const LlcGemmParams* p) {
+  const bool f32 = p->in_dtype == LLC_FLOAT32;
+  if (!f32 && p->in_dtype != LLC_BFLOAT16) return false;
+  if (f32 && p->precision != LLC_PREC_TF32 && p->precision != LLC_PREC_TF32X3) return false;
+  if (p->b_sk != 1) return false;                       // B must be stored [n][k]
+  const int eb = f32 ? 4 : 2;
+  auto ok16 = [&](long long s) { return (s * eb) % 16 == 0; };
+  if (!ok16(p->a_sm) || !ok16(p->a_s0) || !ok16(p->a_s1) || !ok16(p->b_sn) || !ok16(p->b_s0) || !ok16(p->b_s1)) return false;
+  if (p->a_sm < p->k || p->b_sn < p->k) return false;   // overlapping rows are not expressible as a tensor map
+  if (p->a_s0 < 0 || p->a_s1 < 0 || p->b_s0 < 0 || p->b_s1 < 0) return false;
+  if ((reinterpret_cast<uintptr_t>(p->a) | reinterpret_cast<uintptr_t>(p->b)) & 15) return false;
+  if (p->m < 1 || p->n < 1 || p->k < 1) return false;
+  if (p->b0 > (1 << 30) || p->b1 > (1 << 30) || p->m > (1LL << 31) * 64 || p->n > (1LL << 31)) return false;
+  if (p->m * p->n * p->k < (1LL << 18)) return false;   // tiny problems: the FMA kernel has less fixed cost
+  return encodeTiled() != nullptr;
+}
+
+int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
+  const bool f32 = p->in_dtype == LLC_FLOAT32;
+  const int eb = f32 ? 4 : 2;
+  const int bk = kTileKBytes / eb;
+  const long long batch = p->b0 * p->b1;
+  const int bn = chooseBN(p->m, p->n, batch);
+  CUtensorMap ma, mb;
+  if (!makeMap(&ma, p->a, f32, p->k, p->m, p->b1, p->b0, p->a_sm, p->a_s1, p->a_s0, BM) ||
+      !makeMap(&mb, p->b, f32, p->k, p->n, p->b1, p->b0, p->b_sn, p->b_s1, p->b_s0, bn))
+    return setError(LLC_ERR_CUDA, "llc cuda: cuTensorMapEncodeTiled rejected the GEMM operands");
+  TcArgs a{};
+  a.out = p->out; a.scale = p->scale; a.shift = p->shift; a.res = p->res;
+  a.out_dtype = p->out_dtype; a.res_dtype = p->res_dtype; a.act = p->act; a.alpha = p->alpha;
+  a.M = p->m; a.N = p->n; a.K = p->k;
+  a.o_s0 = p->o_s0; a.o_s1 = p->o_s1; a.o_sm = p->o_sm; a.r_s0 = p->r_s0; a.r_s1 = p->r_s1; a.r_sm = p->r_sm; a.r_sn = p->r_sn;
+  a.b1 = (int)p->b1; a.kBlocks = (int)((p->k + bk - 1) / bk);
+  a.aZ0 = p->b0 > 1 && p->a_s0 > 0; a.aZ1 = p->b1 > 1 && p->a_s1 > 0; a.bZ0 = p->b0 > 1 && p->b_s0 > 0; a.bZ1 = p->b1 > 1 && p->b_s1 > 0;
+  const int ob = p->out_dtype == LLC_FLOAT32 ? 4 : 2;
+  a.vecOut = (reinterpret_cast<uintptr_t>(p->out) % (ob * 4)) == 0 && p->o_sm % 4 == 0 && p->o_s0 % 4 == 0 && p->o_s1 % 4 == 0 &&
+             ((reinterpret_cast<uintptr_t>(p->scale) | reinterpret_cast<uintptr_t>(p->shift)) & 15) == 0;
+  const int kind = !f32 ? 0 : (p->precision == LLC_PREC_TF32X3 ? 2 : 1);
+  return dispatch<false>(bn, kind, ma, mb, a, batch, st);
+}
+
+bool tcConvSupported(const LlcConvParams* p) {
+  const bool f32 = p->in_dtype == LLC_FLOAT32;
+  if (!f32 && p->in_dtype != LLC_BFLOAT16) return false;
+  if (f32 && p->precision != LLC_PREC_TF32 && p->precision != LLC_PREC_TF32X3) return false;
+  const int eb = f32 ? 4 : 2;
+  if ((p->c * eb) % 16 != 0) return false;              // a 16-byte chunk must stay inside one filter tap
+  if ((reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->w)) & 15) return false;
+  const long long M = p->n * p->oh * p->ow, K = p->kh * p->kw * p->c;
+  if (M * p->f * K < (1LL << 18)) return false;
+  return encodeTiled() != nullptr;
+}
+
+int tcConv(const LlcConvParams* p, cudaStream_t st) {
+  const bool f32 = p->in_dtype == LLC_FLOAT32;
+  const int eb = f32 ? 4 : 2;
+  const int bk = kTileKBytes / eb;
+  const long long M = p->n * p->oh * p->ow, K = p->kh * p->kw * p->c;
+  const int bn = chooseBN(M, p->f, 1);
+  CUtensorMap mb;
+  if (!makeMap(&mb, p->w, f32, K, p->f, 1, 1, K, 0, 0, bn))
+    return setError(LLC_ERR_CUDA, "llc cuda: cuTensorMapEncodeTiled rejected the convolution weights");
+  TcArgs a{};
+  a.out = p->out; a.scale = p->scale; a.shift = p->shift; a.res = p->res;
+  a.out_dtype = p->out_dtype; a.res_dtype = p->res_dtype; a.act = p->act; a.alpha = p->alpha;
+  a.M = M; a.N = p->f; a.K = K; a.o_sm = p->f; a.r_sm = p->f; a.r_sn = 1; a.b1 = 1;
+  a.kBlocks = (int)((K + bk - 1) / bk);
+  const int ob = p->out_dtype == LLC_FLOAT32 ? 4 : 2;
+  a.vecOut = (reinterpret_cast<uintptr_t>(p->out) % (ob * 4)) == 0 && p->f % 4 == 0 &&
+             ((reinterpret_cast<uintptr_t>(p->scale) | reinterpret_cast<uintptr_t>(p->shift)) & 15) == 0;
+  a.x = p->x; a.H = (int)p->h; a.W = (int)p->w_in; a.C = (int)p->c; a.KH = (int)p->kh; a.KW = (int)p->kw; a.OH = (int)p->oh; a.OW = (int)p->ow;
+  a.sh = p->stride_h; a.sw = p->stride_w; a.ph = p->pad_h; a.pw = p->pad_w; a.dh = p->dil_h; a.dw = p->dil_w;
+  const int kind = !f32 ? 0 : (p->precision == LLC_PREC_TF32X3 ? 2 : 1);
+  return dispatch<true>(bn, kind, mb, mb, a, 1, st);
+}
+
+// Reads and clears the status word the bounded waits write (0 = no wait ever gave up).
+int tcStatus() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_tcStatus, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_tcStatus, &zero, sizeof(int));
+  return v;
+}
+
+}  // namespace llc

@@ -20,6 +20,10 @@ struct IgemmArgs {
   long long a_s0, a_s1, a_sm, b_s0, b_s1, b_sk, b_sn, o_s0, o_s1, o_sm, r_s0, r_s1, r_sm, r_sn;
   int b1; int vecOut;
   int H, W, C, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
+  // split-K: grid.z = batch * splitK; CTA kz reduces K range [kz*kPer, (kz+1)*kPer) into `partial`,
+  // the last CTA to arrive at a tile (counted in `counters`) sums the partials in kz order and
+  // runs the epilogue, then puts the counter back to zero.
+  int splitK; long long kPer; float* partial; unsigned* counters;
 };
 
 constexpr int BK = 16;
@@ -34,7 +38,10 @@ __global__ void __launch_bounds__(256) igemm_simt_kernel(IgemmArgs p) {
 
   const int tid = threadIdx.x, tx = tid & 15, ty = tid >> 4;
   const long long m0 = (long long)blockIdx.x * BM, n0 = (long long)blockIdx.y * BN;
-  const int z = blockIdx.z, zb0 = z / p.b1, zb1 = z % p.b1;
+  const int kz = p.splitK > 1 ? (int)(blockIdx.z % p.splitK) : 0;
+  const int z = p.splitK > 1 ? (int)(blockIdx.z / p.splitK) : (int)blockIdx.z, zb0 = z / p.b1, zb1 = z % p.b1;
+  const long long kBeg = (long long)kz * p.kPer;
+  const long long kEnd = p.splitK > 1 ? (kBeg + p.kPer < p.K ? kBeg + p.kPer : p.K) : p.K;
   const T* A = reinterpret_cast<const T*>(p.a) + (CONV ? 0 : zb0 * p.a_s0 + zb1 * p.a_s1);
   const T* B = reinterpret_cast<const T*>(p.b) + zb0 * p.b_s0 + zb1 * p.b_s1;
   const bool bKMajor = p.b_sk == 1;
@@ -68,7 +75,7 @@ __global__ void __launch_bounds__(256) igemm_simt_kernel(IgemmArgs p) {
         int e = tid + i * 256;
         long long kk = k0 + ((e & 3) << 2);
         float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
-        if (aOk[i] && kk < p.K) {
+        if (aOk[i] && kk < kEnd) {
           if (CONV) {
             int tap = (int)(kk / p.C), c = (int)(kk - (long long)tap * p.C);
             int r = tap / p.KW, s = tap - r * p.KW;
@@ -83,14 +90,14 @@ __global__ void __launch_bounds__(256) igemm_simt_kernel(IgemmArgs p) {
         for (int i = 0; i < BV; ++i) {
           int e = tid + i * 256;
           long long gn = n0 + (e >> 2), kk = k0 + ((e & 3) << 2);
-          rb4[i] = (gn < p.N && kk < p.K) ? Vec4<T>::load(B + gn * p.b_sn + kk) : make_float4(0.f, 0.f, 0.f, 0.f);
+          rb4[i] = (gn < p.N && kk < kEnd) ? Vec4<T>::load(B + gn * p.b_sn + kk) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
       } else {
 #pragma unroll
         for (int i = 0; i < BV; ++i) {
           int e = tid + i * 256;
           int kr = e / (BN / 4); long long gn = n0 + (e % (BN / 4)) * 4, kk = k0 + kr;
-          rb4[i] = (gn < p.N && kk < p.K) ? Vec4<T>::load(B + kk * p.b_sk + gn) : make_float4(0.f, 0.f, 0.f, 0.f);
+          rb4[i] = (gn < p.N && kk < kEnd) ? Vec4<T>::load(B + kk * p.b_sk + gn) : make_float4(0.f, 0.f, 0.f, 0.f);
         }
       }
     } else {
@@ -99,7 +106,7 @@ __global__ void __launch_bounds__(256) igemm_simt_kernel(IgemmArgs p) {
         int e = tid + i * 256;
         long long kk = k0 + (e & 15);
         float v = 0.f;
-        if (aOk[i] && kk < p.K) {
+        if (aOk[i] && kk < kEnd) {
           if (CONV) {
             int tap = (int)(kk / p.C), c = (int)(kk - (long long)tap * p.C);
             int r = tap / p.KW, s = tap - r * p.KW;
@@ -113,7 +120,7 @@ __global__ void __launch_bounds__(256) igemm_simt_kernel(IgemmArgs p) {
       for (int i = 0; i < BS; ++i) {
         int e = tid + i * 256;
         long long gn = n0 + (e >> 4), kk = k0 + (e & 15);
-        rbs[i] = (gn < p.N && kk < p.K) ? toFloat<T>(B[gn * p.b_sn + kk * p.b_sk]) : 0.f;
+        rbs[i] = (gn < p.N && kk < kEnd) ? toFloat<T>(B[gn * p.b_sn + kk * p.b_sk]) : 0.f;
       }
     }
   };
@@ -151,13 +158,13 @@ __global__ void __launch_bounds__(256) igemm_simt_kernel(IgemmArgs p) {
 #pragma unroll
     for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
 
-  const long long nk = (p.K + BK - 1) / BK;
-  loadTile(0);
+  const long long nk = (kEnd - kBeg + BK - 1) / BK;
+  loadTile(kBeg);
   storeTile(0);
   __syncthreads();
   for (long long kt = 0; kt < nk; ++kt) {
     const int buf = (int)(kt & 1);
-    if (kt + 1 < nk) loadTile((kt + 1) * BK);
+    if (kt + 1 < nk) loadTile(kBeg + (kt + 1) * BK);
 #pragma unroll
     for (int kk = 0; kk < BK; ++kk) {
       float a[TM], b[TN];
@@ -178,6 +185,42 @@ __global__ void __launch_bounds__(256) igemm_simt_kernel(IgemmArgs p) {
     }
     if (kt + 1 < nk) storeTile(buf ^ 1);
     __syncthreads();
+  }
+
+  if (p.splitK > 1) {
+    __shared__ int isLast;
+    const long long tileId = ((long long)z * gridDim.y + blockIdx.y) * gridDim.x + blockIdx.x;
+    float* mine = p.partial + (tileId * p.splitK + kz) * (BM * BN);
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int g = 0; g < TN / 4; ++g)
+        *reinterpret_cast<float4*>(mine + ((i >> 2) * 64 + ty * 4 + (i & 3)) * BN + g * 64 + tx * 4) =
+            make_float4(acc[i][g * 4 + 0], acc[i][g * 4 + 1], acc[i][g * 4 + 2], acc[i][g * 4 + 3]);
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      unsigned prev = atomicAdd(&p.counters[tileId], 1u);
+      isLast = prev == (unsigned)(p.splitK - 1);
+      if (isLast) p.counters[tileId] = 0;       // leave the counter at zero for the next launch
+    }
+    __syncthreads();
+    if (!isLast) return;
+    __threadfence();
+#pragma unroll
+    for (int i = 0; i < TM; ++i)
+#pragma unroll
+      for (int j = 0; j < TN; ++j) acc[i][j] = 0.f;
+    for (int q = 0; q < p.splitK; ++q) {
+      const float* part = p.partial + (tileId * p.splitK + q) * (BM * BN);
+#pragma unroll
+      for (int i = 0; i < TM; ++i)
+#pragma unroll
+        for (int g = 0; g < TN / 4; ++g) {
+          float4 v = __ldcg(reinterpret_cast<const float4*>(part + ((i >> 2) * 64 + ty * 4 + (i & 3)) * BN + g * 64 + tx * 4));
+          acc[i][g * 4 + 0] += v.x; acc[i][g * 4 + 1] += v.y; acc[i][g * 4 + 2] += v.z; acc[i][g * 4 + 3] += v.w;
+        }
+    }
   }
 
   // fused epilogue: alpha * scale[n] * acc + shift[n] + res, activation, store
@@ -216,11 +259,31 @@ __global__ void __launch_bounds__(256) igemm_simt_kernel(IgemmArgs p) {
   }
 }
 
+constexpr size_t kCounterBytes = 4096;   // head of the workspace: one counter per output tile
+
 template <typename T, bool CONV, bool VEC>
-int launchTiles(const IgemmArgs& a, long long batch, cudaStream_t st) {
+int launchTiles(IgemmArgs a, long long batch, cudaStream_t st, void* workspace, long long workspaceBytes) {
   auto tiles = [&](long long bm, long long bn) { return ((a.M + bm - 1) / bm) * ((a.N + bn - 1) / bn) * batch; };
   if (a.M <= 0 || a.N <= 0 || batch <= 0) return LLC_OK;
   if (batch > 65535) return setError(LLC_ERR_ARGUMENT, "llc argument: gemm batch count above 65535");
+  a.splitK = 1;
+  // few output tiles and a long reduction: split K over the idle SMs (needs caller scratch)
+  const long long t64 = tiles(64, 64);
+  if (workspace && t64 * 2 <= kNumSMs && a.K >= 512 && t64 <= (long long)(kCounterBytes / 4)) {
+    long long want = kNumSMs / t64; if (want > 32) want = 32; if (want > a.K / 128) want = a.K / 128;
+    long long kPer = ((a.K + want - 1) / want + BK - 1) / BK * BK;
+    long long split = (a.K + kPer - 1) / kPer;
+    size_t need = kCounterBytes + (size_t)t64 * split * 64 * 64 * sizeof(float);
+    if (split > 1 && need <= (size_t)workspaceBytes && batch * split <= 65535) {
+      a.splitK = (int)split; a.kPer = kPer;
+      a.counters = reinterpret_cast<unsigned*>(workspace);
+      a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
+      dim3 g((unsigned)((a.M + 63) / 64), (unsigned)((a.N + 63) / 64), (unsigned)(batch * split));
+      igemm_simt_kernel<T, 64, 64, CONV, VEC><<<g, 256, 0, st>>>(a);
+      LLC_LAUNCH_CHECK("igemm_simt_kernel(split-K)");
+      return LLC_OK;
+    }
+  }
   // largest tile that still fills the 148 SMs at least ~once
   if (a.N > 64 && tiles(128, 128) >= kNumSMs) {
     dim3 g((unsigned)((a.M + 127) / 128), (unsigned)((a.N + 127) / 128), (unsigned)batch);
@@ -240,7 +303,7 @@ bool aligned(const void* p, int bytes) { return (reinterpret_cast<uintptr_t>(p) 
 
 }  // namespace
 
-int igemmSimtGemm(const LlcGemmParams* p, cudaStream_t st) {
+int igemmSimtGemm(const LlcGemmParams* p, cudaStream_t st, void* workspace, long long workspaceBytes) {
   IgemmArgs a{};
   a.a = p->a; a.b = p->b; a.out = p->out; a.scale = p->scale; a.shift = p->shift; a.res = p->res;
   a.out_dtype = p->out_dtype; a.res_dtype = p->res_dtype; a.act = p->act; a.alpha = p->alpha;
@@ -257,8 +320,10 @@ int igemmSimtGemm(const LlcGemmParams* p, cudaStream_t st) {
              p->b_s0 % 4 == 0 && p->b_s1 % 4 == 0 &&
              (p->b_sk == 1 ? p->b_sn % 4 == 0 : (p->n % 4 == 0 && p->b_sk % 4 == 0));
   long long batch = p->b0 * p->b1;
-  if (p->in_dtype == LLC_FLOAT32) return vec ? launchTiles<float, false, true>(a, batch, st) : launchTiles<float, false, false>(a, batch, st);
-  if (p->in_dtype == LLC_BFLOAT16) return vec ? launchTiles<__nv_bfloat16, false, true>(a, batch, st) : launchTiles<__nv_bfloat16, false, false>(a, batch, st);
+  void* ws = workspace; long long wsb = workspaceBytes;
+  if (ws && (reinterpret_cast<uintptr_t>(ws) & 15)) ws = nullptr;
+  if (p->in_dtype == LLC_FLOAT32) return vec ? launchTiles<float, false, true>(a, batch, st, ws, wsb) : launchTiles<float, false, false>(a, batch, st, ws, wsb);
+  if (p->in_dtype == LLC_BFLOAT16) return vec ? launchTiles<__nv_bfloat16, false, true>(a, batch, st, ws, wsb) : launchTiles<__nv_bfloat16, false, false>(a, batch, st, ws, wsb);
   return setError(LLC_ERR_UNSUPPORTED, "llc argument: gemm input type must be f32 or bf16");
 }
 
@@ -273,8 +338,8 @@ int igemmSimtConv(const LlcConvParams* p, cudaStream_t st) {
   const int eb = p->in_dtype == LLC_FLOAT32 ? 4 : 2, ob = p->out_dtype == LLC_FLOAT32 ? 4 : 2;
   a.vecOut = aligned(p->out, ob * 4) && p->f % 4 == 0;
   bool vec = p->c % 4 == 0 && aligned(p->x, eb * 4) && aligned(p->w, eb * 4);
-  if (p->in_dtype == LLC_FLOAT32) return vec ? launchTiles<float, true, true>(a, 1, st) : launchTiles<float, true, false>(a, 1, st);
-  if (p->in_dtype == LLC_BFLOAT16) return vec ? launchTiles<__nv_bfloat16, true, true>(a, 1, st) : launchTiles<__nv_bfloat16, true, false>(a, 1, st);
+  if (p->in_dtype == LLC_FLOAT32) return vec ? launchTiles<float, true, true>(a, 1, st, nullptr, 0) : launchTiles<float, true, false>(a, 1, st, nullptr, 0);
+  if (p->in_dtype == LLC_BFLOAT16) return vec ? launchTiles<__nv_bfloat16, true, true>(a, 1, st, nullptr, 0) : launchTiles<__nv_bfloat16, true, false>(a, 1, st, nullptr, 0);
   return setError(LLC_ERR_UNSUPPORTED, "llc argument: conv input type must be f32 or bf16");
 }
 

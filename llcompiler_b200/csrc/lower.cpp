@@ -665,16 +665,47 @@ struct Lowering {
     if (g && g->i != 1) fail("grouped convolution is not supported by the CUDA pipeline");
     const Attr* lay = op->attr("layout");
     if (lay && lay->s != "NCHW") fail("llh.conv: only NCHW-typed modules are accepted (the NHWC layout is chosen internally)");
-    View x = viewWithStrides(xv, nhwcStrides(xt.shape));
     TV& wt = get(op->operands[1]); toView(wt);
     if (wt.shape.size() != 4) fail("llh.conv expects rank-4 weight");
-    // weight [F,C,KH,KW] -> dense [F,KH,KW,C]
+    // The tensor-core kernel gathers 16-byte chunks that must not straddle a filter tap: pad a small
+    // channel count (the 3-channel stem) to the next multiple of 16 bytes with zeros, in both the
+    // NHWC activation copy and the re-laid-out weight.
+    Expr Cin = xt.shape[1];
+    int64_t cPad = 0;
+    {
+      const int eb = dtypeSize(xt.dtype), mult = 16 / eb;
+      if (gemmPrecision(xt.dtype) != "fp32" && Cin.isConst() && Cin.constant() % mult != 0 && xt.shape[1] == wt.shape[1])
+        cPad = (Cin.constant() + mult - 1) / mult * mult;
+    }
+    View x;
+    if (cPad) {
+      std::vector<Expr> pshape = {xt.shape[0], Expr(cPad), xt.shape[2], xt.shape[3]};
+      std::vector<Expr> pst = nhwcStrides(pshape);
+      toView(xt);
+      x = freshView(xt.dtype, pshape, false, &pst);
+      emitEltwise(constNode(0.0), x, false);                          // zero the padding channels
+      View real = x; real.shape = xt.shape;                           // same strides, real channel extent
+      emitEltwise(leafNode(xt.view), real, false);
+    } else {
+      x = viewWithStrides(xv, nhwcStrides(xt.shape));
+    }
+    // weight [F,C,KH,KW] -> dense [F,KH,KW,C(padded)]
     View wperm = wt.view;
     wperm.shape = {wt.view.shape[0], wt.view.shape[2], wt.view.shape[3], wt.view.shape[1]};
     wperm.strides = {wt.view.strides[0], wt.view.strides[2], wt.view.strides[3], wt.view.strides[1]};
-    std::string key = "wperm:" + wperm.str();
+    std::string key = "wperm:" + wperm.str() + (cPad ? ":pad" + std::to_string(cPad) : "");
     View w;
-    if (constVecCache.count(key)) { w = wperm; w.buf = constVecCache[key]; w.offset = Expr(0); w.strides = rowMajor(wperm.shape); }
+    std::vector<Expr> wshape = wperm.shape;
+    if (cPad) wshape[3] = Expr(cPad);
+    if (constVecCache.count(key)) { w = wperm; w.shape = wshape; w.buf = constVecCache[key]; w.offset = Expr(0); w.strides = rowMajor(wshape); }
+    else if (cPad) {
+      std::vector<Expr> rm = rowMajor(wshape);
+      w = freshView(wperm.dtype, wshape, true, &rm);
+      emitEltwise(constNode(0.0), w, true);
+      View real = w; real.shape = wperm.shape;
+      emitEltwise(leafNode(wperm), real, true);
+      constVecCache[key] = w.buf;
+    }
     else { std::vector<Expr> rm = rowMajor(wperm.shape); w = materializeTree(leafNode(wperm), wperm.dtype, wperm.shape, &rm); constVecCache[key] = w.buf; }
     Expr N = xt.shape[0], H = xt.shape[2], W = xt.shape[3], F = wt.shape[0];
     int64_t KH = wt.shape[2].constant(), KW = wt.shape[3].constant();

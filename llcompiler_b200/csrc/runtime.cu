@@ -23,9 +23,6 @@
 
 namespace llc {
 
-int igemmSimtGemm(const LlcGemmParams* p, cudaStream_t st);
-int igemmSimtConv(const LlcConvParams* p, cudaStream_t st);
-
 namespace {
 
 [[noreturn]] void failArg(const std::string& m) { throw std::runtime_error("llc argument: " + m); }
@@ -124,6 +121,8 @@ struct LlcExec {
   char* stageIn = nullptr; size_t stageInCap = 0;
   char* stageOut = nullptr; size_t stageOutCap = 0;
   int* badIds = nullptr;
+  char* workspace = nullptr;                  // split-K scratch (counters at the head stay zero between launches)
+  static constexpr size_t kWorkspaceBytes = 16u << 20;
   std::map<std::vector<int64_t>, std::unique_ptr<Binding>> bindings;
   int64_t lastLaunches = 0;
   std::vector<char*> base;                    // per-buffer device base pointers for the current call
@@ -135,6 +134,7 @@ struct LlcExec {
     if (stageIn) cudaFree(stageIn);
     if (stageOut) cudaFree(stageOut);
     if (badIds) cudaFree(badIds);
+    if (workspace) cudaFree(workspace);
   }
 
   RView resolve(const View& v, const std::map<std::string, int64_t>& env) const {
@@ -173,6 +173,7 @@ int LlcExec::launch(const RStep& rs, cudaStream_t st) {
     if (const RView* v = rs.view("shift")) p.shift = (const float*)ptr(*v);
     if (const RView* v = rs.view("res")) { p.res = ptr(*v); p.res_dtype = v->dtype; p.r_s0 = v->strides[0]; p.r_s1 = v->strides[1]; p.r_sm = v->strides[2]; p.r_sn = v->strides[3]; }
     p.alpha = std::stof(s.param("alpha", "1")); p.act = actOf();
+    p.workspace = workspace; p.workspace_bytes = (int64_t)kWorkspaceBytes;
     return llc_cuda_gemm(&p, st);
   }
   if (s.kernel == "conv") {
@@ -346,6 +347,8 @@ extern "C" int llc_load(const char* path, int device, LlcExec** out) {
     cudaOk(cudaMalloc(&ex->staticPool, std::max<size_t>(total, 256)), "cudaMalloc(weights)");
     cudaOk(cudaMalloc(&ex->badIds, sizeof(int)), "cudaMalloc(status)");
     cudaOk(cudaMemset(ex->badIds, 0, sizeof(int)), "cudaMemset(status)");
+    cudaOk(cudaMalloc(&ex->workspace, LlcExec::kWorkspaceBytes), "cudaMalloc(workspace)");
+    cudaOk(cudaMemset(ex->workspace, 0, 4096), "cudaMemset(workspace)");
     for (size_t i = 0; i < nb; ++i) {
       auto& b = ex->plan.buffers[i];
       if (b.kind != BufferDecl::Weight && b.kind != BufferDecl::Const) continue;

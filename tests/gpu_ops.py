@@ -21,7 +21,7 @@ def _p(t):
     return None if t is None else c_void_p(t.data_ptr())
 
 
-def gemm(a, b, out, scale=None, shift=None, res=None, alpha=1.0, act="none", prec="fp32"):
+def gemm(a, b, out, scale=None, shift=None, res=None, alpha=1.0, act="none", prec="fp32", workspace=None):
     """a [b0,b1,M,K] (k stride 1), b [b0,b1,K,N] (k or n stride 1), out [b0,b1,M,N] views."""
     p = C.LlcGemmParams()
     p.a, p.b, p.out, p.scale, p.shift, p.res = _p(a), _p(b), _p(out), _p(scale), _p(shift), _p(res)
@@ -35,6 +35,8 @@ def gemm(a, b, out, scale=None, shift=None, res=None, alpha=1.0, act="none", pre
     if res is not None:
         p.r_s0, p.r_s1, p.r_sm, p.r_sn = res.stride(0), res.stride(1), res.stride(2), res.stride(3)
     p.alpha, p.act = alpha, C.ACT[act]
+    if workspace is not None:
+        p.workspace, p.workspace_bytes = _p(workspace), workspace.numel() * workspace.element_size()
     C.check(C.lib().llc_cuda_gemm(byref(p), _stream()))
 
 

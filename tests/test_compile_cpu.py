@@ -53,3 +53,12 @@ def test_bert_two_layers():
     mask[1, 10:] = 0
     comp, got, want = _run(m, (ids, mask))
     assert max_rel_err(got, want) < 1e-4
+
+
+def test_resnet18_tensor_core_plan_pads_the_stem():
+    # at a tensor-core precision the 3-channel stem is zero-padded to 4 channels (16 bytes)
+    m = build_model("resnet18")
+    comp, got, want = _run(m, (torch.randn(2, 3, 64, 64),), precision="tf32x3")
+    assert max_rel_err(got, want) < 1e-4
+    plan = comp.compiled[0].engine.text
+    assert "prec:tf32x3" in plan and "[64,7,7,4;" in plan

@@ -1,0 +1,125 @@
+"""Tensor-core GEMM (tcgen05 + TMA) parity through the C ABI.  bf16 operands multiply exactly
+and accumulate in fp32, so with fp32 output the result must agree with the fp32 CPU oracle on
+the same bf16-rounded inputs to 1e-4 relative (any descriptor or swizzle mistake is O(1)).
+fp32 operands: 5e-5 at precision tf32x3 (three-pass split; what remains is the tensor core's
+truncating fp32 accumulation, which grows with K), 2e-3 at single-pass tf32.  After every
+case the kernels' health word must read 0 (no bounded wait gave up)."""
+import pytest
+import torch
+import torch.nn.functional as F
+
+pytestmark = pytest.mark.gpu
+
+import gpu_ops as G  # noqa: E402
+from llcompiler_b200 import _capi as C  # noqa: E402
+from oracle.models import max_rel_err  # noqa: E402
+
+DEV = "cuda"
+
+
+def _rand(*shape, dtype=torch.float32, seed=0):
+    g = torch.Generator().manual_seed(seed + sum(shape))
+    return torch.randn(*shape, generator=g).to(dtype)
+
+
+def _healthy():
+    assert C.lib().llc_cuda_status() == 0
+
+
+SHAPES = [(128, 128, 64), (64, 64, 64), (256, 256, 512), (300, 200, 136), (1024, 768, 768), (130, 70, 72),
+          (98, 1000, 2048), (4096, 64, 576), (1, 512, 1024), (257, 129, 8)]
+
+
+@pytest.mark.parametrize("m,n,k", SHAPES)
+def test_bf16_fp32_out(m, n, k):
+    a, w = _rand(m, k, dtype=torch.bfloat16), _rand(n, k, dtype=torch.bfloat16, seed=1)
+    bias, res = _rand(n, seed=2), _rand(m, n, seed=3)
+    want = F.gelu(a.float() @ w.float().t() * 0.25 + bias + res)
+    out = torch.full((1, 1, m, n), float("nan"), device=DEV)
+    G.gemm(a.to(DEV)[None, None], w.to(DEV).t()[None, None], out, shift=bias.to(DEV), res=res.to(DEV)[None, None],
+           alpha=0.25, act="gelu", prec="bf16")
+    assert max_rel_err(out[0, 0], want) < 1e-4
+    _healthy()
+
+
+@pytest.mark.parametrize("m,n,k", [(256, 256, 512), (300, 200, 136), (130, 70, 72)])
+def test_bf16_bf16_out_scale_relu(m, n, k):
+    a, w = _rand(m, k, dtype=torch.bfloat16), _rand(n, k, dtype=torch.bfloat16, seed=1)
+    scale, shift = _rand(n, seed=2).abs() + 0.5, _rand(n, seed=3)
+    res = _rand(m, n, dtype=torch.bfloat16, seed=4)
+    want = torch.relu(a.float() @ w.float().t() * scale + shift + res.float())
+    out = torch.empty(1, 1, m, n, device=DEV, dtype=torch.bfloat16)
+    G.gemm(a.to(DEV)[None, None], w.to(DEV).t()[None, None], out, scale=scale.to(DEV), shift=shift.to(DEV),
+           res=res.to(DEV)[None, None], act="relu", prec="bf16")
+    assert max_rel_err(out[0, 0].float(), want) < 2e-2
+    _healthy()
+
+
+@pytest.mark.parametrize("prec,tol", [("tf32x3", 5e-5), ("tf32", 2e-3)])
+@pytest.mark.parametrize("m,n,k", [(128, 128, 32), (256, 256, 512), (300, 200, 136), (64, 512, 784), (1024, 768, 3072), (100, 10, 512)])
+def test_fp32_on_tensor_cores(m, n, k, prec, tol):
+    a, w, bias = _rand(m, k), _rand(n, k, seed=1), _rand(n, seed=2)
+    want = torch.relu((a.double() @ w.double().t()).float() + bias)
+    out = torch.full((1, 1, m, n), float("nan"), device=DEV)
+    G.gemm(a.to(DEV)[None, None], w.to(DEV).t()[None, None], out, shift=bias.to(DEV), act="relu", prec=prec)
+    assert max_rel_err(out[0, 0], want) < tol
+    _healthy()
+
+
+def test_bf16_batched_strided_heads_with_mask():
+    Bn, S, H, D = 2, 384, 12, 64
+    q, k = _rand(Bn, S, H * D, dtype=torch.bfloat16), _rand(Bn, S, H * D, dtype=torch.bfloat16, seed=1)
+    mask = _rand(Bn, 1, 1, S, seed=2)
+    qh, kh = q.float().view(Bn, S, H, D).permute(0, 2, 1, 3), k.float().view(Bn, S, H, D).permute(0, 2, 1, 3)
+    want = qh @ kh.transpose(-1, -2) / 8.0 + mask
+    Q = q.to(DEV).view(Bn, S, H, D).permute(0, 2, 1, 3)
+    K = k.to(DEV).view(Bn, S, H, D).permute(0, 2, 3, 1)
+    out = torch.full((Bn, H, S, S), float("nan"), device=DEV)
+    G.gemm(Q, K, out, res=mask.to(DEV).expand(Bn, H, S, S), alpha=0.125, prec="bf16")
+    assert max_rel_err(out, want) < 1e-4
+    _healthy()
+
+
+def test_bf16_shared_weights_across_batch():
+    # B operand broadcast over the batch dims (stride 0)
+    a, w = _rand(3, 2, 200, 128, dtype=torch.bfloat16), _rand(96, 128, dtype=torch.bfloat16, seed=1)
+    want = a.float() @ w.float().t()
+    out = torch.full((3, 2, 200, 96), float("nan"), device=DEV)
+    G.gemm(a.to(DEV), w.to(DEV).t()[None, None].expand(3, 2, 128, 96), out, prec="bf16")
+    assert max_rel_err(out, want) < 1e-4
+    _healthy()
+
+
+CONV_TC = [
+    # n, c, h, w, f, k, stride, pad, dil   (ResNet layer shapes at a small batch, plus ragged ones)
+    (4, 64, 56, 56, 64, 3, 1, 1, 1), (4, 64, 56, 56, 256, 1, 1, 0, 1), (4, 128, 28, 28, 256, 1, 2, 0, 1),
+    (4, 256, 14, 14, 256, 3, 1, 1, 1), (2, 512, 7, 7, 512, 3, 1, 1, 1), (3, 64, 15, 13, 128, 3, 2, 1, 1),
+    (1, 8, 9, 17, 24, 3, 1, 2, 2), (2, 16, 30, 30, 40, 5, 1, 2, 1), (2, 64, 112, 112, 64, 7, 2, 3, 1),
+]
+
+
+def _conv_case(case, dtype, prec, tol):
+    n, c, h, w, f, k, s, p, d = case
+    x, wt = _rand(n, c, h, w, dtype=dtype), (_rand(f, c, k, k, seed=1) * 0.1).to(dtype)
+    scale, shift = _rand(f, seed=2).abs() + 0.5, _rand(f, seed=3)
+    y = F.conv2d(x.double(), wt.double(), None, s, p, d).float()
+    res = _rand(*y.shape, dtype=dtype, seed=4)
+    want = torch.relu(y * scale.view(1, -1, 1, 1) + shift.view(1, -1, 1, 1) + res.float())
+    X = x.to(DEV).permute(0, 2, 3, 1).contiguous()
+    W = wt.to(DEV).permute(0, 2, 3, 1).contiguous()
+    R = res.to(DEV).permute(0, 2, 3, 1).contiguous()
+    out = torch.full((n, y.shape[2], y.shape[3], f), float("nan"), device=DEV, dtype=torch.float32)
+    G.conv2d(X, W, out, (s, s), (p, p), (d, d), scale=scale.to(DEV), shift=shift.to(DEV), res=R, act="relu", prec=prec)
+    assert max_rel_err(out.permute(0, 3, 1, 2), want) < tol
+    _healthy()
+
+
+@pytest.mark.parametrize("case", CONV_TC)
+def test_conv_bf16_tensor_cores(case):
+    _conv_case(case, torch.bfloat16, "bf16", 1e-4)       # fp32 output: exact products, fp32 accumulation
+
+
+@pytest.mark.parametrize("prec,tol", [("tf32x3", 5e-5), ("tf32", 2e-3)])
+@pytest.mark.parametrize("case", CONV_TC)
+def test_conv_fp32_on_tensor_cores(case, prec, tol):
+    _conv_case(case, torch.float32, prec, tol)

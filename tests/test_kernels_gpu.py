@@ -214,3 +214,20 @@ def test_argument_errors_are_reported():
     bt = torch.empty(1, 1, 4, 4, device=DEV)[:, :, ::2, ::2]      # neither stride is 1
     with pytest.raises(C.LlcError):
         G.gemm(a[:, :, :2, :2], bt, torch.empty(1, 1, 2, 2, device=DEV))
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 512, 784), (64, 10, 512), (7, 100, 4096), (130, 70, 1000)])
+def test_gemm_fp32_split_k_matches_single_pass(m, n, k):
+    # few output tiles and a long K: the FMA kernel spreads K over idle SMs when given scratch
+    a, w, bias = _rand(m, k), _rand(n, k, seed=1), _rand(n, seed=2)
+    want = torch.relu((a.double() @ w.double().t()).float() + bias)
+    ws = torch.zeros(16 << 20, dtype=torch.uint8, device=DEV)
+    A, B = a.to(DEV)[None, None], w.to(DEV).t()[None, None]
+    for _ in range(2):                                   # twice: the tile counters must be back at zero
+        out = torch.full((1, 1, m, n), float("nan"), device=DEV)
+        G.gemm(A, B, out, shift=bias.to(DEV), act="relu", workspace=ws)
+        assert max_rel_err(out[0, 0], want) < 1e-5
+    assert int(ws[:4096].sum().item()) == 0
+    ref = torch.empty(1, 1, m, n, device=DEV)
+    G.gemm(A, B, ref, shift=bias.to(DEV), act="relu")
+    assert max_rel_err(out[0, 0], ref[0, 0].cpu()) < 1e-5

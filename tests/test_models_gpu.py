@@ -111,3 +111,23 @@ def test_wrong_inputs_raise():
     with pytest.raises(RuntimeError):
         eng.run(4, torch.randn(4, 784, dtype=torch.float64).cuda())
     assert max_rel_err(eng.run(4, x.cuda())[0], m(x)) < 1e-4   # the handle stays usable
+
+
+def test_resnet18_fp32_on_tensor_cores_tf32x3():
+    # three-pass TF32 keeps the fp32 configuration inside its 1e-4 tolerance on tensor cores
+    m = build_model("resnet18")
+    x = CONFIGS["resnet18"].make_inputs(batch=8)[0]
+    with torch.no_grad():
+        want = m(x)
+    comp, fn, out = _gpu_run(m, (x,), precision="tf32x3")
+    assert max_rel_err(out, want) < 1e-4
+
+
+@pytest.mark.parametrize("seq", [128, 512])
+def test_encoder_layer_tf32(seq):
+    m = build_model("encoder")
+    x = CONFIGS["encoder"].make_inputs(batch=8, seq=seq)[0]
+    with torch.no_grad():
+        want = m(x)
+    comp, fn, out = _gpu_run(m, (x,), dynamic=True, precision="tf32")
+    assert max_rel_err(out, want) < 2e-2                  # the tolerance stated for TF32 paths
