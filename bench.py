@@ -167,6 +167,7 @@ def main():
     ap.add_argument("--config", default="resnet18", choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--precision", default=None)
+    ap.add_argument("--steps-out", default=None, help="write the per-plan-step CUDA-event table here")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -253,6 +254,12 @@ def main():
 
     # dominant kernel: event-timed per kernel family over a profiled pass (events around every launch)
     prof = eng.profile(*dev_inputs, reps=5)
+    if args.steps_out and rank == 0:
+        with open(args.steps_out, "w") as f:
+            f.write("# step kernel ms GFLOP MB  TFLOP/s GB/s\n")
+            for r in eng.last_profile_steps:
+                f.write(f"{r['index']:4d} {r['kernel']:10s} {r['ms']:9.4f} {r['flops'] / 1e9:10.3f} {r['bytes'] / 1e6:10.2f} "
+                        f"{r['flops'] / max(r['ms'], 1e-9) / 1e9:9.1f} {r['bytes'] / max(r['ms'], 1e-9) / 1e6:9.1f}\n")
     roof = None
     pk = peaks()
     if prof:

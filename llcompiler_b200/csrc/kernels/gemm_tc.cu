@@ -16,7 +16,7 @@
 //               quarter and one column half), alpha*scale[n]*acc + shift[n] + res, activation,
 //               16-byte stores; releases the accumulator as soon as it is in registers so that the
 //               next tile's MMAs overlap the stores.
-//   next 4      convolution only: im2col gather of the A tile (NHWC activations) with 16-byte
+//   next 8      convolution only: im2col gather of the A tile (NHWC activations) with 16-byte
 //               cp.async into the swizzled layout, zero-filling padding taps.
 //   next 4      tf32x3 only: split each landed fp32 tile into its low-order part x - tf32(x)
 //               (same swizzled position in a second buffer) and hand the stage to the issuer.
@@ -66,9 +66,9 @@ __device__ __forceinline__ void cpAsync16(uint32_t dst, const void* src, bool va
 __device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cpAsyncWait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
 
-// KIND: 0 bf16, 1 tf32, 2 tf32x3
-template <int BN, int KIND, bool CONV>
-__global__ void __launch_bounds__((10 + (CONV ? 4 : 0) + (KIND == 2 ? 4 : 0)) * 32, 1)
+// KIND: 0 bf16, 1 tf32, 2 tf32x3.  BMN: B is stored [k][n] (unit stride along n) instead of [n][k].
+template <int BN, int KIND, bool CONV, bool BMN>
+__global__ void __launch_bounds__((10 + (CONV ? 8 : 0) + (KIND == 2 ? 4 : 0)) * 32, 1)
 tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcArgs p) {
   constexpr bool X3 = KIND == 2;
   constexpr bool TF32 = KIND != 0;
@@ -77,11 +77,20 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
   constexpr int kElemBytes = TF32 ? 4 : 2;
   constexpr int BK = kTileKBytes / kElemBytes;          // 64 bf16 / 32 tf32
   constexpr int UMMA_K = 32 / kElemBytes;               // 16 bf16 / 8 tf32 (32 bytes of K per instruction)
-  constexpr uint32_t kIdesc = instrDesc(TF32 ? 2 : 1, BM, BN, 0, 0);
-  constexpr int kAccCols = BN == 256 ? 512 : 2 * BN;    // two accumulators
+  constexpr uint32_t kIdesc = instrDesc(TF32 ? 2 : 1, BM, BN, 0, BMN ? 1 : 0);
+  // Two accumulator sets (double buffering).  tf32x3 splits the K loop over kChains independent
+  // accumulators per set and adds them in the epilogue: the tensor core truncates when it adds into
+  // its fp32 accumulator, so shorter chains mean a smaller (K-proportional) rounding bias.
+  constexpr int kChains = X3 ? 256 / BN : 1;
+  constexpr int kSetCols = X3 ? 256 : BN;
+  constexpr int kAccCols = 2 * kSetCols;
+  static_assert(!X3 || BN <= 128, "tf32x3 uses BN <= 128");
+  constexpr int kAtomN = kTileKBytes / kElemBytes;      // BMN: elements of n per 128-byte slab row
+  constexpr int kSlabBytes = BK * 128;                  // BMN: one slab = BK rows of k x 128 bytes of n
   constexpr int kEpiWarps = 8;
-  constexpr int kGatherWarp0 = 2 + kEpiWarps, kSplitWarp0 = kGatherWarp0 + (CONV ? 4 : 0);
-  constexpr int kFullCount = CONV ? 129 : 1;            // 128 gather threads + the TMA arm
+  constexpr int kGatherWarps = 8;
+  constexpr int kGatherWarp0 = 2 + kEpiWarps, kSplitWarp0 = kGatherWarp0 + (CONV ? kGatherWarps : 0);
+  constexpr int kFullCount = CONV ? kGatherWarps * 32 + 1 : 1;   // gather threads + the TMA arm
 
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
@@ -93,12 +102,14 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
   uint64_t* accFull = bars + 3 * kStages;   // [2] accumulator complete
   uint64_t* accEmpty = bars + 3 * kStages + 2;  // [2] accumulator drained by the epilogue
   uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 4);
+  volatile int* abortWord = reinterpret_cast<volatile int*>(tmemSlot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbarInit(&full[s], kFullCount); mbarInit(&empty[s], 1); mbarInit(&split[s], 128); }
     for (int a = 0; a < 2; ++a) { mbarInit(&accFull[a], 1); mbarInit(&accEmpty[a], kEpiWarps); }
+    *abortWord = 0;
     fenceBarrierInit();
   }
   if (warp == 1) tmemAlloc(tmemSlot, kAccCols);
@@ -126,10 +137,16 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         const int zb0 = z / p.b1, zb1 = z - zb0 * p.b1;
         for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
-          if (!mbarWait(&empty[s], ph ^ 1)) { atomicExch(&g_tcStatus, 1); ok = false; break; }
+          if (!mbarWait(&empty[s], ph ^ 1, abortWord)) { atomicExch(&g_tcStatus, 1); ok = false; break; }
           mbarExpectTx(&full[s], CONV ? S::kBBytes : S::kABytes + S::kBBytes);
           if (!CONV) tmaLoad4d(stageA(s), &mapA, &full[s], kb * BK, tileM * BM, zb1 * p.aZ1, zb0 * p.aZ0);
-          tmaLoad4d(stageB(s), &mapB, &full[s], kb * BK, tileN * BN, zb1 * p.bZ1, zb0 * p.bZ0);
+          if (BMN) {
+#pragma unroll
+            for (int a = 0; a < BN / kAtomN; ++a)
+              tmaLoad4d(stageB(s) + a * kSlabBytes, &mapB, &full[s], tileN * BN + a * kAtomN, kb * BK, zb1 * p.bZ1, zb0 * p.bZ0);
+          } else {
+            tmaLoad4d(stageB(s), &mapB, &full[s], kb * BK, tileN * BN, zb1 * p.bZ1, zb0 * p.bZ0);
+          }
         }
       }
     }
@@ -140,26 +157,29 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       bool ok = true;
       for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++tcount) {
         const int ab = tcount & 1; const uint32_t aph = (tcount >> 1) & 1;
-        if (!mbarWait(&accEmpty[ab], aph ^ 1)) { atomicExch(&g_tcStatus, 2); ok = false; break; }
+        if (!mbarWait(&accEmpty[ab], aph ^ 1, abortWord)) { atomicExch(&g_tcStatus, 2); ok = false; break; }
         tcFenceAfter();
-        const uint32_t acc = tmemBase + (uint32_t)(ab * (kAccCols / 2));
+        const uint32_t accSet = tmemBase + (uint32_t)(ab * kSetCols);
         for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
-          if (!mbarWait(X3 ? &split[s] : &full[s], ph)) { atomicExch(&g_tcStatus, 2); ok = false; break; }
+          if (!mbarWait(X3 ? &split[s] : &full[s], ph, abortWord)) { atomicExch(&g_tcStatus, 2); ok = false; break; }
           tcFenceAfter();
-          const uint64_t dA = smemDescKMajorSw128(smemAddr(stageA(s))), dB = smemDescKMajorSw128(smemAddr(stageB(s)));
+          const uint32_t acc = accSet + (uint32_t)((kb % kChains) * BN);
+          const bool fresh = kb < kChains;                 // first K block of this chain: overwrite
+          const uint64_t dA = smemDescKMajorSw128(smemAddr(stageA(s)));
+          const uint64_t dB = BMN ? smemDescMnMajorSw128(smemAddr(stageB(s)), kSlabBytes) : smemDescKMajorSw128(smemAddr(stageB(s)));
+          constexpr uint64_t kAdvA = (UMMA_K * kElemBytes) >> 4;                      // 32 bytes of K inside the swizzle atom
+          constexpr uint64_t kAdvB = BMN ? (uint64_t)(UMMA_K * 128) >> 4 : kAdvA;     // BMN: UMMA_K rows of 128 bytes
 #pragma unroll
-          for (int k = 0; k < BK / UMMA_K; ++k) {
-            const uint64_t adv = (uint64_t)((k * UMMA_K * kElemBytes) >> 4);   // 32 bytes of K per step inside the swizzle atom
-            mmaSS<TF32>(acc, dA + adv, dB + adv, kIdesc, (kb > 0 || k > 0) ? 1u : 0u);
-          }
+          for (int k = 0; k < BK / UMMA_K; ++k)
+            mmaSS<TF32>(acc, dA + k * kAdvA, dB + k * kAdvB, kIdesc, (!fresh || k > 0) ? 1u : 0u);
           if (X3) {
-            const uint64_t dAl = smemDescKMajorSw128(smemAddr(stageALo(s))), dBl = smemDescKMajorSw128(smemAddr(stageBLo(s)));
+            const uint64_t dAl = smemDescKMajorSw128(smemAddr(stageALo(s)));
+            const uint64_t dBl = BMN ? smemDescMnMajorSw128(smemAddr(stageBLo(s)), kSlabBytes) : smemDescKMajorSw128(smemAddr(stageBLo(s)));
 #pragma unroll
             for (int k = 0; k < BK / UMMA_K; ++k) {
-              const uint64_t adv = (uint64_t)((k * UMMA_K * kElemBytes) >> 4);
-              mmaSS<TF32>(acc, dAl + adv, dB + adv, kIdesc, 1u);
-              mmaSS<TF32>(acc, dA + adv, dBl + adv, kIdesc, 1u);
+              mmaSS<TF32>(acc, dAl + k * kAdvA, dB + k * kAdvB, kIdesc, 1u);
+              mmaSS<TF32>(acc, dA + k * kAdvA, dBl + k * kAdvB, kIdesc, 1u);
             }
           }
           mmaCommit(&empty[s]);
@@ -180,9 +200,10 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       const int tileM = rem / p.nTiles, tileN = rem - tileM * p.nTiles;
       const int zb0 = z / p.b1, zb1 = z - zb0 * p.b1;
       const int ab = tcount & 1; const uint32_t aph = (tcount >> 1) & 1;
-      if (!mbarWait(&accFull[ab], aph)) atomicExch(&g_tcStatus, 4);
+      if (!mbarWait(&accFull[ab], aph, abortWord)) { atomicExch(&g_tcStatus, 4); break; }
       tcFenceAfter();
-      const uint32_t acc = tmemBase + (uint32_t)(ab * (kAccCols / 2)) + ((uint32_t)(q * 32) << 16);
+      const uint32_t acc = tmemBase + (uint32_t)(ab * kSetCols) + ((uint32_t)(q * 32) << 16);
+      const int usedChains = p.kBlocks < kChains ? p.kBlocks : kChains;
       const long long gm = (long long)tileM * BM + q * 32 + lane;
       const bool rowOk = gm < p.M;
       const long long oRow = zb0 * p.o_s0 + zb1 * p.o_s1 + gm * p.o_sm;
@@ -192,6 +213,14 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         float v[32];
         __syncwarp();                                   // the load is warp-collective
         tmemLoad32x32(acc + (uint32_t)c0, v);
+        if (kChains > 1) {
+          for (int ch = 1; ch < usedChains; ++ch) {
+            float w[32];
+            tmemLoad32x32(acc + (uint32_t)(ch * BN + c0), w);
+#pragma unroll
+            for (int j = 0; j < 32; ++j) v[j] += w[j];
+          }
+        }
         if (c0 + 32 >= (half + 1) * kColsPerWarp) {     // this warp's share is in registers: hand the accumulator back
           tcFenceBefore();
           __syncwarp();
@@ -274,42 +303,51 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         }
       }
     }
-  } else if (CONV && warp < kGatherWarp0 + 4) {
+  } else if (CONV && warp < kGatherWarp0 + kGatherWarps) {
     // ---------------------------------------------------------------- im2col gather of A (convolution)
-    // Thread r owns tile row r.  A 16-byte chunk never straddles a filter tap (C * element size is a
-    // multiple of 16), so each chunk is one contiguous load from x[n, ih, iw, c..] or zeros.
+    // 256 threads; thread g owns 16-byte chunk (g & 7) of tile rows (g >> 3) + 32*j, j = 0..3, so that
+    // eight neighbouring lanes fetch one row's 128 contiguous bytes.  A chunk never straddles a filter
+    // tap (C * element size is a multiple of 16), so it is one load from x[n, ih, iw, c..] or zeros.
+    // The tap of a chunk depends only on the K block, not on the row: it is tracked incrementally.
     constexpr int kChunkElems = 16 / kElemBytes;
-    constexpr int kLag = kStages - 1 < 3 ? kStages - 1 : 3;   // stages in flight per thread before it signals
-    const int r = threadIdx.x - kGatherWarp0 * 32;
+    constexpr int kLag = kStages - 1 < 4 ? kStages - 1 : 4;   // stages in flight per thread before it signals
+    const int g = threadIdx.x - kGatherWarp0 * 32;
+    const int chunk = g & 7, row0 = g >> 3;
     const char* X = reinterpret_cast<const char*>(p.x);
+    const uint32_t dstOff = (uint32_t)(row0 * 128 + ((chunk ^ (row0 & 7)) << 4));   // (row0 + 32 j) & 7 == row0 & 7
     uint32_t it = 0, signalled = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
       const int rem = (int)(t % tilesPerBatch);
       const int tileM = rem / p.nTiles;
-      const long long gm = (long long)tileM * BM + r;
-      const bool rowOk = gm < p.M;
-      const long long mm = rowOk ? gm : 0;
-      const int ow = (int)(mm % p.OW); const long long t2 = mm / p.OW; const int oh = (int)(t2 % p.OH); const long long img = t2 / p.OH;
-      const int ih0 = oh * p.sh - p.ph, iw0 = ow * p.sw - p.pw;
-      const long long imgBase = img * p.H * p.W * p.C;
-      int tapR = 0, tapS = 0, cc = 0;                   // filter tap and channel of the next chunk
-      long long kk = 0;
+      long long rowBase[4]; int ih0[4], iw0[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const long long gm = (long long)tileM * BM + row0 + 32 * j;
+        if (gm < p.M) {
+          const int ow = (int)(gm % p.OW); const long long t2 = gm / p.OW; const int oh = (int)(t2 % p.OH); const long long img = t2 / p.OH;
+          ih0[j] = oh * p.sh - p.ph; iw0[j] = ow * p.sw - p.pw;
+          rowBase[j] = ((img * p.H + ih0[j]) * p.W + iw0[j]) * p.C;
+        } else { ih0[j] = -(1 << 28); iw0[j] = 0; rowBase[j] = 0; }   // never in range: the row is zero-filled
+      }
+      int tapR = 0, tapS = 0, cc = chunk * kChunkElems;       // filter tap and channel of this thread's chunk
+      while (cc >= p.C) { cc -= p.C; if (++tapS == p.KW) { tapS = 0; ++tapR; } }
       for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
         const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
-        if (!mbarWait(&empty[s], ph ^ 1)) { atomicExch(&g_tcStatus, 5); ok = false; break; }
-        const uint32_t rowAddr = smemAddr(stageA(s)) + r * 128;
+        if (!mbarWait(&empty[s], ph ^ 1, abortWord)) { atomicExch(&g_tcStatus, 5); ok = false; break; }
+        const int dIh = tapR * p.dh, dIw = tapS * p.dw;
+        const long long tapOff = ((long long)dIh * p.W + dIw) * p.C + cc;
+        const bool tapOk = tapR < p.KH;                        // past the last tap: K tail, zero-filled
+        const uint32_t dst = smemAddr(stageA(s)) + dstOff;
 #pragma unroll
-        for (int c = 0; c < 8; ++c) {
-          const int ih = ih0 + tapR * p.dh, iw = iw0 + tapS * p.dw;
-          const bool valid = rowOk && kk < p.K && ih >= 0 && ih < p.H && iw >= 0 && iw < p.W;
-          const long long off = valid ? (imgBase + ((long long)ih * p.W + iw) * p.C + cc) * kElemBytes : 0;
-          cpAsync16(rowAddr + ((c ^ (r & 7)) << 4), X + off, valid);
-          kk += kChunkElems; cc += kChunkElems;
-          if (cc >= p.C) { cc = 0; if (++tapS == p.KW) { tapS = 0; ++tapR; } }
+        for (int j = 0; j < 4; ++j) {
+          const bool valid = tapOk && (unsigned)(ih0[j] + dIh) < (unsigned)p.H && (unsigned)(iw0[j] + dIw) < (unsigned)p.W;
+          cpAsync16(dst + j * 32 * 128, X + (valid ? (rowBase[j] + tapOff) * kElemBytes : 0), valid);
         }
         cpAsyncCommit();
-        if (it - signalled >= (uint32_t)kLag) {          // the oldest outstanding stage has landed
+        cc += BK;                                              // next K block: 128 bytes further along K
+        while (cc >= p.C) { cc -= p.C; if (++tapS == p.KW) { tapS = 0; ++tapR; } }
+        if (it - signalled >= (uint32_t)kLag) {                // the oldest outstanding stage has landed
           cpAsyncWait<kLag>();
           fenceProxyAsync();
           mbarArrive(&full[signalled % kStages]);
@@ -325,10 +363,11 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     // elementwise, so every 16-byte chunk keeps its swizzled position
     const int et = threadIdx.x - kSplitWarp0 * 32;
     uint32_t it = 0;
-    for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x) {
+    bool ok = true;
+    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
       for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
         const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
-        if (!mbarWait(&full[s], ph)) atomicExch(&g_tcStatus, 3);
+        if (!mbarWait(&full[s], ph, abortWord)) { atomicExch(&g_tcStatus, 3); ok = false; break; }
         const float4* srcA = reinterpret_cast<const float4*>(stageA(s)); float4* dstA = reinterpret_cast<float4*>(stageALo(s));
         const float4* srcB = reinterpret_cast<const float4*>(stageB(s)); float4* dstB = reinterpret_cast<float4*>(stageBLo(s));
         auto lo = [](float x) { return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); };
@@ -378,42 +417,60 @@ bool makeMap(CUtensorMap* map, const void* base, bool f32, long long K, long lon
   return r == CUDA_SUCCESS;
 }
 
+// MN-major operand [b0, b1, K, N] with unit stride along N -> 4-D tensor map, box = 128 bytes of N x boxK rows of K.
+bool makeMapMn(CUtensorMap* map, const void* base, bool f32, long long N, long long K, long long b1, long long b0, long long sK, long long s1,
+               long long s0, int boxK) {
+  EncodeTiledFn enc = encodeTiled();
+  if (!enc) return false;
+  const int eb = f32 ? 4 : 2;
+  const bool has1 = b1 > 1 && s1 > 0, has0 = b0 > 1 && s0 > 0;
+  const long long dense = sK * K;
+  cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)K, (cuuint64_t)(has1 ? b1 : 1), (cuuint64_t)(has0 ? b0 : 1)};
+  cuuint64_t strides[3] = {(cuuint64_t)(sK * eb), (cuuint64_t)((has1 ? s1 : dense) * eb), (cuuint64_t)((has0 ? s0 : dense) * eb)};
+  cuuint32_t box[4] = {(cuuint32_t)(kTileKBytes / eb), (cuuint32_t)boxK, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 int numSMs() {
   static int n = []() { int dev = 0, v = kNumSMs; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev); return v > 0 ? v : kNumSMs; }();
   return n;
 }
 
-template <int BN, int KIND, bool CONV>
+template <int BN, int KIND, bool CONV, bool BMN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, TcArgs a, long long batch, cudaStream_t st) {
   using S = Smem<BN, KIND == 2>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(tc_kernel<BN, KIND, CONV>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(tc_kernel<BN, KIND, CONV, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return cudaFail(e, "cudaFuncSetAttribute(tc_kernel)");
     configured = true;
   }
   a.mTiles = (int)((a.M + BM - 1) / BM); a.nTiles = (int)((a.N + BN - 1) / BN);
   a.tiles = (long long)a.mTiles * a.nTiles * batch;
-  const int threads = (10 + (CONV ? 4 : 0) + (KIND == 2 ? 4 : 0)) * 32;
+  const int threads = (10 + (CONV ? 8 : 0) + (KIND == 2 ? 4 : 0)) * 32;
   const unsigned grid = (unsigned)(a.tiles < numSMs() ? a.tiles : numSMs());
-  tc_kernel<BN, KIND, CONV><<<grid, threads, S::kTotal, st>>>(ma, mb, a);
+  tc_kernel<BN, KIND, CONV, BMN><<<grid, threads, S::kTotal, st>>>(ma, mb, a);
   LLC_LAUNCH_CHECK("tc_kernel");
   return LLC_OK;
 }
 
-template <bool CONV>
+template <bool CONV, bool BMN>
 int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, long long batch, cudaStream_t st) {
-#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, CONV>(ma, mb, a, batch, st);
-  TC_CASE(64, 0) TC_CASE(64, 1) TC_CASE(64, 2) TC_CASE(128, 0) TC_CASE(128, 1) TC_CASE(128, 2) TC_CASE(256, 0) TC_CASE(256, 1) TC_CASE(256, 2)
+#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, CONV, BMN>(ma, mb, a, batch, st);
+  TC_CASE(64, 0) TC_CASE(128, 0)
+  if constexpr (!BMN) { TC_CASE(64, 1) TC_CASE(64, 2) TC_CASE(128, 1) TC_CASE(128, 2) TC_CASE(256, 0) TC_CASE(256, 1) }
 #undef TC_CASE
   return setError(LLC_ERR_INTERNAL, "llc internal: no tensor-core kernel for this tile");
 }
 
 // Tile width: the widest tile that still gives every SM work.
-int chooseBN(long long M, long long N, long long batch) {
+int chooseBN(long long M, long long N, long long batch, bool allow256) {
   const long long mT = (M + BM - 1) / BM;
   auto tiles = [&](long long bn) { return mT * ((N + bn - 1) / bn) * batch; };
-  if (N > 128 && tiles(256) >= numSMs()) return 256;
+  if (allow256 && N > 128 && tiles(256) >= numSMs()) return 256;
   if (N > 64 && tiles(128) >= numSMs()) return 128;
   if (N > 64 && tiles(64) < numSMs() / 2) return 128;   // tiny grids: fewer, larger tiles cost less fixed work
   return 64;
@@ -426,11 +483,13 @@ bool tcGemmSupported(const LlcGemmParams* p) {
   const bool f32 = p->in_dtype == LLC_FLOAT32;
   if (!f32 && p->in_dtype != LLC_BFLOAT16) return false;
   if (f32 && p->precision != LLC_PREC_TF32 && p->precision != LLC_PREC_TF32X3) return false;
-  if (p->b_sk != 1) return false;                       // B must be stored [n][k]
+  const bool bmn = p->b_sk != 1;                        // B stored [k][n]
+  if (bmn && p->b_sn != 1) return false;
+  if (bmn && f32) return false;                         // 32-bit operands are taken K-major only (an MN-major tf32 B produced zeros on B200)
   const int eb = f32 ? 4 : 2;
   auto ok16 = [&](long long s) { return (s * eb) % 16 == 0; };
-  if (!ok16(p->a_sm) || !ok16(p->a_s0) || !ok16(p->a_s1) || !ok16(p->b_sn) || !ok16(p->b_s0) || !ok16(p->b_s1)) return false;
-  if (p->a_sm < p->k || p->b_sn < p->k) return false;   // overlapping rows are not expressible as a tensor map
+  if (!ok16(p->a_sm) || !ok16(p->a_s0) || !ok16(p->a_s1) || !ok16(bmn ? p->b_sk : p->b_sn) || !ok16(p->b_s0) || !ok16(p->b_s1)) return false;
+  if (p->a_sm < p->k || (bmn ? p->b_sk < p->n : p->b_sn < p->k)) return false;   // overlapping rows are not expressible as a tensor map
   if (p->a_s0 < 0 || p->a_s1 < 0 || p->b_s0 < 0 || p->b_s1 < 0) return false;
   if ((reinterpret_cast<uintptr_t>(p->a) | reinterpret_cast<uintptr_t>(p->b)) & 15) return false;
   if (p->m < 1 || p->n < 1 || p->k < 1) return false;
@@ -444,11 +503,14 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   const int eb = f32 ? 4 : 2;
   const int bk = kTileKBytes / eb;
   const long long batch = p->b0 * p->b1;
-  const int bn = chooseBN(p->m, p->n, batch);
+  const bool bmn = p->b_sk != 1;
+  const int kind = !f32 ? 0 : (p->precision == LLC_PREC_TF32X3 ? 2 : 1);
+  const int bn = chooseBN(p->m, p->n, batch, kind != 2 && !bmn);
   CUtensorMap ma, mb;
-  if (!makeMap(&ma, p->a, f32, p->k, p->m, p->b1, p->b0, p->a_sm, p->a_s1, p->a_s0, BM) ||
-      !makeMap(&mb, p->b, f32, p->k, p->n, p->b1, p->b0, p->b_sn, p->b_s1, p->b_s0, bn))
-    return setError(LLC_ERR_CUDA, "llc cuda: cuTensorMapEncodeTiled rejected the GEMM operands");
+  bool okMaps = makeMap(&ma, p->a, f32, p->k, p->m, p->b1, p->b0, p->a_sm, p->a_s1, p->a_s0, BM);
+  okMaps = okMaps && (bmn ? makeMapMn(&mb, p->b, f32, p->n, p->k, p->b1, p->b0, p->b_sk, p->b_s1, p->b_s0, bk)
+                          : makeMap(&mb, p->b, f32, p->k, p->n, p->b1, p->b0, p->b_sn, p->b_s1, p->b_s0, bn));
+  if (!okMaps) return setError(LLC_ERR_CUDA, "llc cuda: cuTensorMapEncodeTiled rejected the GEMM operands");
   TcArgs a{};
   a.out = p->out; a.scale = p->scale; a.shift = p->shift; a.res = p->res;
   a.out_dtype = p->out_dtype; a.res_dtype = p->res_dtype; a.act = p->act; a.alpha = p->alpha;
@@ -459,8 +521,7 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   const int ob = p->out_dtype == LLC_FLOAT32 ? 4 : 2;
   a.vecOut = (reinterpret_cast<uintptr_t>(p->out) % (ob * 4)) == 0 && p->o_sm % 4 == 0 && p->o_s0 % 4 == 0 && p->o_s1 % 4 == 0 &&
              ((reinterpret_cast<uintptr_t>(p->scale) | reinterpret_cast<uintptr_t>(p->shift)) & 15) == 0;
-  const int kind = !f32 ? 0 : (p->precision == LLC_PREC_TF32X3 ? 2 : 1);
-  return dispatch<false>(bn, kind, ma, mb, a, batch, st);
+  return bmn ? dispatch<false, true>(bn, kind, ma, mb, a, batch, st) : dispatch<false, false>(bn, kind, ma, mb, a, batch, st);
 }
 
 bool tcConvSupported(const LlcConvParams* p) {
@@ -480,7 +541,8 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
   const int eb = f32 ? 4 : 2;
   const int bk = kTileKBytes / eb;
   const long long M = p->n * p->oh * p->ow, K = p->kh * p->kw * p->c;
-  const int bn = chooseBN(M, p->f, 1);
+  const int kind = !f32 ? 0 : (p->precision == LLC_PREC_TF32X3 ? 2 : 1);
+  const int bn = chooseBN(M, p->f, 1, kind != 2);
   CUtensorMap mb;
   if (!makeMap(&mb, p->w, f32, K, p->f, 1, 1, K, 0, 0, bn))
     return setError(LLC_ERR_CUDA, "llc cuda: cuTensorMapEncodeTiled rejected the convolution weights");
@@ -494,8 +556,7 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
              ((reinterpret_cast<uintptr_t>(p->scale) | reinterpret_cast<uintptr_t>(p->shift)) & 15) == 0;
   a.x = p->x; a.H = (int)p->h; a.W = (int)p->w_in; a.C = (int)p->c; a.KH = (int)p->kh; a.KW = (int)p->kw; a.OH = (int)p->oh; a.OW = (int)p->ow;
   a.sh = p->stride_h; a.sw = p->stride_w; a.ph = p->pad_h; a.pw = p->pad_w; a.dh = p->dil_h; a.dw = p->dil_w;
-  const int kind = !f32 ? 0 : (p->precision == LLC_PREC_TF32X3 ? 2 : 1);
-  return dispatch<true>(bn, kind, mb, mb, a, 1, st);
+  return dispatch<true, false>(bn, kind, mb, mb, a, 1, st);
 }
 
 // Reads and clears the status word the bounded waits write (0 = no wait ever gave up).

@@ -344,3 +344,4 @@ int igemmSimtConv(const LlcConvParams* p, cudaStream_t st) {
 }
 
 }  // namespace llc
+

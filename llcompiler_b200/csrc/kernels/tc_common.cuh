@@ -12,7 +12,7 @@
 namespace llc {
 namespace tc {
 
-constexpr uint32_t kSpinLimit = 1u << 22;
+constexpr uint32_t kSpinLimit = 1u << 21;
 
 __device__ __forceinline__ uint32_t smemAddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 
@@ -26,8 +26,10 @@ __device__ __forceinline__ void mbarExpectTx(uint64_t* bar, uint32_t bytes) {
 __device__ __forceinline__ void mbarArrive(uint64_t* bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smemAddr(bar)) : "memory");
 }
-// Returns false when the wait gave up.
-__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity) {
+// Returns false when the wait gave up.  `abortWord` is a CTA-wide flag in shared memory: the first
+// wait that gives up sets it, and every other wait of the CTA then returns at its next check, so a
+// CTA whose pipeline broke drains in milliseconds instead of timing out once per remaining tile.
+__device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity, volatile int* abortWord) {
   uint32_t addr = smemAddr(bar);
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
     uint32_t ok;
@@ -37,7 +39,9 @@ __device__ __forceinline__ bool mbarWait(uint64_t* bar, uint32_t parity) {
         "selp.u32 %0, 1, 0, p;\n\t}"
         : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
     if (ok) return true;
+    if ((i & 255) == 255 && *abortWord) return false;
   }
+  *abortWord = 1;
   return false;
 }
 

@@ -87,17 +87,30 @@ std::vector<char> readNpy(const std::string& path, DType want, size_t numel) {
 
 struct RView { int buf; long long off; int rank; long long shape[6], strides[6]; int dtype; };
 
+// A plan step resolved for one symbol binding: the kernel's parameter block is filled once, only the
+// pointers (which depend on where the caller's tensors and the arena are) are patched per call.
+struct PtrPatch { void** slot; int buf; long long byteOff; };
+enum StepKind { kGemm, kConv, kPool, kReduce, kSoftmax, kLayerNorm, kGather, kEltwise };
 struct RStep {
   const Step* step;
   std::vector<std::pair<std::string, RView>> views;
   const RView* view(const char* n) const { for (auto& v : views) if (v.first == n) return &v.second; return nullptr; }
+  int kind = -1;
+  LlcGemmParams gemm{}; LlcConvParams conv{}; LlcPoolParams pool{}; LlcEltwiseParams elt{};
+  std::string prog;
+  void* sp[4] = {nullptr, nullptr, nullptr, nullptr};   // pointer operands of the row kernels
+  int sdt[3] = {0, 0, 0}; long long sd[3] = {0, 0, 0}; int sop = 0; float seps = 0.f;
+  std::vector<PtrPatch> patches;
+  RStep() {}
+  RStep(const RStep&) = delete;             // patches point into this object
+  RStep& operator=(const RStep&) = delete;
 };
 
 struct Binding {
   std::map<std::string, int64_t> env;
   std::vector<size_t> bufBytes, arenaOffset;   // per buffer
   size_t arenaBytes = 0;
-  std::vector<RStep> steps;
+  std::vector<std::unique_ptr<RStep>> steps;
   std::vector<std::vector<int64_t>> inShapes, outShapes;
 };
 
@@ -146,21 +159,26 @@ struct LlcExec {
   }
   void* ptr(const RView& v) const { return base[v.buf] + v.off * dtypeSize(plan.buffers[v.buf].dtype); }
 
-  int launch(const RStep& rs, cudaStream_t st);
+  void prepare(RStep& rs);
+  int launch(RStep& rs, cudaStream_t st);
   Binding& bind(const int64_t* symbols, int nsym, const LlcTensor* in, int nin);
-  void runSteps(const std::vector<RStep>& steps, cudaStream_t st);
+  void runSteps(std::vector<std::unique_ptr<RStep>>& steps, cudaStream_t st);
 };
 
-// One kernel call of the plan.
-int LlcExec::launch(const RStep& rs, cudaStream_t st) {
+// Fills the parameter block of one plan step (everything except the pointers).
+void LlcExec::prepare(RStep& rs) {
   const Step& s = *rs.step;
   auto need = [&](const char* n) -> const RView& { const RView* v = rs.view(n); if (!v) throw std::runtime_error(std::string("llc internal: step '") + s.kernel + "' lacks operand " + n); return *v; };
   auto actOf = [&]() { std::string a = s.param("act", "none"); return a == "relu" ? LLC_ACT_RELU : a == "gelu" ? LLC_ACT_GELU : LLC_ACT_NONE; };
   auto precOf = [&]() { std::string p = s.param("prec", "fp32"); return p == "tf32" ? LLC_PREC_TF32 : p == "tf32x3" ? LLC_PREC_TF32X3 : p == "bf16" ? LLC_PREC_BF16 : LLC_PREC_FP32; };
+  auto patch = [&](const void* slot, const RView& v) {
+    rs.patches.push_back({reinterpret_cast<void**>(const_cast<void*>(slot)), v.buf, v.off * dtypeSize(plan.buffers[v.buf].dtype)});
+  };
   if (s.kernel == "gemm") {
+    rs.kind = kGemm;
     const RView &a = need("a"), &b = need("b"), &o = need("out");
-    LlcGemmParams p{};
-    p.a = ptr(a); p.b = ptr(b); p.out = ptr(o);
+    LlcGemmParams& p = rs.gemm;
+    patch(&p.a, a); patch(&p.b, b); patch(&p.out, o);
     p.in_dtype = a.dtype; p.out_dtype = o.dtype; p.precision = precOf();
     p.b0 = o.shape[0]; p.b1 = o.shape[1]; p.m = o.shape[2]; p.n = o.shape[3]; p.k = a.shape[3];
     p.a_s0 = a.strides[0]; p.a_s1 = a.strides[1]; p.a_sm = a.strides[2];
@@ -169,79 +187,98 @@ int LlcExec::launch(const RStep& rs, cudaStream_t st) {
     p.o_s0 = o.strides[0]; p.o_s1 = o.strides[1]; p.o_sm = o.strides[2];
     if (a.shape[3] != 1 && a.strides[3] != 1) failArg("gemm A operand must have unit stride along k");
     if (o.strides[3] != 1 && o.shape[3] != 1) failArg("gemm output must have unit stride along n");
-    if (const RView* v = rs.view("scale")) p.scale = (const float*)ptr(*v);
-    if (const RView* v = rs.view("shift")) p.shift = (const float*)ptr(*v);
-    if (const RView* v = rs.view("res")) { p.res = ptr(*v); p.res_dtype = v->dtype; p.r_s0 = v->strides[0]; p.r_s1 = v->strides[1]; p.r_sm = v->strides[2]; p.r_sn = v->strides[3]; }
+    if (const RView* v = rs.view("scale")) patch(&p.scale, *v);
+    if (const RView* v = rs.view("shift")) patch(&p.shift, *v);
+    if (const RView* v = rs.view("res")) { patch(&p.res, *v); p.res_dtype = v->dtype; p.r_s0 = v->strides[0]; p.r_s1 = v->strides[1]; p.r_sm = v->strides[2]; p.r_sn = v->strides[3]; }
     p.alpha = std::stof(s.param("alpha", "1")); p.act = actOf();
     p.workspace = workspace; p.workspace_bytes = (int64_t)kWorkspaceBytes;
-    return llc_cuda_gemm(&p, st);
-  }
-  if (s.kernel == "conv") {
+  } else if (s.kernel == "conv") {
+    rs.kind = kConv;
     const RView &x = need("x"), &w = need("w"), &o = need("out");
-    LlcConvParams p{};
-    p.x = ptr(x); p.w = ptr(w); p.out = ptr(o);
+    LlcConvParams& p = rs.conv;
+    patch(&p.x, x); patch(&p.w, w); patch(&p.out, o);
     p.in_dtype = x.dtype; p.out_dtype = o.dtype; p.precision = precOf();
     p.n = x.shape[0]; p.c = x.shape[1]; p.h = x.shape[2]; p.w_in = x.shape[3];
     p.f = w.shape[0]; p.kh = w.shape[1]; p.kw = w.shape[2]; p.oh = o.shape[2]; p.ow = o.shape[3];
     auto st2 = ints(s.param("stride", "1,1")), pd = ints(s.param("pad", "0,0,0,0")), dl = ints(s.param("dil", "1,1"));
     p.stride_h = (int)st2[0]; p.stride_w = (int)st2[1]; p.pad_h = (int)pd[0]; p.pad_w = (int)pd[1]; p.dil_h = (int)dl[0]; p.dil_w = (int)dl[1];
-    if (const RView* v = rs.view("scale")) p.scale = (const float*)ptr(*v);
-    if (const RView* v = rs.view("shift")) p.shift = (const float*)ptr(*v);
-    if (const RView* v = rs.view("res")) { p.res = ptr(*v); p.res_dtype = v->dtype; }
+    if (const RView* v = rs.view("scale")) patch(&p.scale, *v);
+    if (const RView* v = rs.view("shift")) patch(&p.shift, *v);
+    if (const RView* v = rs.view("res")) { patch(&p.res, *v); p.res_dtype = v->dtype; }
     p.alpha = std::stof(s.param("alpha", "1")); p.act = actOf();
-    return llc_cuda_conv2d(&p, st);
-  }
-  if (s.kernel == "maxpool") {
+  } else if (s.kernel == "maxpool") {
+    rs.kind = kPool;
     const RView &x = need("x"), &o = need("out");
-    LlcPoolParams p{};
-    p.x = ptr(x); p.out = ptr(o); p.in_dtype = x.dtype; p.out_dtype = o.dtype;
+    LlcPoolParams& p = rs.pool;
+    patch(&p.x, x); patch(&p.out, o); p.in_dtype = x.dtype; p.out_dtype = o.dtype;
     p.n = x.shape[0]; p.c = x.shape[1]; p.h = x.shape[2]; p.w = x.shape[3]; p.oh = o.shape[2]; p.ow = o.shape[3];
     auto k = ints(s.param("kernel")), st2 = ints(s.param("stride", "1,1")), pd = ints(s.param("pad", "0,0,0,0")), dl = ints(s.param("dil", "1,1"));
     p.kh = (int)k[0]; p.kw = (int)k[1]; p.stride_h = (int)st2[0]; p.stride_w = (int)st2[1]; p.pad_h = (int)pd[0]; p.pad_w = (int)pd[1]; p.dil_h = (int)dl[0]; p.dil_w = (int)dl[1];
-    return llc_cuda_maxpool2d(&p, st);
-  }
-  if (s.kernel == "reduce") {
+  } else if (s.kernel == "reduce") {
+    rs.kind = kReduce;
     const RView &x = need("x"), &o = need("out");
     std::string op = s.param("op", "sum");
-    int code = op == "max" ? 1 : op == "min" ? 2 : op == "mean" ? 3 : 0;
-    return llc_cuda_reduce(ptr(x), ptr(o), x.dtype, o.dtype, x.shape[0], x.shape[1], x.shape[2], code, st);
-  }
-  if (s.kernel == "softmax") {
+    rs.sop = op == "max" ? 1 : op == "min" ? 2 : op == "mean" ? 3 : 0;
+    patch(&rs.sp[0], x); patch(&rs.sp[1], o);
+    rs.sdt[0] = x.dtype; rs.sdt[1] = o.dtype; rs.sd[0] = x.shape[0]; rs.sd[1] = x.shape[1]; rs.sd[2] = x.shape[2];
+  } else if (s.kernel == "softmax") {
+    rs.kind = kSoftmax;
     const RView &x = need("x"), &o = need("out");
-    return llc_cuda_softmax(ptr(x), ptr(o), x.dtype, o.dtype, x.shape[0], x.shape[1], st);
-  }
-  if (s.kernel == "layernorm") {
+    patch(&rs.sp[0], x); patch(&rs.sp[1], o);
+    rs.sdt[0] = x.dtype; rs.sdt[1] = o.dtype; rs.sd[0] = x.shape[0]; rs.sd[1] = x.shape[1];
+  } else if (s.kernel == "layernorm") {
+    rs.kind = kLayerNorm;
     const RView &x = need("x"), &g = need("gamma"), &b = need("beta"), &o = need("out");
     if (g.dtype != b.dtype) failArg("layernorm scale and bias types differ");
-    return llc_cuda_layernorm(ptr(x), ptr(g), ptr(b), ptr(o), x.dtype, g.dtype, o.dtype, x.shape[0], x.shape[1], std::stof(s.param("eps", "1e-5")), st);
-  }
-  if (s.kernel == "gather") {
+    patch(&rs.sp[0], x); patch(&rs.sp[1], g); patch(&rs.sp[2], b); patch(&rs.sp[3], o);
+    rs.sdt[0] = x.dtype; rs.sdt[1] = g.dtype; rs.sdt[2] = o.dtype; rs.sd[0] = x.shape[0]; rs.sd[1] = x.shape[1];
+    rs.seps = std::stof(s.param("eps", "1e-5"));
+  } else if (s.kernel == "gather") {
+    rs.kind = kGather;
     const RView &t = need("table"), &ids = need("ids"), &o = need("out");
     if (ids.dtype != LLC_INT64) failArg("gather indices must be int64");
-    return llc_cuda_gather(ptr(t), (const int64_t*)ptr(ids), ptr(o), t.dtype, o.dtype, o.shape[0], o.shape[1], t.shape[0], badIds, st);
-  }
-  if (s.kernel == "eltwise") {
+    patch(&rs.sp[0], t); patch(&rs.sp[1], ids); patch(&rs.sp[2], o);
+    rs.sdt[0] = t.dtype; rs.sdt[1] = o.dtype; rs.sd[0] = o.shape[0]; rs.sd[1] = o.shape[1]; rs.sd[2] = t.shape[0];
+  } else if (s.kernel == "eltwise") {
+    rs.kind = kEltwise;
     const RView& o = need("out");
-    LlcEltwiseParams p{};
-    p.out = ptr(o); p.out_dtype = o.dtype; p.rank = o.rank;
+    LlcEltwiseParams& p = rs.elt;
+    patch(&p.out, o); p.out_dtype = o.dtype; p.rank = o.rank;
     for (int d = 0; d < o.rank; ++d) { p.shape[d] = o.shape[d]; p.out_strides[d] = o.strides[d]; }
-    std::string prog = s.param("prog");
-    p.prog = prog.c_str();
+    rs.prog = s.param("prog");
+    p.prog = rs.prog.c_str();
     for (int k = 0; k < 8; ++k) {
       const RView* v = rs.view(("in" + std::to_string(k)).c_str());
       if (!v) break;
-      p.in[k].data = ptr(*v); p.in[k].dtype = v->dtype;
+      patch(&p.in[k].data, *v); p.in[k].dtype = v->dtype;
       for (int d = 0; d < v->rank; ++d) p.in[k].strides[d] = v->strides[d];
       p.n_in = k + 1;
     }
-    return llc_cuda_eltwise(&p, st);
+  } else {
+    throw std::runtime_error("llc internal: unknown kernel '" + s.kernel + "' in plan");
   }
-  throw std::runtime_error("llc internal: unknown kernel '" + s.kernel + "' in plan");
 }
 
-void LlcExec::runSteps(const std::vector<RStep>& steps, cudaStream_t st) {
+// One kernel call of the plan: patch the pointers for this call, launch.
+int LlcExec::launch(RStep& rs, cudaStream_t st) {
+  if (rs.kind < 0) prepare(rs);
+  for (auto& pp : rs.patches) *pp.slot = base[pp.buf] + pp.byteOff;
+  switch (rs.kind) {
+    case kGemm: return llc_cuda_gemm(&rs.gemm, st);
+    case kConv: return llc_cuda_conv2d(&rs.conv, st);
+    case kPool: return llc_cuda_maxpool2d(&rs.pool, st);
+    case kReduce: return llc_cuda_reduce(rs.sp[0], rs.sp[1], rs.sdt[0], rs.sdt[1], rs.sd[0], rs.sd[1], rs.sd[2], rs.sop, st);
+    case kSoftmax: return llc_cuda_softmax(rs.sp[0], rs.sp[1], rs.sdt[0], rs.sdt[1], rs.sd[0], rs.sd[1], st);
+    case kLayerNorm: return llc_cuda_layernorm(rs.sp[0], rs.sp[1], rs.sp[2], rs.sp[3], rs.sdt[0], rs.sdt[1], rs.sdt[2], rs.sd[0], rs.sd[1], rs.seps, st);
+    case kGather: return llc_cuda_gather(rs.sp[0], (const int64_t*)rs.sp[1], rs.sp[2], rs.sdt[0], rs.sdt[1], rs.sd[0], rs.sd[1], rs.sd[2], badIds, st);
+    case kEltwise: return llc_cuda_eltwise(&rs.elt, st);
+  }
+  throw std::runtime_error("llc internal: unprepared plan step");
+}
+
+void LlcExec::runSteps(std::vector<std::unique_ptr<RStep>>& steps, cudaStream_t st) {
   for (auto& rs : steps) {
-    int rc = launch(rs, st);
+    int rc = launch(*rs, st);
     if (rc != LLC_OK) throw std::runtime_error(std::string(llc_last_error()));
     ++lastLaunches;
   }
@@ -282,13 +319,14 @@ Binding& LlcExec::bind(const int64_t* symbols, int nsym, const LlcTensor* in, in
   std::vector<int> firstUse(nb, -1), lastUse(nb, -1);
   for (auto& s : plan.steps) {
     if (s.init) continue;
-    RStep rs; rs.step = &s;
+    std::unique_ptr<RStep> rs(new RStep()); rs->step = &s;
     for (auto& v : s.views) {
-      rs.views.emplace_back(v.first, resolve(v.second, env));
+      rs->views.emplace_back(v.first, resolve(v.second, env));
       int id = v.second.buf, idx = (int)b->steps.size();
       if (firstUse[id] < 0) firstUse[id] = idx;
       lastUse[id] = idx;
     }
+    prepare(*rs);
     b->steps.push_back(std::move(rs));
   }
   // first-fit packing of temporaries by lifetime
@@ -375,11 +413,11 @@ extern "C" int llc_load(const char* path, int device, LlcExec** out) {
       }
     }
     // load-time kernels: weight re-layout, folded batch-norm vectors
-    std::vector<RStep> init;
+    std::vector<std::unique_ptr<RStep>> init;
     for (auto& s : ex->plan.steps) {
       if (!s.init) continue;
-      RStep rs; rs.step = &s;
-      for (auto& v : s.views) rs.views.emplace_back(v.first, ex->resolve(v.second, empty));
+      std::unique_ptr<RStep> rs(new RStep()); rs->step = &s;
+      for (auto& v : s.views) rs->views.emplace_back(v.first, ex->resolve(v.second, empty));
       init.push_back(std::move(rs));
     }
     ex->runSteps(init, 0);
@@ -519,7 +557,7 @@ extern "C" int llc_profile(LlcExec* ex, const int64_t* symbols, int nsym, const 
     for (int r = 0; r < reps + 1; ++r) {   // the first pass is a warm-up
       for (size_t i = 0; i < n; ++i) {
         cudaOk(cudaEventRecord(ev[2 * i], st), "cudaEventRecord");
-        int rc = ex->launch(b.steps[i], st);
+        int rc = ex->launch(*b.steps[i], st);
         if (rc != LLC_OK) throw std::runtime_error(std::string(llc_last_error()));
         cudaOk(cudaEventRecord(ev[2 * i + 1], st), "cudaEventRecord");
       }
@@ -534,10 +572,10 @@ extern "C" int llc_profile(LlcExec* ex, const int64_t* symbols, int nsym, const 
     std::ostringstream o;
     o.precision(9);
     for (size_t i = 0; i < n; ++i) {
-      double f, by; stepWork(b.steps[i], f, by);
-      Agg& a = agg[b.steps[i].step->kernel];
+      double f, by; stepWork(*b.steps[i], f, by);
+      Agg& a = agg[b.steps[i]->step->kernel];
       a.launches += 1; a.ms += ms[i] / reps; a.flops += f; a.bytes += by;
-      o << "step " << i << " " << b.steps[i].step->kernel << " " << ms[i] / reps << " " << f << " " << by << "\n";
+      o << "step " << i << " " << b.steps[i]->step->kernel << " " << ms[i] / reps << " " << f << " " << by << "\n";
     }
     for (auto& kv : agg) o << "kernel " << kv.first << " " << kv.second.launches << " " << kv.second.ms << " " << kv.second.flops << " " << kv.second.bytes << "\n";
     std::string text = o.str();

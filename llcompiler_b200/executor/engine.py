@@ -34,6 +34,7 @@ class ExecutionEngine:
         self.executor = Execution()
         self.executor.load(so_file, self.device)
         self.gen_outs_call = None
+        self._out_meta = {}
 
     def run(self, *args) -> Any:
         raise NotImplementedError
@@ -62,12 +63,17 @@ class Torch_ExecutionEngine(ExecutionEngine):
         if len(args) == 1 and isinstance(args[0], (list, tuple)):
             args = tuple(args[0])
         symbols = [int(a) for a in args if isinstance(a, int) and not isinstance(a, bool)]
-        tensors = [a.detach().contiguous() for a in args if isinstance(a, torch.Tensor)]
+        tensors = [a if a.is_contiguous() else a.contiguous() for a in args if isinstance(a, torch.Tensor)]
         inputs = self.trans_to_tensor(*tensors)
         on_gpu = any(t.is_cuda for t in tensors)
         out_device = torch.device("cuda", self.device) if on_gpu else torch.device("cpu")
-        outputs = [torch.empty(shape, dtype=TYPE_TO_TORCH_DTYPE[code], device=out_device)
-                   for shape, code in self.executor.output_shapes(symbols, inputs)]
+        # output extents depend only on the symbol values and the input extents: ask once per signature
+        key = (tuple(symbols), tuple(tuple(t.shape) for t in tensors))
+        meta = self._out_meta.get(key)
+        if meta is None:
+            meta = [(tuple(shape), TYPE_TO_TORCH_DTYPE[code]) for shape, code in self.executor.output_shapes(symbols, inputs)]
+            self._out_meta[key] = meta
+        outputs = [torch.empty(shape, dtype=dt, device=out_device) for shape, dt in meta]
         outputs_ = self.trans_to_tensor(*outputs)
         stream = torch.cuda.current_stream(self.device).cuda_stream
         if symbols:

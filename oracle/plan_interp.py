@@ -254,4 +254,5 @@ def _as_view(mem, v, env) -> torch.Tensor:
     base = mem[v["buf"]]
     if _DT[v["dtype"]] != base.dtype:
         raise TypeError(f"view dtype {v['dtype']} does not match buffer dtype {base.dtype}")
-    return torch.as_strided(base, shape, strides, _ev(v["offset"], env))
+    # as_strided takes an offset into the underlying storage, not into `base`
+    return torch.as_strided(base, shape, strides, base.storage_offset() + _ev(v["offset"], env))

@@ -123,3 +123,27 @@ def test_conv_bf16_tensor_cores(case):
 @pytest.mark.parametrize("case", CONV_TC)
 def test_conv_fp32_on_tensor_cores(case, prec, tol):
     _conv_case(case, torch.float32, prec, tol)
+
+
+@pytest.mark.parametrize("prec,dtype,tol", [("bf16", torch.bfloat16, 1e-4), ("tf32x3", torch.float32, 5e-5), ("tf32", torch.float32, 2e-3)])
+@pytest.mark.parametrize("m,n,k", [(128, 64, 64), (256, 128, 512), (300, 200, 136), (384, 64, 384), (1000, 72, 264)])
+def test_b_operand_stored_k_by_n(m, n, k, prec, dtype, tol):
+    # B given as [K, N] row-major (unit stride along n): the MN-major tensor-core operand
+    a, b = _rand(m, k, dtype=dtype), _rand(k, n, dtype=dtype, seed=1)
+    want = (a.double() @ b.double()).float()
+    out = torch.full((1, 1, m, n), float("nan"), device=DEV)
+    G.gemm(a.to(DEV)[None, None], b.to(DEV)[None, None], out, prec=prec)
+    assert max_rel_err(out[0, 0], want) < tol
+    _healthy()
+
+
+def test_bf16_attention_pv_strided_heads():
+    # P [B,H,S,S] times V read in place from [B,S,H*D] storage (unit stride along the head dim)
+    Bn, S, H, D = 2, 384, 12, 64
+    pmat = torch.softmax(_rand(Bn, H, S, S), -1).to(torch.bfloat16)
+    v = _rand(Bn, S, H * D, dtype=torch.bfloat16, seed=3)
+    want = pmat.float() @ v.float().view(Bn, S, H, D).permute(0, 2, 1, 3)
+    out = torch.full((Bn, H, S, D), float("nan"), device=DEV)
+    G.gemm(pmat.to(DEV), v.to(DEV).view(Bn, S, H, D).permute(0, 2, 1, 3), out, prec="bf16")
+    assert max_rel_err(out, want) < 1e-4
+    _healthy()
