@@ -47,6 +47,17 @@ typedef struct LlcGemmParams {
 } LlcGemmParams;
 int llc_cuda_gemm(const LlcGemmParams* p, void* stream);
 
+/* llc_cuda_gemm on the FMA path for callers that must not allocate device memory (a process whose
+ * own pool already owns the GPU, a loop that cannot take the synchronisation an allocation
+ * implies).  No counterpart in the reference.  The split-K scratch is a 1 MiB array built into the
+ * library (each GPU that loads the library holds it until exit); `workspace` in the parameter block
+ * is ignored.  A shape whose split needs more than 1 MiB is refused with LLC_ERR_ARGUMENT.  The
+ * first call on a device looks up the array's device address (cudaGetSymbolAddress); make that
+ * first call before starting any stream capture.  All calls share the one array: launches that
+ * overlap on the GPU (different streams, threads or processes' contexts on one device) race.
+ * Calls no cudaMalloc / cudaFree. */
+int llc_cuda_gemm_static_scratch(const LlcGemmParams* p, void* stream);
+
 /* Health word of the tensor-core kernels.  Their waits on memory barriers are bounded; a wait that
  * gives up records 1 (producer), 2 (issuer), 3 (operand split) or 4 (epilogue) and the launch's
  * result is then invalid.  Returns the recorded code (0 = healthy) and clears it; -1 if the device

@@ -8,6 +8,8 @@
 // (As[k][m], Bs[k][n]) so that each thread reads its m/n fragments as float4.
 // Bound: fp32 FMA throughput (148 SMs x 128 lanes x 2 flop x clock); HBM traffic is
 // M*K + N*K + M*N elements per call plus re-reads of A across the N/BN column tiles (L2 hits).
+#include <mutex>
+
 #include "common.cuh"
 
 namespace llc {
@@ -345,3 +347,70 @@ int igemmSimtConv(const LlcConvParams* p, cudaStream_t st) {
 
 }  // namespace llc
 
+// ---- entry point that allocates nothing ----------------------------------------------------------
+// Some hosts of this library cannot allocate device memory when they call it: a serving process
+// that handed the whole GPU to its own pool at start-up (a cudaMalloc here would fail or eat into
+// that pool), or a control loop that cannot afford the device-wide synchronisation and driver lock
+// an allocation takes.  For them the split-K GEMM keeps its scratch (tile counters + fp32 partial
+// tiles) in a fixed array that is part of the library image: every GPU that loads the library
+// holds these kStaticScratchBytes until the process exits.
+namespace llc {
+namespace {
+
+constexpr size_t kStaticScratchBytes = 1u << 20;   // 1 MiB: 4096 bytes of counters + partial tiles
+static __device__ __align__(256) unsigned char g_staticScratch[kStaticScratchBytes];
+
+constexpr int kMaxDevices = 64;
+void* g_staticScratchPtr[kMaxDevices] = {nullptr};
+std::mutex g_staticScratchMutex;
+
+// Device address of the array on the current device.  In host code the array's name is only a
+// handle for the runtime, not something a kernel can dereference; the address comes from
+// cudaGetSymbolAddress, asked once per device with that device current.
+int staticScratchAddress(void** out) {
+  int dev = 0;
+  LLC_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDevices) return setError(LLC_ERR_ARGUMENT, "llc argument: device ordinal above 63");
+  std::lock_guard<std::mutex> lock(g_staticScratchMutex);
+  if (!g_staticScratchPtr[dev]) {
+    void* ptr = nullptr;
+    LLC_CUDA_CHECK(cudaGetSymbolAddress(&ptr, g_staticScratch));
+    if (!ptr) return setError(LLC_ERR_CUDA, "llc cuda: cudaGetSymbolAddress returned a null address");
+    g_staticScratchPtr[dev] = ptr;
+  }
+  *out = g_staticScratchPtr[dev];
+  return LLC_OK;
+}
+
+}  // namespace
+}  // namespace llc
+
+extern "C" int llc_cuda_gemm_static_scratch(const LlcGemmParams* p, void* stream) {
+  using namespace llc;
+  if (!p) return setError(LLC_ERR_ARGUMENT, "llc argument: gemm null parameter block");
+  if (p->m < 0 || p->n < 0 || p->k < 0 || p->b0 < 0 || p->b1 < 0) return setError(LLC_ERR_ARGUMENT, "llc argument: gemm negative extent");
+  if (p->m == 0 || p->n == 0 || p->b0 == 0 || p->b1 == 0) return LLC_OK;
+  if (!p->a || !p->b || !p->out) return setError(LLC_ERR_ARGUMENT, "llc argument: gemm null operand");
+  auto floatIo = [](int32_t dt) { return dt == LLC_FLOAT32 || dt == LLC_BFLOAT16; };
+  if (!floatIo(p->in_dtype) || !floatIo(p->out_dtype) || (p->res && !floatIo(p->res_dtype)))
+    return setError(LLC_ERR_UNSUPPORTED, "llc argument: gemm operands must be f32 or bf16");
+  // the same split the workspace path would choose; a shape whose split does not fit is refused
+  const long long batch = p->b0 * p->b1;
+  const long long t64 = ((p->m + 63) / 64) * ((p->n + 63) / 64) * batch;
+  if (t64 * 2 <= kNumSMs && p->k >= 512) {
+    long long want = kNumSMs / t64; if (want > 32) want = 32; if (want > p->k / 128) want = p->k / 128;
+    const long long kPer = ((p->k + want - 1) / want + BK - 1) / BK * BK;
+    const long long split = (p->k + kPer - 1) / kPer;
+    const size_t need = kCounterBytes + (size_t)t64 * split * 64 * 64 * sizeof(float);
+    if (split > 1 && need > kStaticScratchBytes)
+      return setError(LLC_ERR_ARGUMENT, "llc argument: this GEMM needs " + std::to_string(need) + " bytes of split-K scratch, the built-in array holds " +
+                                            std::to_string(kStaticScratchBytes));
+  }
+  void* scratch = nullptr;
+  int rc = staticScratchAddress(&scratch);
+  if (rc != LLC_OK) return rc;
+  cudaStream_t st = (cudaStream_t)stream;
+  // the array keeps whatever the previous call left: the tile counters must start at zero
+  LLC_CUDA_CHECK(cudaMemsetAsync(scratch, 0, kCounterBytes, st));
+  return igemmSimtGemm(p, st, scratch, (long long)kStaticScratchBytes);
+}

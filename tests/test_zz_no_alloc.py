@@ -1,0 +1,65 @@
+"""The GEMM entry point that allocates nothing (llc_cuda_gemm_static_scratch).
+
+It exists for callers that cannot allocate device memory at call time -- a process whose own
+pool already owns the whole GPU, a loop that cannot take the synchronisation an allocation
+implies -- and keeps its split-K scratch in a 1 MiB array that is part of the library.  The
+test calls it through the C ABI twice in a row (the second call finds the first call's contents
+in the shared array) and compares each result with llc_cuda_gemm on the same operands, at the
+1e-5 relative tolerance the fp32 kernel tests use; it also checks that an over-sized split is
+refused.  The file name sorts last so that a run stopping at the first failure has already run
+every other test."""
+import ctypes
+from ctypes import byref, c_void_p
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+import gpu_ops as G  # noqa: E402
+from llcompiler_b200 import _capi as C  # noqa: E402
+from oracle.models import max_rel_err  # noqa: E402
+
+DEV = "cuda"
+
+
+def _params(a, b, out, shift, act):
+    p = C.LlcGemmParams()
+    p.a, p.b, p.out, p.shift = c_void_p(a.data_ptr()), c_void_p(b.data_ptr()), c_void_p(out.data_ptr()), c_void_p(shift.data_ptr())
+    p.in_dtype = p.out_dtype = p.res_dtype = 4
+    p.precision = C.PREC["fp32"]
+    p.b0, p.b1, p.m, p.n, p.k = 1, 1, out.shape[2], out.shape[3], a.shape[3]
+    p.a_sm, p.b_sk, p.b_sn, p.o_sm = a.stride(2), b.stride(2), b.stride(3), out.stride(2)
+    p.alpha, p.act = 1.0, C.ACT[act]
+    return p
+
+
+@pytest.mark.parametrize("m,n,k", [(64, 512, 784), (64, 10, 512), (200, 300, 64)])
+def test_static_scratch_gemm_matches_the_allocating_entry_point(m, n, k):
+    g = torch.Generator().manual_seed(m + n + k)
+    a, w, bias = torch.randn(m, k, generator=g), torch.randn(n, k, generator=g), torch.randn(n, generator=g)
+    A, B, S = a.to(DEV)[None, None], w.to(DEV).t()[None, None], bias.to(DEV)
+    ref = torch.empty(1, 1, m, n, device=DEV)
+    G.gemm(A, B, ref, shift=S, act="relu")                       # existing entry point
+    want = torch.relu((a.double() @ w.double().t()).float() + bias)
+    assert max_rel_err(ref[0, 0], want) < 1e-5
+    fn = C.lib().llc_cuda_gemm_static_scratch
+    stream = c_void_p(torch.cuda.current_stream().cuda_stream)
+    for _ in range(2):                                           # two calls in a row share the array
+        out = torch.full((1, 1, m, n), float("nan"), device=DEV)
+        p = _params(A, B, out, S, "relu")
+        C.check(fn(byref(p), stream))
+        torch.cuda.synchronize()
+        assert max_rel_err(out[0, 0], ref[0, 0].cpu()) < 1e-5
+
+
+def test_static_scratch_gemm_refuses_a_split_that_does_not_fit():
+    # 37 output tiles x 4 K slices x 16 KiB per partial tile is more than the 1 MiB array
+    m, n, k = 64 * 37, 64, 16384
+    A = torch.zeros(1, 1, m, k, device=DEV)
+    B = torch.zeros(n, k, device=DEV).t()[None, None]
+    out = torch.empty(1, 1, m, n, device=DEV)
+    p = _params(A, B, out, torch.zeros(n, device=DEV), "none")
+    rc = C.lib().llc_cuda_gemm_static_scratch(byref(p), c_void_p(torch.cuda.current_stream().cuda_stream))
+    assert rc == 3
+    assert b"built-in array" in C.lib().llc_last_error()
