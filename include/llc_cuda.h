@@ -111,6 +111,12 @@ int llc_cuda_layernorm(const void* x, const void* gamma, const void* beta, void*
 int llc_cuda_gather(const void* table, const int64_t* ids, void* out, int32_t table_dtype, int32_t out_dtype,
                     int64_t rows, int64_t d, int64_t vocab, int32_t* bad_ids, void* stream);
 
+/* x [n, c, hw] (NCHW planes) -> out [n, hw, c_pad] (NHWC pixels), channels c..c_pad-1 written as
+ * zeros.  The layout change the reference expresses as llh.transpose perms [0,2,3,1] around conv
+ * (src/Dialect/LLH/Transforms/TransformLayout.cpp:141-198), with the channel padding the
+ * tensor-core convolution wants for a 3-channel stem. */
+int llc_cuda_nchw_to_nhwc(const void* x, void* out, int32_t dtype, int64_t n, int64_t c, int64_t hw, int64_t c_pad, void* stream);
+
 /* Fused elementwise chain: one coalesced pass that evaluates a small register program per
  * output element.  Replaces chains of llh.add/sub/mul/div/max/min/abs/sqrt/exp/where/compare/
  * convert_to/broadcast_to (-> stablehlo elementwise ops, LLHToHLO.cpp:479-490) and strided

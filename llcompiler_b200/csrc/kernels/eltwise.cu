@@ -238,10 +238,68 @@ __global__ void __launch_bounds__(256) gather_rows_kernel(const void* table, con
   for (long long c = lane; c < d; c += 32) storeAs(out, row * d + c, odt, ok ? loadAs(table, id * d + c, tdt) : 0.f);
 }
 
+// ---- NCHW -> NHWC re-layout with optional zero padding of the channel count --------------------
+// Few channels (the image stem): one thread per pixel reads its C planes (coalesced across the
+// warp) and writes the padded pixel with 16-byte stores.
+template <typename T, int CP>
+__global__ void __launch_bounds__(256) nchw_to_nhwc_small_kernel(const T* __restrict__ x, T* __restrict__ out, long long n, int c, long long hw) {
+  long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * hw) return;
+  long long img = idx / hw, px = idx - img * hw;
+  __align__(16) T v[CP];
+#pragma unroll
+  for (int k = 0; k < CP; ++k) v[k] = k < c ? x[(img * c + k) * hw + px] : T(0.f);
+  constexpr int kVec = CP * sizeof(T) / 16;
+  uint4* dst = reinterpret_cast<uint4*>(out + idx * CP);
+#pragma unroll
+  for (int k = 0; k < kVec; ++k) dst[k] = reinterpret_cast<const uint4*>(v)[k];
+}
+// Many channels: 32 x 32 tiles of the [C, HW] plane of one image go through shared memory so that
+// both the read (along HW) and the write (along C) are coalesced.
+template <typename T>
+__global__ void __launch_bounds__(256) nchw_to_nhwc_tiled_kernel(const T* __restrict__ x, T* __restrict__ out, int c, long long hw, int cp) {
+  __shared__ T tile[32][33];
+  const long long img = blockIdx.z;
+  const long long p0 = (long long)blockIdx.x * 32; const int c0 = blockIdx.y * 32;
+  const int tx = threadIdx.x & 31, ty = threadIdx.x >> 5;   // 32 x 8
+  for (int r = ty; r < 32; r += 8) {
+    int ch = c0 + r; long long px = p0 + tx;
+    tile[r][tx] = (ch < c && px < hw) ? x[(img * c + ch) * hw + px] : T(0.f);
+  }
+  __syncthreads();
+  for (int r = ty; r < 32; r += 8) {
+    long long px = p0 + r; int ch = c0 + tx;
+    if (px < hw && ch < cp) out[(img * hw + px) * cp + ch] = tile[tx][r];
+  }
+}
+
 }  // namespace
 }  // namespace llc
 
 using namespace llc;
+
+extern "C" int llc_cuda_nchw_to_nhwc(const void* x, void* out, int32_t dtype, int64_t n, int64_t c, int64_t hw, int64_t c_pad, void* stream) {
+  if (n <= 0 || c <= 0 || hw <= 0) return LLC_OK;
+  if (!x || !out) return setError(LLC_ERR_ARGUMENT, "llc argument: nchw_to_nhwc null pointer");
+  if (c_pad < c) return setError(LLC_ERR_ARGUMENT, "llc argument: padded channel count below the channel count");
+  if (dtype != LLC_FLOAT32 && dtype != LLC_BFLOAT16) return setError(LLC_ERR_UNSUPPORTED, "llc argument: nchw_to_nhwc type must be f32 or bf16");
+  if (n > 65535) return setError(LLC_ERR_ARGUMENT, "llc argument: nchw_to_nhwc batch above 65535");
+  cudaStream_t st = (cudaStream_t)stream;
+  const bool f32 = dtype == LLC_FLOAT32;
+  const bool aligned = (reinterpret_cast<uintptr_t>(out) & 15) == 0;
+  const unsigned blocks = (unsigned)((n * hw + 255) / 256);
+  if (aligned && f32 && c_pad == 4) nchw_to_nhwc_small_kernel<float, 4><<<blocks, 256, 0, st>>>((const float*)x, (float*)out, n, (int)c, hw);
+  else if (aligned && f32 && c_pad == 8) nchw_to_nhwc_small_kernel<float, 8><<<blocks, 256, 0, st>>>((const float*)x, (float*)out, n, (int)c, hw);
+  else if (aligned && !f32 && c_pad == 8) nchw_to_nhwc_small_kernel<__nv_bfloat16, 8><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, (int)c, hw);
+  else if (aligned && !f32 && c_pad == 16) nchw_to_nhwc_small_kernel<__nv_bfloat16, 16><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, (int)c, hw);
+  else {
+    dim3 g((unsigned)((hw + 31) / 32), (unsigned)((c_pad + 31) / 32), (unsigned)n);
+    if (f32) nchw_to_nhwc_tiled_kernel<float><<<g, 256, 0, st>>>((const float*)x, (float*)out, (int)c, hw, (int)c_pad);
+    else nchw_to_nhwc_tiled_kernel<__nv_bfloat16><<<g, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, (int)c, hw, (int)c_pad);
+  }
+  LLC_LAUNCH_CHECK("nchw_to_nhwc_kernel");
+  return LLC_OK;
+}
 
 extern "C" int llc_cuda_eltwise(const LlcEltwiseParams* q, void* stream) {
   if (!q || !q->out) return setError(LLC_ERR_ARGUMENT, "llc argument: eltwise null pointer");

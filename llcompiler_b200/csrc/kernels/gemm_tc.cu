@@ -200,16 +200,29 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       const int tileM = rem / p.nTiles, tileN = rem - tileM * p.nTiles;
       const int zb0 = z / p.b1, zb1 = z - zb0 * p.b1;
       const int ab = tcount & 1; const uint32_t aph = (tcount >> 1) & 1;
-      if (!mbarWait(&accFull[ab], aph, abortWord)) { atomicExch(&g_tcStatus, 4); break; }
-      tcFenceAfter();
-      const uint32_t acc = tmemBase + (uint32_t)(ab * kSetCols) + ((uint32_t)(q * 32) << 16);
-      const int usedChains = p.kBlocks < kChains ? p.kBlocks : kChains;
       const long long gm = (long long)tileM * BM + q * 32 + lane;
       const bool rowOk = gm < p.M;
       const long long oRow = zb0 * p.o_s0 + zb1 * p.o_s1 + gm * p.o_sm;
       const long long rRow = zb0 * p.r_s0 + zb1 * p.r_s1 + gm * p.r_sm;
-#pragma unroll 1
-      for (int c0 = half * kColsPerWarp; c0 < (half + 1) * kColsPerWarp; c0 += 32) {
+      // The residual rows of this warp's share are fetched while the tile's MMAs still run: issued
+      // after the accumulator is ready, these scattered loads would have nothing to hide behind.
+      constexpr int kPre = kColsPerWarp / 8;            // 16-byte pieces (8 bf16) per row share
+      uint4 rpre[CONV ? 1 : kPre];
+      const long long preCol = (long long)tileN * BN + half * kColsPerWarp;
+      const bool pre = !CONV && p.res != nullptr && p.res_dtype == LLC_BFLOAT16 && p.r_sn == 1 && p.vecOut && rowOk &&
+                       preCol + kColsPerWarp <= p.N && ((rRow + preCol) & 7) == 0;
+      if (!CONV && pre) {
+        const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.res) + rRow + preCol);
+#pragma unroll
+        for (int i = 0; i < kPre; ++i) rpre[i] = __ldg(rp + i);
+      }
+      if (!mbarWait(&accFull[ab], aph, abortWord)) { atomicExch(&g_tcStatus, 4); break; }
+      tcFenceAfter();
+      const uint32_t acc = tmemBase + (uint32_t)(ab * kSetCols) + ((uint32_t)(q * 32) << 16);
+      const int usedChains = p.kBlocks < kChains ? p.kBlocks : kChains;
+#pragma unroll
+      for (int ci = 0; ci < kColsPerWarp / 32; ++ci) {
+        const int c0 = half * kColsPerWarp + ci * 32;
         float v[32];
         __syncwarp();                                   // the load is warp-collective
         tmemLoad32x32(acc + (uint32_t)c0, v);
@@ -243,7 +256,15 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
 #pragma unroll
             for (int j = 0; j < 8; ++j) { float4 s4 = __ldg(sh + j); v[4 * j] += s4.x; v[4 * j + 1] += s4.y; v[4 * j + 2] += s4.z; v[4 * j + 3] += s4.w; }
           }
-          if (p.res && rowOk) {
+          if (!CONV && pre) {
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 r = rpre[CONV ? 0 : ci * 4 + j];
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); v[8 * j + 2 * e] += f.x; v[8 * j + 2 * e + 1] += f.y; }
+            }
+          } else if (p.res && rowOk) {
             if (p.r_sn == 1 && p.res_dtype == LLC_BFLOAT16 && ((rRow + gn0) & 3) == 0) {
               const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(p.res) + rRow + gn0;
 #pragma unroll

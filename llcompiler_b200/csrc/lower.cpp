@@ -678,14 +678,24 @@ struct Lowering {
         cPad = (Cin.constant() + mult - 1) / mult * mult;
     }
     View x;
-    if (cPad) {
-      std::vector<Expr> pshape = {xt.shape[0], Expr(cPad), xt.shape[2], xt.shape[3]};
+    settle(xt);
+    const bool denseNchw = xt.kind == TV::ViewK && isContiguous(xt.view) && isFloat(xt.dtype) && dtypeSize(xt.dtype) <= 4 && !xt.isConst;
+    if (cPad || (denseNchw && !xt.shape[1].isConst(1))) {
+      // NCHW data entering a conv chain: one re-layout kernel (with the channel padding if any)
+      std::vector<Expr> pshape = {xt.shape[0], cPad ? Expr(cPad) : xt.shape[1], xt.shape[2], xt.shape[3]};
       std::vector<Expr> pst = nhwcStrides(pshape);
-      toView(xt);
-      x = freshView(xt.dtype, pshape, false, &pst);
-      emitEltwise(constNode(0.0), x, false);                          // zero the padding channels
-      View real = x; real.shape = xt.shape;                           // same strides, real channel extent
-      emitEltwise(leafNode(xt.view), real, false);
+      if (denseNchw) {
+        x = freshView(xt.dtype, pshape, false, &pst);
+        Step st; st.kernel = "nchw2nhwc";
+        st.views.emplace_back("x", xt.view); st.views.emplace_back("out", x);
+        plan.steps.push_back(st);
+      } else {
+        toView(xt);
+        x = freshView(xt.dtype, pshape, false, &pst);
+        emitEltwise(constNode(0.0), x, false);                          // zero the padding channels
+        View real = x; real.shape = xt.shape;                           // same strides, real channel extent
+        emitEltwise(leafNode(xt.view), real, false);
+      }
     } else {
       x = viewWithStrides(xv, nhwcStrides(xt.shape));
     }
@@ -1130,6 +1140,20 @@ struct Lowering {
       TV& t = raw(v);
       settle(t);
       if (t.kind == TV::Scalar) fail("returning scalars is not supported");
+      // the caller allocates the result with the declared element type
+      const DType want = v->type.elt;
+      if (want != DType::None && want != t.dtype) {
+        if (t.kind == TV::Pending && v->users.size() == 1 && isFloat(want) && isFloat(t.dtype)) {
+          PendingK& P = pend[t.pending];
+          P.nativeOut.dtype = want; plan.buffers[P.buf].dtype = want; t.dtype = want; t.view.dtype = want;
+        } else if (t.kind == TV::Lazy) {
+          t.dtype = want;
+        } else {
+          toView(t);
+          TV conv = makeLazy(opNode("cast", leafNode(t.view)), want, t.shape);
+          t = conv;
+        }
+      }
       IoDecl io; io.dtype = t.dtype; io.shape = t.shape;
       std::vector<Expr> rm = rowMajor(t.shape);
       bool direct = false;
@@ -1212,6 +1236,11 @@ struct Lowering {
           // float -> float: arithmetic is fp32 everywhere, only the storage type of whatever is
           // materialised next changes, so the conversion does not break a fusion
           settle(x);
+          // widening (bf16 -> f32) of stored data is exact: keep the narrow storage and let the
+          // consumers read it as it is (they all compute in fp32)
+          if (dtypeSize(to) > dtypeSize(x.dtype) && (x.kind == TV::Pending || x.kind == TV::ViewK || x.kind == TV::Deferred)) {
+            TV c = x; tvs[op->results[0]] = c; continue;
+          }
           if (x.kind == TV::Pending && op->operands[0]->users.size() == 1) {
             PendingK& P = pend[x.pending];
             P.nativeOut.dtype = to; plan.buffers[P.buf].dtype = to;

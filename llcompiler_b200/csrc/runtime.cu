@@ -90,7 +90,7 @@ struct RView { int buf; long long off; int rank; long long shape[6], strides[6];
 // A plan step resolved for one symbol binding: the kernel's parameter block is filled once, only the
 // pointers (which depend on where the caller's tensors and the arena are) are patched per call.
 struct PtrPatch { void** slot; int buf; long long byteOff; };
-enum StepKind { kGemm, kConv, kPool, kReduce, kSoftmax, kLayerNorm, kGather, kEltwise };
+enum StepKind { kGemm, kConv, kPool, kReduce, kSoftmax, kLayerNorm, kGather, kEltwise, kNchw2Nhwc };
 struct RStep {
   const Step* step;
   std::vector<std::pair<std::string, RView>> views;
@@ -239,6 +239,13 @@ void LlcExec::prepare(RStep& rs) {
     if (ids.dtype != LLC_INT64) failArg("gather indices must be int64");
     patch(&rs.sp[0], t); patch(&rs.sp[1], ids); patch(&rs.sp[2], o);
     rs.sdt[0] = t.dtype; rs.sdt[1] = o.dtype; rs.sd[0] = o.shape[0]; rs.sd[1] = o.shape[1]; rs.sd[2] = t.shape[0];
+  } else if (s.kernel == "nchw2nhwc") {
+    rs.kind = kNchw2Nhwc;
+    const RView &x = need("x"), &o = need("out");      // both logical [N, C, H, W]
+    if (x.dtype != o.dtype) failArg("nchw2nhwc input and output types differ");
+    patch(&rs.sp[0], x); patch(&rs.sp[1], o);
+    rs.sdt[0] = x.dtype; rs.sd[0] = x.shape[0]; rs.sd[1] = x.shape[1]; rs.sd[2] = x.shape[2] * x.shape[3];
+    rs.sop = (int)o.shape[1];
   } else if (s.kernel == "eltwise") {
     rs.kind = kEltwise;
     const RView& o = need("out");
@@ -272,6 +279,7 @@ int LlcExec::launch(RStep& rs, cudaStream_t st) {
     case kLayerNorm: return llc_cuda_layernorm(rs.sp[0], rs.sp[1], rs.sp[2], rs.sp[3], rs.sdt[0], rs.sdt[1], rs.sdt[2], rs.sd[0], rs.sd[1], rs.seps, st);
     case kGather: return llc_cuda_gather(rs.sp[0], (const int64_t*)rs.sp[1], rs.sp[2], rs.sdt[0], rs.sdt[1], rs.sd[0], rs.sd[1], rs.sd[2], badIds, st);
     case kEltwise: return llc_cuda_eltwise(&rs.elt, st);
+    case kNchw2Nhwc: return llc_cuda_nchw_to_nhwc(rs.sp[0], rs.sp[1], rs.sdt[0], rs.sd[0], rs.sd[1], rs.sd[2], rs.sop, st);
   }
   throw std::runtime_error("llc internal: unprepared plan step");
 }

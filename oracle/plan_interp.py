@@ -184,6 +184,13 @@ class PlanInterpreter:
         out = F.layer_norm(x, (x.shape[-1],), v["gamma"].float(), v["beta"].float(), float(p["eps"]))
         v["out"].copy_(out.to(v["out"].dtype))
 
+    def _k_nchw2nhwc(self, v, p):
+        # llh.transpose perms [0,2,3,1] around conv (src/Dialect/LLH/Transforms/TransformLayout.cpp:141-198);
+        # the output view is logical NCHW over an NHWC buffer, extra channels are zero
+        out, x = v["out"], v["x"]
+        out.zero_()
+        out[:, : x.shape[1]].copy_(x)
+
     def _k_gather(self, v, p):
         v["out"].copy_(v["table"][v["ids"].long()].to(v["out"].dtype))
 

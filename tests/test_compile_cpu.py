@@ -35,7 +35,7 @@ def test_resnet18_fuses_to_conv_steps():
     assert max_rel_err(got, want) < 1e-4
     plan = comp.compiled[0].engine.text
     assert plan.count("step conv") == 20 and plan.count("step maxpool") == 1
-    assert plan.count("step eltwise") == 1      # only the NCHW->NHWC input re-layout
+    assert plan.count("step eltwise") == 0 and plan.count("step nchw2nhwc") == 1   # only the input re-layout
 
 
 def test_encoder_layer_dynamic_seq():

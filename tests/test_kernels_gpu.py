@@ -231,3 +231,20 @@ def test_gemm_fp32_split_k_matches_single_pass(m, n, k):
     ref = torch.empty(1, 1, m, n, device=DEV)
     G.gemm(A, B, ref, shift=bias.to(DEV), act="relu")
     assert max_rel_err(out[0, 0], ref[0, 0].cpu()) < 1e-5
+
+
+@pytest.mark.parametrize("n,c,h,w,cp", [(2, 3, 37, 41, 4), (2, 3, 37, 41, 8), (3, 3, 16, 16, 3), (2, 64, 14, 14, 64), (1, 70, 9, 5, 72)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_nchw_to_nhwc_bit_exact_with_zero_padding(n, c, h, w, cp, dtype):
+    import ctypes
+    from ctypes import c_void_p
+    from llcompiler_b200 import _capi as C
+    x = _rand(n, c, h, w, dtype=dtype)
+    out = torch.full((n, h, w, cp), float("nan"), device=DEV, dtype=dtype)
+    f = C.lib().llc_cuda_nchw_to_nhwc
+    f.argtypes = [c_void_p, c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64, c_void_p]
+    X = x.to(DEV)
+    C.check(f(X.data_ptr(), out.data_ptr(), 4 if dtype == torch.float32 else 8, n, c, h * w, cp, torch.cuda.current_stream().cuda_stream))
+    want = torch.zeros(n, h, w, cp, dtype=dtype)
+    want[..., :c] = x.permute(0, 2, 3, 1)
+    assert torch.equal(out.cpu(), want)
