@@ -34,9 +34,9 @@ import torch  # noqa: E402
 WORKLOADS = {
     # name: (oracle config, per-GPU batch, extra make_inputs kwargs, dtype label, precision option)
     "mlp": ("mlp", 64, {}, "f32", "auto"),
-    "resnet18": ("resnet18", 32, {}, "f32", "auto"),
-    "encoder128": ("encoder", 8, {"seq": 128}, "f32", "auto"),
-    "encoder512": ("encoder", 8, {"seq": 512}, "f32", "auto"),
+    "resnet18": ("resnet18", 32, {}, "f32", "tf32x3"),      # fp32 storage, three-pass TF32 on tensor cores (1e-4)
+    "encoder128": ("encoder", 8, {"seq": 128}, "f32", "tf32"),  # the configuration names TF32 matmuls (2e-2)
+    "encoder512": ("encoder", 8, {"seq": 512}, "f32", "tf32"),
     "resnet50": ("resnet50", 256, {}, "bf16", "auto"),
     "bert": ("bert", 256, {}, "bf16", "auto"),
 }

@@ -65,6 +65,11 @@ __device__ __forceinline__ void cpAsync16(uint32_t dst, const void* src, bool va
 }
 __device__ __forceinline__ void cpAsyncCommit() { asm volatile("cp.async.commit_group;" ::: "memory"); }
 template <int N> __device__ __forceinline__ void cpAsyncWait() { asm volatile("cp.async.wait_group %0;" ::"n"(N) : "memory"); }
+// The barrier receives one arrival (counted against its expected count) when every cp.async this
+// thread has issued so far has landed: the thread itself never waits for its copies.
+__device__ __forceinline__ void cpAsyncArriveOn(uint64_t* bar) {
+  asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smemAddr(bar)) : "memory");
+}
 
 // KIND: 0 bf16, 1 tf32, 2 tf32x3.  BMN: B is stored [k][n] (unit stride along n) instead of [n][k].
 template <int BN, int KIND, bool CONV, bool BMN>
@@ -163,6 +168,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
           if (!mbarWait(X3 ? &split[s] : &full[s], ph, abortWord)) { atomicExch(&g_tcStatus, 2); ok = false; break; }
+          if (CONV && !X3) fenceProxyAsync();               // the gathered A tile was written through the generic proxy
           tcFenceAfter();
           const uint32_t acc = accSet + (uint32_t)((kb % kChains) * BN);
           const bool fresh = kb < kChains;                 // first K block of this chain: overwrite
@@ -283,7 +289,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
           } else if (p.act == LLC_ACT_GELU) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = geluErf(v[j]);
+            for (int j = 0; j < 32; ++j) v[j] = geluFast(v[j]);
           }
           if (rowOk) {
             if (outF32) {
@@ -331,12 +337,11 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     // tap (C * element size is a multiple of 16), so it is one load from x[n, ih, iw, c..] or zeros.
     // The tap of a chunk depends only on the K block, not on the row: it is tracked incrementally.
     constexpr int kChunkElems = 16 / kElemBytes;
-    constexpr int kLag = kStages - 1 < 4 ? kStages - 1 : 4;   // stages in flight per thread before it signals
     const int g = threadIdx.x - kGatherWarp0 * 32;
     const int chunk = g & 7, row0 = g >> 3;
     const char* X = reinterpret_cast<const char*>(p.x);
     const uint32_t dstOff = (uint32_t)(row0 * 128 + ((chunk ^ (row0 & 7)) << 4));   // (row0 + 32 j) & 7 == row0 & 7
-    uint32_t it = 0, signalled = 0;
+    uint32_t it = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
       const int rem = (int)(t % tilesPerBatch);
@@ -365,20 +370,13 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           const bool valid = tapOk && (unsigned)(ih0[j] + dIh) < (unsigned)p.H && (unsigned)(iw0[j] + dIw) < (unsigned)p.W;
           cpAsync16(dst + j * 32 * 128, X + (valid ? (rowBase[j] + tapOff) * kElemBytes : 0), valid);
         }
-        cpAsyncCommit();
+        cpAsyncArriveOn(&full[s]);                           // arrives when the four copies above have landed
         cc += BK;                                              // next K block: 128 bytes further along K
         while (cc >= p.C) { cc -= p.C; if (++tapS == p.KW) { tapS = 0; ++tapR; } }
-        if (it - signalled >= (uint32_t)kLag) {                // the oldest outstanding stage has landed
-          cpAsyncWait<kLag>();
-          fenceProxyAsync();
-          mbarArrive(&full[signalled % kStages]);
-          ++signalled;
-        }
       }
     }
-    cpAsyncWait<0>();
-    fenceProxyAsync();
-    for (; signalled < it; ++signalled) mbarArrive(&full[signalled % kStages]);
+    cpAsyncCommit();
+    cpAsyncWait<0>();                                          // nothing of this thread is in flight at exit
   } else if (X3 && warp >= kSplitWarp0) {
     // ---------------------------------------------------------------- low-order tiles (tf32x3)
     // elementwise, so every 16-byte chunk keeps its swizzled position

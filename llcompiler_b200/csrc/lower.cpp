@@ -976,9 +976,36 @@ struct Lowering {
       r.kind = xt.kind; r.view = nv; r.pending = xt.pending;
       tvs[op->results[0]] = r; return;
     }
+    if (xt.kind == TV::Pending && xv->users.size() == 1 && relayoutPending(xt) && reshapeView(xt.view, shape, nv)) {
+      r.kind = xt.kind; r.view = nv; r.pending = xt.pending;
+      tvs[op->results[0]] = r; return;
+    }
     if (xt.kind == TV::Pending) toView(xt);
     r.kind = TV::Deferred; r.view = xt.view;
     tvs[op->results[0]] = r;
+  }
+  // A GEMM result that has only been permuted so far (attention's [B,H,S,D] -> [B,S,H,D]) and is now
+  // reshaped: nothing has been emitted yet, so the kernel can write its tile rows straight into the
+  // permuted order (it takes arbitrary batch and row strides) and the copy disappears.
+  bool relayoutPending(TV& t) {
+    PendingK& P = pend[t.pending];
+    if (P.emitted || P.step.kernel != "gemm" || P.hasRes || !t.view.offset.isConst(0)) return false;
+    const View& nat = P.nativeOut;
+    std::vector<int> logicalOf(nat.rank(), -1);
+    std::vector<bool> used(t.view.rank(), false);
+    for (size_t d = 0; d < nat.rank(); ++d) {
+      if (nat.shape[d].isConst(1)) continue;
+      for (size_t l = 0; l < t.view.rank(); ++l)
+        if (!used[l] && !t.view.shape[l].isConst(1) && t.view.shape[l] == nat.shape[d] && t.view.strides[l] == nat.strides[d]) { logicalOf[d] = (int)l; used[l] = true; break; }
+      if (logicalOf[d] < 0) return false;
+    }
+    for (size_t l = 0; l < t.view.rank(); ++l) if (!used[l] && !t.view.shape[l].isConst(1)) return false;
+    std::vector<Expr> fresh = rowMajor(t.view.shape);
+    const size_t nDim = nat.rank() - 1;
+    if (logicalOf[nDim] >= 0 && !fresh[logicalOf[nDim]].isConst(1)) return false;   // the kernel needs unit stride along n
+    for (size_t d = 0; d < nat.rank(); ++d) if (logicalOf[d] >= 0) P.nativeOut.strides[d] = fresh[logicalOf[d]];
+    t.view.strides = fresh;
+    return true;
   }
   void transpose(Op* op) {
     Value* xv = op->operands[0];
