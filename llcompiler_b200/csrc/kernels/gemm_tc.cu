@@ -45,6 +45,7 @@ struct TcArgs {
   long long M, N, K;
   long long o_s0, o_s1, o_sm, r_s0, r_s1, r_sm, r_sn;
   int b1; int kBlocks; int vecOut;
+  int tmaOut;               // 0, or the bytes per row of the output box the epilogue stores through TMA (64 or 128)
   int aZ0, aZ1, bZ0, bZ1;   // 1: the operand has this batch dim, 0: it is broadcast (coordinate 0)
   int mTiles, nTiles; long long tiles;
   // convolution (A gathered from NHWC activations)
@@ -54,9 +55,10 @@ struct TcArgs {
 template <int BN, bool X3> struct Smem {
   static constexpr int kABytes = BM * kTileKBytes, kBBytes = BN * kTileKBytes;
   static constexpr int kStageBytes = (kABytes + kBBytes) * (X3 ? 2 : 1);
-  static constexpr int kStages = (200 * 1024) / kStageBytes > 8 ? 8 : (200 * 1024) / kStageBytes;
+  static constexpr int kStages = (192 * 1024) / kStageBytes > 8 ? 8 : (192 * 1024) / kStageBytes;
   static constexpr int kBarrierBytes = 1024;
-  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + 1024;   // + alignment slack
+  static constexpr int kStagingBytes = 8 * 4096;   // one 32-row x 128-byte output box per epilogue warp
+  static constexpr int kTotal = kStages * kStageBytes + kBarrierBytes + kStagingBytes + 1024;   // + alignment slack
 };
 
 __device__ __forceinline__ void cpAsync16(uint32_t dst, const void* src, bool valid) {
@@ -74,7 +76,7 @@ __device__ __forceinline__ void cpAsyncArriveOn(uint64_t* bar) {
 // KIND: 0 bf16, 1 tf32, 2 tf32x3.  BMN: B is stored [k][n] (unit stride along n) instead of [n][k].
 template <int BN, int KIND, bool CONV, bool BMN>
 __global__ void __launch_bounds__((10 + (CONV ? 8 : 0) + (KIND == 2 ? 4 : 0)) * 32, 1)
-tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const TcArgs p) {
+tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapO, const TcArgs p) {
   constexpr bool X3 = KIND == 2;
   constexpr bool TF32 = KIND != 0;
   using S = Smem<BN, X3>;
@@ -108,11 +110,13 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
   uint64_t* accEmpty = bars + 3 * kStages + 2;  // [2] accumulator drained by the epilogue
   uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 4);
   volatile int* abortWord = reinterpret_cast<volatile int*>(tmemSlot + 1);
+  uint8_t* staging = smem + kStages * S::kStageBytes + S::kBarrierBytes;   // 1024-byte aligned
+  constexpr int kStagingPerWarp = 4096;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
-    for (int s = 0; s < kStages; ++s) { mbarInit(&full[s], kFullCount); mbarInit(&empty[s], 1); mbarInit(&split[s], 128); }
+    for (int s = 0; s < kStages; ++s) { mbarInit(&full[s], kFullCount); mbarInit(&empty[s], 1); mbarInit(&split[s], 4); }
     for (int a = 0; a < 2; ++a) { mbarInit(&accFull[a], 1); mbarInit(&accEmpty[a], kEpiWarps); }
     *abortWord = 0;
     fenceBarrierInit();
@@ -200,6 +204,8 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     constexpr int kColsPerWarp = BN / 2;
     char* outBase = reinterpret_cast<char*>(p.out);
     const bool outF32 = p.out_dtype == LLC_FLOAT32;
+    const int tmaW = p.tmaOut;                                  // bytes per staged row; 0: direct stores
+    uint8_t* outStage = staging + (warp - 2) * kStagingPerWarp;
     uint32_t tcount = 0;
     for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++tcount) {
       const int z = (int)(t / tilesPerBatch); const int rem = (int)(t - z * tilesPerBatch);
@@ -246,8 +252,9 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           if (lane == 0) mbarArrive(&accEmpty[ab]);
         }
         const long long gn0 = (long long)tileN * BN + c0;
-        if (gn0 >= p.N) continue;
-        if (p.vecOut && gn0 + 32 <= p.N) {
+        const bool inside = gn0 < p.N;
+        const bool whole = p.vecOut && gn0 + 32 <= p.N;
+        if (whole) {
           // whole chunk inside the matrix: flag tests hoisted out of the element loops
           if (p.scale) {
             const float4* sc = reinterpret_cast<const float4*>(p.scale + gn0);
@@ -288,10 +295,67 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
           } else if (p.act == LLC_ACT_GELU) {
+            if (outF32) {
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = geluFast(v[j]);
+              for (int j = 0; j < 32; ++j) v[j] = geluFast(v[j]);
+            } else {
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] = geluTanhBf16(v[j]);
+            }
           }
-          if (rowOk) {
+        } else if (inside && rowOk) {
+          // ragged edge: element by element
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const long long n = gn0 + j;
+            if (n < p.N) {
+              float x = v[j] * p.alpha;
+              if (p.scale) x *= __ldg(p.scale + n);
+              if (p.shift) x += __ldg(p.shift + n);
+              if (p.res) x += loadAs(p.res, rRow + n * p.r_sn, p.res_dtype);
+              v[j] = applyAct(x, p.act);
+            }
+          }
+        }
+        if (tmaW) {
+          // Stage the rows in shared memory (swizzled: conflict-free 16-byte writes) and let one TMA
+          // store write them out as whole lines; rows >= M and columns >= N are clipped by the store.
+          const int sub = (!outF32 && tmaW == 128) ? (ci & 1) : 0;        // bf16: two chunks fill a 128-byte row
+          const bool opens = sub == 0, closes = outF32 || tmaW == 64 || sub == 1;
+          const long long x0 = gn0 - sub * 32;
+          if (x0 < p.N) {
+            if (opens) { if (lane == 0) bulkWaitRead(); __syncwarp(); }   // the previous store has read the buffer
+            if (inside) {
+              const uint32_t rowOff = (uint32_t)lane * (uint32_t)tmaW;
+              const uint32_t swz = (rowOff >> 7) & (uint32_t)(tmaW / 16 - 1);
+              const uint32_t rowAddr = smemAddr(outStage) + rowOff;
+              if (outF32) {
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + (((uint32_t)j ^ swz) << 4)), "f"(v[4 * j]), "f"(v[4 * j + 1]),
+                               "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
+              } else {
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                  __nv_bfloat162 a0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), a1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                  __nv_bfloat162 a2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), a3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + (((uint32_t)(sub * 4 + j) ^ swz) << 4)),
+                               "r"(*reinterpret_cast<unsigned*>(&a0)), "r"(*reinterpret_cast<unsigned*>(&a1)), "r"(*reinterpret_cast<unsigned*>(&a2)),
+                               "r"(*reinterpret_cast<unsigned*>(&a3)) : "memory");
+                }
+              }
+            }
+            if (closes) {
+              fenceProxyAsync();
+              __syncwarp();
+              if (lane == 0 && (long long)tileM * BM + q * 32 < p.M) {
+                tmaStore4d(&mapO, outStage, (int)x0, tileM * BM + q * 32, zb1, zb0);
+                bulkCommit();
+              }
+            }
+          }
+        } else if (inside && rowOk) {
+          if (whole) {
             if (outF32) {
               float* dst = reinterpret_cast<float*>(outBase) + oRow + gn0;
 #pragma unroll
@@ -313,23 +377,15 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                 for (int j = 0; j < 32; j += 4) Vec4<__nv_bfloat16>::store(d2 + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
               }
             }
-          }
-        } else if (rowOk) {
-          // ragged edge: element by element
+          } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const long long n = gn0 + j;
-            if (n < p.N) {
-              float x = v[j] * p.alpha;
-              if (p.scale) x *= __ldg(p.scale + n);
-              if (p.shift) x += __ldg(p.shift + n);
-              if (p.res) x += loadAs(p.res, rRow + n * p.r_sn, p.res_dtype);
-              storeAs(p.out, oRow + n, p.out_dtype, applyAct(x, p.act));
-            }
+            for (int j = 0; j < 32; ++j)
+              if (gn0 + j < p.N) storeAs(p.out, oRow + gn0 + j, p.out_dtype, v[j]);
           }
         }
       }
     }
+    if (tmaW && lane == 0) bulkWaitRead();   // shared memory stays valid until the last store has read it
   } else if (CONV && warp < kGatherWarp0 + kGatherWarps) {
     // ---------------------------------------------------------------- im2col gather of A (convolution)
     // 256 threads; thread g owns 16-byte chunk (g & 7) of tile rows (g >> 3) + 32*j, j = 0..3, so that
@@ -395,7 +451,8 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
 #pragma unroll 4
         for (int i = et; i < S::kBBytes / 16; i += 128) { float4 v = srcB[i]; dstB[i] = make_float4(lo(v.x), lo(v.y), lo(v.z), lo(v.w)); }
         fenceProxyAsync();
-        mbarArrive(&split[s]);
+        __syncwarp();
+        if (lane == 0) mbarArrive(&split[s]);
       }
     }
   }
@@ -453,13 +510,43 @@ bool makeMapMn(CUtensorMap* map, const void* base, bool f32, long long N, long l
   return r == CUDA_SUCCESS;
 }
 
+// Output [b0, b1, M, N] with unit stride along N -> 4-D tensor map for the epilogue's stores; box = rowBytes of N x 32 rows,
+// swizzle span = rowBytes (64 or 128).  Returns false when the layout cannot be described (the epilogue then stores directly).
+bool makeOutMap(CUtensorMap* map, void* base, bool f32, long long N, long long M, long long b1, long long b0, long long sRow, long long s1,
+                long long s0, int rowBytes) {
+  EncodeTiledFn enc = encodeTiled();
+  if (!enc) return false;
+  const int eb = f32 ? 4 : 2;
+  const bool has1 = b1 > 1, has0 = b0 > 1;
+  auto ok16 = [&](long long s) { return s > 0 && (s * eb) % 16 == 0; };
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || !ok16(sRow) || sRow < N || (has1 && !ok16(s1)) || (has0 && !ok16(s0))) return false;
+  if (N > (1LL << 31) || M > (1LL << 31)) return false;
+  const long long dense = sRow * M;
+  cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)(has1 ? b1 : 1), (cuuint64_t)(has0 ? b0 : 1)};
+  cuuint64_t strides[3] = {(cuuint64_t)(sRow * eb), (cuuint64_t)((has1 ? s1 : dense) * eb), (cuuint64_t)((has0 ? s0 : dense) * eb)};
+  cuuint32_t box[4] = {(cuuint32_t)(rowBytes / eb), 32, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, base, dims, strides, box, estr,
+                   CU_TENSOR_MAP_INTERLEAVE_NONE, rowBytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B,
+                   CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+// Bytes per row of the output box: a 32-column chunk of fp32, or as much of a warp's share of bf16 columns as fits 128 bytes.
+int outBoxBytes(int bn, bool outF32) { return outF32 ? 128 : (bn / 2 >= 64 ? 128 : 64); }
+
 int numSMs() {
   static int n = []() { int dev = 0, v = kNumSMs; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev); return v > 0 ? v : kNumSMs; }();
   return n;
 }
 
+// LLC_TC_DIRECT_STORES=1 keeps the epilogue on direct global stores (used to compare the two paths).
+bool tmaEpilogueEnabled() {
+  static const bool on = []() { const char* e = getenv("LLC_TC_DIRECT_STORES"); return !(e && e[0] == '1'); }();
+  return on;
+}
+
 template <int BN, int KIND, bool CONV, bool BMN>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, TcArgs a, long long batch, cudaStream_t st) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, TcArgs a, long long batch, cudaStream_t st) {
   using S = Smem<BN, KIND == 2>;
   static bool configured = false;
   if (!configured) {
@@ -471,14 +558,14 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, TcArgs a, long long bat
   a.tiles = (long long)a.mTiles * a.nTiles * batch;
   const int threads = (10 + (CONV ? 8 : 0) + (KIND == 2 ? 4 : 0)) * 32;
   const unsigned grid = (unsigned)(a.tiles < numSMs() ? a.tiles : numSMs());
-  tc_kernel<BN, KIND, CONV, BMN><<<grid, threads, S::kTotal, st>>>(ma, mb, a);
+  tc_kernel<BN, KIND, CONV, BMN><<<grid, threads, S::kTotal, st>>>(ma, mb, mo, a);
   LLC_LAUNCH_CHECK("tc_kernel");
   return LLC_OK;
 }
 
 template <bool CONV, bool BMN>
-int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const TcArgs& a, long long batch, cudaStream_t st) {
-#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, CONV, BMN>(ma, mb, a, batch, st);
+int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcArgs& a, long long batch, cudaStream_t st) {
+#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, CONV, BMN>(ma, mb, mo, a, batch, st);
   TC_CASE(64, 0) TC_CASE(128, 0)
   if constexpr (!BMN) { TC_CASE(64, 1) TC_CASE(64, 2) TC_CASE(128, 1) TC_CASE(128, 2) TC_CASE(256, 0) TC_CASE(256, 1) }
 #undef TC_CASE
@@ -540,7 +627,10 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   const int ob = p->out_dtype == LLC_FLOAT32 ? 4 : 2;
   a.vecOut = (reinterpret_cast<uintptr_t>(p->out) % (ob * 4)) == 0 && p->o_sm % 4 == 0 && p->o_s0 % 4 == 0 && p->o_s1 % 4 == 0 &&
              ((reinterpret_cast<uintptr_t>(p->scale) | reinterpret_cast<uintptr_t>(p->shift)) & 15) == 0;
-  return bmn ? dispatch<false, true>(bn, kind, ma, mb, a, batch, st) : dispatch<false, false>(bn, kind, ma, mb, a, batch, st);
+  CUtensorMap mo = ma;   // a valid map even when unused
+  const int boxBytes = outBoxBytes(bn, ob == 4);
+  if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->n, p->m, p->b1, p->b0, p->o_sm, p->o_s1, p->o_s0, boxBytes)) a.tmaOut = boxBytes;
+  return bmn ? dispatch<false, true>(bn, kind, ma, mb, mo, a, batch, st) : dispatch<false, false>(bn, kind, ma, mb, mo, a, batch, st);
 }
 
 bool tcConvSupported(const LlcConvParams* p) {
@@ -575,7 +665,10 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
              ((reinterpret_cast<uintptr_t>(p->scale) | reinterpret_cast<uintptr_t>(p->shift)) & 15) == 0;
   a.x = p->x; a.H = (int)p->h; a.W = (int)p->w_in; a.C = (int)p->c; a.KH = (int)p->kh; a.KW = (int)p->kw; a.OH = (int)p->oh; a.OW = (int)p->ow;
   a.sh = p->stride_h; a.sw = p->stride_w; a.ph = p->pad_h; a.pw = p->pad_w; a.dh = p->dil_h; a.dw = p->dil_w;
-  return dispatch<true, false>(bn, kind, mb, mb, a, 1, st);
+  CUtensorMap mo = mb;
+  const int boxBytes = outBoxBytes(bn, ob == 4);
+  if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->f, M, 1, 1, p->f, 0, 0, boxBytes)) a.tmaOut = boxBytes;
+  return dispatch<true, false>(bn, kind, mb, mb, mo, a, 1, st);
 }
 
 // Reads and clears the status word the bounded waits write (0 = no wait ever gave up).

@@ -54,6 +54,15 @@ __device__ __forceinline__ void tmaLoad4d(void* smemDst, const CUtensorMap* map,
       ::"r"(smemAddr(smemDst)), "l"((uint64_t)map), "r"(smemAddr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// Tile store from shared memory (bulk-group completion).  Elements of the box that lie past the
+// tensor's extents are not written, which is how M and N tails are clipped.
+__device__ __forceinline__ void tmaStore4d(const CUtensorMap* map, const void* smemSrc, int c0, int c1, int c2, int c3) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.tile.bulk_group [%0, {%2, %3, %4, %5}], [%1];"
+               ::"l"((uint64_t)map), "r"(smemAddr(smemSrc)), "r"(c0), "r"(c1), "r"(c2), "r"(c3) : "memory");
+}
+__device__ __forceinline__ void bulkCommit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// Waits until the bulk stores this thread committed have finished reading shared memory.
+__device__ __forceinline__ void bulkWaitRead() { asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory"); }
 __device__ __forceinline__ void prefetchTensorMap(const CUtensorMap* map) {
   asm volatile("prefetch.tensormap [%0];" ::"l"((uint64_t)map) : "memory");
 }
