@@ -74,11 +74,16 @@ __device__ __forceinline__ void cpAsyncArriveOn(uint64_t* bar) {
 }
 
 // KIND: 0 bf16, 1 tf32, 2 tf32x3.  BMN: B is stored [k][n] (unit stride along n) instead of [n][k].
-template <int BN, int KIND, bool CONV, bool BMN>
-__global__ void __launch_bounds__((10 + (CONV ? 8 : 0) + (KIND == 2 ? 4 : 0)) * 32, 1)
+// MODE: 0 dense GEMM (A by tiled TMA), 1 convolution with A gathered by warps (any channel count that keeps a
+// 16-byte chunk inside one filter tap), 2 convolution with A loaded by TMA in im2col mode (a K block of 128
+// bytes lies inside one filter tap: channels * element size is a multiple of 128).
+template <int BN, int KIND, int MODE, bool BMN>
+__global__ void __launch_bounds__((10 + (MODE == 1 ? 8 : 0) + (KIND == 2 ? 4 : 0)) * 32, 1)
 tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapO, const TcArgs p) {
   constexpr bool X3 = KIND == 2;
   constexpr bool TF32 = KIND != 0;
+  constexpr bool CONV = MODE == 1;      // the gather warps exist
+  constexpr bool IM2COL = MODE == 2;
   using S = Smem<BN, X3>;
   constexpr int kStages = S::kStages;
   constexpr int kElemBytes = TF32 ? 4 : 2;
@@ -137,6 +142,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     // ---------------------------------------------------------------- TMA producer
     if (lane == 0) {
       if (!CONV) prefetchTensorMap(&mapA);
+      int ow0 = 0, oh0 = 0, img0 = 0;
       prefetchTensorMap(&mapB);
       uint32_t it = 0;
       bool ok = true;
@@ -144,11 +150,23 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         const int z = (int)(t / tilesPerBatch); const int rem = (int)(t - z * tilesPerBatch);
         const int tileM = rem / p.nTiles, tileN = rem - tileM * p.nTiles;
         const int zb0 = z / p.b1, zb1 = z - zb0 * p.b1;
+        int tapR = 0, tapS = 0, cc = 0;                      // im2col: filter tap and first channel of the K block
+        if (IM2COL) {
+          const long long m0 = (long long)tileM * BM;          // first output pixel of the tile
+          ow0 = (int)(m0 % p.OW); const long long t2 = m0 / p.OW; oh0 = (int)(t2 % p.OH); img0 = (int)(t2 / p.OH);
+        }
         for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
           if (!mbarWait(&empty[s], ph ^ 1, abortWord)) { atomicExch(&g_tcStatus, 1); ok = false; break; }
           mbarExpectTx(&full[s], CONV ? S::kBBytes : S::kABytes + S::kBBytes);
-          if (!CONV) tmaLoad4d(stageA(s), &mapA, &full[s], kb * BK, tileM * BM, zb1 * p.aZ1, zb0 * p.aZ0);
+          if (MODE == 0) tmaLoad4d(stageA(s), &mapA, &full[s], kb * BK, tileM * BM, zb1 * p.aZ1, zb0 * p.aZ0);
+          if (IM2COL) {
+            // 128 output pixels from (img0, oh0, ow0) on, in w -> h -> n order; the coordinates name the input pixel
+            // under filter tap (0, 0), the offsets select the tap
+            tmaLoadIm2col4d(stageA(s), &mapA, &full[s], cc, ow0 * p.sw - p.pw, oh0 * p.sh - p.ph, img0, (uint16_t)(tapS * p.dw), (uint16_t)(tapR * p.dh));
+            cc += BK;
+            if (cc >= p.C) { cc = 0; if (++tapS == p.KW) { tapS = 0; ++tapR; } }
+          }
           if (BMN) {
 #pragma unroll
             for (int a = 0; a < BN / kAtomN; ++a)
@@ -493,6 +511,55 @@ bool makeMap(CUtensorMap* map, const void* base, bool f32, long long K, long lon
   return r == CUDA_SUCCESS;
 }
 
+typedef CUresult (*EncodeIm2colFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const int*, const int*,
+                                   cuuint32_t, cuuint32_t, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                   CUtensorMapFloatOOBfill);
+EncodeIm2colFn encodeIm2col() {
+  static EncodeIm2colFn fn = []() -> EncodeIm2colFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeIm2col", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeIm2colFn>(p);
+  }();
+  return fn;
+}
+
+// NHWC activations -> im2col tensor map: a load brings 128 output positions x 128 bytes of channels for one filter tap.
+// The bounding box is the set of input pixels that sit under tap (0, 0) of some output position: it starts `pad` pixels
+// before the image and ends (kernel extent - 1 - pad) pixels before its end; the traversal strides are the convolution's.
+bool makeIm2colMap(CUtensorMap* map, const LlcConvParams* p, bool f32) {
+  EncodeIm2colFn enc = encodeIm2col();
+  if (!enc) return false;
+  const int eb = f32 ? 4 : 2;
+  cuuint64_t dims[4] = {(cuuint64_t)p->c, (cuuint64_t)p->w_in, (cuuint64_t)p->h, (cuuint64_t)p->n};
+  cuuint64_t strides[3] = {(cuuint64_t)(p->c * eb), (cuuint64_t)(p->w_in * p->c * eb), (cuuint64_t)(p->h * p->w_in * p->c * eb)};
+  int lower[2] = {-p->pad_w, -p->pad_h};
+  int upper[2] = {p->pad_w - (int)(p->kw - 1) * p->dil_w, p->pad_h - (int)(p->kh - 1) * p->dil_h};
+  cuuint32_t estr[4] = {1, (cuuint32_t)p->stride_w, (cuuint32_t)p->stride_h, 1};
+  CUresult r = enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(p->x), dims, strides, lower, upper,
+                   (cuuint32_t)(kTileKBytes / eb), (cuuint32_t)BM, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                   CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+// Whether the im2col load can serve this convolution: a K block inside one tap, corners and tap offsets inside the
+// ranges the 4-D descriptor and instruction encode, and the output extents exactly those the bounding box yields.
+bool im2colEligible(const LlcConvParams* p, bool f32) {
+  const int eb = f32 ? 4 : 2;
+  static const bool off = []() { const char* e = getenv("LLC_TC_CONV_GATHER"); return e && e[0] == '1'; }();
+  if (off || (p->c * eb) % kTileKBytes != 0) return false;
+  const int lowW = -p->pad_w, lowH = -p->pad_h;
+  const int upW = p->pad_w - (int)(p->kw - 1) * p->dil_w, upH = p->pad_h - (int)(p->kh - 1) * p->dil_h;
+  auto in8 = [](int v) { return v >= -128 && v <= 127; };
+  if (!in8(lowW) || !in8(lowH) || !in8(upW) || !in8(upH)) return false;
+  if ((p->kw - 1) * p->dil_w > 255 || (p->kh - 1) * p->dil_h > 255) return false;
+  if (p->stride_w < 1 || p->stride_w > 8 || p->stride_h < 1 || p->stride_h > 8) return false;
+  const long long extW = p->w_in + upW - lowW, extH = p->h + upH - lowH;     // base positions per row / column
+  if (extW < 1 || extH < 1) return false;
+  if ((extW - 1) / p->stride_w + 1 != p->ow || (extH - 1) / p->stride_h + 1 != p->oh) return false;
+  if (p->n * p->oh * p->ow > (1LL << 31)) return false;
+  return encodeIm2col() != nullptr;
+}
+
 // MN-major operand [b0, b1, K, N] with unit stride along N -> 4-D tensor map, box = 128 bytes of N x boxK rows of K.
 bool makeMapMn(CUtensorMap* map, const void* base, bool f32, long long N, long long K, long long b1, long long b0, long long sK, long long s1,
                long long s0, int boxK) {
@@ -545,27 +612,27 @@ bool tmaEpilogueEnabled() {
   return on;
 }
 
-template <int BN, int KIND, bool CONV, bool BMN>
+template <int BN, int KIND, int MODE, bool BMN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, TcArgs a, long long batch, cudaStream_t st) {
   using S = Smem<BN, KIND == 2>;
   static bool configured = false;
   if (!configured) {
-    cudaError_t e = cudaFuncSetAttribute(tc_kernel<BN, KIND, CONV, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(tc_kernel<BN, KIND, MODE, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return cudaFail(e, "cudaFuncSetAttribute(tc_kernel)");
     configured = true;
   }
   a.mTiles = (int)((a.M + BM - 1) / BM); a.nTiles = (int)((a.N + BN - 1) / BN);
   a.tiles = (long long)a.mTiles * a.nTiles * batch;
-  const int threads = (10 + (CONV ? 8 : 0) + (KIND == 2 ? 4 : 0)) * 32;
+  const int threads = (10 + (MODE == 1 ? 8 : 0) + (KIND == 2 ? 4 : 0)) * 32;
   const unsigned grid = (unsigned)(a.tiles < numSMs() ? a.tiles : numSMs());
-  tc_kernel<BN, KIND, CONV, BMN><<<grid, threads, S::kTotal, st>>>(ma, mb, mo, a);
+  tc_kernel<BN, KIND, MODE, BMN><<<grid, threads, S::kTotal, st>>>(ma, mb, mo, a);
   LLC_LAUNCH_CHECK("tc_kernel");
   return LLC_OK;
 }
 
-template <bool CONV, bool BMN>
+template <int MODE, bool BMN>
 int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcArgs& a, long long batch, cudaStream_t st) {
-#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, CONV, BMN>(ma, mb, mo, a, batch, st);
+#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, MODE, BMN>(ma, mb, mo, a, batch, st);
   TC_CASE(64, 0) TC_CASE(128, 0)
   if constexpr (!BMN) { TC_CASE(64, 1) TC_CASE(64, 2) TC_CASE(128, 1) TC_CASE(128, 2) TC_CASE(256, 0) TC_CASE(256, 1) }
 #undef TC_CASE
@@ -630,7 +697,7 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   CUtensorMap mo = ma;   // a valid map even when unused
   const int boxBytes = outBoxBytes(bn, ob == 4);
   if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->n, p->m, p->b1, p->b0, p->o_sm, p->o_s1, p->o_s0, boxBytes)) a.tmaOut = boxBytes;
-  return bmn ? dispatch<false, true>(bn, kind, ma, mb, mo, a, batch, st) : dispatch<false, false>(bn, kind, ma, mb, mo, a, batch, st);
+  return bmn ? dispatch<0, true>(bn, kind, ma, mb, mo, a, batch, st) : dispatch<0, false>(bn, kind, ma, mb, mo, a, batch, st);
 }
 
 bool tcConvSupported(const LlcConvParams* p) {
@@ -668,7 +735,11 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
   CUtensorMap mo = mb;
   const int boxBytes = outBoxBytes(bn, ob == 4);
   if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->f, M, 1, 1, p->f, 0, 0, boxBytes)) a.tmaOut = boxBytes;
-  return dispatch<true, false>(bn, kind, mb, mb, mo, a, 1, st);
+  if (im2colEligible(p, f32)) {
+    CUtensorMap ma;
+    if (makeIm2colMap(&ma, p, f32)) return dispatch<2, false>(bn, kind, ma, mb, mo, a, 1, st);
+  }
+  return dispatch<1, false>(bn, kind, mb, mb, mo, a, 1, st);
 }
 
 // Reads and clears the status word the bounded waits write (0 = no wait ever gave up).

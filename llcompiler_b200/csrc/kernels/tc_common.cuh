@@ -54,6 +54,17 @@ __device__ __forceinline__ void tmaLoad4d(void* smemDst, const CUtensorMap* map,
       ::"r"(smemAddr(smemDst)), "l"((uint64_t)map), "r"(smemAddr(bar)), "r"(c0), "r"(c1), "r"(c2), "r"(c3)
       : "memory");
 }
+// Im2col-mode load of an NHWC activation tensor: `pixelsPerColumn` (tensor map) consecutive output positions starting at
+// the input pixel (w, h) of image n, walked in w -> h -> n order inside the map's bounding box with its traversal
+// strides; every pixel is displaced by the filter-tap offset (offW, offH); c is the first channel.  Pixels that fall
+// outside the tensor are filled with zeros (padding).
+__device__ __forceinline__ void tmaLoadIm2col4d(void* smemDst, const CUtensorMap* map, uint64_t* bar, int c, int w, int h, int n, uint16_t offW,
+                                                uint16_t offH) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.im2col.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5, %6}], [%2], {%7, %8};"
+      ::"r"(smemAddr(smemDst)), "l"((uint64_t)map), "r"(smemAddr(bar)), "r"(c), "r"(w), "r"(h), "r"(n), "h"(offW), "h"(offH)
+      : "memory");
+}
 // Tile store from shared memory (bulk-group completion).  Elements of the box that lie past the
 // tensor's extents are not written, which is how M and N tails are clipped.
 __device__ __forceinline__ void tmaStore4d(const CUtensorMap* map, const void* smemSrc, int c0, int c1, int c2, int c3) {

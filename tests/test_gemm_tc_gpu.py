@@ -95,6 +95,8 @@ CONV_TC = [
     (4, 64, 56, 56, 64, 3, 1, 1, 1), (4, 64, 56, 56, 256, 1, 1, 0, 1), (4, 128, 28, 28, 256, 1, 2, 0, 1),
     (4, 256, 14, 14, 256, 3, 1, 1, 1), (2, 512, 7, 7, 512, 3, 1, 1, 1), (3, 64, 15, 13, 128, 3, 2, 1, 1),
     (1, 8, 9, 17, 24, 3, 1, 2, 2), (2, 16, 30, 30, 40, 5, 1, 2, 1), (2, 64, 112, 112, 64, 7, 2, 3, 1),
+    # channel counts the im2col TMA load takes (128-byte K blocks inside one tap): dilation, stride with a remainder, asymmetric extents
+    (1, 64, 9, 17, 32, 3, 1, 2, 2), (2, 32, 14, 14, 64, 3, 2, 1, 1), (5, 128, 10, 6, 72, 3, 1, 0, 1), (2, 64, 20, 11, 64, 5, 3, 2, 1),
 ]
 
 
