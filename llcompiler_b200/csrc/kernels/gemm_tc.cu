@@ -639,14 +639,25 @@ int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, con
   return setError(LLC_ERR_INTERNAL, "llc internal: no tensor-core kernel for this tile");
 }
 
-// Tile width: the widest tile that still gives every SM work.
-int chooseBN(long long M, long long N, long long batch, bool allow256) {
+// Tile width by a cost model: a persistent CTA works through ceil(tiles / SMs) tiles, and a tile costs the longer of its
+// main loop (K blocks x a per-block time that grows slowly with the width, because narrow tiles are bound by operand
+// traffic and latency rather than by the tensor pipe) and its epilogue.  Times in microseconds, measured on B200.
+int chooseBN(long long M, long long N, long long batch, bool allow256, int kind, int kBlocks) {
+  static const float kBlockUs[3][3] = {{0.22f, 0.25f, 0.40f}, {0.28f, 0.33f, 0.50f}, {0.60f, 0.75f, 0.f}};   // [kind][width]
+  static const float epilogueUs[3] = {0.8f, 1.2f, 2.0f};
   const long long mT = (M + BM - 1) / BM;
-  auto tiles = [&](long long bn) { return mT * ((N + bn - 1) / bn) * batch; };
-  if (allow256 && N > 128 && tiles(256) >= numSMs()) return 256;
-  if (N > 64 && tiles(128) >= numSMs()) return 128;
-  if (N > 64 && tiles(64) < numSMs() / 2) return 128;   // tiny grids: fewer, larger tiles cost less fixed work
-  return 64;
+  int best = 64; float bestCost = 0.f;
+  for (int i = 0; i < 3; ++i) {
+    const int bn = 64 << i;
+    if (bn == 256 && (!allow256 || kind == 2)) continue;
+    if (i > 0 && N <= bn / 2) continue;                    // at least half of the tile's columns exist
+    const long long tiles = mT * ((N + bn - 1) / bn) * batch;
+    const long long rounds = (tiles + numSMs() - 1) / numSMs();
+    const float loop = kBlocks * kBlockUs[kind][i];
+    const float cost = (float)rounds * ((loop > epilogueUs[i] ? loop : epilogueUs[i]) + 0.3f);
+    if (i == 0 || cost <= bestCost) { best = bn; bestCost = cost; }
+  }
+  return best;
 }
 
 }  // namespace
@@ -678,7 +689,7 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   const long long batch = p->b0 * p->b1;
   const bool bmn = p->b_sk != 1;
   const int kind = !f32 ? 0 : (p->precision == LLC_PREC_TF32X3 ? 2 : 1);
-  const int bn = chooseBN(p->m, p->n, batch, kind != 2 && !bmn);
+  const int bn = chooseBN(p->m, p->n, batch, !bmn, kind, (int)((p->k + bk - 1) / bk));
   CUtensorMap ma, mb;
   bool okMaps = makeMap(&ma, p->a, f32, p->k, p->m, p->b1, p->b0, p->a_sm, p->a_s1, p->a_s0, BM);
   okMaps = okMaps && (bmn ? makeMapMn(&mb, p->b, f32, p->n, p->k, p->b1, p->b0, p->b_sk, p->b_s1, p->b_s0, bk)
@@ -718,7 +729,7 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
   const int bk = kTileKBytes / eb;
   const long long M = p->n * p->oh * p->ow, K = p->kh * p->kw * p->c;
   const int kind = !f32 ? 0 : (p->precision == LLC_PREC_TF32X3 ? 2 : 1);
-  const int bn = chooseBN(M, p->f, 1, kind != 2);
+  const int bn = chooseBN(M, p->f, 1, true, kind, (int)((K + bk - 1) / bk));
   CUtensorMap mb;
   if (!makeMap(&mb, p->w, f32, K, p->f, 1, 1, K, 0, 0, bn))
     return setError(LLC_ERR_CUDA, "llc cuda: cuTensorMapEncodeTiled rejected the convolution weights");
