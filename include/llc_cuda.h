@@ -58,8 +58,29 @@ int llc_cuda_gemm(const LlcGemmParams* p, void* stream);
  * Calls no cudaMalloc / cudaFree. */
 int llc_cuda_gemm_static_scratch(const LlcGemmParams* p, void* stream);
 
+/* out[b0,b1,m,:] = softmax_n(scale * sum_d Q[b0,b1,m,d] K[b0,b1,n,d] + mask[b0,b1,m,n]) V[b0,b1,n,:] in one kernel: the
+ * scores stay in tensor memory, the probabilities in shared memory.  Replaces the chain llh.batch_matmul -> llh.div /
+ * llh.add (scale, mask) -> softmax (decomposed by llcompiler/compiler/torch_compile_config.py:24) -> llh.batch_matmul that
+ * the reference lowers op by op (src/Conversion/LLHToHLO/LLHToHLO.cpp:363-382).  bf16 operands and output with unit
+ * stride along d, d == 64, 1 <= n <= 384; every other stride a non-negative multiple of 8 elements (0 = broadcast for
+ * batch strides), pointers 16-byte aligned.  mask may be NULL; it has unit stride along n and may broadcast over
+ * b0, b1 and m (stride 0).  Anything else returns LLC_ERR_UNSUPPORTED. */
+typedef struct LlcAttentionParams {
+  const void* q; const void* k; const void* v; const void* mask; void* out;
+  int32_t dtype;        /* LLC_BFLOAT16 */
+  int32_t mask_dtype;   /* LLC_FLOAT32 or LLC_BFLOAT16 */
+  int64_t b0, b1, m, n, d;
+  int64_t q_s0, q_s1, q_sm;
+  int64_t k_s0, k_s1, k_sn;
+  int64_t v_s0, v_s1, v_sn;
+  int64_t o_s0, o_s1, o_sm;
+  int64_t mask_s0, mask_s1, mask_sm;
+  float scale;
+} LlcAttentionParams;
+int llc_cuda_attention(const LlcAttentionParams* p, void* stream);
+
 /* Health word of the tensor-core kernels.  Their waits on memory barriers are bounded; a wait that
- * gives up records 1 (producer), 2 (issuer), 3 (operand split) or 4 (epilogue) and the launch's
+ * gives up records 1 (producer), 2 (issuer), 3 (operand split), 4 (epilogue), 5 (gather), 6 or 7 (attention) and the launch's
  * result is then invalid.  Returns the recorded code (0 = healthy) and clears it; -1 if the device
  * cannot be read.  Synchronises the device.  No counterpart in the reference. */
 int llc_cuda_status(void);

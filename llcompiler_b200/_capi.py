@@ -109,6 +109,13 @@ class LlcConvParams(Structure):
                [("alpha", c_float), ("act", c_int32)]
 
 
+class LlcAttentionParams(Structure):
+    _fields_ = [("q", c_void_p), ("k", c_void_p), ("v", c_void_p), ("mask", c_void_p), ("out", c_void_p),
+                ("dtype", c_int32), ("mask_dtype", c_int32)] + [(n, c_int64) for n in (
+                    "b0", "b1", "m", "n", "d", "q_s0", "q_s1", "q_sm", "k_s0", "k_s1", "k_sn", "v_s0", "v_s1", "v_sn",
+                    "o_s0", "o_s1", "o_sm", "mask_s0", "mask_s1", "mask_sm")] + [("scale", c_float)]
+
+
 class LlcPoolParams(Structure):
     _fields_ = [("x", c_void_p), ("out", c_void_p), ("in_dtype", c_int32), ("out_dtype", c_int32)] + \
                [(n, c_int64) for n in ("n", "h", "w", "c", "oh", "ow")] + \
@@ -128,5 +135,5 @@ EXPORTED_SYMBOLS = [
     "llc_compile", "llc_run_pass", "llc_load", "llc_num_inputs", "llc_num_outputs", "llc_num_symbols",
     "llc_output_shape", "llc_run", "llc_profile", "llc_last_launch_count", "llc_arena_bytes", "llc_free", "llc_last_error",
     "llc_version", "llc_cuda_gemm", "llc_cuda_conv2d", "llc_cuda_maxpool2d", "llc_cuda_reduce",
-    "llc_cuda_softmax", "llc_cuda_layernorm", "llc_cuda_gather", "llc_cuda_eltwise", "llc_cuda_status", "llc_cuda_nchw_to_nhwc", "llc_cuda_gemm_static_scratch",
+    "llc_cuda_softmax", "llc_cuda_layernorm", "llc_cuda_gather", "llc_cuda_eltwise", "llc_cuda_status", "llc_cuda_nchw_to_nhwc", "llc_cuda_gemm_static_scratch", "llc_cuda_attention",
 ]

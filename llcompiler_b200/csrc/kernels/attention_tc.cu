@@ -1,0 +1,270 @@
+// Fused attention for sm_100a: out = softmax(scale * Q K^T + mask) V for one (batch, head, 128-query block)
+// per CTA, bf16 operands, head size 64, up to 384 keys.  The score tile never leaves the SM:
+//   warp 8, lane 0   TMA loads of Q, K and V (128-byte swizzle), then tcgen05.mma S = Q K^T into tensor memory
+//                    (128 lanes x up to 384 fp32 columns); after the softmax warps have written P, O = P V into 64
+//                    further columns.
+//   warps 0-7        softmax straight out of tensor memory: thread = one query row and every other 32-column chunk;
+//                    pass 1 row maximum, pass 2 exp2 and row sum, P written as bf16 into shared memory in the K-major
+//                    swizzled layout the second MMA reads; then the epilogue O / rowsum -> bf16 -> global.
+// Replaces batch_matmul -> (scale, mask add) -> softmax -> batch_matmul of the reference's decomposed attention
+// (llcompiler/compiler/torch_compile_config.py:24 decomposes aten._softmax; the matmuls lower through
+// src/Conversion/LLHToHLO/LLHToHLO.cpp:363-382).  Algorithmic HBM bytes: Q + K + V + out (+ mask); the S x S
+// scores and probabilities of the unfused path (3 x b0*b1*M*N elements of traffic) never reach memory.
+#include "common.cuh"
+#include "tc_common.cuh"
+
+namespace llc {
+__device__ int g_attnStatus = 0;   // non-zero after a bounded wait gave up: 6 loader/issuer thread, 7 softmax warps
+
+namespace {
+using namespace tc;
+
+constexpr int kD = 64;            // head size (one 128-byte swizzle atom of bf16)
+constexpr int kBM = 128;          // query rows per CTA
+constexpr int kMaxN = 384;        // keys: 384 score columns + 64 output columns of tensor memory
+constexpr int kTile = kBM * 128;  // bytes of a 128-row x 128-byte tile
+constexpr int kSoftmaxThreads = 256;
+constexpr float kLog2e = 1.4426950408889634f;
+
+struct AttnArgs {
+  void* out; const void* mask; int mask_dtype;
+  long long M, N;
+  long long o_s0, o_s1, o_sm, m_s0, m_s1, m_sm;
+  int b1, mTiles, nBlocks, kAtoms;   // key blocks of 128 (first MMA), key atoms of 64 (second MMA)
+  int qZ0, qZ1, kZ0, kZ1, vZ0, vZ1;  // 1: the operand has this batch dim, 0: broadcast
+  float scaleLog2e;
+};
+
+constexpr int kSmemBytes = kTile /*Q*/ + 3 * kTile /*K*/ + 3 * kTile /*V*/ + 6 * kTile /*P*/ + 4096 /*barriers, row statistics, mask row*/ + 1024;
+
+__device__ __forceinline__ float fastExp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
+__device__ __forceinline__ void softmaxBarrier() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory"); }
+
+__global__ void __launch_bounds__(kSoftmaxThreads + 32, 1)
+attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
+                 const AttnArgs p) {
+  extern __shared__ uint8_t smemRaw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
+  uint8_t* sQ = smem;
+  uint8_t* sK = sQ + kTile;
+  uint8_t* sV = sK + 3 * kTile;
+  uint8_t* sP = sV + 3 * kTile;
+  uint8_t* misc = sP + 6 * kTile;
+  uint64_t* bars = reinterpret_cast<uint64_t*>(misc);          // [0] Q,K landed  [1] V landed  [2] S done  [3] P written  [4] O done
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(misc + 64);
+  volatile int* abortWord = reinterpret_cast<volatile int*>(misc + 68);
+  float* sMax = reinterpret_cast<float*>(misc + 128);           // [2][128]
+  float* sSum = sMax + 256;                                     // [2][128]
+  float* sMask = sSum + 256;                                    // [384] mask row * log2(e); -inf past the last key
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int z = blockIdx.x / p.mTiles, tileM = blockIdx.x - z * p.mTiles;
+  const int zb0 = z / p.b1, zb1 = z - zb0 * p.b1;
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < 5; ++i) mbarInit(&bars[i], 1);
+    *abortWord = 0;
+    fenceBarrierInit();
+  }
+  if (warp == 8) tmemAlloc(tmemSlot, 512);
+  tcFenceBefore();
+  __syncthreads();
+  tcFenceAfter();
+  const uint32_t tmemBase = *tmemSlot;
+  const bool rowMask = p.mask == nullptr || p.m_sm == 0;        // the mask does not depend on the query row
+
+  if (warp == 8) {
+    if (lane == 0) {
+      prefetchTensorMap(&mapQ); prefetchTensorMap(&mapK); prefetchTensorMap(&mapV);
+      mbarExpectTx(&bars[0], (1 + p.nBlocks) * kTile);
+      tmaLoad4d(sQ, &mapQ, &bars[0], 0, tileM * kBM, zb1 * p.qZ1, zb0 * p.qZ0);
+      for (int j = 0; j < p.nBlocks; ++j) tmaLoad4d(sK + j * kTile, &mapK, &bars[0], 0, j * 128, zb1 * p.kZ1, zb0 * p.kZ0);
+      mbarExpectTx(&bars[1], p.nBlocks * kTile);
+      for (int j = 0; j < p.nBlocks; ++j) tmaLoad4d(sV + j * kTile, &mapV, &bars[1], 0, j * 128, zb1 * p.vZ1, zb0 * p.vZ0);
+      // S = Q K^T: one 128 x 128 block of scores per 128 keys, K = 64 in four steps of 16
+      bool ok = mbarWait(&bars[0], 0, abortWord);
+      if (!ok) atomicExch(&g_attnStatus, 6);
+      tcFenceAfter();
+      constexpr uint32_t idescS = instrDesc(1, kBM, 128, 0, 0);
+      const uint64_t dQ = smemDescKMajorSw128(smemAddr(sQ));
+      for (int j = 0; j < p.nBlocks; ++j) {
+        const uint64_t dK = smemDescKMajorSw128(smemAddr(sK + j * kTile));
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mmaSS<false>(tmemBase + (uint32_t)(j * 128), dQ + 2 * k, dK + 2 * k, idescS, k > 0 ? 1u : 0u);
+      }
+      mmaCommit(&bars[2]);
+      // O = P V: P is K-major (keys along K) in atoms of 64 keys, V is the MN-major operand (head dim contiguous)
+      ok = mbarWait(&bars[3], 0, abortWord) && mbarWait(&bars[1], 0, abortWord);
+      if (!ok) atomicExch(&g_attnStatus, 6);
+      tcFenceAfter();
+      constexpr uint32_t idescO = instrDesc(1, kBM, kD, 0, 1);
+      for (int a = 0; a < p.kAtoms; ++a) {
+        const uint64_t dP = smemDescKMajorSw128(smemAddr(sP + a * kTile));
+        const uint64_t dV = smemDescMnMajorSw128(smemAddr(sV + a * 64 * 128), 64 * 128);
+#pragma unroll
+        for (int k = 0; k < 4; ++k) mmaSS<false>(tmemBase + kMaxN, dP + 2 * k, dV + (uint64_t)(k * ((16 * 128) >> 4)), idescO, (a > 0 || k > 0) ? 1u : 0u);
+      }
+      mmaCommit(&bars[4]);
+    }
+  } else {
+    // ---------------------------------------------------------------- softmax and epilogue (warps 0-7)
+    const int q = warp & 3, h = warp >> 2;             // tensor-memory lane quarter (a hardware rule) and chunk parity
+    const int row = q * 32 + lane;
+    const long long gm = (long long)tileM * kBM + row;
+    const uint32_t trow = tmemBase + ((uint32_t)(q * 32) << 16);
+    const int nChunks = p.nBlocks * 4;
+    // mask row (times log2 e) into shared memory; columns past the last key get -inf
+    if (rowMask) {
+      const long long mBase = zb0 * p.m_s0 + zb1 * p.m_s1;
+      for (int c = threadIdx.x; c < kMaxN; c += kSoftmaxThreads)
+        sMask[c] = c < p.N ? (p.mask ? loadAs(p.mask, mBase + c, p.mask_dtype) * kLog2e : 0.f) : -INFINITY;
+    }
+    softmaxBarrier();
+    const long long mRow = zb0 * p.m_s0 + zb1 * p.m_s1 + gm * p.m_sm;
+    auto logit = [&](float s, int col) -> float {      // scaled score plus mask, in units of log2
+      if (rowMask) return fmaf(s, p.scaleLog2e, sMask[col]);
+      if (col >= p.N || gm >= p.M) return col < p.N ? s * p.scaleLog2e : -INFINITY;
+      return fmaf(s, p.scaleLog2e, loadAs(p.mask, mRow + col, p.mask_dtype) * kLog2e);
+    };
+    bool ok = mbarWait(&bars[2], 0, abortWord);
+    if (!ok) atomicExch(&g_attnStatus, 7);
+    tcFenceAfter();
+    float mx = -INFINITY;
+    for (int c = h; c < nChunks; c += 2) {
+      float v[32];
+      __syncwarp();
+      tmemLoad32x32(trow + (uint32_t)(c * 32), v);
+#pragma unroll
+      for (int j = 0; j < 32; ++j) mx = fmaxf(mx, logit(v[j], c * 32 + j));
+    }
+    sMax[h * 128 + row] = mx;
+    softmaxBarrier();
+    mx = fmaxf(sMax[row], sMax[128 + row]);
+    if (mx == -INFINITY) mx = 0.f;                     // a fully masked row: all probabilities become 0
+    float sum = 0.f;
+    for (int c = h; c < nChunks; c += 2) {
+      float v[32];
+      __syncwarp();
+      tmemLoad32x32(trow + (uint32_t)(c * 32), v);
+      const uint32_t rowAddr = smemAddr(sP + (c >> 1) * kTile) + (uint32_t)row * 128u;
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 pk[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          const int col = c * 32 + j * 8 + e * 2;
+          pk[e] = __floats2bfloat162_rn(fastExp2(logit(v[j * 8 + e * 2], col) - mx), fastExp2(logit(v[j * 8 + e * 2 + 1], col + 1) - mx));
+          const float2 f = __bfloat1622float2(pk[e]);
+          sum += f.x + f.y;                            // the sum of what the second MMA will actually read
+        }
+        const uint32_t chunk = (uint32_t)((c & 1) * 4 + j);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + ((chunk ^ (uint32_t)(row & 7)) << 4)), "r"(*reinterpret_cast<unsigned*>(&pk[0])),
+                     "r"(*reinterpret_cast<unsigned*>(&pk[1])), "r"(*reinterpret_cast<unsigned*>(&pk[2])), "r"(*reinterpret_cast<unsigned*>(&pk[3])) : "memory");
+      }
+    }
+    sSum[h * 128 + row] = sum;
+    tcFenceBefore();
+    fenceProxyAsync();                                 // P was written through the generic proxy, the MMA reads it through the async proxy
+    softmaxBarrier();
+    if (threadIdx.x == 0) mbarArrive(&bars[3]);
+    const float inv = 1.f / (sSum[row] + sSum[128 + row]);
+    ok = mbarWait(&bars[4], 0, abortWord);
+    if (!ok) atomicExch(&g_attnStatus, 7);
+    tcFenceAfter();
+    float o[32];
+    __syncwarp();
+    tmemLoad32x32(trow + (uint32_t)(kMaxN + h * 32), o);
+    if (gm < p.M) {
+      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + zb0 * p.o_s0 + zb1 * p.o_s1 + gm * p.o_sm + h * 32);
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        __nv_bfloat162 a0 = __floats2bfloat162_rn(o[8 * j] * inv, o[8 * j + 1] * inv), a1 = __floats2bfloat162_rn(o[8 * j + 2] * inv, o[8 * j + 3] * inv);
+        __nv_bfloat162 a2 = __floats2bfloat162_rn(o[8 * j + 4] * inv, o[8 * j + 5] * inv), a3 = __floats2bfloat162_rn(o[8 * j + 6] * inv, o[8 * j + 7] * inv);
+        uint4 pk; pk.x = *reinterpret_cast<unsigned*>(&a0); pk.y = *reinterpret_cast<unsigned*>(&a1); pk.z = *reinterpret_cast<unsigned*>(&a2); pk.w = *reinterpret_cast<unsigned*>(&a3);
+        dst[j] = pk;
+      }
+    }
+  }
+  tcFenceBefore();
+  __syncthreads();
+  if (warp == 8) { tcFenceAfter(); tmemDealloc(tmemBase, 512); }
+}
+
+// ---- host side ------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*, const cuuint32_t*,
+                                  const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeTiledFn encodeTiled() {
+  static EncodeTiledFn fn = []() -> EncodeTiledFn {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess || q != cudaDriverEntryPointSuccess) return nullptr;
+    return reinterpret_cast<EncodeTiledFn>(p);
+  }();
+  return fn;
+}
+
+// bf16 operand [b0, b1, rows, 64] with unit stride along the head dim -> 4-D tensor map, box = 64 elements x 128 rows.
+bool makeHeadMap(CUtensorMap* map, const void* base, long long rows, long long b1, long long b0, long long sRow, long long s1, long long s0) {
+  EncodeTiledFn enc = encodeTiled();
+  if (!enc) return false;
+  const bool has1 = b1 > 1 && s1 > 0, has0 = b0 > 1 && s0 > 0;
+  const long long dense = sRow * rows;
+  cuuint64_t dims[4] = {(cuuint64_t)kD, (cuuint64_t)rows, (cuuint64_t)(has1 ? b1 : 1), (cuuint64_t)(has0 ? b0 : 1)};
+  cuuint64_t strides[3] = {(cuuint64_t)(sRow * 2), (cuuint64_t)((has1 ? s1 : dense) * 2), (cuuint64_t)((has0 ? s0 : dense) * 2)};
+  cuuint32_t box[4] = {(cuuint32_t)kD, 128, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  return enc(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+             CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+}  // namespace
+
+// Reads and clears the attention kernel's status word.
+int attnStatus() {
+  int v = 0, zero = 0;
+  if (cudaMemcpyFromSymbol(&v, g_attnStatus, sizeof(int)) != cudaSuccess) return -1;
+  if (v) cudaMemcpyToSymbol(g_attnStatus, &zero, sizeof(int));
+  return v;
+}
+
+}  // namespace llc
+
+using namespace llc;
+
+extern "C" int llc_cuda_attention(const LlcAttentionParams* p, void* stream) {
+  if (!p || !p->q || !p->k || !p->v || !p->out) return setError(LLC_ERR_ARGUMENT, "llc_cuda_attention: null operand");
+  if (p->dtype != LLC_BFLOAT16) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: operands must be bf16");
+  if (p->d != kD) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: head size must be 64");
+  if (p->n < 1 || p->n > kMaxN) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: 1 to 384 keys");
+  if (p->m < 1 || p->b0 < 1 || p->b1 < 1) return setError(LLC_ERR_ARGUMENT, "llc_cuda_attention: empty problem");
+  if (p->mask && p->mask_dtype != LLC_FLOAT32 && p->mask_dtype != LLC_BFLOAT16) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: mask must be f32 or bf16");
+  auto ok8 = [](long long s) { return s >= 0 && s % 8 == 0; };    // 16-byte multiples of bf16
+  if (!ok8(p->q_s0) || !ok8(p->q_s1) || !ok8(p->q_sm) || !ok8(p->k_s0) || !ok8(p->k_s1) || !ok8(p->k_sn) || !ok8(p->v_s0) || !ok8(p->v_s1) || !ok8(p->v_sn) ||
+      !ok8(p->o_s0) || !ok8(p->o_s1) || !ok8(p->o_sm) || p->q_sm < kD || p->k_sn < kD || p->v_sn < kD || p->o_sm < kD)
+    return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: strides must be non-negative multiples of 8 elements and rows must not overlap");
+  if ((reinterpret_cast<uintptr_t>(p->q) | reinterpret_cast<uintptr_t>(p->k) | reinterpret_cast<uintptr_t>(p->v) | reinterpret_cast<uintptr_t>(p->out)) & 15)
+    return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: operands must be 16-byte aligned");
+  const long long batch = p->b0 * p->b1, mTiles = (p->m + kBM - 1) / kBM;
+  if (batch * mTiles > 0x7FFFFFFFLL) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: too many tiles");
+  CUtensorMap mq, mk, mv;
+  if (!makeHeadMap(&mq, p->q, p->m, p->b1, p->b0, p->q_sm, p->q_s1, p->q_s0) || !makeHeadMap(&mk, p->k, p->n, p->b1, p->b0, p->k_sn, p->k_s1, p->k_s0) ||
+      !makeHeadMap(&mv, p->v, p->n, p->b1, p->b0, p->v_sn, p->v_s1, p->v_s0))
+    return setError(LLC_ERR_CUDA, "llc cuda: cuTensorMapEncodeTiled rejected the attention operands");
+  AttnArgs a{};
+  a.out = p->out; a.mask = p->mask; a.mask_dtype = p->mask_dtype;
+  a.M = p->m; a.N = p->n;
+  a.o_s0 = p->o_s0; a.o_s1 = p->o_s1; a.o_sm = p->o_sm; a.m_s0 = p->mask_s0; a.m_s1 = p->mask_s1; a.m_sm = p->mask_sm;
+  a.b1 = (int)p->b1; a.mTiles = (int)mTiles; a.nBlocks = (int)((p->n + 127) / 128); a.kAtoms = (int)((p->n + 63) / 64);
+  a.qZ0 = p->b0 > 1 && p->q_s0 > 0; a.qZ1 = p->b1 > 1 && p->q_s1 > 0; a.kZ0 = p->b0 > 1 && p->k_s0 > 0; a.kZ1 = p->b1 > 1 && p->k_s1 > 0;
+  a.vZ0 = p->b0 > 1 && p->v_s0 > 0; a.vZ1 = p->b1 > 1 && p->v_s1 > 0;
+  a.scaleLog2e = p->scale * kLog2e;
+  static bool configured = false;
+  if (!configured) {
+    cudaError_t e = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e != cudaSuccess) return cudaFail(e, "cudaFuncSetAttribute(attention_kernel)");
+    configured = true;
+  }
+  attention_kernel<<<(unsigned)(batch * mTiles), kSoftmaxThreads + 32, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, a);
+  LLC_LAUNCH_CHECK("attention_kernel");
+  return LLC_OK;
+}

@@ -10,6 +10,7 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st);
 bool tcConvSupported(const LlcConvParams* p);
 int tcConv(const LlcConvParams* p, cudaStream_t st);
 int tcStatus();
+int attnStatus();
 }  // namespace llc
 
 using namespace llc;
@@ -27,7 +28,10 @@ extern "C" int llc_cuda_gemm(const LlcGemmParams* p, void* stream) {
   return igemmSimtGemm(p, (cudaStream_t)stream, p->workspace, p->workspace_bytes);
 }
 
-extern "C" int llc_cuda_status(void) { return tcStatus(); }
+extern "C" int llc_cuda_status(void) {
+  const int a = tcStatus(), b = attnStatus();
+  return a ? a : b;
+}
 
 extern "C" int llc_cuda_conv2d(const LlcConvParams* p, void* stream) {
   if (!p) return setError(LLC_ERR_ARGUMENT, "llc argument: conv null parameter block");

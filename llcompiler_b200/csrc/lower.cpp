@@ -36,7 +36,7 @@ struct ENode {
 };
 
 struct TV {
-  enum Kind { None, Scalar, ViewK, Lazy, Pending, Deferred } kind = None;
+  enum Kind { None, Scalar, ViewK, Lazy, Pending, Deferred, AttnProb } kind = None;
   Expr scalar;                 // Scalar (i64)
   double fscalar = 0; bool isFloatScalar = false;
   DType dtype = DType::F32;
@@ -44,8 +44,14 @@ struct TV {
   View view;                   // ViewK / Pending (logical view onto the result buffer) / Deferred (source)
   int root = -1;               // Lazy
   int pending = -1;            // Pending
+  int attn = -1;               // AttnProb: softmax of a not-yet-emitted score GEMM (index into Lowering::attn); view = where the
+                               // probabilities go if some consumer other than the second GEMM needs them
   bool isConst = false;        // computable at load time
 };
+
+// softmax(Q K^T) waiting for its consumer: a GEMM with V turns the three ops into one attention step, anything else
+// materialises the scores and the probabilities the ordinary way.
+struct AttnCand { int pending = -1; bool materialized = false; };
 
 struct PendingK {
   Step step;
@@ -155,6 +161,7 @@ struct Lowering {
   Plan plan;
   std::vector<ENode> nodes;
   std::vector<PendingK> pend;
+  std::vector<AttnCand> attn;
   std::map<Value*, TV> tvs;
   std::map<std::string, int> constVecCache;
 
@@ -305,6 +312,7 @@ struct Lowering {
     p.emitted = true;
     Step s = p.step;
     s.views.emplace_back("out", p.nativeOut);
+    if (s.kernel == "attention") { plan.steps.push_back(s); return; }
     double alpha = 1.0;
     Expr C = p.nativeOut.shape[p.chanDim];
     auto vec = [&](int root, const char* name) {
@@ -335,13 +343,29 @@ struct Lowering {
     if (it == tvs.end()) fail("value " + v->name + " used before definition");
     return it->second;
   }
-  void settle(TV& t) { if (t.kind == TV::Pending && pend[t.pending].emitted) { t.kind = TV::ViewK; } }
+  void settle(TV& t) {
+    if (t.kind == TV::Pending && pend[t.pending].emitted) { t.kind = TV::ViewK; }
+    if (t.kind == TV::AttnProb && attn[t.attn].materialized) { t.kind = TV::ViewK; }
+  }
 
   // Forces a value into a strided view (emitting whatever produces it).
   void toView(TV& t) {
     settle(t);
     if (t.kind == TV::ViewK) return;
     if (t.kind == TV::Pending) { emitPending(t.pending); t.kind = TV::ViewK; return; }
+    if (t.kind == TV::AttnProb) {
+      // not consumed by a GEMM with V after all: scores, then a row softmax into the buffer t.view lives in
+      AttnCand& c = attn[t.attn];
+      PendingK& P = pend[c.pending];
+      emitPending(c.pending);
+      const View& sc = P.nativeOut;
+      Expr rows = sc.shape[0] * sc.shape[1] * sc.shape[2];
+      View x2 = sc; x2.shape = {rows, sc.shape[3]}; x2.strides = {sc.shape[3], Expr(1)};
+      View o2 = t.view; o2.offset = Expr(0); o2.shape = x2.shape; o2.strides = x2.strides;
+      Step st; st.kernel = "softmax"; st.views.emplace_back("x", x2); st.views.emplace_back("out", o2);
+      plan.steps.push_back(st);
+      c.materialized = true; t.kind = TV::ViewK; return;
+    }
     if (t.kind == TV::Lazy) {
       View v = materializeTree(t.root, t.dtype, t.shape);
       t.isConst = bufIsConst(v.buf);
@@ -361,7 +385,7 @@ struct Lowering {
     TV& t = raw(v);
     settle(t);
     // a value with several consumers is computed once
-    if (v->users.size() > 1 && (t.kind == TV::Pending || (t.kind == TV::Lazy && nodes[t.root].kind != ENode::Const && !isCheap(t.root))))
+    if (v->users.size() > 1 && (t.kind == TV::Pending || t.kind == TV::AttnProb || (t.kind == TV::Lazy && nodes[t.root].kind != ENode::Const && !isCheap(t.root))))
       toView(t);
     return t;
   }
@@ -476,6 +500,7 @@ struct Lowering {
     settle(pt);
     if (pt.kind != TV::Pending || pv->users.size() != 1) return false;
     PendingK& P = pend[pt.pending];
+    if (P.step.kernel == "attention") return false;
     // channel dim of the current logical view: unit stride, extent = channel count
     Expr C = P.nativeOut.shape[P.chanDim];
     int cd = -1;
@@ -606,7 +631,73 @@ struct Lowering {
     if (!ok) { std::vector<Expr> rm = rowMajor(x.shape); x = materializeTree(leafNode(x), x.dtype, x.shape, &rm); }
     return x;
   }
+  // Whether a pending GEMM is the score matrix the fused attention kernel can produce itself: bf16 Q and K with a
+  // head size of 64 read along their unit-stride dim, at most 384 keys (a compile-time constant), nothing absorbed but
+  // a constant scale and an additive mask with unit stride along the keys, and the logical view still the plain
+  // [.., M, N] matrix.
+  bool attentionScores(const TV& t) {
+    if (opts.fuseAttention == false) return false;
+    const PendingK& P = pend[t.pending];
+    if (P.emitted || P.step.kernel != "gemm" || P.act != "none" || P.shiftRoot >= 0) return false;
+    if (P.scaleRoot >= 0 && nodes[P.scaleRoot].kind != ENode::Const) return false;
+    const View* a = nullptr; const View* b = nullptr;
+    for (auto& v : P.step.views) { if (v.first == "a") a = &v.second; if (v.first == "b") b = &v.second; }
+    if (!a || !b || a->dtype != DType::BF16 || b->dtype != DType::BF16) return false;
+    if (!a->shape[3].isConst(64) || !a->strides[3].isConst(1) || !b->strides[2].isConst(1)) return false;
+    const Expr& N = b->shape[3];
+    if (!N.isConst() || N.constant() < 1 || N.constant() > 384) return false;
+    auto mult8 = [](const Expr& e) { return e.isConst() && e.constant() >= 0 && e.constant() % 8 == 0; };
+    if (!mult8(a->strides[0]) || !mult8(a->strides[1]) || !mult8(a->strides[2]) || !mult8(b->strides[0]) || !mult8(b->strides[1]) || !mult8(b->strides[3]) ||
+        !mult8(a->offset) || !mult8(b->offset)) return false;
+    if (P.hasRes && !(P.res.strides[3].isConst(1) || P.res.shape[3].isConst(1))) return false;
+    if (t.view.shape.empty() || !(t.view.shape.back() == N) || t.view.strides != rowMajor(t.view.shape) || !t.view.offset.isConst(0)) return false;
+    return true;
+  }
+  // probs x V where probs is the softmax of pending scores: one attention step instead of GEMM, softmax, GEMM.
+  bool tryAttention(Op* op, TV& pt, bool batched) {
+    PendingK& S = pend[attn[pt.attn].pending];
+    if (S.emitted || attn[pt.attn].materialized) return false;
+    if (pt.view.shape.empty() || pt.view.strides != rowMajor(pt.view.shape) || !(pt.view.shape.back() == S.nativeOut.shape[3])) return false;
+    std::vector<Expr> splitB;
+    View v = gemmOperand(op->operands[1], true, &splitB);
+    const Expr b0 = S.nativeOut.shape[0], b1 = S.nativeOut.shape[1], M = S.nativeOut.shape[2], N = S.nativeOut.shape[3];
+    View v4;
+    if (v.rank() == 4) v4 = v;
+    else if (v.rank() == 3) { v4 = v; v4.shape = {b0, b1, v.shape[1], v.shape[2]}; v4.strides = {v.strides[0] * b1, v.strides[0], v.strides[1], v.strides[2]}; }
+    else if (v.rank() == 2) { v4 = v; v4.shape = {Expr(1), Expr(1), v.shape[0], v.shape[1]}; v4.strides = {Expr(0), Expr(0), v.strides[0], v.strides[1]}; }
+    else return false;
+    if (v.rank() == 3 && !(v.shape[0] == b0 * b1)) return false;
+    if (v.rank() == 4 && (!(v4.shape[0] == b0) || !(v4.shape[1] == b1))) return false;
+    auto mult8 = [](const Expr& e) { return e.isConst() && e.constant() >= 0 && e.constant() % 8 == 0; };
+    if (v4.dtype != DType::BF16 || !v4.shape[3].isConst(64) || !v4.strides[3].isConst(1) || !(v4.shape[2] == N)) return false;
+    if (!mult8(v4.strides[0]) || !mult8(v4.strides[1]) || !mult8(v4.strides[2]) || !mult8(v4.offset)) return false;
+    DType dt = op->results[0]->type.elt;
+    if (dt != DType::BF16) return false;
+    PendingK P;
+    P.step.kernel = "attention";
+    for (auto& sv : S.step.views) { if (sv.first == "a") P.step.views.emplace_back("q", sv.second); if (sv.first == "b") P.step.views.emplace_back("k", sv.second); }
+    P.step.views.emplace_back("v", v4);
+    if (S.hasRes) P.step.views.emplace_back("mask", S.res);
+    P.step.params.emplace_back("scale", fmtDouble(S.scaleRoot >= 0 ? nodes[S.scaleRoot].cst : 1.0));
+    std::vector<Expr> nshape = {b0, b1, M, Expr(64)};
+    P.nativeOut = freshView(dt, nshape, false);
+    P.buf = P.nativeOut.buf;
+    P.chanDim = 3;
+    pend.push_back(P);
+    S.emitted = true;                     // the scores are never written
+    attn[pt.attn].materialized = false;
+    TV t; t.kind = TV::Pending; t.pending = (int)pend.size() - 1; t.dtype = dt;
+    t.shape = batched ? std::vector<Expr>{b0 * b1, M, Expr(64)} : std::vector<Expr>{M, Expr(64)};
+    t.view = pend.back().nativeOut; t.view.shape = t.shape; t.view.strides = rowMajor(t.shape);
+    tvs[op->results[0]] = t;
+    return true;
+  }
   void gemm(Op* op, bool batched) {
+    {
+      TV& a0 = raw(op->operands[0]);
+      settle(a0);
+      if (a0.kind == TV::AttnProb && op->operands[0]->users.size() == 1 && tryAttention(op, a0, batched)) return;
+    }
     std::vector<Expr> splitA, splitB;
     View a = gemmOperand(op->operands[0], false, &splitA);
     View b = gemmOperand(op->operands[1], true, &splitB);
@@ -871,6 +962,18 @@ struct Lowering {
     int64_t axis = a ? a->i : (int64_t)r - 1;
     if (axis < 0) axis += (int64_t)r;
     if (axis != (int64_t)r - 1) fail("llh.softmax: only the last axis is supported");
+    {
+      TV& x0 = raw(xv);
+      settle(x0);
+      if (x0.kind == TV::Pending && xv->users.size() == 1 && attentionScores(x0)) {
+        // scores of an attention: wait for the consumer before emitting anything
+        AttnCand c; c.pending = x0.pending; attn.push_back(c);
+        View out = freshView(resultDtype(op->results[0]), x0.shape, false);
+        TV t; t.kind = TV::AttnProb; t.attn = (int)attn.size() - 1; t.pending = x0.pending; t.dtype = out.dtype; t.shape = x0.shape; t.view = out;
+        tvs[op->results[0]] = t;
+        return;
+      }
+    }
     View x = contiguousLeafOrView(xv);
     Expr rows(1); for (size_t d = 0; d + 1 < r; ++d) rows = rows * xt.shape[d];
     View x2 = x; x2.shape = {rows, xt.shape[r - 1]}; x2.strides = {xt.shape[r - 1], Expr(1)};
@@ -973,14 +1076,14 @@ struct Lowering {
     if (xt.kind == TV::Deferred) toView(xt);
     View nv;
     if (reshapeView(xt.view, shape, nv)) {
-      r.kind = xt.kind; r.view = nv; r.pending = xt.pending;
+      r.kind = xt.kind; r.view = nv; r.pending = xt.pending; r.attn = xt.attn;
       tvs[op->results[0]] = r; return;
     }
     if (xt.kind == TV::Pending && xv->users.size() == 1 && relayoutPending(xt) && reshapeView(xt.view, shape, nv)) {
       r.kind = xt.kind; r.view = nv; r.pending = xt.pending;
       tvs[op->results[0]] = r; return;
     }
-    if (xt.kind == TV::Pending) toView(xt);
+    if (xt.kind == TV::Pending || xt.kind == TV::AttnProb) toView(xt);
     r.kind = TV::Deferred; r.view = xt.view;
     tvs[op->results[0]] = r;
   }
@@ -989,7 +1092,7 @@ struct Lowering {
   // permuted order (it takes arbitrary batch and row strides) and the copy disappears.
   bool relayoutPending(TV& t) {
     PendingK& P = pend[t.pending];
-    if (P.emitted || P.step.kernel != "gemm" || P.hasRes || !t.view.offset.isConst(0)) return false;
+    if (P.emitted || (P.step.kernel != "gemm" && P.step.kernel != "attention") || P.hasRes || !t.view.offset.isConst(0)) return false;
     const View& nat = P.nativeOut;
     std::vector<int> logicalOf(nat.rank(), -1);
     std::vector<bool> used(t.view.rank(), false);
@@ -1040,7 +1143,7 @@ struct Lowering {
       int root = mapLeaves(xt.root, [&](const View& l, View& o) { o = broadcastView(l, shape, cast); return true; }, memo, ok);
       tvs[op->results[0]] = makeLazy(root, xt.dtype, shape); return;
     }
-    if (xt.kind == TV::Pending && xt.shape.size() == shape.size()) {   // identity broadcast keeps the producer open
+    if ((xt.kind == TV::Pending || xt.kind == TV::AttnProb) && xt.shape.size() == shape.size()) {   // identity broadcast keeps the producer open
       bool same = true; for (size_t i = 0; i < shape.size(); ++i) if (cast[i] != (int64_t)i || xt.shape[i] != shape[i]) same = false;
       if (same) { TV r = xt; tvs[op->results[0]] = r; return; }
     }
@@ -1263,6 +1366,11 @@ struct Lowering {
           // float -> float: arithmetic is fp32 everywhere, only the storage type of whatever is
           // materialised next changes, so the conversion does not break a fusion
           settle(x);
+          if (x.kind == TV::AttnProb) {      // probabilities keep whatever storage type is the narrowest asked for
+            TV r = x;
+            if (dtypeSize(to) < dtypeSize(x.dtype)) { r.dtype = to; r.view.dtype = to; plan.buffers[r.view.buf].dtype = to; }
+            tvs[op->results[0]] = r; continue;
+          }
           // widening (bf16 -> f32) of stored data is exact: keep the narrow storage and let the
           // consumers read it as it is (they all compute in fp32)
           if (dtypeSize(to) > dtypeSize(x.dtype) && (x.kind == TV::Pending || x.kind == TV::ViewK || x.kind == TV::Deferred)) {

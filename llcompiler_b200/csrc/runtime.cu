@@ -90,13 +90,13 @@ struct RView { int buf; long long off; int rank; long long shape[6], strides[6];
 // A plan step resolved for one symbol binding: the kernel's parameter block is filled once, only the
 // pointers (which depend on where the caller's tensors and the arena are) are patched per call.
 struct PtrPatch { void** slot; int buf; long long byteOff; };
-enum StepKind { kGemm, kConv, kPool, kReduce, kSoftmax, kLayerNorm, kGather, kEltwise, kNchw2Nhwc };
+enum StepKind { kGemm, kConv, kPool, kReduce, kSoftmax, kLayerNorm, kGather, kEltwise, kNchw2Nhwc, kAttention };
 struct RStep {
   const Step* step;
   std::vector<std::pair<std::string, RView>> views;
   const RView* view(const char* n) const { for (auto& v : views) if (v.first == n) return &v.second; return nullptr; }
   int kind = -1;
-  LlcGemmParams gemm{}; LlcConvParams conv{}; LlcPoolParams pool{}; LlcEltwiseParams elt{};
+  LlcGemmParams gemm{}; LlcConvParams conv{}; LlcPoolParams pool{}; LlcEltwiseParams elt{}; LlcAttentionParams attn{};
   std::string prog;
   void* sp[4] = {nullptr, nullptr, nullptr, nullptr};   // pointer operands of the row kernels
   int sdt[3] = {0, 0, 0}; long long sd[3] = {0, 0, 0}; int sop = 0; float seps = 0.f;
@@ -192,6 +192,26 @@ void LlcExec::prepare(RStep& rs) {
     if (const RView* v = rs.view("res")) { patch(&p.res, *v); p.res_dtype = v->dtype; p.r_s0 = v->strides[0]; p.r_s1 = v->strides[1]; p.r_sm = v->strides[2]; p.r_sn = v->strides[3]; }
     p.alpha = std::stof(s.param("alpha", "1")); p.act = actOf();
     p.workspace = workspace; p.workspace_bytes = (int64_t)kWorkspaceBytes;
+  } else if (s.kernel == "attention") {
+    rs.kind = kAttention;
+    const RView &q = need("q"), &k = need("k"), &v = need("v"), &o = need("out");   // q, out [b0,b1,M,D]; k [b0,b1,D,N]; v [b0,b1,N,D]
+    LlcAttentionParams& p = rs.attn;
+    patch(&p.q, q); patch(&p.k, k); patch(&p.v, v); patch(&p.out, o);
+    if (q.dtype != k.dtype || q.dtype != v.dtype || q.dtype != o.dtype) failArg("attention operand types differ");
+    p.dtype = q.dtype;
+    p.b0 = o.shape[0]; p.b1 = o.shape[1]; p.m = o.shape[2]; p.d = o.shape[3]; p.n = k.shape[3];
+    if (q.strides[3] != 1 || k.strides[2] != 1 || v.strides[3] != 1 || o.strides[3] != 1) failArg("attention operands must have unit stride along the head dim");
+    auto bs = [](const RView& t, int d) { return t.shape[d] == 1 ? 0 : t.strides[d]; };
+    p.q_s0 = bs(q, 0); p.q_s1 = bs(q, 1); p.q_sm = q.strides[2];
+    p.k_s0 = bs(k, 0); p.k_s1 = bs(k, 1); p.k_sn = k.strides[3];
+    p.v_s0 = bs(v, 0); p.v_s1 = bs(v, 1); p.v_sn = v.strides[2];
+    p.o_s0 = o.strides[0]; p.o_s1 = o.strides[1]; p.o_sm = o.strides[2];
+    if (const RView* mk = rs.view("mask")) {
+      patch(&p.mask, *mk); p.mask_dtype = mk->dtype;
+      if (mk->strides[3] != 1 && mk->shape[3] != 1) failArg("attention mask must have unit stride along the keys");
+      p.mask_s0 = mk->strides[0]; p.mask_s1 = mk->strides[1]; p.mask_sm = mk->strides[2];
+    }
+    p.scale = std::stof(s.param("scale", "1"));
   } else if (s.kernel == "conv") {
     rs.kind = kConv;
     const RView &x = need("x"), &w = need("w"), &o = need("out");
@@ -273,6 +293,7 @@ int LlcExec::launch(RStep& rs, cudaStream_t st) {
   switch (rs.kind) {
     case kGemm: return llc_cuda_gemm(&rs.gemm, st);
     case kConv: return llc_cuda_conv2d(&rs.conv, st);
+    case kAttention: return llc_cuda_attention(&rs.attn, st);
     case kPool: return llc_cuda_maxpool2d(&rs.pool, st);
     case kReduce: return llc_cuda_reduce(rs.sp[0], rs.sp[1], rs.sdt[0], rs.sdt[1], rs.sd[0], rs.sd[1], rs.sd[2], rs.sop, st);
     case kSoftmax: return llc_cuda_softmax(rs.sp[0], rs.sp[1], rs.sdt[0], rs.sdt[1], rs.sd[0], rs.sd[1], st);
@@ -548,6 +569,7 @@ static void stepWork(const RStep& rs, double& flops, double& bytes) {
   }
   const std::string& k = rs.step->kernel;
   if (k == "gemm") { const RView* a = rs.view("a"); const RView* o = rs.view("out"); flops = 2.0 * o->shape[0] * o->shape[1] * o->shape[2] * o->shape[3] * a->shape[3]; }
+  if (k == "attention") { const RView* kk = rs.view("k"); const RView* o = rs.view("out"); flops = 4.0 * o->shape[0] * o->shape[1] * o->shape[2] * o->shape[3] * kk->shape[3]; }
   if (k == "conv") { const RView* w = rs.view("w"); const RView* o = rs.view("out"); flops = 2.0 * o->shape[0] * o->shape[2] * o->shape[3] * w->shape[0] * w->shape[1] * w->shape[2] * w->shape[3]; }
 }
 

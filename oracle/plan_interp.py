@@ -179,6 +179,13 @@ class PlanInterpreter:
         e = torch.exp(x - m)
         v["out"].copy_((e / e.sum(-1, keepdim=True)).to(v["out"].dtype))
 
+    def _k_attention(self, v, p):
+        # q, out [b0,b1,M,D]; k [b0,b1,D,N]; v [b0,b1,N,D]; mask broadcast view [b0,b1,M,N]
+        s = torch.matmul(v["q"].float(), v["k"].float()) * float(p.get("scale", "1"))
+        if "mask" in v:
+            s = s + v["mask"].float()
+        v["out"].copy_(torch.matmul(torch.softmax(s, -1), v["v"].float()).to(v["out"].dtype))
+
     def _k_layernorm(self, v, p):
         x = v["x"].float()
         out = F.layer_norm(x, (x.shape[-1],), v["gamma"].float(), v["beta"].float(), float(p["eps"]))

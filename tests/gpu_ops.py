@@ -40,6 +40,24 @@ def gemm(a, b, out, scale=None, shift=None, res=None, alpha=1.0, act="none", pre
     C.check(C.lib().llc_cuda_gemm(byref(p), _stream()))
 
 
+def attention(q, k, v, out, mask=None, scale=1.0):
+    """q [b0,b1,M,D], k and v [b0,b1,N,D], out [b0,b1,M,D] views with unit stride along D; mask broadcastable
+    [b0,b1,M,N] view (stride 0 where it broadcasts) with unit stride along N."""
+    p = C.LlcAttentionParams()
+    p.q, p.k, p.v, p.mask, p.out = _p(q), _p(k), _p(v), _p(mask), _p(out)
+    p.dtype = _DT[q.dtype]
+    p.mask_dtype = _DT[mask.dtype] if mask is not None else 4
+    p.b0, p.b1, p.m, p.d, p.n = q.shape[0], q.shape[1], q.shape[2], q.shape[3], k.shape[2]
+    p.q_s0, p.q_s1, p.q_sm = q.stride(0), q.stride(1), q.stride(2)
+    p.k_s0, p.k_s1, p.k_sn = k.stride(0), k.stride(1), k.stride(2)
+    p.v_s0, p.v_s1, p.v_sn = v.stride(0), v.stride(1), v.stride(2)
+    p.o_s0, p.o_s1, p.o_sm = out.stride(0), out.stride(1), out.stride(2)
+    if mask is not None:
+        p.mask_s0, p.mask_s1, p.mask_sm = mask.stride(0), mask.stride(1), mask.stride(2)
+    p.scale = scale
+    C.check(C.lib().llc_cuda_attention(byref(p), _stream()))
+
+
 def conv2d(x_nhwc, w_fhwc, out_nhwc, stride, pad, dil=(1, 1), scale=None, shift=None, res=None, alpha=1.0,
            act="none", prec="fp32"):
     p = C.LlcConvParams()

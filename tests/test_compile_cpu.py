@@ -62,3 +62,34 @@ def test_resnet18_tensor_core_plan_pads_the_stem():
     assert max_rel_err(got, want) < 1e-4
     plan = comp.compiled[0].engine.text
     assert "prec:tf32x3" in plan and "[64,7,7,4;" in plan
+
+
+def _bert_bf16(monkeypatch, fuse, dynamic=False, seq=16):
+    from oracle.models import round_to_bf16_
+    monkeypatch.setenv("LLC_FUSE_ATTENTION", "1" if fuse else "0")
+    ref = round_to_bf16_(build_model("bert", n_layers=2))
+    ids = torch.randint(0, 30522, (2, seq))
+    mask = torch.ones(2, seq, dtype=torch.int64)
+    mask[1, seq - 5:] = 0
+    with torch.no_grad():
+        want = ref(ids, mask)
+    comp = InterpreterCompiler(precision="auto")
+    with torch.no_grad():
+        got = compile_with(comp, build_model("bert", n_layers=2).to(torch.bfloat16), dynamic)(ids, mask)
+    return comp.compiled[0].engine.text, got.float(), want
+
+
+def test_bert_bf16_attention_becomes_one_step(monkeypatch):
+    # batch_matmul -> scale -> mask -> softmax -> batch_matmul: one attention step per layer that reads the heads in
+    # place from the projections' [B, S, H*D] outputs and writes [B, S, H, D] directly
+    plan, got, want = _bert_bf16(monkeypatch, fuse=True)
+    assert plan.count("step attention") == 2 and plan.count("step softmax") == 0
+    assert plan.count("step gemm") == 12 and plan.count("step eltwise") == 2
+    assert "scale:0.125" in plan and " mask=" in plan
+    assert max_rel_err(got, want) < 2e-2
+
+
+def test_bert_bf16_unfused_attention_is_the_same_function(monkeypatch):
+    plan, got, want = _bert_bf16(monkeypatch, fuse=False)
+    assert plan.count("step attention") == 0 and plan.count("step softmax") == 2 and plan.count("step gemm") == 16
+    assert max_rel_err(got, want) < 2e-2
