@@ -50,6 +50,14 @@ DESCRIPTION = {
 }
 
 
+# DRAM bytes per launch of the dominant kernel family (dram__bytes_read.sum + dram__bytes_write.sum averaged over the
+# launches of one forward), from the ncu capture summarised in profiles/launch_list_resnet18_fp32_b32.md.
+NCU_TRAFFIC = {("resnet18", "conv", 32): 21.3e6}
+# Share of the measured bf16 peak a precision can reach at best: tf32 MMAs run at half the bf16 rate, tf32x3 issues
+# three of them per algorithmic multiply-add.
+PRECISION_CEILING = {"bf16": 1.0, "auto": 1.0, "tf32": 0.5, "tf32x3": 1.0 / 6.0, "fp32": None}
+
+
 def peaks():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -267,8 +275,10 @@ def main():
         if top["flops"] > 0 and top["kernel"] in ("conv", "gemm"):
             achieved = top["flops"] / (top["ms"] * 1e-3) / 1e12
             roof = {"bound": "tensor", "kernel": top["kernel"], "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / pk["tflops"], "traffic": None, "peak_source": pk["source"], "launches": top["launches"],
-                    "share_of_step": top["ms"] / max(sum(r["ms"] for r in prof), 1e-9)}
+                    "frac": achieved / pk["tflops"], "traffic": NCU_TRAFFIC.get((args.config, top["kernel"], batch)),
+                    "peak_source": pk["source"], "launches": top["launches"],
+                    "share_of_step": top["ms"] / max(sum(r["ms"] for r in prof), 1e-9),
+                    "precision_ceiling_frac": PRECISION_CEILING.get(prec)}
         else:
             achieved = top["bytes"] / (top["ms"] * 1e-3) / 1e9
             roof = {"bound": "hbm", "kernel": top["kernel"], "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",

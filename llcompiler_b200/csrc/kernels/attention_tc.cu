@@ -23,19 +23,21 @@ constexpr int kD = 64;            // head size (one 128-byte swizzle atom of bf1
 constexpr int kBM = 128;          // query rows per CTA
 constexpr int kMaxN = 384;        // keys: 384 score columns + 64 output columns of tensor memory
 constexpr int kTile = kBM * 128;  // bytes of a 128-row x 128-byte tile
-constexpr int kSoftmaxThreads = 256;
+constexpr int kGroups = 4;              // softmax warps per lane quarter: group h takes every kGroups-th 32-column chunk
+constexpr int kSoftmaxThreads = 4 * kGroups * 32;
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnArgs {
   void* out; const void* mask; int mask_dtype;
   long long M, N;
   long long o_s0, o_s1, o_sm, m_s0, m_s1, m_sm;
+  long long tiles;                   // (batch, head, query block) triples, walked by persistent CTAs
   int b1, mTiles, nBlocks, kAtoms;   // key blocks of 128 (first MMA), key atoms of 64 (second MMA)
   int qZ0, qZ1, kZ0, kZ1, vZ0, vZ1;  // 1: the operand has this batch dim, 0: broadcast
   float scaleLog2e;
 };
 
-constexpr int kSmemBytes = kTile /*Q*/ + 3 * kTile /*K*/ + 3 * kTile /*V*/ + 6 * kTile /*P*/ + 4096 /*barriers, row statistics, mask row*/ + 1024;
+constexpr int kSmemBytes = kTile /*Q*/ + 3 * kTile /*K*/ + 3 * kTile /*V*/ + 6 * kTile /*P*/ + 8192 /*barriers, row statistics, mask row*/ + 1024;
 
 __device__ __forceinline__ float fastExp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ void softmaxBarrier() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory"); }
@@ -50,144 +52,177 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   uint8_t* sV = sK + 3 * kTile;
   uint8_t* sP = sV + 3 * kTile;
   uint8_t* misc = sP + 6 * kTile;
-  uint64_t* bars = reinterpret_cast<uint64_t*>(misc);          // [0] Q,K landed  [1] V landed  [2] S done  [3] P written  [4] O done
+  // One phase per tile on every barrier: [0] Q,K landed  [1] V landed  [2] S complete  [3] P written  [4] O complete  [5] O read
+  uint64_t* bars = reinterpret_cast<uint64_t*>(misc);
   uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(misc + 64);
   volatile int* abortWord = reinterpret_cast<volatile int*>(misc + 68);
-  float* sMax = reinterpret_cast<float*>(misc + 128);           // [2][128]
-  float* sSum = sMax + 256;                                     // [2][128]
-  float* sMask = sSum + 256;                                    // [384] mask row * log2(e); -inf past the last key
+  float* sMax = reinterpret_cast<float*>(misc + 128);           // [kGroups][128]
+  float* sSum = sMax + kGroups * 128;                           // [kGroups][128]
+  float* sMask = sSum + kGroups * 128;                          // [384] mask row * log2(e); -inf past the last key
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int z = blockIdx.x / p.mTiles, tileM = blockIdx.x - z * p.mTiles;
-  const int zb0 = z / p.b1, zb1 = z - zb0 * p.b1;
+  constexpr int kIssuerWarp = kSoftmaxThreads / 32;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < 5; ++i) mbarInit(&bars[i], 1);
+    mbarInit(&bars[5], kSoftmaxThreads / 32);
     *abortWord = 0;
     fenceBarrierInit();
   }
-  if (warp == 8) tmemAlloc(tmemSlot, 512);
+  if (warp == kIssuerWarp) tmemAlloc(tmemSlot, 512);
   tcFenceBefore();
   __syncthreads();
   tcFenceAfter();
   const uint32_t tmemBase = *tmemSlot;
   const bool rowMask = p.mask == nullptr || p.m_sm == 0;        // the mask does not depend on the query row
+  auto coords = [&](long long t, int& tileM, int& zb0, int& zb1) {
+    const int z = (int)(t / p.mTiles); tileM = (int)(t - (long long)z * p.mTiles);
+    zb0 = z / p.b1; zb1 = z - zb0 * p.b1;
+  };
 
-  if (warp == 8) {
+  if (warp == kIssuerWarp) {
     if (lane == 0) {
+      // Loader and MMA issuer.  Per tile: S = Q K^T as soon as Q and K are there; once that MMA is complete (Q, K
+      // and, from the previous tile, V and P are free again) the next tile's Q, K and this tile's V are requested,
+      // so their flight time hides behind the softmax; O = P V when the softmax warps have written P.
       prefetchTensorMap(&mapQ); prefetchTensorMap(&mapK); prefetchTensorMap(&mapV);
-      mbarExpectTx(&bars[0], (1 + p.nBlocks) * kTile);
-      tmaLoad4d(sQ, &mapQ, &bars[0], 0, tileM * kBM, zb1 * p.qZ1, zb0 * p.qZ0);
-      for (int j = 0; j < p.nBlocks; ++j) tmaLoad4d(sK + j * kTile, &mapK, &bars[0], 0, j * 128, zb1 * p.kZ1, zb0 * p.kZ0);
-      mbarExpectTx(&bars[1], p.nBlocks * kTile);
-      for (int j = 0; j < p.nBlocks; ++j) tmaLoad4d(sV + j * kTile, &mapV, &bars[1], 0, j * 128, zb1 * p.vZ1, zb0 * p.vZ0);
-      // S = Q K^T: one 128 x 128 block of scores per 128 keys, K = 64 in four steps of 16
-      bool ok = mbarWait(&bars[0], 0, abortWord);
-      if (!ok) atomicExch(&g_attnStatus, 6);
-      tcFenceAfter();
+      auto loadQK = [&](long long t) {
+        int tileM, zb0, zb1; coords(t, tileM, zb0, zb1);
+        mbarExpectTx(&bars[0], (1 + p.nBlocks) * kTile);
+        tmaLoad4d(sQ, &mapQ, &bars[0], 0, tileM * kBM, zb1 * p.qZ1, zb0 * p.qZ0);
+        for (int j = 0; j < p.nBlocks; ++j) tmaLoad4d(sK + j * kTile, &mapK, &bars[0], 0, j * 128, zb1 * p.kZ1, zb0 * p.kZ0);
+      };
       constexpr uint32_t idescS = instrDesc(1, kBM, 128, 0, 0);
-      const uint64_t dQ = smemDescKMajorSw128(smemAddr(sQ));
-      for (int j = 0; j < p.nBlocks; ++j) {
-        const uint64_t dK = smemDescKMajorSw128(smemAddr(sK + j * kTile));
-#pragma unroll
-        for (int k = 0; k < 4; ++k) mmaSS<false>(tmemBase + (uint32_t)(j * 128), dQ + 2 * k, dK + 2 * k, idescS, k > 0 ? 1u : 0u);
-      }
-      mmaCommit(&bars[2]);
-      // O = P V: P is K-major (keys along K) in atoms of 64 keys, V is the MN-major operand (head dim contiguous)
-      ok = mbarWait(&bars[3], 0, abortWord) && mbarWait(&bars[1], 0, abortWord);
-      if (!ok) atomicExch(&g_attnStatus, 6);
-      tcFenceAfter();
       constexpr uint32_t idescO = instrDesc(1, kBM, kD, 0, 1);
-      for (int a = 0; a < p.kAtoms; ++a) {
-        const uint64_t dP = smemDescKMajorSw128(smemAddr(sP + a * kTile));
-        const uint64_t dV = smemDescMnMajorSw128(smemAddr(sV + a * 64 * 128), 64 * 128);
+      const uint64_t dQ = smemDescKMajorSw128(smemAddr(sQ));
+      if ((long long)blockIdx.x < p.tiles) loadQK(blockIdx.x);
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it) {
+        const uint32_t ph = it & 1;
+        int tileM, zb0, zb1; coords(t, tileM, zb0, zb1);
+        ok = mbarWait(&bars[0], ph, abortWord);
+        tcFenceAfter();
+        for (int j = 0; j < p.nBlocks; ++j) {           // one 128 x 128 block of scores per 128 keys, K = 64 in four steps of 16
+          const uint64_t dK = smemDescKMajorSw128(smemAddr(sK + j * kTile));
 #pragma unroll
-        for (int k = 0; k < 4; ++k) mmaSS<false>(tmemBase + kMaxN, dP + 2 * k, dV + (uint64_t)(k * ((16 * 128) >> 4)), idescO, (a > 0 || k > 0) ? 1u : 0u);
+          for (int k = 0; k < 4; ++k) mmaSS<false>(tmemBase + (uint32_t)(j * 128), dQ + 2 * k, dK + 2 * k, idescS, k > 0 ? 1u : 0u);
+        }
+        mmaCommit(&bars[2]);
+        ok = ok && mbarWait(&bars[2], ph, abortWord);   // every MMA issued so far is complete
+        if (t + gridDim.x < p.tiles) loadQK(t + gridDim.x);
+        mbarExpectTx(&bars[1], p.nBlocks * kTile);
+        for (int j = 0; j < p.nBlocks; ++j) tmaLoad4d(sV + j * kTile, &mapV, &bars[1], 0, j * 128, zb1 * p.vZ1, zb0 * p.vZ0);
+        ok = ok && mbarWait(&bars[3], ph, abortWord) && mbarWait(&bars[1], ph, abortWord);
+        if (it > 0) ok = ok && mbarWait(&bars[5], ph ^ 1, abortWord);   // the previous tile's O has been read
+        tcFenceAfter();
+        for (int a = 0; a < p.kAtoms; ++a) {            // P is K-major in atoms of 64 keys, V the MN-major operand (head dim contiguous)
+          const uint64_t dP = smemDescKMajorSw128(smemAddr(sP + a * kTile));
+          const uint64_t dV = smemDescMnMajorSw128(smemAddr(sV + a * 64 * 128), 64 * 128);
+#pragma unroll
+          for (int k = 0; k < 4; ++k) mmaSS<false>(tmemBase + kMaxN, dP + 2 * k, dV + (uint64_t)(k * ((16 * 128) >> 4)), idescO, (a > 0 || k > 0) ? 1u : 0u);
+        }
+        mmaCommit(&bars[4]);                            // also reached after a failed wait, so that the other warps do not spin out
+        if (!ok) atomicExch(&g_attnStatus, 6);
       }
-      mmaCommit(&bars[4]);
     }
   } else {
-    // ---------------------------------------------------------------- softmax and epilogue (warps 0-7)
-    const int q = warp & 3, h = warp >> 2;             // tensor-memory lane quarter (a hardware rule) and chunk parity
+    // ---------------------------------------------------------------- softmax and epilogue
+    const int q = warp & 3, h = warp >> 2;             // tensor-memory lane quarter (a hardware rule) and chunk group
     const int row = q * 32 + lane;
-    const long long gm = (long long)tileM * kBM + row;
     const uint32_t trow = tmemBase + ((uint32_t)(q * 32) << 16);
     const int nChunks = p.nBlocks * 4;
-    // mask row (times log2 e) into shared memory; columns past the last key get -inf
-    if (rowMask) {
-      const long long mBase = zb0 * p.m_s0 + zb1 * p.m_s1;
-      for (int c = threadIdx.x; c < kMaxN; c += kSoftmaxThreads)
-        sMask[c] = c < p.N ? (p.mask ? loadAs(p.mask, mBase + c, p.mask_dtype) * kLog2e : 0.f) : -INFINITY;
-    }
-    softmaxBarrier();
-    const long long mRow = zb0 * p.m_s0 + zb1 * p.m_s1 + gm * p.m_sm;
-    auto logit = [&](float s, int col) -> float {      // scaled score plus mask, in units of log2
-      if (rowMask) return fmaf(s, p.scaleLog2e, sMask[col]);
-      if (col >= p.N || gm >= p.M) return col < p.N ? s * p.scaleLog2e : -INFINITY;
-      return fmaf(s, p.scaleLog2e, loadAs(p.mask, mRow + col, p.mask_dtype) * kLog2e);
-    };
-    bool ok = mbarWait(&bars[2], 0, abortWord);
-    if (!ok) atomicExch(&g_attnStatus, 7);
-    tcFenceAfter();
-    float mx = -INFINITY;
-    for (int c = h; c < nChunks; c += 2) {
-      float v[32];
-      __syncwarp();
-      tmemLoad32x32(trow + (uint32_t)(c * 32), v);
-#pragma unroll
-      for (int j = 0; j < 32; ++j) mx = fmaxf(mx, logit(v[j], c * 32 + j));
-    }
-    sMax[h * 128 + row] = mx;
-    softmaxBarrier();
-    mx = fmaxf(sMax[row], sMax[128 + row]);
-    if (mx == -INFINITY) mx = 0.f;                     // a fully masked row: all probabilities become 0
-    float sum = 0.f;
-    for (int c = h; c < nChunks; c += 2) {
-      float v[32];
-      __syncwarp();
-      tmemLoad32x32(trow + (uint32_t)(c * 32), v);
-      const uint32_t rowAddr = smemAddr(sP + (c >> 1) * kTile) + (uint32_t)row * 128u;
-#pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        __nv_bfloat162 pk[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int col = c * 32 + j * 8 + e * 2;
-          pk[e] = __floats2bfloat162_rn(fastExp2(logit(v[j * 8 + e * 2], col) - mx), fastExp2(logit(v[j * 8 + e * 2 + 1], col + 1) - mx));
-          const float2 f = __bfloat1622float2(pk[e]);
-          sum += f.x + f.y;                            // the sum of what the second MMA will actually read
-        }
-        const uint32_t chunk = (uint32_t)((c & 1) * 4 + j);
-        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + ((chunk ^ (uint32_t)(row & 7)) << 4)), "r"(*reinterpret_cast<unsigned*>(&pk[0])),
-                     "r"(*reinterpret_cast<unsigned*>(&pk[1])), "r"(*reinterpret_cast<unsigned*>(&pk[2])), "r"(*reinterpret_cast<unsigned*>(&pk[3])) : "memory");
+    int maskZ = -1;
+    uint32_t it = 0;
+    bool ok = true;                                    // after a wait gave up the loop still runs (every thread must reach every barrier)
+    for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++it) {
+      const uint32_t ph = it & 1;
+      int tileM, zb0, zb1; coords(t, tileM, zb0, zb1);
+      const long long gm = (long long)tileM * kBM + row;
+      const int z = zb0 * p.b1 + zb1;
+      if (rowMask && z != maskZ) {                     // mask row (times log2 e); columns past the last key get -inf
+        const long long mBase = zb0 * p.m_s0 + zb1 * p.m_s1;
+        for (int c = threadIdx.x; c < kMaxN; c += kSoftmaxThreads)
+          sMask[c] = c < p.N ? (p.mask ? loadAs(p.mask, mBase + c, p.mask_dtype) * kLog2e : 0.f) : -INFINITY;
+        maskZ = z;
       }
-    }
-    sSum[h * 128 + row] = sum;
-    tcFenceBefore();
-    fenceProxyAsync();                                 // P was written through the generic proxy, the MMA reads it through the async proxy
-    softmaxBarrier();
-    if (threadIdx.x == 0) mbarArrive(&bars[3]);
-    const float inv = 1.f / (sSum[row] + sSum[128 + row]);
-    ok = mbarWait(&bars[4], 0, abortWord);
-    if (!ok) atomicExch(&g_attnStatus, 7);
-    tcFenceAfter();
-    float o[32];
-    __syncwarp();
-    tmemLoad32x32(trow + (uint32_t)(kMaxN + h * 32), o);
-    if (gm < p.M) {
-      uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + zb0 * p.o_s0 + zb1 * p.o_s1 + gm * p.o_sm + h * 32);
+      softmaxBarrier();
+      const long long mRow = zb0 * p.m_s0 + zb1 * p.m_s1 + gm * p.m_sm;
+      auto logit = [&](float s, int col) -> float {    // scaled score plus mask, in units of log2
+        if (rowMask) return fmaf(s, p.scaleLog2e, sMask[col]);
+        if (col >= p.N || gm >= p.M) return col < p.N ? s * p.scaleLog2e : -INFINITY;
+        return fmaf(s, p.scaleLog2e, loadAs(p.mask, mRow + col, p.mask_dtype) * kLog2e);
+      };
+      if (ok && !mbarWait(&bars[2], ph, abortWord)) { atomicExch(&g_attnStatus, 7); ok = false; }
+      tcFenceAfter();
+      float mx = -INFINITY;
+      for (int c = h; c < nChunks; c += kGroups) {
+        float v[32];
+        __syncwarp();
+        tmemLoad32x32(trow + (uint32_t)(c * 32), v);
 #pragma unroll
-      for (int j = 0; j < 4; ++j) {
-        __nv_bfloat162 a0 = __floats2bfloat162_rn(o[8 * j] * inv, o[8 * j + 1] * inv), a1 = __floats2bfloat162_rn(o[8 * j + 2] * inv, o[8 * j + 3] * inv);
-        __nv_bfloat162 a2 = __floats2bfloat162_rn(o[8 * j + 4] * inv, o[8 * j + 5] * inv), a3 = __floats2bfloat162_rn(o[8 * j + 6] * inv, o[8 * j + 7] * inv);
-        uint4 pk; pk.x = *reinterpret_cast<unsigned*>(&a0); pk.y = *reinterpret_cast<unsigned*>(&a1); pk.z = *reinterpret_cast<unsigned*>(&a2); pk.w = *reinterpret_cast<unsigned*>(&a3);
-        dst[j] = pk;
+        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, logit(v[j], c * 32 + j));
+      }
+      sMax[h * 128 + row] = mx;
+      softmaxBarrier();
+#pragma unroll
+      for (int g = 0; g < kGroups; ++g) mx = fmaxf(mx, sMax[g * 128 + row]);
+      if (mx == -INFINITY) mx = 0.f;                   // a fully masked row: all probabilities become 0
+      float sum = 0.f;
+      for (int c = h; c < nChunks; c += kGroups) {
+        float v[32];
+        __syncwarp();
+        tmemLoad32x32(trow + (uint32_t)(c * 32), v);
+        const uint32_t rowAddr = smemAddr(sP + (c >> 1) * kTile) + (uint32_t)row * 128u;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          __nv_bfloat162 pk[4];
+#pragma unroll
+          for (int e = 0; e < 4; ++e) {
+            const int col = c * 32 + j * 8 + e * 2;
+            pk[e] = __floats2bfloat162_rn(fastExp2(logit(v[j * 8 + e * 2], col) - mx), fastExp2(logit(v[j * 8 + e * 2 + 1], col + 1) - mx));
+            const float2 f = __bfloat1622float2(pk[e]);
+            sum += f.x + f.y;                          // the sum of what the second MMA will actually read
+          }
+          const uint32_t chunk = (uint32_t)((c & 1) * 4 + j);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + ((chunk ^ (uint32_t)(row & 7)) << 4)), "r"(*reinterpret_cast<unsigned*>(&pk[0])),
+                       "r"(*reinterpret_cast<unsigned*>(&pk[1])), "r"(*reinterpret_cast<unsigned*>(&pk[2])), "r"(*reinterpret_cast<unsigned*>(&pk[3])) : "memory");
+        }
+      }
+      sSum[h * 128 + row] = sum;
+      tcFenceBefore();                                 // this thread's reads of S are done before the next tile's MMA may overwrite it
+      fenceProxyAsync();                               // P was written through the generic proxy, the MMA reads it through the async proxy
+      softmaxBarrier();
+      if (threadIdx.x == 0) mbarArrive(&bars[3]);
+      float tot = 0.f;
+#pragma unroll
+      for (int g = 0; g < kGroups; ++g) tot += sSum[g * 128 + row];
+      const float inv = 1.f / tot;
+      if (ok && !mbarWait(&bars[4], ph, abortWord)) { atomicExch(&g_attnStatus, 7); ok = false; }
+      tcFenceAfter();
+      // epilogue: group h takes 64 / kGroups output columns of its rows
+      constexpr int kCols = kD / kGroups;
+      float o[kCols];
+      __syncwarp();
+      tmemLoadCols<kCols>(trow + (uint32_t)(kMaxN + h * kCols), o);
+      tcFenceBefore();
+      __syncwarp();
+      if (lane == 0) mbarArrive(&bars[5]);             // O is in registers: the next tile's second MMA may overwrite it
+      if (gm < p.M) {
+        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + zb0 * p.o_s0 + zb1 * p.o_s1 + gm * p.o_sm + h * kCols);
+#pragma unroll
+        for (int j = 0; j < kCols / 8; ++j) {
+          __nv_bfloat162 a0 = __floats2bfloat162_rn(o[8 * j] * inv, o[8 * j + 1] * inv), a1 = __floats2bfloat162_rn(o[8 * j + 2] * inv, o[8 * j + 3] * inv);
+          __nv_bfloat162 a2 = __floats2bfloat162_rn(o[8 * j + 4] * inv, o[8 * j + 5] * inv), a3 = __floats2bfloat162_rn(o[8 * j + 6] * inv, o[8 * j + 7] * inv);
+          uint4 pk; pk.x = *reinterpret_cast<unsigned*>(&a0); pk.y = *reinterpret_cast<unsigned*>(&a1); pk.z = *reinterpret_cast<unsigned*>(&a2); pk.w = *reinterpret_cast<unsigned*>(&a3);
+          dst[j] = pk;
+        }
       }
     }
   }
   tcFenceBefore();
   __syncthreads();
-  if (warp == 8) { tcFenceAfter(); tmemDealloc(tmemBase, 512); }
+  if (warp == kIssuerWarp) { tcFenceAfter(); tmemDealloc(tmemBase, 512); }
 }
 
 // ---- host side ------------------------------------------------------------------------------
@@ -264,7 +299,11 @@ extern "C" int llc_cuda_attention(const LlcAttentionParams* p, void* stream) {
     if (e != cudaSuccess) return cudaFail(e, "cudaFuncSetAttribute(attention_kernel)");
     configured = true;
   }
-  attention_kernel<<<(unsigned)(batch * mTiles), kSoftmaxThreads + 32, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, a);
+  a.tiles = batch * mTiles;
+  int dev = 0, sms = kNumSMs;
+  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const unsigned grid = (unsigned)(a.tiles < sms ? a.tiles : sms);
+  attention_kernel<<<grid, kSoftmaxThreads + 32, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, a);
   LLC_LAUNCH_CHECK("attention_kernel");
   return LLC_OK;
 }

@@ -3,6 +3,7 @@ command that profiler captures are taken on.
 
   python tests/kernel_case.py conv  N C H W F K STRIDE PAD PREC [REPS]
   python tests/kernel_case.py gemm  M N K PREC [REPS]
+  python tests/kernel_case.py attention  BATCH HEADS SEQ [REPS]      (bf16, head size 64, row mask)
 PREC: bf16 | tf32 | tf32x3 | fp32
 """
 import os
@@ -41,6 +42,15 @@ def main(argv):
         out = torch.empty(1, 1, m, n, device="cuda", dtype=dt)
         for _ in range(reps):
             G.gemm(a[None, None], b.t()[None, None], out, prec=prec)
+    elif kind == "attention":
+        b, h, sq = (int(a) for a in argv[1:4])
+        reps = int(argv[4]) if len(argv) > 4 else 3
+        q, k, v = (torch.randn(b, sq, h * 64, device="cuda").to(torch.bfloat16) for _ in range(3))
+        out = torch.empty_like(q)
+        mask = torch.zeros(b, 1, 1, sq, device="cuda").expand(b, h, sq, sq)
+        heads = lambda t: t.view(b, sq, h, 64).permute(0, 2, 1, 3)
+        for _ in range(reps):
+            G.attention(heads(q), heads(k), heads(v), heads(out), mask=mask, scale=0.125)
     else:
         raise SystemExit(__doc__)
     torch.cuda.synchronize()
