@@ -45,6 +45,7 @@ struct TcArgs {
   long long M, N, K;
   long long o_s0, o_s1, o_sm, r_s0, r_s1, r_sm, r_sn;
   int b1; int kBlocks; int vecOut;
+  int resTile;              // the residual can be fetched as 32-row x 128-byte boxes with 16-byte loads
   int tmaOut;               // 0, or the bytes per row of the output box the epilogue stores through TMA (64 or 128)
   int aZ0, aZ1, bZ0, bZ1;   // 1: the operand has this batch dim, 0: it is broadcast (coordinate 0)
   int mTiles, nTiles; long long tiles;
@@ -234,23 +235,32 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       const bool rowOk = gm < p.M;
       const long long oRow = zb0 * p.o_s0 + zb1 * p.o_s1 + gm * p.o_sm;
       const long long rRow = zb0 * p.r_s0 + zb1 * p.r_s1 + gm * p.r_sm;
-      // The residual rows of this warp's share are fetched while the tile's MMAs still run: issued
-      // after the accumulator is ready, these scattered loads would have nothing to hide behind.
-      constexpr int kPre = kColsPerWarp / 8;            // 16-byte pieces (8 bf16) per row share
-      uint4 rpre[CONV ? 1 : kPre];
-      const long long preCol = (long long)tileN * BN + half * kColsPerWarp;
-      const bool pre = !CONV && p.res != nullptr && p.res_dtype == LLC_BFLOAT16 && p.r_sn == 1 && p.vecOut && rowOk &&
-                       preCol + kColsPerWarp <= p.N && ((rRow + preCol) & 7) == 0;
-      if (!CONV && pre) {
-        const uint4* rp = reinterpret_cast<const uint4*>(reinterpret_cast<const __nv_bfloat16*>(p.res) + rRow + preCol);
+      // Residual tile.  A box of the residual (32 rows x 128 bytes, the same box the output store writes) is fetched with
+      // coalesced 16-byte loads (eight lanes per row), passed through this warp's staging buffer and read back one row
+      // per lane: lane = row is how the accumulator arrives, but loading global memory that way touches 32 lines per
+      // instruction.  The loads of the first box are issued here, while the tile's MMAs still run, those of box b + 1
+      // when box b is taken over.
+      const bool resTile = !CONV && p.resTile && tmaW == 128;   // (the gather kernel has no registers to spare and its layers no residual)
+      constexpr bool kPrefetchNext = !X3;                       // tf32x3 holds two accumulator chunks at a time: it fetches later boxes when it needs them
+      const int boxCols = outF32 ? 32 : 64;
+      const int esz = outF32 ? 4 : 2;
+      uint4 rpre[8], rrow[8];
+      auto issueRes = [&](int b) {
+        const int chunk = lane & 7, r0 = lane >> 3;
+        const long long gcol = (long long)tileN * BN + half * kColsPerWarp + b * boxCols + chunk * (16 / esz);
+        const char* base = reinterpret_cast<const char*>(p.res) + (zb0 * p.r_s0 + zb1 * p.r_s1 + gcol) * esz;
 #pragma unroll
-        for (int i = 0; i < kPre; ++i) rpre[i] = __ldg(rp + i);
-      }
+        for (int j = 0; j < 8; ++j) {
+          const long long gr = (long long)tileM * BM + q * 32 + j * 4 + r0;
+          rpre[j] = (gr < p.M && gcol < p.N) ? __ldg(reinterpret_cast<const uint4*>(base + gr * p.r_sm * esz)) : make_uint4(0u, 0u, 0u, 0u);
+        }
+      };
+      if (resTile) issueRes(0);
       if (!mbarWait(&accFull[ab], aph, abortWord)) { atomicExch(&g_tcStatus, 4); break; }
       tcFenceAfter();
       const uint32_t acc = tmemBase + (uint32_t)(ab * kSetCols) + ((uint32_t)(q * 32) << 16);
       const int usedChains = p.kBlocks < kChains ? p.kBlocks : kChains;
-#pragma unroll
+#pragma unroll 1
       for (int ci = 0; ci < kColsPerWarp / 32; ++ci) {
         const int c0 = half * kColsPerWarp + ci * 32;
         float v[32];
@@ -272,28 +282,102 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         const long long gn0 = (long long)tileN * BN + c0;
         const bool inside = gn0 < p.N;
         const bool whole = p.vecOut && gn0 + 32 <= p.N;
+        bool packed = false;
+        __nv_bfloat162 pk[16];
+        const int sub = (tmaW == 128 && !outF32) ? (ci & 1) : 0;          // bf16: two chunks fill a 128-byte row of the box
+        const long long x0 = gn0 - sub * 32;
+        if (tmaW && sub == 0 && x0 < p.N) {
+          if (lane == 0) bulkWaitRead();                                  // the previous store has read the staging buffer
+          __syncwarp();
+          if (resTile) {
+            const uint32_t st = smemAddr(outStage);
+            const int b = (ci * 32) / boxCols;
+            if (!kPrefetchNext && b > 0) issueRes(b);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+              const uint32_t row = (uint32_t)(j * 4 + (lane >> 3));
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(st + row * 128u + ((((uint32_t)lane & 7u) ^ (row & 7u)) << 4)), "r"(rpre[j].x),
+                           "r"(rpre[j].y), "r"(rpre[j].z), "r"(rpre[j].w) : "memory");
+            }
+            __syncwarp();
+#pragma unroll
+            for (int c = 0; c < 8; ++c)
+              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rrow[c].x), "=r"(rrow[c].y), "=r"(rrow[c].z), "=r"(rrow[c].w)
+                           : "r"(st + (uint32_t)lane * 128u + ((((uint32_t)c) ^ ((uint32_t)lane & 7u)) << 4)) : "memory");
+            __syncwarp();                                                 // every lane has its row before the buffer is rewritten
+            if (kPrefetchNext && (b + 1) * boxCols < kColsPerWarp) issueRes(b + 1);
+          }
+        }
         if (whole) {
           // whole chunk inside the matrix: flag tests hoisted out of the element loops
           if (p.scale) {
             const float4* sc = reinterpret_cast<const float4*>(p.scale + gn0);
+            if (p.shift) {                                // the folded batch norm: one fused multiply-add per element
+              const float4* sh = reinterpret_cast<const float4*>(p.shift + gn0);
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { float4 s4 = __ldg(sc + j); v[4 * j] *= p.alpha * s4.x; v[4 * j + 1] *= p.alpha * s4.y; v[4 * j + 2] *= p.alpha * s4.z; v[4 * j + 3] *= p.alpha * s4.w; }
+              for (int j = 0; j < 8; ++j) {
+                float4 s4 = __ldg(sc + j); const float4 b4 = __ldg(sh + j);
+                if (p.alpha != 1.f) { s4.x *= p.alpha; s4.y *= p.alpha; s4.z *= p.alpha; s4.w *= p.alpha; }
+                v[4 * j] = fmaf(v[4 * j], s4.x, b4.x); v[4 * j + 1] = fmaf(v[4 * j + 1], s4.y, b4.y);
+                v[4 * j + 2] = fmaf(v[4 * j + 2], s4.z, b4.z); v[4 * j + 3] = fmaf(v[4 * j + 3], s4.w, b4.w);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { float4 s4 = __ldg(sc + j); v[4 * j] *= p.alpha * s4.x; v[4 * j + 1] *= p.alpha * s4.y; v[4 * j + 2] *= p.alpha * s4.z; v[4 * j + 3] *= p.alpha * s4.w; }
+            }
+          } else if (p.shift) {
+            const float4* sh = reinterpret_cast<const float4*>(p.shift + gn0);
+            if (p.alpha != 1.f) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { const float4 b4 = __ldg(sh + j); v[4 * j] = fmaf(v[4 * j], p.alpha, b4.x); v[4 * j + 1] = fmaf(v[4 * j + 1], p.alpha, b4.y); v[4 * j + 2] = fmaf(v[4 * j + 2], p.alpha, b4.z); v[4 * j + 3] = fmaf(v[4 * j + 3], p.alpha, b4.w); }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) { const float4 b4 = __ldg(sh + j); v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w; }
+            }
           } else if (p.alpha != 1.f) {
 #pragma unroll
             for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
           }
-          if (p.shift) {
-            const float4* sh = reinterpret_cast<const float4*>(p.shift + gn0);
+          // bf16 output through the staging buffer: residual add and ReLU on packed pairs after the conversion (the
+          // rounding order of a bf16 graph: the producer's result is rounded, then added to the bf16 residual)
+          packed = !TF32 && !outF32 && tmaW != 0 && (!p.res || resTile) && !(p.act == LLC_ACT_GELU && p.res);
+          if (packed) {
+            if (p.act == LLC_ACT_GELU) {
 #pragma unroll
-            for (int j = 0; j < 8; ++j) { float4 s4 = __ldg(sh + j); v[4 * j] += s4.x; v[4 * j + 1] += s4.y; v[4 * j + 2] += s4.z; v[4 * j + 3] += s4.w; }
-          }
-          if (!CONV && pre) {
+              for (int j = 0; j < 32; ++j) v[j] = geluTanhBf16(v[j]);
+            }
 #pragma unroll
-            for (int j = 0; j < 4; ++j) {
-              const uint4 r = rpre[CONV ? 0 : ci * 4 + j];
-              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+            for (int j = 0; j < 16; ++j) pk[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
+            if (resTile) {
 #pragma unroll
-              for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); v[8 * j + 2 * e] += f.x; v[8 * j + 2 * e + 1] += f.y; }
+              for (int j = 0; j < 4; ++j) {
+                const uint4 r = (ci & 1) ? rrow[4 + j] : rrow[j];
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) pk[4 * j + e] = __hadd2(pk[4 * j + e], h[e]);
+              }
+            }
+            if (p.act == LLC_ACT_RELU) {
+              const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
+#pragma unroll
+              for (int j = 0; j < 16; ++j) pk[j] = __hmax2(pk[j], zero2);
+            }
+          } else {
+          if (resTile) {
+            if (outF32) {
+#pragma unroll
+              for (int j = 0; j < 8; ++j) {
+                v[4 * j] += __uint_as_float(rrow[j].x); v[4 * j + 1] += __uint_as_float(rrow[j].y);
+                v[4 * j + 2] += __uint_as_float(rrow[j].z); v[4 * j + 3] += __uint_as_float(rrow[j].w);
+              }
+            } else {
+#pragma unroll
+              for (int j = 0; j < 4; ++j) {
+                const uint4 r = (ci & 1) ? rrow[4 + j] : rrow[j];
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); v[8 * j + 2 * e] += f.x; v[8 * j + 2 * e + 1] += f.y; }
+              }
             }
           } else if (p.res && rowOk) {
             if (p.r_sn == 1 && p.res_dtype == LLC_BFLOAT16 && ((rRow + gn0) & 3) == 0) {
@@ -321,6 +405,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
               for (int j = 0; j < 32; ++j) v[j] = geluTanhBf16(v[j]);
             }
           }
+          }
         } else if (inside && rowOk) {
           // ragged edge: element by element
 #pragma unroll
@@ -338,11 +423,8 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         if (tmaW) {
           // Stage the rows in shared memory (swizzled: conflict-free 16-byte writes) and let one TMA
           // store write them out as whole lines; rows >= M and columns >= N are clipped by the store.
-          const int sub = (!outF32 && tmaW == 128) ? (ci & 1) : 0;        // bf16: two chunks fill a 128-byte row
-          const bool opens = sub == 0, closes = outF32 || tmaW == 64 || sub == 1;
-          const long long x0 = gn0 - sub * 32;
+          const bool closes = outF32 || tmaW == 64 || sub == 1;
           if (x0 < p.N) {
-            if (opens) { if (lane == 0) bulkWaitRead(); __syncwarp(); }   // the previous store has read the buffer
             if (inside) {
               const uint32_t rowOff = (uint32_t)lane * (uint32_t)tmaW;
               const uint32_t swz = (rowOff >> 7) & (uint32_t)(tmaW / 16 - 1);
@@ -355,8 +437,12 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
               } else {
 #pragma unroll
                 for (int j = 0; j < 4; ++j) {
-                  __nv_bfloat162 a0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]), a1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                  __nv_bfloat162 a2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]), a3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                  __nv_bfloat162 a0, a1, a2, a3;
+                  if (packed) { a0 = pk[4 * j]; a1 = pk[4 * j + 1]; a2 = pk[4 * j + 2]; a3 = pk[4 * j + 3]; }
+                  else {
+                    a0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]); a1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
+                    a2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]); a3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                  }
                   asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + (((uint32_t)(sub * 4 + j) ^ swz) << 4)),
                                "r"(*reinterpret_cast<unsigned*>(&a0)), "r"(*reinterpret_cast<unsigned*>(&a1)), "r"(*reinterpret_cast<unsigned*>(&a2)),
                                "r"(*reinterpret_cast<unsigned*>(&a3)) : "memory");
@@ -708,6 +794,9 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   CUtensorMap mo = ma;   // a valid map even when unused
   const int boxBytes = outBoxBytes(bn, ob == 4);
   if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->n, p->m, p->b1, p->b0, p->o_sm, p->o_s1, p->o_s0, boxBytes)) a.tmaOut = boxBytes;
+  auto r16 = [&](long long st) { return st >= 0 && (st * ob) % 16 == 0; };
+  a.resTile = p->res && p->r_sn == 1 && p->res_dtype == p->out_dtype && (reinterpret_cast<uintptr_t>(p->res) & 15) == 0 && r16(p->r_sm) && r16(p->r_s0) &&
+              r16(p->r_s1) && p->n % (16 / ob) == 0;
   return bmn ? dispatch<0, true>(bn, kind, ma, mb, mo, a, batch, st) : dispatch<0, false>(bn, kind, ma, mb, mo, a, batch, st);
 }
 
@@ -746,6 +835,7 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
   CUtensorMap mo = mb;
   const int boxBytes = outBoxBytes(bn, ob == 4);
   if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->f, M, 1, 1, p->f, 0, 0, boxBytes)) a.tmaOut = boxBytes;
+  a.resTile = p->res && p->res_dtype == p->out_dtype && (reinterpret_cast<uintptr_t>(p->res) & 15) == 0 && (p->f * ob) % 16 == 0;
   if (im2colEligible(p, f32)) {
     CUtensorMap ma;
     if (makeIm2colMap(&ma, p, f32)) return dispatch<2, false>(bn, kind, ma, mb, mo, a, 1, st);
