@@ -167,6 +167,7 @@ std::string Module::str() const {
   if (!symName.empty()) o << " @" << symName;
   if (!attrs.empty()) o << " attributes {" << attrListStr(attrs) << "}";
   o << " {\n";
+  for (auto& n : symbolDecls) o << "  \"llh.symbolic_int\"() <{sym_name = \"" << n << "\"}> : () -> ()\n";
   for (auto& f : funcs) {
     o << "  func.func @" << f.name << "(";
     for (size_t i = 0; i < f.args.size(); ++i) {

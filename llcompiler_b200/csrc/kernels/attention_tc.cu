@@ -160,8 +160,17 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         float v[32];
         __syncwarp();
         tmemLoad32x32(trow + (uint32_t)(c * 32), v);
+        if (rowMask) {                                   // the common case: the mask row sits in shared memory, four columns per load
+          const float4* m4 = reinterpret_cast<const float4*>(sMask + c * 32);
 #pragma unroll
-        for (int j = 0; j < 32; ++j) mx = fmaxf(mx, logit(v[j], c * 32 + j));
+          for (int j = 0; j < 8; ++j) {
+            const float4 mk = m4[j];
+            mx = fmaxf(fmaxf(mx, fmaf(v[4 * j], p.scaleLog2e, mk.x)), fmaxf(fmaf(v[4 * j + 1], p.scaleLog2e, mk.y), fmaxf(fmaf(v[4 * j + 2], p.scaleLog2e, mk.z), fmaf(v[4 * j + 3], p.scaleLog2e, mk.w))));
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, logit(v[j], c * 32 + j));
+        }
       }
       sMax[h * 128 + row] = mx;
       softmaxBarrier();
@@ -177,13 +186,19 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
 #pragma unroll
         for (int j = 0; j < 4; ++j) {
           __nv_bfloat162 pk[4];
+          float e8[8];
+          if (rowMask) {
+            const float4 ma = reinterpret_cast<const float4*>(sMask + c * 32 + j * 8)[0], mb = reinterpret_cast<const float4*>(sMask + c * 32 + j * 8)[1];
+            e8[0] = fmaf(v[j * 8], p.scaleLog2e, ma.x); e8[1] = fmaf(v[j * 8 + 1], p.scaleLog2e, ma.y); e8[2] = fmaf(v[j * 8 + 2], p.scaleLog2e, ma.z); e8[3] = fmaf(v[j * 8 + 3], p.scaleLog2e, ma.w);
+            e8[4] = fmaf(v[j * 8 + 4], p.scaleLog2e, mb.x); e8[5] = fmaf(v[j * 8 + 5], p.scaleLog2e, mb.y); e8[6] = fmaf(v[j * 8 + 6], p.scaleLog2e, mb.z); e8[7] = fmaf(v[j * 8 + 7], p.scaleLog2e, mb.w);
+          } else {
 #pragma unroll
-          for (int e = 0; e < 4; ++e) {
-            const int col = c * 32 + j * 8 + e * 2;
-            pk[e] = __floats2bfloat162_rn(fastExp2(logit(v[j * 8 + e * 2], col) - mx), fastExp2(logit(v[j * 8 + e * 2 + 1], col + 1) - mx));
-            const float2 f = __bfloat1622float2(pk[e]);
-            sum += f.x + f.y;                          // the sum of what the second MMA will actually read
+            for (int e = 0; e < 8; ++e) e8[e] = logit(v[j * 8 + e], c * 32 + j * 8 + e);
           }
+#pragma unroll
+          for (int e = 0; e < 8; ++e) { e8[e] = fastExp2(e8[e] - mx); sum += e8[e]; }
+#pragma unroll
+          for (int e = 0; e < 4; ++e) pk[e] = __floats2bfloat162_rn(e8[2 * e], e8[2 * e + 1]);
           const uint32_t chunk = (uint32_t)((c & 1) * 4 + j);
           asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + ((chunk ^ (uint32_t)(row & 7)) << 4)), "r"(*reinterpret_cast<unsigned*>(&pk[0])),
                        "r"(*reinterpret_cast<unsigned*>(&pk[1])), "r"(*reinterpret_cast<unsigned*>(&pk[2])), "r"(*reinterpret_cast<unsigned*>(&pk[3])) : "memory");

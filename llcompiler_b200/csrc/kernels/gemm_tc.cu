@@ -225,6 +225,12 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     const bool outF32 = p.out_dtype == LLC_FLOAT32;
     const int tmaW = p.tmaOut;                                  // bytes per staged row; 0: direct stores
     uint8_t* outStage = staging + (warp - 2) * kStagingPerWarp;
+    auto stagedRow = [&](int c) -> uint4 {                       // 16-byte piece c of this lane's row of the staged box
+      uint4 r;
+      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
+                   : "r"(smemAddr(outStage) + (uint32_t)lane * 128u + ((((uint32_t)c) ^ ((uint32_t)lane & 7u)) << 4)) : "memory");
+      return r;
+    };
     uint32_t tcount = 0;
     for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++tcount) {
       const int z = (int)(t / tilesPerBatch); const int rem = (int)(t - z * tilesPerBatch);
@@ -241,21 +247,36 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       // instruction.  The loads of the first box are issued here, while the tile's MMAs still run, those of box b + 1
       // when box b is taken over.
       const bool resTile = !CONV && p.resTile && tmaW == 128;   // (the gather kernel has no registers to spare and its layers no residual)
-      constexpr bool kPrefetchNext = !X3;                       // tf32x3 holds two accumulator chunks at a time: it fetches later boxes when it needs them
+      // tf32x3 holds two accumulator chunks at a time and keeps one box in flight; the others keep two (a whole
+      // 128 x 256 bf16 tile's share), requested before the accumulator is waited for.
+      constexpr int kAhead = X3 ? 1 : 2;
       const int boxCols = outF32 ? 32 : 64;
       const int esz = outF32 ? 4 : 2;
-      uint4 rpre[8], rrow[8];
+      const int nBoxes = kColsPerWarp / boxCols;
+      uint4 rA[8], rB[X3 ? 1 : 8];
       auto issueRes = [&](int b) {
         const int chunk = lane & 7, r0 = lane >> 3;
         const long long gcol = (long long)tileN * BN + half * kColsPerWarp + b * boxCols + chunk * (16 / esz);
         const char* base = reinterpret_cast<const char*>(p.res) + (zb0 * p.r_s0 + zb1 * p.r_s1 + gcol) * esz;
+        const bool colOk = gcol < p.N;
+        if (kAhead == 1 || !(b & 1)) {
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const long long gr = (long long)tileM * BM + q * 32 + j * 4 + r0;
-          rpre[j] = (gr < p.M && gcol < p.N) ? __ldg(reinterpret_cast<const uint4*>(base + gr * p.r_sm * esz)) : make_uint4(0u, 0u, 0u, 0u);
+          for (int j = 0; j < 8; ++j) {
+            const long long gr = (long long)tileM * BM + q * 32 + j * 4 + r0;
+            rA[j] = (gr < p.M && colOk) ? __ldg(reinterpret_cast<const uint4*>(base + gr * p.r_sm * esz)) : make_uint4(0u, 0u, 0u, 0u);
+          }
+        } else {
+#pragma unroll
+          for (int j = 0; j < (X3 ? 1 : 8); ++j) {
+            const long long gr = (long long)tileM * BM + q * 32 + j * 4 + r0;
+            rB[j] = (gr < p.M && colOk) ? __ldg(reinterpret_cast<const uint4*>(base + gr * p.r_sm * esz)) : make_uint4(0u, 0u, 0u, 0u);
+          }
         }
       };
-      if (resTile) issueRes(0);
+      if (resTile) {
+        issueRes(0);
+        if (kAhead == 2 && nBoxes > 1) issueRes(1);
+      }
       if (!mbarWait(&accFull[ab], aph, abortWord)) { atomicExch(&g_tcStatus, 4); break; }
       tcFenceAfter();
       const uint32_t acc = tmemBase + (uint32_t)(ab * kSetCols) + ((uint32_t)(q * 32) << 16);
@@ -292,20 +313,16 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           if (resTile) {
             const uint32_t st = smemAddr(outStage);
             const int b = (ci * 32) / boxCols;
-            if (!kPrefetchNext && b > 0) issueRes(b);
+            const bool useB = kAhead == 2 && (b & 1);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const uint32_t row = (uint32_t)(j * 4 + (lane >> 3));
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(st + row * 128u + ((((uint32_t)lane & 7u) ^ (row & 7u)) << 4)), "r"(rpre[j].x),
-                           "r"(rpre[j].y), "r"(rpre[j].z), "r"(rpre[j].w) : "memory");
+              const uint4 r = useB ? rB[X3 ? 0 : j] : rA[j];
+              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(st + row * 128u + ((((uint32_t)lane & 7u) ^ (row & 7u)) << 4)), "r"(r.x), "r"(r.y),
+                           "r"(r.z), "r"(r.w) : "memory");
             }
-            __syncwarp();
-#pragma unroll
-            for (int c = 0; c < 8; ++c)
-              asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(rrow[c].x), "=r"(rrow[c].y), "=r"(rrow[c].z), "=r"(rrow[c].w)
-                           : "r"(st + (uint32_t)lane * 128u + ((((uint32_t)c) ^ ((uint32_t)lane & 7u)) << 4)) : "memory");
-            __syncwarp();                                                 // every lane has its row before the buffer is rewritten
-            if (kPrefetchNext && (b + 1) * boxCols < kColsPerWarp) issueRes(b + 1);
+            __syncwarp();                                                 // from here on every lane touches only its own row
+            if (b + kAhead < nBoxes) issueRes(b + kAhead);
           }
         }
         if (whole) {
@@ -351,7 +368,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             if (resTile) {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const uint4 r = (ci & 1) ? rrow[4 + j] : rrow[j];
+                const uint4 r = stagedRow((ci & 1) * 4 + j);
                 const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) pk[4 * j + e] = __hadd2(pk[4 * j + e], h[e]);
@@ -367,13 +384,14 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             if (outF32) {
 #pragma unroll
               for (int j = 0; j < 8; ++j) {
-                v[4 * j] += __uint_as_float(rrow[j].x); v[4 * j + 1] += __uint_as_float(rrow[j].y);
-                v[4 * j + 2] += __uint_as_float(rrow[j].z); v[4 * j + 3] += __uint_as_float(rrow[j].w);
+                const uint4 r = stagedRow(j);
+                v[4 * j] += __uint_as_float(r.x); v[4 * j + 1] += __uint_as_float(r.y);
+                v[4 * j + 2] += __uint_as_float(r.z); v[4 * j + 3] += __uint_as_float(r.w);
               }
             } else {
 #pragma unroll
               for (int j = 0; j < 4; ++j) {
-                const uint4 r = (ci & 1) ? rrow[4 + j] : rrow[j];
+                const uint4 r = stagedRow((ci & 1) * 4 + j);
                 const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
 #pragma unroll
                 for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); v[8 * j + 2 * e] += f.x; v[8 * j + 2 * e + 1] += f.y; }

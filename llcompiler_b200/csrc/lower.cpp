@@ -376,7 +376,7 @@ struct Lowering {
       std::vector<Expr> rm = rowMajor(t.view.shape);
       View dense = materializeTree(leafNode(t.view), t.dtype, t.view.shape, &rm);
       View r;
-      if (!reshapeView(dense, t.shape, r)) fail("internal: reshape of a dense buffer failed");
+      if (!reshapeView(dense, t.shape, r)) { r = dense; r.shape = t.shape; r.strides = rowMajor(t.shape); }   // dense: any shape of the same count
       t.view = r; t.kind = TV::ViewK; t.isConst = bufIsConst(r.buf); return;
     }
     fail("expected a tensor value");
@@ -1075,7 +1075,13 @@ struct Lowering {
     }
     if (xt.kind == TV::Deferred) toView(xt);
     View nv;
-    if (reshapeView(xt.view, shape, nv)) {
+    bool viewOk = reshapeView(xt.view, shape, nv);
+    if (!viewOk && (xt.kind == TV::ViewK) && isContiguous(xt.view)) {
+      // a dense row-major source takes any shape of the same element count, whether or not the equality of the
+      // symbolic products can be proved here (the module asserts it by construction)
+      nv = xt.view; nv.shape = shape; nv.strides = rowMajor(shape); viewOk = true;
+    }
+    if (viewOk) {
       r.kind = xt.kind; r.view = nv; r.pending = xt.pending; r.attn = xt.attn;
       tvs[op->results[0]] = r; return;
     }
@@ -1468,7 +1474,19 @@ void runInferSymbolShape(Module& m) {
       v->type.encoding.push_back(e.isConst() ? "c" + std::to_string(e.constant()) : e.str());
     }
   }
+  // every symbol an encoding names is declared once at the head of the module, arguments first, then in program order
+  // (the reference's pass materialises them as llh.symbolic_int ops, SymbolAnalysis.cpp:266-330)
+  m.symbolDecls.clear();
+  std::set<std::string> declared;
+  auto declare = [&](const Value* v) {
+    if (!v->type.isTensor()) return;
+    for (auto& n : v->type.encoding) if (declared.insert(n).second) m.symbolDecls.push_back(n);
+  };
   Func* f = m.entrance();
+  if (f) {
+    for (Value* a : f->args) declare(a);
+    for (Op* op : f->ops) for (Value* r : op->results) declare(r);
+  }
   if (f) {
     f->resultTypes.clear();
     for (Op* op : f->ops) if (op->name == "func.return") for (Value* v : op->operands) f->resultTypes.push_back(v->type);

@@ -35,15 +35,72 @@ static void replaceAllUses(Module& m, Value* from, Value* to) {
 // Rank-0 tensors become tensor<1xT>, integer `axis` attributes become arrays
 // (src/Dialect/LLH/Transforms/Operationlegalization.cpp:109-230 does the same normalisation).
 void runOperationLegalization(Module& m) {
+  // rank-0 tensors become tensor<1x..> (Operationlegalization.cpp: "weight_refine", "extract" patterns), also in the
+  // function's declared result types
   for (auto& v : m.valueStore)
     if (v->type.isTensor() && !v->type.unranked && v->type.dims.empty()) v->type.dims.push_back(1);
-  for (auto& f : m.funcs)
+  for (auto& f : m.funcs) {
+    for (auto& t : f.resultTypes)
+      if (t.isTensor() && !t.unranked && t.dims.empty()) t.dims.push_back(1);
+    // the number of leading i64 (symbol) arguments is recorded on the function
+    int64_t nSym = 0;
+    for (Value* a : f.args) { if (a->type.isTensor()) break; ++nSym; }
+    if (nSym > 0 && !findAttr(f.attrs, "symbol_int_arg_nums")) f.attrs.emplace_back("symbol_int_arg_nums", Attr::integer(nSym));
+    std::vector<Op*> out;
+    int fresh = 0;
     for (Op* op : f.ops) {
       if (op->name == "llh.reduce_max" || op->name == "llh.reduce_min" || op->name == "llh.reduce_sum" || op->name == "llh.reduce_mean") {
         const Attr* a = op->attr("axis");
         if (a && a->kind == Attr::Int) op->setProp("axis", Attr::array({a->i}));
       }
+      // broadcast_to of a lower-rank operand: reshape it to the result's rank first (extent 1 in the new dims), so that
+      // cast_dims is always the identity
+      if (op->name == "llh.broadcast_to" && !op->operands.empty() && !op->results.empty()) {
+        Value* x = op->operands[0];
+        const size_t rank = op->operands.size() - 1;
+        const Attr* cd = op->attr("cast_dims");
+        if (x->type.isTensor() && !x->type.unranked && x->type.dims.size() < rank && cd && cd->kind == Attr::IntArray &&
+            cd->ints.size() == x->type.dims.size()) {
+          auto name = [&]() { return "%lg" + std::to_string(fresh++); };
+          Op* one = m.newOp("llh.constant");
+          one->setProp("value", Attr::integer(1));
+          Value* oneV = m.newValue(Type::scalar(DType::I64), name()); oneV->def = one; one->results.push_back(oneV);
+          out.push_back(one);
+          std::vector<Value*> dims(rank, oneV);
+          Type rt = x->type; rt.dims.assign(rank, 1); rt.encoding.clear();
+          for (size_t i = 0; i < cd->ints.size(); ++i) {
+            const int64_t d = cd->ints[i];
+            if (d < 0 || (size_t)d >= rank) continue;
+            rt.dims[d] = x->type.dims[i];
+            if (x->type.dims[i] == kDynamic) {
+              Op* idx = m.newOp("llh.constant"); idx->setProp("value", Attr::integer((int64_t)i));
+              Value* idxV = m.newValue(Type::scalar(DType::I64), name()); idxV->def = idx; idx->results.push_back(idxV);
+              Op* dim = m.newOp("llh.dim"); dim->operands = {x, idxV};
+              Value* dimV = m.newValue(Type::scalar(DType::I64), name()); dimV->def = dim; dim->results.push_back(dimV);
+              out.push_back(idx); out.push_back(dim);
+              dims[d] = dimV;
+            } else {
+              Op* c = m.newOp("llh.constant"); c->setProp("value", Attr::integer(x->type.dims[i]));
+              Value* cV = m.newValue(Type::scalar(DType::I64), name()); cV->def = c; c->results.push_back(cV);
+              out.push_back(c);
+              dims[d] = cV;
+            }
+          }
+          Op* rs = m.newOp("llh.reshape");
+          rs->operands.push_back(x);
+          for (Value* d : dims) rs->operands.push_back(d);
+          Value* rv = m.newValue(rt, name()); rv->def = rs; rs->results.push_back(rv);
+          out.push_back(rs);
+          op->operands[0] = rv;
+          std::vector<int64_t> ident(rank); for (size_t i = 0; i < rank; ++i) ident[i] = (int64_t)i;
+          op->setProp("cast_dims", Attr::array(ident));
+        }
+      }
+      out.push_back(op);
     }
+    f.ops.swap(out);
+  }
+  m.recomputeUsers();
 }
 
 // Drops bookkeeping ops and identity data movement
