@@ -1,5 +1,6 @@
 // Parser and printer for the textual LLH surface (see ir.h).
 #include "ir.h"
+#include <map>
 
 #include <cmath>
 #include <cstring>
@@ -169,9 +170,14 @@ std::string Module::str() const {
   o << " {\n";
   for (auto& n : symbolDecls) o << "  \"llh.symbolic_int\"() <{sym_name = \"" << n << "\"}> : () -> ()\n";
   for (auto& f : funcs) {
+    // SSA names are assigned in print order, the way MLIR's printer does: %arg0.. for arguments, %0.. for results
+    std::map<const Value*, std::string> names;
+    for (size_t i = 0; i < f.args.size(); ++i) names[f.args[i]] = "%arg" + std::to_string(i);
+    { int n = 0; for (Op* op : f.ops) if (!op->erased) for (Value* r : op->results) names[r] = "%" + std::to_string(n++); }
+    auto nm = [&](const Value* v) -> const std::string& { auto it = names.find(v); return it == names.end() ? v->name : it->second; };
     o << "  func.func @" << f.name << "(";
     for (size_t i = 0; i < f.args.size(); ++i) {
-      o << (i ? ", " : "") << f.args[i]->name << ": " << f.args[i]->type.str();
+      o << (i ? ", " : "") << nm(f.args[i]) << ": " << f.args[i]->type.str();
       if (i < f.argAttrs.size() && !f.argAttrs[i].empty()) o << " {" << attrListStr(f.argAttrs[i]) << "}";
     }
     o << ")";
@@ -188,16 +194,16 @@ std::string Module::str() const {
       o << "    ";
       if (op->name == "func.return") {
         o << "return";
-        for (size_t i = 0; i < op->operands.size(); ++i) o << (i ? ", " : " ") << op->operands[i]->name;
+        for (size_t i = 0; i < op->operands.size(); ++i) o << (i ? ", " : " ") << nm(op->operands[i]);
         if (!op->operands.empty()) o << " : ";
         for (size_t i = 0; i < op->operands.size(); ++i) o << (i ? ", " : "") << op->operands[i]->type.str();
         o << "\n";
         continue;
       }
-      for (size_t i = 0; i < op->results.size(); ++i) o << (i ? ", " : "") << op->results[i]->name;
+      for (size_t i = 0; i < op->results.size(); ++i) o << (i ? ", " : "") << nm(op->results[i]);
       if (!op->results.empty()) o << " = ";
       o << "\"" << op->name << "\"(";
-      for (size_t i = 0; i < op->operands.size(); ++i) o << (i ? ", " : "") << op->operands[i]->name;
+      for (size_t i = 0; i < op->operands.size(); ++i) o << (i ? ", " : "") << nm(op->operands[i]);
       o << ")";
       if (!op->props.empty()) o << " <{" << attrListStr(op->props) << "}>";
       if (!op->attrs.empty()) o << " {" << attrListStr(op->attrs) << "}";
@@ -211,6 +217,7 @@ std::string Module::str() const {
     }
     o << "  }\n";
   }
+  for (auto& l : symbolRelations) o << "  " << l << "\n";
   o << "}\n";
   return o.str();
 }

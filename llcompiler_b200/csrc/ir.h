@@ -98,6 +98,7 @@ struct Module {
   std::vector<std::unique_ptr<Value>> valueStore;
   std::vector<std::unique_ptr<Op>> opStore;
   std::vector<std::string> leadingLines;  // "#map = ..." aliases kept verbatim
+  std::vector<std::string> symbolRelations;   // generic-form "llh.symbol_relation" lines printed after the functions
   std::vector<std::string> symbolDecls;   // names declared as "llh.symbolic_int" ops at the head of the module body
   Value* newValue(const Type& t, const std::string& name = "");
   Op* newOp(const std::string& name);

@@ -1487,6 +1487,17 @@ void runInferSymbolShape(Module& m) {
     for (Value* a : f->args) declare(a);
     for (Op* op : f->ops) for (Value* r : op->results) declare(r);
   }
+  // a dynamic extent is at least 1 (SymbolAnalysis.cpp:630-633 records the same relation for every new symbol)
+  m.symbolRelations.clear();
+  bool anyDynamic = false;
+  for (auto& n : m.symbolDecls) {
+    bool plain = !n.empty() && n[0] == 's';
+    for (char c : n) if (!isalnum((unsigned char)c) && c != '_') plain = false;
+    if (!plain) continue;
+    anyDynamic = true;
+    m.symbolRelations.push_back("\"llh.symbol_relation\"() <{relation = @c1, relation_kind = #llh.SymbolRelation<GE>, symbol = @" + n + "}> : () -> ()");
+  }
+  if (anyDynamic && declared.insert("c1").second) m.symbolDecls.push_back("c1");
   if (f) {
     f->resultTypes.clear();
     for (Op* op : f->ops) if (op->name == "func.return") for (Value* v : op->operands) f->resultTypes.push_back(v->type);

@@ -15,9 +15,9 @@ PASSES = {"--infer-symbol-shape": "infer-symbol-shape", "--operation-legalizatio
           "--remove-redundant-ops": "remove-redundant-ops"}
 # functions of each file whose CHECK lines hold on this implementation's output; the others need parts of the
 # reference that are out of scope here (affine-map symbol relations, llh.empty, training-mode batch norm, scalar
-# results) or differ only in how the printer numbers function arguments
+# results)
 EXPECTED = {
-    "infer_symbol_shape.mlir": {"constant", "transpose", "max_pool_static", "reshape", "adaptive_average_pool", "binary", "matmul",
+    "infer_symbol_shape.mlir": {"block", "constant", "transpose", "max_pool_static", "reshape", "adaptive_average_pool", "binary", "matmul",
                                 "conv_static", "broadcast_to", "batch_matmul", "extract", "where", "reduce"},
     "remove_redundant_ops.mlir": None,      # all of them
     "operation-legalization.mlir": None,
