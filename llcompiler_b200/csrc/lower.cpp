@@ -1336,6 +1336,12 @@ struct Lowering {
       std::string s = n.substr(4);
       if (s == "constant") constant(op);
       else if (s == "weight") weight(op);
+      else if (s == "empty") {           // uninitialised storage of the given extents (LLHOps.td: llh.empty)
+        std::vector<Expr> shape;
+        for (Value* d : op->operands) shape.push_back(scalarOf(d));
+        DType dt = op->results[0]->type.elt == DType::None ? DType::F32 : op->results[0]->type.elt;
+        tvs[op->results[0]] = makeView(freshView(dt, shape, false), false);
+      }
       else if (s == "torch_symbolic_int" || s == "symbolic_int") {
         const Attr* a = op->attr("sym_name");
         if (!a) fail("symbolic int without sym_name");

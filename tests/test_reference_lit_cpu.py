@@ -14,10 +14,10 @@ REF = "/root/reference/test/Dialect/LLH"
 PASSES = {"--infer-symbol-shape": "infer-symbol-shape", "--operation-legalization": "operation-legalization",
           "--remove-redundant-ops": "remove-redundant-ops"}
 # functions of each file whose CHECK lines hold on this implementation's output; the others need parts of the
-# reference that are out of scope here (affine-map symbol relations, llh.empty, training-mode batch norm, scalar
+# reference that are out of scope here (affine-map symbol relations, training-mode batch norm, scalar
 # results)
 EXPECTED = {
-    "infer_symbol_shape.mlir": {"block", "constant", "transpose", "max_pool_static", "reshape", "adaptive_average_pool", "binary", "matmul",
+    "infer_symbol_shape.mlir": {"block", "constant", "empty", "transpose", "max_pool_static", "reshape", "adaptive_average_pool", "binary", "matmul",
                                 "conv_static", "broadcast_to", "batch_matmul", "extract", "where", "reduce"},
     "remove_redundant_ops.mlir": None,      # all of them
     "operation-legalization.mlir": None,
