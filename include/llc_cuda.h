@@ -44,6 +44,9 @@ typedef struct LlcGemmParams {
    * NULL disables split-K.  Launches that share one workspace must not overlap on the GPU. */
   void* workspace;
   int64_t workspace_bytes;
+  /* Optional, precision tf32x3 only: B - truncate_to_tf32(B), laid out exactly like b (same strides).  When given, the
+   * kernel loads it instead of splitting every B tile itself; weights are split once at load time this way. */
+  const void* b_lo;
 } LlcGemmParams;
 int llc_cuda_gemm(const LlcGemmParams* p, void* stream);
 
@@ -97,6 +100,7 @@ typedef struct LlcConvParams {
   int32_t stride_h, stride_w, pad_h, pad_w, dil_h, dil_w;
   float alpha;
   int32_t act;
+  const void* w_lo;   /* optional, precision tf32x3: w - truncate_to_tf32(w), same layout as w (see LlcGemmParams.b_lo) */
 } LlcConvParams;
 int llc_cuda_conv2d(const LlcConvParams* p, void* stream);
 

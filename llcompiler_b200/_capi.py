@@ -98,7 +98,7 @@ class LlcGemmParams(Structure):
                 ("precision", c_int32)] + [(n, c_int64) for n in (
                     "m", "n", "k", "b0", "b1", "a_s0", "a_s1", "a_sm", "b_s0", "b_s1", "b_sk", "b_sn",
                     "o_s0", "o_s1", "o_sm", "r_s0", "r_s1", "r_sm", "r_sn")] + [("alpha", c_float), ("act", c_int32),
-                                                                               ("workspace", c_void_p), ("workspace_bytes", c_int64)]
+                                                                               ("workspace", c_void_p), ("workspace_bytes", c_int64), ("b_lo", c_void_p)]
 
 
 class LlcConvParams(Structure):
@@ -106,7 +106,7 @@ class LlcConvParams(Structure):
                 ("res", c_void_p), ("in_dtype", c_int32), ("out_dtype", c_int32), ("res_dtype", c_int32),
                 ("precision", c_int32)] + [(n, c_int64) for n in ("n", "h", "w_in", "c", "f", "kh", "kw", "oh", "ow")] + \
                [(n, c_int32) for n in ("stride_h", "stride_w", "pad_h", "pad_w", "dil_h", "dil_w")] + \
-               [("alpha", c_float), ("act", c_int32)]
+               [("alpha", c_float), ("act", c_int32), ("w_lo", c_void_p)]
 
 
 class LlcAttentionParams(Structure):

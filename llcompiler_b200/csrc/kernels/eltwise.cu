@@ -17,7 +17,7 @@ constexpr int kMaxIn = 8;
 
 enum EltOp : int {
   E_LD = 0, E_IMM, E_ADD, E_SUB, E_MUL, E_DIV, E_MAX, E_MIN, E_POW, E_RELU, E_ABS, E_SQRT, E_RSQRT, E_EXP, E_GELU, E_TANH,
-  E_ERF, E_SIGMOID, E_NEG, E_CAST, E_TRUNC, E_WHERE, E_EQ, E_NE, E_GE, E_GT, E_LE, E_LT
+  E_ERF, E_SIGMOID, E_NEG, E_CAST, E_TRUNC, E_TF32LO, E_WHERE, E_EQ, E_NE, E_GE, E_GT, E_LE, E_LT
 };
 
 struct EltProgram {
@@ -57,6 +57,7 @@ __device__ __forceinline__ float evalOp(int op, float x, float y, float z, float
     case E_NEG: return -x;
     case E_CAST: return x;
     case E_TRUNC: return truncf(x);
+    case E_TF32LO: return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u);   // what a tf32 operand read drops
     case E_WHERE: return x != 0.f ? y : z;
     case E_EQ: return x == y ? 1.f : 0.f;
     case E_NE: return x != y ? 1.f : 0.f;
@@ -149,7 +150,7 @@ int parseProgram(const char* text, EltProgram& prog, int nin) {
   static const struct { const char* name; int op; int arity; } table[] = {
       {"add", E_ADD, 2}, {"sub", E_SUB, 2}, {"mul", E_MUL, 2}, {"div", E_DIV, 2}, {"max", E_MAX, 2}, {"min", E_MIN, 2}, {"pow", E_POW, 2},
       {"relu", E_RELU, 1}, {"abs", E_ABS, 1}, {"sqrt", E_SQRT, 1}, {"rsqrt", E_RSQRT, 1}, {"exp", E_EXP, 1}, {"gelu", E_GELU, 1},
-      {"tanh", E_TANH, 1}, {"erf", E_ERF, 1}, {"sigmoid", E_SIGMOID, 1}, {"neg", E_NEG, 1}, {"cast", E_CAST, 1}, {"trunc", E_TRUNC, 1},
+      {"tanh", E_TANH, 1}, {"erf", E_ERF, 1}, {"sigmoid", E_SIGMOID, 1}, {"neg", E_NEG, 1}, {"cast", E_CAST, 1}, {"trunc", E_TRUNC, 1}, {"tf32lo", E_TF32LO, 1},
       {"where", E_WHERE, 3}, {"eq", E_EQ, 2}, {"ne", E_NE, 2}, {"ge", E_GE, 2}, {"gt", E_GT, 2}, {"le", E_LE, 2}, {"lt", E_LT, 2}};
   prog.n = 0;
   std::string s = text ? text : "";

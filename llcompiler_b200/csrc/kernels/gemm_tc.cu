@@ -46,6 +46,7 @@ struct TcArgs {
   long long o_s0, o_s1, o_sm, r_s0, r_s1, r_sm, r_sn;
   int b1; int kBlocks; int vecOut;
   int resTile;              // the residual can be fetched as 32-row x 128-byte boxes with 16-byte loads
+  int hasBLo;               // tf32x3: the low-order part of B comes from memory (mapBLo) instead of the split warps
   int tmaOut;               // 0, or the bytes per row of the output box the epilogue stores through TMA (64 or 128)
   int aZ0, aZ1, bZ0, bZ1;   // 1: the operand has this batch dim, 0: it is broadcast (coordinate 0)
   int mTiles, nTiles; long long tiles;
@@ -80,7 +81,8 @@ __device__ __forceinline__ void cpAsyncArriveOn(uint64_t* bar) {
 // bytes lies inside one filter tap: channels * element size is a multiple of 128).
 template <int BN, int KIND, int MODE, bool BMN>
 __global__ void __launch_bounds__((10 + (MODE == 1 ? 8 : 0) + (KIND == 2 ? 4 : 0)) * 32, 1)
-tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapO, const TcArgs p) {
+tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapO,
+          const __grid_constant__ CUtensorMap mapBLo, const TcArgs p) {
   constexpr bool X3 = KIND == 2;
   constexpr bool TF32 = KIND != 0;
   constexpr bool CONV = MODE == 1;      // the gather warps exist
@@ -159,7 +161,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
           if (!mbarWait(&empty[s], ph ^ 1, abortWord)) { atomicExch(&g_tcStatus, 1); ok = false; break; }
-          mbarExpectTx(&full[s], CONV ? S::kBBytes : S::kABytes + S::kBBytes);
+          mbarExpectTx(&full[s], (CONV ? S::kBBytes : S::kABytes + S::kBBytes) + ((X3 && p.hasBLo) ? S::kBBytes : 0));
           if (MODE == 0) tmaLoad4d(stageA(s), &mapA, &full[s], kb * BK, tileM * BM, zb1 * p.aZ1, zb0 * p.aZ0);
           if (IM2COL) {
             // 128 output pixels from (img0, oh0, ow0) on, in w -> h -> n order; the coordinates name the input pixel
@@ -174,6 +176,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
               tmaLoad4d(stageB(s) + a * kSlabBytes, &mapB, &full[s], tileN * BN + a * kAtomN, kb * BK, zb1 * p.bZ1, zb0 * p.bZ0);
           } else {
             tmaLoad4d(stageB(s), &mapB, &full[s], kb * BK, tileN * BN, zb1 * p.bZ1, zb0 * p.bZ0);
+            if (X3 && p.hasBLo) tmaLoad4d(stageBLo(s), &mapBLo, &full[s], kb * BK, tileN * BN, zb1 * p.bZ1, zb0 * p.bZ0);
           }
         }
       }
@@ -570,8 +573,10 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         auto lo = [](float x) { return x - __uint_as_float(__float_as_uint(x) & 0xFFFFE000u); };
 #pragma unroll 4
         for (int i = et; i < S::kABytes / 16; i += 128) { float4 v = srcA[i]; dstA[i] = make_float4(lo(v.x), lo(v.y), lo(v.z), lo(v.w)); }
+        if (!p.hasBLo) {
 #pragma unroll 4
-        for (int i = et; i < S::kBBytes / 16; i += 128) { float4 v = srcB[i]; dstB[i] = make_float4(lo(v.x), lo(v.y), lo(v.z), lo(v.w)); }
+          for (int i = et; i < S::kBBytes / 16; i += 128) { float4 v = srcB[i]; dstB[i] = make_float4(lo(v.x), lo(v.y), lo(v.z), lo(v.w)); }
+        }
         fenceProxyAsync();
         __syncwarp();
         if (lane == 0) mbarArrive(&split[s]);
@@ -717,7 +722,7 @@ bool tmaEpilogueEnabled() {
 }
 
 template <int BN, int KIND, int MODE, bool BMN>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, TcArgs a, long long batch, cudaStream_t st) {
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mbl, TcArgs a, long long batch, cudaStream_t st) {
   using S = Smem<BN, KIND == 2>;
   static bool configured = false;
   if (!configured) {
@@ -729,14 +734,14 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, 
   a.tiles = (long long)a.mTiles * a.nTiles * batch;
   const int threads = (10 + (MODE == 1 ? 8 : 0) + (KIND == 2 ? 4 : 0)) * 32;
   const unsigned grid = (unsigned)(a.tiles < numSMs() ? a.tiles : numSMs());
-  tc_kernel<BN, KIND, MODE, BMN><<<grid, threads, S::kTotal, st>>>(ma, mb, mo, a);
+  tc_kernel<BN, KIND, MODE, BMN><<<grid, threads, S::kTotal, st>>>(ma, mb, mo, mbl, a);
   LLC_LAUNCH_CHECK("tc_kernel");
   return LLC_OK;
 }
 
 template <int MODE, bool BMN>
-int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const TcArgs& a, long long batch, cudaStream_t st) {
-#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, MODE, BMN>(ma, mb, mo, a, batch, st);
+int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mbl, const TcArgs& a, long long batch, cudaStream_t st) {
+#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, MODE, BMN>(ma, mb, mo, mbl, a, batch, st);
   TC_CASE(64, 0) TC_CASE(128, 0)
   if constexpr (!BMN) { TC_CASE(64, 1) TC_CASE(64, 2) TC_CASE(128, 1) TC_CASE(128, 2) TC_CASE(256, 0) TC_CASE(256, 1) }
 #undef TC_CASE
@@ -815,7 +820,11 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   auto r16 = [&](long long st) { return st >= 0 && (st * ob) % 16 == 0; };
   a.resTile = p->res && p->r_sn == 1 && p->res_dtype == p->out_dtype && (reinterpret_cast<uintptr_t>(p->res) & 15) == 0 && r16(p->r_sm) && r16(p->r_s0) &&
               r16(p->r_s1) && p->n % (16 / ob) == 0;
-  return bmn ? dispatch<0, true>(bn, kind, ma, mb, mo, a, batch, st) : dispatch<0, false>(bn, kind, ma, mb, mo, a, batch, st);
+  CUtensorMap mbl = mb;
+  if (kind == 2 && !bmn && p->b_lo && (reinterpret_cast<uintptr_t>(p->b_lo) & 15) == 0 &&
+      makeMap(&mbl, p->b_lo, f32, p->k, p->n, p->b1, p->b0, p->b_sn, p->b_s1, p->b_s0, bn))
+    a.hasBLo = 1;
+  return bmn ? dispatch<0, true>(bn, kind, ma, mb, mo, mbl, a, batch, st) : dispatch<0, false>(bn, kind, ma, mb, mo, mbl, a, batch, st);
 }
 
 bool tcConvSupported(const LlcConvParams* p) {
@@ -854,11 +863,13 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
   const int boxBytes = outBoxBytes(bn, ob == 4);
   if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->f, M, 1, 1, p->f, 0, 0, boxBytes)) a.tmaOut = boxBytes;
   a.resTile = p->res && p->res_dtype == p->out_dtype && (reinterpret_cast<uintptr_t>(p->res) & 15) == 0 && (p->f * ob) % 16 == 0;
+  CUtensorMap mbl = mb;
+  if (kind == 2 && p->w_lo && (reinterpret_cast<uintptr_t>(p->w_lo) & 15) == 0 && makeMap(&mbl, p->w_lo, f32, K, p->f, 1, 1, K, 0, 0, bn)) a.hasBLo = 1;
   if (im2colEligible(p, f32)) {
     CUtensorMap ma;
-    if (makeIm2colMap(&ma, p, f32)) return dispatch<2, false>(bn, kind, ma, mb, mo, a, 1, st);
+    if (makeIm2colMap(&ma, p, f32)) return dispatch<2, false>(bn, kind, ma, mb, mo, mbl, a, 1, st);
   }
-  return dispatch<1, false>(bn, kind, mb, mb, mo, a, 1, st);
+  return dispatch<1, false>(bn, kind, mb, mb, mo, mbl, a, 1, st);
 }
 
 // Reads and clears the status word the bounded waits write (0 = no wait ever gave up).

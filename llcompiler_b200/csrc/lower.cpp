@@ -723,6 +723,12 @@ struct Lowering {
     P.step.kernel = "gemm";
     P.step.views.emplace_back("a", a);
     P.step.views.emplace_back("b", b);
+    // tf32x3 with a constant (weight) B: its low-order part is computed once at load time and handed to the kernel,
+    // which otherwise derives it from every B tile it loads
+    if (gemmPrecision(a.dtype) == "tf32x3" && b.dtype == DType::F32 && bufIsConst(b.buf) && b.strides[2].isConst(1)) {
+      View lo = materializeTree(opNode("tf32lo", leafNode(b)), DType::F32, b.shape, &b.strides);
+      if (lo.strides == b.strides) P.step.views.emplace_back("b_lo", lo);
+    }
     P.step.params.emplace_back("prec", gemmPrecision(a.dtype));
     std::vector<Expr> nshape = {a.shape[0], a.shape[1], M, N};
     if (a.shape[0].isConst(1) && !b.shape[0].isConst(1)) nshape[0] = b.shape[0];
@@ -820,6 +826,10 @@ struct Lowering {
     P.step.kernel = "conv";
     P.step.views.emplace_back("x", x);
     P.step.views.emplace_back("w", w);
+    if (gemmPrecision(x.dtype) == "tf32x3" && w.dtype == DType::F32 && bufIsConst(w.buf) && isContiguous(w)) {
+      View lo = materializeTree(opNode("tf32lo", leafNode(w)), DType::F32, w.shape);
+      P.step.views.emplace_back("w_lo", lo);
+    }
     auto arr = [](const std::vector<int64_t>& v) { std::string o; for (size_t i = 0; i < v.size(); ++i) o += (i ? "," : "") + std::to_string(v[i]); return o; };
     P.step.params.emplace_back("stride", arr(stride));
     P.step.params.emplace_back("pad", arr(pad));

@@ -192,6 +192,10 @@ void LlcExec::prepare(RStep& rs) {
     if (const RView* v = rs.view("res")) { patch(&p.res, *v); p.res_dtype = v->dtype; p.r_s0 = v->strides[0]; p.r_s1 = v->strides[1]; p.r_sm = v->strides[2]; p.r_sn = v->strides[3]; }
     p.alpha = std::stof(s.param("alpha", "1")); p.act = actOf();
     p.workspace = workspace; p.workspace_bytes = (int64_t)kWorkspaceBytes;
+    if (const RView* v = rs.view("b_lo")) {
+      if (v->strides[0] != b.strides[0] || v->strides[1] != b.strides[1] || v->strides[2] != b.strides[2] || v->strides[3] != b.strides[3]) failArg("gemm b_lo must be laid out like b");
+      patch(&p.b_lo, *v);
+    }
   } else if (s.kernel == "attention") {
     rs.kind = kAttention;
     const RView &q = need("q"), &k = need("k"), &v = need("v"), &o = need("out");   // q, out [b0,b1,M,D]; k [b0,b1,D,N]; v [b0,b1,N,D]
@@ -225,6 +229,7 @@ void LlcExec::prepare(RStep& rs) {
     if (const RView* v = rs.view("scale")) patch(&p.scale, *v);
     if (const RView* v = rs.view("shift")) patch(&p.shift, *v);
     if (const RView* v = rs.view("res")) { patch(&p.res, *v); p.res_dtype = v->dtype; }
+    if (const RView* v = rs.view("w_lo")) patch(&p.w_lo, *v);
     p.alpha = std::stof(s.param("alpha", "1")); p.act = actOf();
   } else if (s.kernel == "maxpool") {
     rs.kind = kPool;

@@ -226,6 +226,7 @@ _ELT = {
     "relu": torch.relu, "abs": torch.abs, "sqrt": torch.sqrt, "rsqrt": torch.rsqrt, "exp": torch.exp,
     "gelu": F.gelu, "tanh": torch.tanh, "erf": torch.erf, "sigmoid": torch.sigmoid, "neg": torch.neg,
     "cast": lambda a: a, "trunc": torch.trunc,
+    "tf32lo": lambda a: a - (a.contiguous().view(torch.int32) & -8192).view(torch.float32),
     "where": lambda c, a, b: torch.where(c != 0, a, b),
     "eq": lambda a, b: (a == b).float(), "ne": lambda a, b: (a != b).float(), "ge": lambda a, b: (a >= b).float(),
     "gt": lambda a, b: (a > b).float(), "le": lambda a, b: (a <= b).float(), "lt": lambda a, b: (a < b).float(),

@@ -21,7 +21,7 @@ def _p(t):
     return None if t is None else c_void_p(t.data_ptr())
 
 
-def gemm(a, b, out, scale=None, shift=None, res=None, alpha=1.0, act="none", prec="fp32", workspace=None):
+def gemm(a, b, out, scale=None, shift=None, res=None, alpha=1.0, act="none", prec="fp32", workspace=None, b_lo=None):
     """a [b0,b1,M,K] (k stride 1), b [b0,b1,K,N] (k or n stride 1), out [b0,b1,M,N] views."""
     p = C.LlcGemmParams()
     p.a, p.b, p.out, p.scale, p.shift, p.res = _p(a), _p(b), _p(out), _p(scale), _p(shift), _p(res)
@@ -37,6 +37,7 @@ def gemm(a, b, out, scale=None, shift=None, res=None, alpha=1.0, act="none", pre
     p.alpha, p.act = alpha, C.ACT[act]
     if workspace is not None:
         p.workspace, p.workspace_bytes = _p(workspace), workspace.numel() * workspace.element_size()
+    p.b_lo = _p(b_lo)
     C.check(C.lib().llc_cuda_gemm(byref(p), _stream()))
 
 
@@ -59,7 +60,7 @@ def attention(q, k, v, out, mask=None, scale=1.0):
 
 
 def conv2d(x_nhwc, w_fhwc, out_nhwc, stride, pad, dil=(1, 1), scale=None, shift=None, res=None, alpha=1.0,
-           act="none", prec="fp32"):
+           act="none", prec="fp32", w_lo=None):
     p = C.LlcConvParams()
     p.x, p.w, p.out, p.scale, p.shift, p.res = _p(x_nhwc), _p(w_fhwc), _p(out_nhwc), _p(scale), _p(shift), _p(res)
     p.in_dtype, p.out_dtype = _DT[x_nhwc.dtype], _DT[out_nhwc.dtype]
@@ -70,6 +71,7 @@ def conv2d(x_nhwc, w_fhwc, out_nhwc, stride, pad, dil=(1, 1), scale=None, shift=
     p.oh, p.ow = out_nhwc.shape[1], out_nhwc.shape[2]
     p.stride_h, p.stride_w, p.pad_h, p.pad_w, p.dil_h, p.dil_w = stride[0], stride[1], pad[0], pad[1], dil[0], dil[1]
     p.alpha, p.act = alpha, C.ACT[act]
+    p.w_lo = _p(w_lo)
     C.check(C.lib().llc_cuda_conv2d(byref(p), _stream()))
 
 

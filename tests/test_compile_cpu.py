@@ -62,6 +62,8 @@ def test_resnet18_tensor_core_plan_pads_the_stem():
     assert max_rel_err(got, want) < 1e-4
     plan = comp.compiled[0].engine.text
     assert "prec:tf32x3" in plan and "[64,7,7,4;" in plan
+    # weights are split into their tf32 high and low parts once, at load time
+    assert plan.count(" w_lo=") == 20 and plan.count(" b_lo=") == 1 and plan.count("tf32lo") == 21
 
 
 def _bert_bf16(monkeypatch, fuse, dynamic=False, seq=16):

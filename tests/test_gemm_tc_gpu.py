@@ -149,3 +149,26 @@ def test_bf16_attention_pv_strided_heads():
     G.gemm(pmat.to(DEV), v.to(DEV).view(Bn, S, H, D).permute(0, 2, 1, 3), out, prec="bf16")
     assert max_rel_err(out, want) < 1e-4
     _healthy()
+
+
+def _tf32_lo(t):
+    return t - (t.contiguous().view(torch.int32) & -8192).view(torch.float32)
+
+
+def test_tf32x3_presplit_weight_operand():
+    # the low-order part of a constant B (and of convolution weights) may be handed in instead of being derived from
+    # every tile: same result to the last bit (the kernel computes the same values itself otherwise)
+    m, n, k = 300, 200, 520
+    a, w = _rand(m, k).to(DEV), _rand(n, k, seed=1).to(DEV)
+    o1 = torch.empty(1, 1, m, n, device=DEV); o2 = torch.empty_like(o1)
+    G.gemm(a[None, None], w.t()[None, None], o1, prec="tf32x3")
+    G.gemm(a[None, None], w.t()[None, None], o2, prec="tf32x3", b_lo=_tf32_lo(w).t()[None, None])
+    assert torch.equal(o1, o2)
+    want = (a.double() @ w.double().t()).float()
+    assert max_rel_err(o2[0, 0], want) < 5e-5
+    x = _rand(2, 30, 30, 64).to(DEV); wt = (_rand(72, 3, 3, 64, seed=1) * 0.1).to(DEV)
+    c1 = torch.empty(2, 30, 30, 72, device=DEV); c2 = torch.empty_like(c1)
+    G.conv2d(x, wt, c1, (1, 1), (1, 1), prec="tf32x3")
+    G.conv2d(x, wt, c2, (1, 1), (1, 1), prec="tf32x3", w_lo=_tf32_lo(wt))
+    assert torch.equal(c1, c2)
+    _healthy()
