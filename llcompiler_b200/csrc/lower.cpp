@@ -162,6 +162,7 @@ struct Lowering {
   std::vector<ENode> nodes;
   std::vector<PendingK> pend;
   std::vector<AttnCand> attn;
+  bool shapesOnly = false;     // infer-symbol-shape: the plan is discarded, so results need not be materialised (scalars may be returned)
   std::map<Value*, TV> tvs;
   std::map<std::string, int> constVecCache;
 
@@ -1341,7 +1342,7 @@ struct Lowering {
     for (Op* op : f->ops) {
       if (op->erased) continue;
       const std::string& n = op->name;
-      if (n == "func.return") { finishOutputs(op); continue; }
+      if (n == "func.return") { if (!shapesOnly) finishOutputs(op); continue; }
       if (n.compare(0, 4, "llh.") != 0) fail("operation '" + n + "' is not part of the LLH surface");
       std::string s = n.substr(4);
       if (s == "constant") constant(op);
@@ -1478,6 +1479,7 @@ void runInferSymbolShape(Module& m) {
   runOperationLegalization(m);
   CompileOptionsData opts;
   Lowering L(m, opts);
+  L.shapesOnly = true;
   L.run();
   for (auto& kv : L.tvs) {
     Value* v = kv.first;
@@ -1502,6 +1504,18 @@ void runInferSymbolShape(Module& m) {
   if (f) {
     for (Value* a : f->args) declare(a);
     for (Op* op : f->ops) for (Value* r : op->results) declare(r);
+  }
+  // an i64 argument that names no symbol yet gets the next free one (it is a symbol too: SymbolAnalysis buildNewSymbol)
+  if (f) {
+    int next = 0;
+    for (auto& n : m.symbolDecls) if (n.size() > 1 && n[0] == 's' && isdigit((unsigned char)n[1])) next = std::max(next, atoi(n.c_str() + 1) + 1);
+    if (f->argAttrs.size() < f->args.size()) f->argAttrs.resize(f->args.size());
+    for (size_t i = 0; i < f->args.size(); ++i) {
+      if (f->args[i]->type.isTensor() || f->args[i]->type.elt != DType::I64 || findAttr(f->argAttrs[i], "func.symbol_int")) continue;
+      Attr a; a.kind = Attr::SymRef; a.s = "s" + std::to_string(next++);
+      f->argAttrs[i].emplace_back("func.symbol_int", a);
+      if (declared.insert(a.s).second) m.symbolDecls.push_back(a.s);
+    }
   }
   // a dynamic extent is at least 1 (SymbolAnalysis.cpp:630-633 records the same relation for every new symbol)
   m.symbolRelations.clear();

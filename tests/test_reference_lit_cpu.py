@@ -18,7 +18,7 @@ PASSES = {"--infer-symbol-shape": "infer-symbol-shape", "--operation-legalizatio
 # results)
 EXPECTED = {
     "infer_symbol_shape.mlir": {"block", "constant", "empty", "transpose", "max_pool_static", "reshape", "adaptive_average_pool", "binary", "matmul",
-                                "conv_static", "broadcast_to", "batch_matmul", "extract", "where", "reduce"},
+                                "conv_static", "broadcast_to", "batch_matmul", "extract", "where", "reduce", "checkIsReturnOperand"},
     "remove_redundant_ops.mlir": None,      # all of them
     "operation-legalization.mlir": None,
 }
