@@ -718,6 +718,15 @@ struct Lowering {
       conv(a); conv(b);
     }
     a = lift(a); b = lift(b);
+    // fp32 operands reach the tensor cores only K-major (a 32-bit MN-major B tile produced zeros on B200): a run-time B
+    // stored [k][n] (attention's V) is copied once into [n][k] order, which costs far less than the FMA kernel would
+    {
+      const std::string prec = gemmPrecision(a.dtype);
+      if ((prec == "tf32" || prec == "tf32x3") && b.dtype == DType::F32 && !b.strides[2].isConst(1) && !b.shape[2].isConst(1)) {
+        std::vector<Expr> st = {b.shape[1] * b.shape[2] * b.shape[3], b.shape[2] * b.shape[3], Expr(1), b.shape[2]};
+        b = materializeTree(leafNode(b), DType::F32, b.shape, &st);
+      }
+    }
     Expr M = a.shape[2], K = a.shape[3], N = b.shape[3];
     DType dt = op->results[0]->type.elt;
     PendingK P;
