@@ -258,9 +258,9 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       // instruction.  The loads of the first box are issued here, while the tile's MMAs still run, those of box b + 1
       // when box b is taken over.
       const bool resTile = !CONV && p.resTile && tmaW == 128;   // (the gather kernel has no registers to spare and its layers no residual)
-      // tf32x3 holds two accumulator chunks at a time and keeps one box in flight; the others keep two (a whole
-      // 128 x 256 bf16 tile's share), requested before the accumulator is waited for.
-      constexpr int kAhead = (X3 || WIDE) ? 1 : 2;               // (sixteen epilogue warps keep enough boxes in flight between them)
+      // One box is in flight per warp: the first is requested before the accumulator is waited for, box b + 1 when
+      // box b is taken over.
+      constexpr int kAhead = 1;                                  // (two boxes ahead measured no faster and cost 32 registers)
       const int boxCols = outF32 ? 32 : 64;
       const int esz = outF32 ? 4 : 2;
       const int nBoxes = kColsPerWarp / boxCols;
@@ -764,8 +764,8 @@ bool wideEpilogue(int bn, int kind, int kBlocks) {
   const char* e = getenv("LLC_TC_WIDE");
   const int forced = e && *e ? atoi(e) : -1;
   if (bn != 256 || kind == 2) return false;
+  if (forced == 2) return kBlocks <= 8;      // the intended policy, while it is being measured
   if (forced >= 0) return forced != 0;
-  (void)kBlocks;
   return false;
 }
 

