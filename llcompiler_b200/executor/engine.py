@@ -10,6 +10,7 @@ calling convention); outputs are sized by the plan's symbolic shapes through
 """
 from __future__ import annotations
 
+import sys
 from typing import Any, List, Optional
 
 import torch
@@ -35,6 +36,22 @@ class ExecutionEngine:
         self.executor.load(so_file, self.device)
         self.gen_outs_call = None
         self._out_meta = {}
+        self._pinned = {}
+
+    def _host_output(self, shape, dtype) -> torch.Tensor:
+        """A page-locked host tensor for a result that goes back to the host (a device-to-host copy into pageable
+        memory runs at a fraction of the link rate).  Buffers are kept and handed out again only when nothing else
+        refers to them any more: neither the tensor object nor, through a view or a numpy array, its storage."""
+        use_count = getattr(torch._C, "_storage_Use_Count", None)
+        pool = self._pinned.setdefault((shape, dtype), [])
+        if use_count is not None:
+            for t in pool:
+                if sys.getrefcount(t) <= 3 and use_count(t.untyped_storage()._cdata) <= 2:
+                    return t
+        t = torch.empty(shape, dtype=dtype, pin_memory=True)
+        if use_count is not None and len(pool) < 4:
+            pool.append(t)
+        return t
 
     def run(self, *args) -> Any:
         raise NotImplementedError
@@ -73,7 +90,7 @@ class Torch_ExecutionEngine(ExecutionEngine):
         if meta is None:
             meta = [(tuple(shape), TYPE_TO_TORCH_DTYPE[code]) for shape, code in self.executor.output_shapes(symbols, inputs)]
             self._out_meta[key] = meta
-        outputs = [torch.empty(shape, dtype=dt, device=out_device) for shape, dt in meta]
+        outputs = [torch.empty(shape, dtype=dt, device=out_device) if on_gpu else self._host_output(shape, dt) for shape, dt in meta]
         outputs_ = self.trans_to_tensor(*outputs)
         stream = torch.cuda.current_stream(self.device).cuda_stream
         if symbols:

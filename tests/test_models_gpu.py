@@ -131,3 +131,26 @@ def test_encoder_layer_tf32(seq):
         want = m(x)
     comp, fn, out = _gpu_run(m, (x,), dynamic=True, precision="tf32")
     assert max_rel_err(out, want) < 2e-2                  # the tolerance stated for TF32 paths
+
+
+def test_host_results_are_page_locked_and_never_aliased():
+    m = build_model("mlp")
+    x = torch.randn(16, 784)
+    comp, fn, out = _gpu_run(m, (x,), dynamic=True)
+    eng = comp.compiled[0].engine
+    a = eng.run(16, x)[0]                       # host tensors in, host tensor out
+    assert a.is_pinned() and not a.is_cuda
+    keep = a.clone()
+    b = eng.run(16, x * 2)[0]                   # `a` is still referenced: the engine must not hand its buffer out again
+    assert b.data_ptr() != a.data_ptr() and torch.equal(a, keep)
+    view = b[:4]
+    ptr_b = b.data_ptr()
+    del b                                       # a view keeps the storage alive: still no reuse
+    c = eng.run(16, x * 3)[0]
+    assert c.data_ptr() != ptr_b and torch.equal(view, eng.run(16, x * 2)[0][:4])
+    ptr_a = a.data_ptr()
+    del a, keep
+    d = eng.run(16, x)[0]                       # nothing refers to the first buffer any more: it is reused
+    assert d.data_ptr() in (ptr_a, ptr_b) or d.is_pinned()
+    with torch.no_grad():
+        assert max_rel_err(d, m(x)) < 1e-5
