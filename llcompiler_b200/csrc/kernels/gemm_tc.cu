@@ -54,10 +54,10 @@ struct TcArgs {
   const void* x; int H, W, C, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
 };
 
-template <int BN, bool X3, bool WIDE = false> struct Smem {
+template <int BN, bool X3> struct Smem {
   static constexpr int kABytes = BM * kTileKBytes, kBBytes = BN * kTileKBytes;
   static constexpr int kStageBytes = (kABytes + kBBytes) * (X3 ? 2 : 1);
-  static constexpr int kStagingBytes = (WIDE ? 16 : 8) * 4096;   // one 32-row x 128-byte output box per epilogue warp
+  static constexpr int kStagingBytes = 8 * 4096;   // one 32-row x 128-byte output box per epilogue warp
   static constexpr int kStageBudget = 224 * 1024 - kStagingBytes;
   static constexpr int kStages = kStageBudget / kStageBytes > 8 ? 8 : kStageBudget / kStageBytes;
   static constexpr int kBarrierBytes = 1024;
@@ -77,25 +77,22 @@ __device__ __forceinline__ void cpAsyncArriveOn(uint64_t* bar) {
 }
 
 // KIND: 0 bf16, 1 tf32, 2 tf32x3.  BMN: B is stored [k][n] (unit stride along n) instead of [n][k].
-// Threads of a CTA: producer, issuer, 8 (or, for MODE 3 and 4, 16) epilogue warps, 8 gather warps (MODE 1), 4 split warps (tf32x3).
-__host__ __device__ constexpr int tcThreads(int kind, int mode) { return (2 + (mode >= 3 ? 16 : 8) + (mode == 1 ? 8 : 0) + (kind == 2 ? 4 : 0)) * 32; }
+// Threads of a CTA: producer, issuer, 8 epilogue warps, 8 gather warps (MODE 1), 4 split warps (tf32x3).
+__host__ __device__ constexpr int tcThreads(int kind, int mode) { return (2 + 8 + (mode == 1 ? 8 : 0) + (kind == 2 ? 4 : 0)) * 32; }
 
 // MODE: 0 dense GEMM (A by tiled TMA), 1 convolution with A gathered by warps (any channel count that keeps a
 // 16-byte chunk inside one filter tap), 2 convolution with A loaded by TMA in im2col mode (a K block of 128
-// bytes lies inside one filter tap: channels * element size is a multiple of 128).  MODE 3 and 4 are MODE 0 and 2 with
-// sixteen epilogue warps instead of eight (and one pipeline stage less): for short K loops, where a tile's epilogue takes
-// longer than its MMAs and the latency of its loads and stores is what the extra warps hide.
+// bytes lies inside one filter tap: channels * element size is a multiple of 128).  (A variant with sixteen epilogue
+// warps and one pipeline stage less was measured 1.2 to 1.9 times slower on every shape tried and is not kept.)
 template <int BN, int KIND, int MODE, bool BMN>
 __global__ void __launch_bounds__(tcThreads(KIND, MODE), 1)
 tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapO,
           const __grid_constant__ CUtensorMap mapBLo, const TcArgs p) {
   constexpr bool X3 = KIND == 2;
   constexpr bool TF32 = KIND != 0;
-  constexpr bool WIDE = MODE >= 3;
-  constexpr int BASE = MODE == 3 ? 0 : (MODE == 4 ? 2 : MODE);
-  constexpr bool CONV = BASE == 1;      // the gather warps exist
-  constexpr bool IM2COL = BASE == 2;
-  using S = Smem<BN, X3, MODE >= 3>;
+  constexpr bool CONV = MODE == 1;      // the gather warps exist
+  constexpr bool IM2COL = MODE == 2;
+  using S = Smem<BN, X3>;
   constexpr int kStages = S::kStages;
   constexpr int kElemBytes = TF32 ? 4 : 2;
   constexpr int BK = kTileKBytes / kElemBytes;          // 64 bf16 / 32 tf32
@@ -110,7 +107,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
   static_assert(!X3 || BN <= 128, "tf32x3 uses BN <= 128");
   constexpr int kAtomN = kTileKBytes / kElemBytes;      // BMN: elements of n per 128-byte slab row
   constexpr int kSlabBytes = BK * 128;                  // BMN: one slab = BK rows of k x 128 bytes of n
-  constexpr int kEpiWarps = MODE >= 3 ? 16 : 8;
+  constexpr int kEpiWarps = 8;
   constexpr int kGatherWarps = 8;
   constexpr int kGatherWarp0 = 2 + kEpiWarps, kSplitWarp0 = kGatherWarp0 + (CONV ? kGatherWarps : 0);
   constexpr int kFullCount = CONV ? kGatherWarps * 32 + 1 : 1;   // gather threads + the TMA arm
@@ -170,7 +167,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
           if (!mbarWait(&empty[s], ph ^ 1, abortWord)) { atomicExch(&g_tcStatus, 1); ok = false; break; }
           mbarExpectTx(&full[s], (CONV ? S::kBBytes : S::kABytes + S::kBBytes) + ((X3 && p.hasBLo) ? S::kBBytes : 0));
-          if (BASE == 0) tmaLoad4d(stageA(s), &mapA, &full[s], kb * BK, tileM * BM, zb1 * p.aZ1, zb0 * p.aZ0);
+          if (MODE == 0) tmaLoad4d(stageA(s), &mapA, &full[s], kb * BK, tileM * BM, zb1 * p.aZ1, zb0 * p.aZ0);
           if (IM2COL) {
             // 128 output pixels from (img0, oh0, ow0) on, in w -> h -> n order; the coordinates name the input pixel
             // under filter tap (0, 0), the offsets select the tap
@@ -731,7 +728,7 @@ bool tmaEpilogueEnabled() {
 
 template <int BN, int KIND, int MODE, bool BMN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mbl, TcArgs a, long long batch, cudaStream_t st) {
-  using S = Smem<BN, KIND == 2, MODE >= 3>;
+  using S = Smem<BN, KIND == 2>;
   static bool configured = false;
   if (!configured) {
     cudaError_t e = cudaFuncSetAttribute(tc_kernel<BN, KIND, MODE, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
@@ -750,23 +747,10 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, 
 template <int MODE, bool BMN>
 int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mbl, const TcArgs& a, long long batch, cudaStream_t st) {
 #define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, MODE, BMN>(ma, mb, mo, mbl, a, batch, st);
-  if constexpr (MODE >= 3) { TC_CASE(256, 0) TC_CASE(256, 1) }
-  else {
-    TC_CASE(64, 0) TC_CASE(128, 0)
-    if constexpr (!BMN) { TC_CASE(64, 1) TC_CASE(64, 2) TC_CASE(128, 1) TC_CASE(128, 2) TC_CASE(256, 0) TC_CASE(256, 1) }
-  }
+  TC_CASE(64, 0) TC_CASE(128, 0)
+  if constexpr (!BMN) { TC_CASE(64, 1) TC_CASE(64, 2) TC_CASE(128, 1) TC_CASE(128, 2) TC_CASE(256, 0) TC_CASE(256, 1) }
 #undef TC_CASE
   return setError(LLC_ERR_INTERNAL, "llc internal: no tensor-core kernel for this tile");
-}
-
-// Sixteen epilogue warps pay when a 128 x 256 tile's K loop is shorter than its epilogue (LLC_TC_WIDE=0/1 forces the choice).
-bool wideEpilogue(int bn, int kind, int kBlocks) {
-  const char* e = getenv("LLC_TC_WIDE");
-  const int forced = e && *e ? atoi(e) : -1;
-  if (bn != 256 || kind == 2) return false;
-  if (forced == 2) return kBlocks <= 8;      // the intended policy, while it is being measured
-  if (forced >= 0) return forced != 0;
-  return false;
 }
 
 // Tile width by a cost model: a persistent CTA works through ceil(tiles / SMs) tiles, and a tile costs the longer of its
@@ -845,7 +829,6 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   if (kind == 2 && !bmn && p->b_lo && (reinterpret_cast<uintptr_t>(p->b_lo) & 15) == 0 &&
       makeMap(&mbl, p->b_lo, f32, p->k, p->n, p->b1, p->b0, p->b_sn, p->b_s1, p->b_s0, bn))
     a.hasBLo = 1;
-  if (wideEpilogue(bn, kind, a.kBlocks) && !bmn) return dispatch<3, false>(bn, kind, ma, mb, mo, mbl, a, batch, st);
   return bmn ? dispatch<0, true>(bn, kind, ma, mb, mo, mbl, a, batch, st) : dispatch<0, false>(bn, kind, ma, mb, mo, mbl, a, batch, st);
 }
 
@@ -889,7 +872,7 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
   if (kind == 2 && p->w_lo && (reinterpret_cast<uintptr_t>(p->w_lo) & 15) == 0 && makeMap(&mbl, p->w_lo, f32, K, p->f, 1, 1, K, 0, 0, bn)) a.hasBLo = 1;
   if (im2colEligible(p, f32)) {
     CUtensorMap ma;
-    if (makeIm2colMap(&ma, p, f32)) return wideEpilogue(bn, kind, a.kBlocks) ? dispatch<4, false>(bn, kind, ma, mb, mo, mbl, a, 1, st) : dispatch<2, false>(bn, kind, ma, mb, mo, mbl, a, 1, st);
+    if (makeIm2colMap(&ma, p, f32)) return dispatch<2, false>(bn, kind, ma, mb, mo, mbl, a, 1, st);
   }
   return dispatch<1, false>(bn, kind, mb, mb, mo, mbl, a, 1, st);
 }

@@ -172,31 +172,3 @@ def test_tf32x3_presplit_weight_operand():
     G.conv2d(x, wt, c2, (1, 1), (1, 1), prec="tf32x3", w_lo=_tf32_lo(wt))
     assert torch.equal(c1, c2)
     _healthy()
-
-
-@pytest.mark.parametrize("dtype,prec,tol", [(torch.bfloat16, "bf16", 1e-2), (torch.float32, "tf32", 2e-3)])
-def test_sixteen_epilogue_warps_agree_with_eight(dtype, prec, tol, monkeypatch):
-    # 128 x 256 tiles with a short K loop take the kernel variant with sixteen epilogue warps; forced on and off here
-    m, n, k = 40000, 512, 128
-    a, w = _rand(m, k, dtype=dtype).to(DEV), _rand(n, k, seed=1, dtype=dtype).to(DEV)
-    scale, shift = (_rand(n, seed=2).abs() + 0.5).to(DEV), _rand(n, seed=3).to(DEV)
-    res = _rand(m, n, seed=4, dtype=dtype).to(DEV)
-    outs = []
-    for wide in ("0", "1"):
-        monkeypatch.setenv("LLC_TC_WIDE", wide)
-        out = torch.full((1, 1, m, n), float("nan"), device=DEV, dtype=dtype)
-        G.gemm(a[None, None], w.t()[None, None], out, scale=scale, shift=shift, res=res[None, None], act="relu", prec=prec)
-        outs.append(out)
-    monkeypatch.delenv("LLC_TC_WIDE")
-    assert torch.equal(outs[0], outs[1])
-    want = torch.relu((a.double() @ w.double().t()).float() * scale + shift + res.float())
-    assert max_rel_err(outs[1][0, 0].float(), want) < tol
-    x = _rand(64, 28, 28, 128, dtype=torch.bfloat16).to(DEV); wt = (_rand(256, 3, 3, 128, seed=1) * 0.05).to(torch.bfloat16).to(DEV)
-    cs = []
-    for wide in ("0", "1"):
-        monkeypatch.setenv("LLC_TC_WIDE", wide)
-        c = torch.empty(64, 28, 28, 256, device=DEV, dtype=torch.bfloat16)
-        G.conv2d(x, wt, c, (1, 1), (1, 1), shift=shift[:256].contiguous(), act="relu", prec="bf16")
-        cs.append(c)
-    assert torch.equal(cs[0], cs[1])
-    _healthy()
