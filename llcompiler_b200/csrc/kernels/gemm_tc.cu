@@ -255,36 +255,23 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       // instruction.  The loads of the first box are issued here, while the tile's MMAs still run, those of box b + 1
       // when box b is taken over.
       const bool resTile = !CONV && p.resTile && tmaW == 128;   // (the gather kernel has no registers to spare and its layers no residual)
-      // One box is in flight per warp: the first is requested before the accumulator is waited for, box b + 1 when
-      // box b is taken over.
-      constexpr int kAhead = 1;                                  // (two boxes ahead measured no faster and cost 32 registers)
+      // One box is in flight per warp (two were measured no faster and cost 32 registers).
       const int boxCols = outF32 ? 32 : 64;
       const int esz = outF32 ? 4 : 2;
       const int nBoxes = kColsPerWarp / boxCols;
-      uint4 rA[8], rB[kAhead == 1 ? 1 : 8];
+      uint4 rA[8];
       auto issueRes = [&](int b) {
         const int chunk = lane & 7, r0 = lane >> 3;
         const long long gcol = (long long)tileN * BN + half * kColsPerWarp + b * boxCols + chunk * (16 / esz);
         const char* base = reinterpret_cast<const char*>(p.res) + (zb0 * p.r_s0 + zb1 * p.r_s1 + gcol) * esz;
         const bool colOk = gcol < p.N;
-        if (kAhead == 1 || !(b & 1)) {
 #pragma unroll
-          for (int j = 0; j < 8; ++j) {
-            const long long gr = (long long)tileM * BM + q * 32 + j * 4 + r0;
-            rA[j] = (gr < p.M && colOk) ? __ldg(reinterpret_cast<const uint4*>(base + gr * p.r_sm * esz)) : make_uint4(0u, 0u, 0u, 0u);
-          }
-        } else {
-#pragma unroll
-          for (int j = 0; j < (kAhead == 1 ? 1 : 8); ++j) {
-            const long long gr = (long long)tileM * BM + q * 32 + j * 4 + r0;
-            rB[j] = (gr < p.M && colOk) ? __ldg(reinterpret_cast<const uint4*>(base + gr * p.r_sm * esz)) : make_uint4(0u, 0u, 0u, 0u);
-          }
+        for (int j = 0; j < 8; ++j) {
+          const long long gr = (long long)tileM * BM + q * 32 + j * 4 + r0;
+          rA[j] = (gr < p.M && colOk) ? __ldg(reinterpret_cast<const uint4*>(base + gr * p.r_sm * esz)) : make_uint4(0u, 0u, 0u, 0u);
         }
       };
-      if (resTile) {
-        issueRes(0);
-        if (kAhead == 2 && nBoxes > 1) issueRes(1);
-      }
+      if (resTile) issueRes(0);
       if (!mbarWait(&accFull[ab], aph, abortWord)) { atomicExch(&g_tcStatus, 4); break; }
       tcFenceAfter();
       const uint32_t acc = tmemBase + (uint32_t)(ab * kSetCols) + ((uint32_t)(q * 32) << 16);
@@ -321,16 +308,15 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           if (resTile) {
             const uint32_t st = smemAddr(outStage);
             const int b = (ci * 32) / boxCols;
-            const bool useB = kAhead == 2 && (b & 1);
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
               const uint32_t row = (uint32_t)(j * 4 + (lane >> 3));
-              const uint4 r = useB ? rB[kAhead == 1 ? 0 : j] : rA[j];
+              const uint4 r = rA[j];
               asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(st + row * 128u + ((((uint32_t)lane & 7u) ^ (row & 7u)) << 4)), "r"(r.x), "r"(r.y),
                            "r"(r.z), "r"(r.w) : "memory");
             }
             __syncwarp();                                                 // from here on every lane touches only its own row
-            if (b + kAhead < nBoxes) issueRes(b + kAhead);
+            if (b + 1 < nBoxes) issueRes(b + 1);
           }
         }
         if (whole) {
