@@ -513,6 +513,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     const int chunk = g & 7, row0 = g >> 3;
     const char* X = reinterpret_cast<const char*>(p.x);
     const uint32_t dstOff = (uint32_t)(row0 * 128 + ((chunk ^ (row0 & 7)) << 4));   // (row0 + 32 j) & 7 == row0 & 7
+    const int tapsPerBlock = (p.C <= BK && BK % p.C == 0) ? BK / p.C : 0;          // whole taps per K block
     uint32_t it = 0;
     bool ok = true;
     for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
@@ -543,8 +544,9 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           cpAsync16(dst + j * 32 * 128, X + (valid ? (rowBase[j] + tapOff) * kElemBytes : 0), valid);
         }
         cpAsyncArriveOn(&full[s]);                           // arrives when the four copies above have landed
-        cc += BK;                                              // next K block: 128 bytes further along K
-        while (cc >= p.C) { cc -= p.C; if (++tapS == p.KW) { tapS = 0; ++tapR; } }
+        // next K block: 128 bytes further along K.  Narrow channel counts (the padded stem) step over several taps at once.
+        if (tapsPerBlock > 0) { tapS += tapsPerBlock; while (tapS >= p.KW) { tapS -= p.KW; ++tapR; } }
+        else { cc += BK; while (cc >= p.C) { cc -= p.C; if (++tapS == p.KW) { tapS = 0; ++tapR; } } }
       }
     }
     cpAsyncCommit();
