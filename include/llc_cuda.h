@@ -101,6 +101,11 @@ typedef struct LlcConvParams {
   float alpha;
   int32_t act;
   const void* w_lo;   /* optional, precision tf32x3: w - truncate_to_tf32(w), same layout as w (see LlcGemmParams.b_lo) */
+  /* Optional element strides of x along n, h and w (the channel stride is 1); all 0 = dense [N,H,W,C].  The strides may
+   * describe an overlapping view: with x_sw < c every "pixel" is a window of c consecutive elements that advances by x_sw,
+   * which turns a filter row of a narrow-channel convolution into the channels of a 1-wide kernel.  Tensor-core precisions
+   * only (bf16, tf32, tf32x3); c * element size must then be a multiple of 16 bytes and so must the strides. */
+  int64_t x_sn, x_sh, x_sw;
 } LlcConvParams;
 int llc_cuda_conv2d(const LlcConvParams* p, void* stream);
 
@@ -141,6 +146,13 @@ int llc_cuda_gather(const void* table, const int64_t* ids, void* out, int32_t ta
  * (src/Dialect/LLH/Transforms/TransformLayout.cpp:141-198), with the channel padding the
  * tensor-core convolution wants for a 3-channel stem. */
 int llc_cuda_nchw_to_nhwc(const void* x, void* out, int32_t dtype, int64_t n, int64_t c, int64_t hw, int64_t c_pad, void* stream);
+
+/* The same re-layout into rows of w_total pixels: the image starts at column w_left, the columns left and right of it are
+ * zeros.  out is [n, h, w_total, c_pad]; f32 with c_pad 4 or bf16 with c_pad 8 (16 bytes per pixel).  With the halo in
+ * memory, eight neighbouring pixels of a narrow-channel input are one contiguous 128-byte run, which is what lets the stem
+ * convolution read a whole filter row per K block (see LlcConvParams.x_sw). */
+int llc_cuda_nchw_to_nhwc_wide(const void* x, void* out, int32_t dtype, int64_t n, int64_t c, int64_t h, int64_t w, int64_t c_pad, int64_t w_left,
+                               int64_t w_total, void* stream);
 
 /* Fused elementwise chain: one coalesced pass that evaluates a small register program per
  * output element.  Replaces chains of llh.add/sub/mul/div/max/min/abs/sqrt/exp/where/compare/

@@ -106,7 +106,7 @@ class LlcConvParams(Structure):
                 ("res", c_void_p), ("in_dtype", c_int32), ("out_dtype", c_int32), ("res_dtype", c_int32),
                 ("precision", c_int32)] + [(n, c_int64) for n in ("n", "h", "w_in", "c", "f", "kh", "kw", "oh", "ow")] + \
                [(n, c_int32) for n in ("stride_h", "stride_w", "pad_h", "pad_w", "dil_h", "dil_w")] + \
-               [("alpha", c_float), ("act", c_int32), ("w_lo", c_void_p)]
+               [("alpha", c_float), ("act", c_int32), ("w_lo", c_void_p), ("x_sn", c_int64), ("x_sh", c_int64), ("x_sw", c_int64)]
 
 
 class LlcAttentionParams(Structure):
@@ -135,5 +135,5 @@ EXPORTED_SYMBOLS = [
     "llc_compile", "llc_run_pass", "llc_load", "llc_num_inputs", "llc_num_outputs", "llc_num_symbols",
     "llc_output_shape", "llc_run", "llc_profile", "llc_last_launch_count", "llc_arena_bytes", "llc_free", "llc_last_error",
     "llc_version", "llc_cuda_gemm", "llc_cuda_conv2d", "llc_cuda_maxpool2d", "llc_cuda_reduce",
-    "llc_cuda_softmax", "llc_cuda_layernorm", "llc_cuda_gather", "llc_cuda_eltwise", "llc_cuda_status", "llc_cuda_nchw_to_nhwc", "llc_cuda_gemm_static_scratch", "llc_cuda_attention",
+    "llc_cuda_softmax", "llc_cuda_layernorm", "llc_cuda_gather", "llc_cuda_eltwise", "llc_cuda_status", "llc_cuda_nchw_to_nhwc", "llc_cuda_gemm_static_scratch", "llc_cuda_attention", "llc_cuda_nchw_to_nhwc_wide",
 ]

@@ -43,16 +43,18 @@ extern "C" int llc_cuda_conv2d(const LlcConvParams* p, void* stream) {
   if (!floatIo(p->in_dtype) || !floatIo(p->out_dtype) || (p->res && !floatIo(p->res_dtype)))
     return setError(LLC_ERR_UNSUPPORTED, "llc argument: conv operands must be f32 or bf16");
   if (p->h * p->w_in * p->c >= (1LL << 31) || p->kh * p->kw * p->c >= (1LL << 31)) return setError(LLC_ERR_UNSUPPORTED, "llc argument: conv image or filter too large");
-  if (p->kh == 1 && p->kw == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_h == 0 && p->pad_w == 0) {
+  const bool strided = p->x_sn != 0 || p->x_sh != 0 || p->x_sw != 0;
+  if (!strided && p->kh == 1 && p->kw == 1 && p->stride_h == 1 && p->stride_w == 1 && p->pad_h == 0 && p->pad_w == 0) {
     // a 1x1 stride-1 convolution over NHWC data is a plain GEMM: [N*H*W, C] x [F, C]^T
     LlcGemmParams g{};
     g.a = p->x; g.b = p->w; g.out = p->out; g.scale = p->scale; g.shift = p->shift; g.res = p->res;
     g.in_dtype = p->in_dtype; g.out_dtype = p->out_dtype; g.res_dtype = p->res_dtype; g.precision = p->precision;
     g.m = p->n * p->oh * p->ow; g.n = p->f; g.k = p->c; g.b0 = g.b1 = 1;
     g.a_sm = p->c; g.b_sk = 1; g.b_sn = p->c; g.o_sm = p->f; g.r_sm = p->f; g.r_sn = 1;
-    g.alpha = p->alpha; g.act = p->act;
+    g.alpha = p->alpha; g.act = p->act; g.b_lo = p->w_lo;
     if (tcGemmSupported(&g)) return tcGemm(&g, (cudaStream_t)stream);
   }
   if (tcConvSupported(p)) return tcConv(p, (cudaStream_t)stream);
+  if (strided) return setError(LLC_ERR_UNSUPPORTED, "llc argument: conv with explicit activation strides needs a tensor-core precision and 16-byte aligned strides");
   return igemmSimtConv(p, (cudaStream_t)stream);
 }

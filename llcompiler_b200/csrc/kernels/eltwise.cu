@@ -279,6 +279,44 @@ __global__ void __launch_bounds__(256) nchw_to_nhwc_tiled_kernel(const T* __rest
 
 using namespace llc;
 
+// Same with the rows widened: output pixel (img, h, wq) of a [n, h, w_total, CP] buffer is input pixel wq - w_left, or
+// zeros in the halo columns left and right of the image.
+template <typename T, int CP>
+__global__ void __launch_bounds__(256) nchw_to_nhwc_wide_kernel(const T* __restrict__ x, T* __restrict__ out, long long n, int c, int h, int w, int w_left,
+                                                                 int w_total) {
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= n * h * w_total) return;
+  const int wq = (int)(idx % w_total); const long long t = idx / w_total; const int row = (int)(t % h); const long long img = t / h;
+  const int wi = wq - w_left;
+  const bool inside = wi >= 0 && wi < w;
+  const long long hw = (long long)h * w, px = (long long)row * w + wi;
+  __align__(16) T v[CP];
+#pragma unroll
+  for (int k = 0; k < CP; ++k) v[k] = (inside && k < c) ? x[(img * c + k) * hw + px] : T(0.f);
+  constexpr int kVec = CP * sizeof(T) / 16;
+  uint4* dst = reinterpret_cast<uint4*>(out + idx * CP);
+#pragma unroll
+  for (int k = 0; k < kVec; ++k) dst[k] = reinterpret_cast<const uint4*>(v)[k];
+}
+
+extern "C" int llc_cuda_nchw_to_nhwc_wide(const void* x, void* out, int32_t dtype, int64_t n, int64_t c, int64_t h, int64_t w, int64_t c_pad, int64_t w_left,
+                                          int64_t w_total, void* stream) {
+  if (n <= 0 || h <= 0 || w <= 0 || c <= 0) return LLC_OK;
+  if (!x || !out) return setError(LLC_ERR_ARGUMENT, "llc argument: nchw_to_nhwc_wide null pointer");
+  if (c_pad < c || w_left < 0 || w_total < w_left + w) return setError(LLC_ERR_ARGUMENT, "llc argument: nchw_to_nhwc_wide padding smaller than the image");
+  if (reinterpret_cast<uintptr_t>(out) % 16 != 0) return setError(LLC_ERR_ARGUMENT, "llc argument: nchw_to_nhwc_wide output must be 16-byte aligned");
+  const bool f32 = dtype == LLC_FLOAT32;
+  if (!((f32 && c_pad == 4) || (dtype == LLC_BFLOAT16 && c_pad == 8)))
+    return setError(LLC_ERR_UNSUPPORTED, "llc argument: nchw_to_nhwc_wide takes f32 padded to 4 channels or bf16 padded to 8");
+  const long long total = n * h * w_total;
+  const unsigned blocks = (unsigned)((total + 255) / 256);
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  if (f32) nchw_to_nhwc_wide_kernel<float, 4><<<blocks, 256, 0, st>>>((const float*)x, (float*)out, n, (int)c, (int)h, (int)w, (int)w_left, (int)w_total);
+  else nchw_to_nhwc_wide_kernel<__nv_bfloat16, 8><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, (int)c, (int)h, (int)w, (int)w_left, (int)w_total);
+  LLC_LAUNCH_CHECK("nchw_to_nhwc_wide_kernel");
+  return LLC_OK;
+}
+
 extern "C" int llc_cuda_nchw_to_nhwc(const void* x, void* out, int32_t dtype, int64_t n, int64_t c, int64_t hw, int64_t c_pad, void* stream) {
   if (n <= 0 || c <= 0 || hw <= 0) return LLC_OK;
   if (!x || !out) return setError(LLC_ERR_ARGUMENT, "llc argument: nchw_to_nhwc null pointer");

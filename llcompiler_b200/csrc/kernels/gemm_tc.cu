@@ -52,6 +52,7 @@ struct TcArgs {
   int mTiles, nTiles; long long tiles;
   // convolution (A gathered from NHWC activations)
   const void* x; int H, W, C, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
+  long long xs_n, xs_h, xs_w;   // element strides of x along image, row and pixel (dense NHWC: H*W*C, W*C, C)
 };
 
 template <int BN, bool X3> struct Smem {
@@ -526,7 +527,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         if (gm < p.M) {
           const int ow = (int)(gm % p.OW); const long long t2 = gm / p.OW; const int oh = (int)(t2 % p.OH); const long long img = t2 / p.OH;
           ih0[j] = oh * p.sh - p.ph; iw0[j] = ow * p.sw - p.pw;
-          rowBase[j] = ((img * p.H + ih0[j]) * p.W + iw0[j]) * p.C;
+          rowBase[j] = img * p.xs_n + (long long)ih0[j] * p.xs_h + (long long)iw0[j] * p.xs_w;
         } else { ih0[j] = -(1 << 28); iw0[j] = 0; rowBase[j] = 0; }   // never in range: the row is zero-filled
       }
       int tapR = 0, tapS = 0, cc = chunk * kChunkElems;       // filter tap and channel of this thread's chunk
@@ -535,7 +536,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
         if (!mbarWait(&empty[s], ph ^ 1, abortWord)) { atomicExch(&g_tcStatus, 5); ok = false; break; }
         const int dIh = tapR * p.dh, dIw = tapS * p.dw;
-        const long long tapOff = ((long long)dIh * p.W + dIw) * p.C + cc;
+        const long long tapOff = (long long)dIh * p.xs_h + (long long)dIw * p.xs_w + cc;
         const bool tapOk = tapR < p.KH;                        // past the last tap: K tail, zero-filled
         const uint32_t dst = smemAddr(stageA(s)) + dstOff;
 #pragma unroll
@@ -634,7 +635,9 @@ bool makeIm2colMap(CUtensorMap* map, const LlcConvParams* p, bool f32) {
   if (!enc) return false;
   const int eb = f32 ? 4 : 2;
   cuuint64_t dims[4] = {(cuuint64_t)p->c, (cuuint64_t)p->w_in, (cuuint64_t)p->h, (cuuint64_t)p->n};
-  cuuint64_t strides[3] = {(cuuint64_t)(p->c * eb), (cuuint64_t)(p->w_in * p->c * eb), (cuuint64_t)(p->h * p->w_in * p->c * eb)};
+  const bool dense = p->x_sn == 0 && p->x_sh == 0 && p->x_sw == 0;
+  cuuint64_t strides[3] = {(cuuint64_t)((dense ? p->c : p->x_sw) * eb), (cuuint64_t)((dense ? p->w_in * p->c : p->x_sh) * eb),
+                           (cuuint64_t)((dense ? p->h * p->w_in * p->c : p->x_sn) * eb)};
   int lower[2] = {-p->pad_w, -p->pad_h};
   int upper[2] = {p->pad_w - (int)(p->kw - 1) * p->dil_w, p->pad_h - (int)(p->kh - 1) * p->dil_h};
   cuuint32_t estr[4] = {1, (cuuint32_t)p->stride_w, (cuuint32_t)p->stride_h, 1};
@@ -826,6 +829,7 @@ bool tcConvSupported(const LlcConvParams* p) {
   if (f32 && p->precision != LLC_PREC_TF32 && p->precision != LLC_PREC_TF32X3) return false;
   const int eb = f32 ? 4 : 2;
   if ((p->c * eb) % 16 != 0) return false;              // a 16-byte chunk must stay inside one filter tap
+  if ((p->x_sn * eb) % 16 != 0 || (p->x_sh * eb) % 16 != 0 || (p->x_sw * eb) % 16 != 0 || p->x_sn < 0 || p->x_sh < 0 || p->x_sw < 0) return false;
   if ((reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->w)) & 15) return false;
   const long long M = p->n * p->oh * p->ow, K = p->kh * p->kw * p->c;
   if (M * p->f * K < (1LL << 18)) return false;
@@ -852,6 +856,10 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
              ((reinterpret_cast<uintptr_t>(p->scale) | reinterpret_cast<uintptr_t>(p->shift)) & 15) == 0;
   a.x = p->x; a.H = (int)p->h; a.W = (int)p->w_in; a.C = (int)p->c; a.KH = (int)p->kh; a.KW = (int)p->kw; a.OH = (int)p->oh; a.OW = (int)p->ow;
   a.sh = p->stride_h; a.sw = p->stride_w; a.ph = p->pad_h; a.pw = p->pad_w; a.dh = p->dil_h; a.dw = p->dil_w;
+  {
+    const bool dense = p->x_sn == 0 && p->x_sh == 0 && p->x_sw == 0;
+    a.xs_w = dense ? p->c : p->x_sw; a.xs_h = dense ? p->w_in * p->c : p->x_sh; a.xs_n = dense ? p->h * p->w_in * p->c : p->x_sn;
+  }
   CUtensorMap mo = mb;
   const int boxBytes = outBoxBytes(bn, ob == 4);
   if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->f, M, 1, 1, p->f, 0, 0, boxBytes)) a.tmaOut = boxBytes;

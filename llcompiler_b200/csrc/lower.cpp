@@ -787,14 +787,31 @@ struct Lowering {
     View x;
     settle(xt);
     const bool denseNchw = xt.kind == TV::ViewK && isContiguous(xt.view) && isFloat(xt.dtype) && dtypeSize(xt.dtype) <= 4 && !xt.isConst;
+    // A narrow-channel stem (16 bytes per padded pixel, kernel at most 8 wide): eight neighbouring pixels are one
+    // contiguous 128-byte run of the channel-last copy, so a whole filter row becomes the "channels" of a kernel that is one
+    // pixel wide over an overlapping view (pixel stride 16 bytes, 8 * cPad channels), provided the copy carries the zero
+    // padding columns itself.  One K block of the tensor-core kernel is then one filter row, loaded by a single TMA
+    // im2col box instead of being gathered tap by tap.  (The eighth pixel of a row meets zero weights.)
+    bool rowMerge = false; int64_t wLeft = 0, wTotal = 0, mergedW = 0;
+    if (cPad && denseNchw && cPad * dtypeSize(xt.dtype) == 16 && wt.shape[2].isConst() && wt.shape[3].isConst() && wt.shape[3].constant() <= 8 &&
+        wt.shape[3].constant() > 1 && dil[1] == 1 && xt.shape[3].isConst() && opts.mergeStemRows) {
+      const int64_t W = xt.shape[3].constant(), KW = wt.shape[3].constant();
+      const int64_t OWc = (W + pad[1] + pad[3] - (KW - 1) - 1) / stride[1] + 1;
+      if (OWc >= 1) { rowMerge = true; wLeft = pad[1]; wTotal = std::max(pad[1] + W, (OWc - 1) * stride[1] + 8); mergedW = (OWc - 1) * stride[1] + 1; }
+    }
     if (cPad || (denseNchw && !xt.shape[1].isConst(1))) {
       // NCHW data entering a conv chain: one re-layout kernel (with the channel padding if any)
-      std::vector<Expr> pshape = {xt.shape[0], cPad ? Expr(cPad) : xt.shape[1], xt.shape[2], xt.shape[3]};
+      std::vector<Expr> pshape = {xt.shape[0], cPad ? Expr(cPad) : xt.shape[1], xt.shape[2], rowMerge ? Expr(wTotal) : xt.shape[3]};
       std::vector<Expr> pst = nhwcStrides(pshape);
       if (denseNchw) {
         x = freshView(xt.dtype, pshape, false, &pst);
         Step st; st.kernel = "nchw2nhwc";
         st.views.emplace_back("x", xt.view); st.views.emplace_back("out", x);
+        if (rowMerge) {
+          st.params.emplace_back("wide", std::to_string(wLeft) + "," + std::to_string(wTotal));
+          // the convolution's view: [N, 8 * cPad, H, mergedW], a window of eight pixels per position
+          x.shape = {xt.shape[0], Expr(8 * cPad), xt.shape[2], Expr(mergedW)};
+        }
         plan.steps.push_back(st);
       } else {
         toView(xt);
@@ -810,10 +827,11 @@ struct Lowering {
     View wperm = wt.view;
     wperm.shape = {wt.view.shape[0], wt.view.shape[2], wt.view.shape[3], wt.view.shape[1]};
     wperm.strides = {wt.view.strides[0], wt.view.strides[2], wt.view.strides[3], wt.view.strides[1]};
-    std::string key = "wperm:" + wperm.str() + (cPad ? ":pad" + std::to_string(cPad) : "");
+    std::string key = "wperm:" + wperm.str() + (cPad ? ":pad" + std::to_string(cPad) : "") + (rowMerge ? ":rows" : "");
     View w;
     std::vector<Expr> wshape = wperm.shape;
     if (cPad) wshape[3] = Expr(cPad);
+    if (rowMerge) wshape[2] = Expr(8);
     if (constVecCache.count(key)) { w = wperm; w.shape = wshape; w.buf = constVecCache[key]; w.offset = Expr(0); w.strides = rowMajor(wshape); }
     else if (cPad) {
       std::vector<Expr> rm = rowMajor(wshape);
@@ -824,6 +842,10 @@ struct Lowering {
       constVecCache[key] = w.buf;
     }
     else { std::vector<Expr> rm = rowMajor(wperm.shape); w = materializeTree(leafNode(wperm), wperm.dtype, wperm.shape, &rm); constVecCache[key] = w.buf; }
+    if (rowMerge) {                          // [F, KH, 8, cPad] read as [F, KH, 1, 8 * cPad]
+      w.shape = {wshape[0], wshape[1], Expr(1), Expr(8 * cPad)};
+      w.strides = rowMajor(w.shape);
+    }
     Expr N = xt.shape[0], H = xt.shape[2], W = xt.shape[3], F = wt.shape[0];
     int64_t KH = wt.shape[2].constant(), KW = wt.shape[3].constant();
     if (!wt.shape[2].isConst() || !wt.shape[3].isConst()) fail("symbolic kernel extent");
@@ -842,7 +864,7 @@ struct Lowering {
     }
     auto arr = [](const std::vector<int64_t>& v) { std::string o; for (size_t i = 0; i < v.size(); ++i) o += (i ? "," : "") + std::to_string(v[i]); return o; };
     P.step.params.emplace_back("stride", arr(stride));
-    P.step.params.emplace_back("pad", arr(pad));
+    P.step.params.emplace_back("pad", rowMerge ? arr({pad[0], 0, pad[2], 0}) : arr(pad));   // the copy holds the left and right padding
     P.step.params.emplace_back("dil", arr(dil));
     P.step.params.emplace_back("prec", gemmPrecision(x.dtype));
     std::vector<Expr> ost = nhwcStrides(oshape);

@@ -69,6 +69,7 @@ struct CompileOptionsData {
   std::string logRoot, logLevel = "debug", cpu, mtriple;
   std::string precision = "auto";  // fp32 | tf32 | tf32x3 | bf16 | auto
   bool displayMlirPasses = false, displayLlvmPasses = false;
+  bool mergeStemRows = true;       // narrow-channel stem convolutions read a filter row per K block (LLC_MERGE_STEM_ROWS=0 disables)
   bool fuseAttention = true;       // batch_matmul -> softmax -> batch_matmul as one attention step where the kernel's limits allow
 };
 

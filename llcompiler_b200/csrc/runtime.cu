@@ -100,6 +100,7 @@ struct RStep {
   std::string prog;
   void* sp[4] = {nullptr, nullptr, nullptr, nullptr};   // pointer operands of the row kernels
   int sdt[3] = {0, 0, 0}; long long sd[3] = {0, 0, 0}; int sop = 0; float seps = 0.f;
+  long long wide[4] = {0, 0, 0, 0};             // nchw2nhwc with a halo: left columns, total columns, h, w
   std::vector<PtrPatch> patches;
   RStep() {}
   RStep(const RStep&) = delete;             // patches point into this object
@@ -230,6 +231,11 @@ void LlcExec::prepare(RStep& rs) {
     if (const RView* v = rs.view("shift")) patch(&p.shift, *v);
     if (const RView* v = rs.view("res")) { patch(&p.res, *v); p.res_dtype = v->dtype; }
     if (const RView* v = rs.view("w_lo")) patch(&p.w_lo, *v);
+    // x is the logical [N, C, H, W] view of channel-last storage: anything but the dense strides is passed on
+    if (x.strides[1] != 1 && x.shape[1] != 1) failArg("conv input must have unit stride along the channels");
+    if (!(x.strides[3] == p.c && x.strides[2] == p.w_in * p.c && (x.strides[0] == p.h * p.w_in * p.c || p.n == 1))) {
+      p.x_sn = x.strides[0]; p.x_sh = x.strides[2]; p.x_sw = x.strides[3];
+    }
     p.alpha = std::stof(s.param("alpha", "1")); p.act = actOf();
   } else if (s.kernel == "maxpool") {
     rs.kind = kPool;
@@ -271,6 +277,12 @@ void LlcExec::prepare(RStep& rs) {
     patch(&rs.sp[0], x); patch(&rs.sp[1], o);
     rs.sdt[0] = x.dtype; rs.sd[0] = x.shape[0]; rs.sd[1] = x.shape[1]; rs.sd[2] = x.shape[2] * x.shape[3];
     rs.sop = (int)o.shape[1];
+    // rows widened by a zero halo ("wide" = left columns, total columns): the out view is then the whole widened buffer
+    rs.wide[0] = rs.wide[1] = 0;
+    if (!s.param("wide", "").empty()) {
+      auto wl = ints(s.param("wide"));
+      rs.wide[0] = wl[0]; rs.wide[1] = wl[1]; rs.wide[2] = x.shape[2]; rs.wide[3] = x.shape[3];
+    }
   } else if (s.kernel == "eltwise") {
     rs.kind = kEltwise;
     const RView& o = need("out");
@@ -305,7 +317,9 @@ int LlcExec::launch(RStep& rs, cudaStream_t st) {
     case kLayerNorm: return llc_cuda_layernorm(rs.sp[0], rs.sp[1], rs.sp[2], rs.sp[3], rs.sdt[0], rs.sdt[1], rs.sdt[2], rs.sd[0], rs.sd[1], rs.seps, st);
     case kGather: return llc_cuda_gather(rs.sp[0], (const int64_t*)rs.sp[1], rs.sp[2], rs.sdt[0], rs.sdt[1], rs.sd[0], rs.sd[1], rs.sd[2], badIds, st);
     case kEltwise: return llc_cuda_eltwise(&rs.elt, st);
-    case kNchw2Nhwc: return llc_cuda_nchw_to_nhwc(rs.sp[0], rs.sp[1], rs.sdt[0], rs.sd[0], rs.sd[1], rs.sd[2], rs.sop, st);
+    case kNchw2Nhwc:
+      if (rs.wide[1] > 0) return llc_cuda_nchw_to_nhwc_wide(rs.sp[0], rs.sp[1], rs.sdt[0], rs.sd[0], rs.sd[1], rs.wide[2], rs.wide[3], rs.sop, rs.wide[0], rs.wide[1], st);
+      return llc_cuda_nchw_to_nhwc(rs.sp[0], rs.sp[1], rs.sdt[0], rs.sd[0], rs.sd[1], rs.sd[2], rs.sop, st);
   }
   throw std::runtime_error("llc internal: unprepared plan step");
 }

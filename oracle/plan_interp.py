@@ -196,7 +196,11 @@ class PlanInterpreter:
         # the output view is logical NCHW over an NHWC buffer, extra channels are zero
         out, x = v["out"], v["x"]
         out.zero_()
-        out[:, : x.shape[1]].copy_(x)
+        if "wide" in p:                                    # rows widened by a zero halo: image at column `left`
+            left = _ints(p["wide"])[0]
+            out[:, : x.shape[1], :, left: left + x.shape[3]].copy_(x)
+        else:
+            out[:, : x.shape[1]].copy_(x)
 
     def _k_gather(self, v, p):
         v["out"].copy_(v["table"][v["ids"].long()].to(v["out"].dtype))

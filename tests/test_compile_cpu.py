@@ -61,7 +61,8 @@ def test_resnet18_tensor_core_plan_pads_the_stem():
     comp, got, want = _run(m, (torch.randn(2, 3, 64, 64),), precision="tf32x3")
     assert max_rel_err(got, want) < 1e-4
     plan = comp.compiled[0].engine.text
-    assert "prec:tf32x3" in plan and "[64,7,7,4;" in plan
+    # ... and a filter row (7 taps x 4 channels, padded to 8 x 4) is the channel dim of a 1-wide kernel over the widened copy
+    assert "prec:tf32x3" in plan and "w=b104@0[64,7,1,32;" in plan and "wide:3,230" in plan and "pad:3,0,3,0" in plan
     # weights are split into their tf32 high and low parts once, at load time
     assert plan.count(" w_lo=") == 20 and plan.count(" b_lo=") == 1 and plan.count("tf32lo") == 21
 
@@ -95,3 +96,12 @@ def test_bert_bf16_unfused_attention_is_the_same_function(monkeypatch):
     plan, got, want = _bert_bf16(monkeypatch, fuse=False)
     assert plan.count("step attention") == 0 and plan.count("step softmax") == 2 and plan.count("step gemm") == 16
     assert max_rel_err(got, want) < 2e-2
+
+
+def test_resnet18_stem_without_row_merging(monkeypatch):
+    monkeypatch.setenv("LLC_MERGE_STEM_ROWS", "0")
+    m = build_model("resnet18")
+    comp, got, want = _run(m, (torch.randn(2, 3, 64, 64),), precision="tf32x3")
+    assert max_rel_err(got, want) < 1e-4
+    plan = comp.compiled[0].engine.text
+    assert "[64,7,7,4;" in plan and "wide:" not in plan

@@ -172,3 +172,30 @@ def test_tf32x3_presplit_weight_operand():
     G.conv2d(x, wt, c2, (1, 1), (1, 1), prec="tf32x3", w_lo=_tf32_lo(wt))
     assert torch.equal(c1, c2)
     _healthy()
+
+
+@pytest.mark.parametrize("dtype,prec,c_pad,tol", [(torch.float32, "tf32x3", 4, 5e-5), (torch.float32, "tf32", 4, 2e-3), (torch.bfloat16, "bf16", 8, 1e-4)])
+@pytest.mark.parametrize("n,h,w,f,k,s,pad", [(4, 224, 224, 64, 7, 2, 3), (2, 37, 29, 32, 5, 1, 2), (3, 16, 40, 24, 3, 2, 0)])
+def test_stem_rows_as_channels_over_a_widened_copy(dtype, prec, c_pad, tol, n, h, w, f, k, s, pad):
+    # 3-channel NCHW input -> channel-last copy with zero halo columns; the convolution then reads eight pixels (one filter
+    # row, zero-padded to eight taps) as the channels of a kernel one pixel wide, through an overlapping strided view
+    x = _rand(n, 3, h, w, dtype=dtype)
+    wt = (_rand(f, 3, k, k, seed=1) * 0.1).to(dtype)
+    shift = _rand(f, seed=2)
+    want = torch.relu(F.conv2d(x.double(), wt.double(), None, s, pad).float() + shift.view(1, -1, 1, 1))
+    oh, ow = want.shape[2], want.shape[3]
+    w_total = max(pad + w, (ow - 1) * s + 8)
+    wide = torch.full((n, h, w_total, c_pad), float("nan"), device=DEV, dtype=dtype)
+    G.nchw_to_nhwc_wide(x.to(DEV), wide, c_pad, pad, w_total)
+    ref_wide = torch.zeros(n, h, w_total, c_pad, dtype=dtype)
+    ref_wide[:, :, pad: pad + w, :3] = x.permute(0, 2, 3, 1)
+    assert torch.equal(wide.cpu(), ref_wide)                       # a copy: bit-exact
+    wm = torch.zeros(f, k, 8, c_pad, dtype=dtype)
+    wm[:, :, :k, :3] = wt.permute(0, 2, 3, 1)
+    wm = wm.reshape(f, k, 1, 8 * c_pad).contiguous().to(DEV)
+    out = torch.full((n, oh, ow, f), float("nan"), device=DEV, dtype=torch.float32)
+    merged_w = (ow - 1) * s + 1
+    G.conv2d(wide, wm, out, (s, s), (pad, 0), shift=shift.to(DEV), act="relu", prec=prec,
+             x_strides=(h * w_total * c_pad, w_total * c_pad, c_pad), x_shape=(n, h, merged_w, 8 * c_pad))
+    assert max_rel_err(out.permute(0, 3, 1, 2), want) < tol
+    _healthy()
