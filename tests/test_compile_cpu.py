@@ -62,7 +62,7 @@ def test_resnet18_tensor_core_plan_pads_the_stem():
     assert max_rel_err(got, want) < 1e-4
     plan = comp.compiled[0].engine.text
     # ... and a filter row (7 taps x 4 channels, padded to 8 x 4) is the channel dim of a 1-wide kernel over the widened copy
-    assert "prec:tf32x3" in plan and "w=b104@0[64,7,1,32;" in plan and "wide:3,230" in plan and "pad:3,0,3,0" in plan
+    assert "prec:tf32x3" in plan and "w=b104@0[64,7,1,32;" in plan and "wide:3,70" in plan and "pad:3,0,3,0" in plan
     # weights are split into their tf32 high and low parts once, at load time
     assert plan.count(" w_lo=") == 20 and plan.count(" b_lo=") == 1 and plan.count("tf32lo") == 21
 
