@@ -400,6 +400,32 @@ extern "C" int llc_cuda_eltwise(const LlcEltwiseParams* q, void* stream) {
   return LLC_OK;
 }
 
+// bf16 with a channel count that is a multiple of 8: 16-byte loads, maxima taken on packed pairs (exact).
+__global__ void __launch_bounds__(256) maxpool_nhwc_bf16x8_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, LlcPoolParams p) {
+  const long long cv = p.c / 8;
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= p.n * p.oh * p.ow * cv) return;
+  const int c = (int)(idx % cv) * 8; long long t = idx / cv;
+  const int ow = (int)(t % p.ow); t /= p.ow; const int oh = (int)(t % p.oh); const long long n = t / p.oh;
+  const __nv_bfloat162 lowest = __floats2bfloat162_rn(-INFINITY, -INFINITY);
+  __nv_bfloat162 m[4] = {lowest, lowest, lowest, lowest};
+  for (int r = 0; r < p.kh; ++r) {
+    const int ih = oh * p.stride_h - p.pad_h + r * p.dil_h;
+    if (ih < 0 || ih >= p.h) continue;
+    for (int s = 0; s < p.kw; ++s) {
+      const int iw = ow * p.stride_w - p.pad_w + s * p.dil_w;
+      if (iw < 0 || iw >= p.w) continue;
+      const uint4 q = __ldg(reinterpret_cast<const uint4*>(x + ((n * p.h + ih) * p.w + iw) * p.c + c));
+      const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&q);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) m[e] = __hmax2(m[e], h[e]);
+    }
+  }
+  uint4 o;
+  o.x = *reinterpret_cast<unsigned*>(&m[0]); o.y = *reinterpret_cast<unsigned*>(&m[1]); o.z = *reinterpret_cast<unsigned*>(&m[2]); o.w = *reinterpret_cast<unsigned*>(&m[3]);
+  *reinterpret_cast<uint4*>(out + ((n * p.oh + oh) * p.ow + ow) * p.c + c) = o;
+}
+
 extern "C" int llc_cuda_maxpool2d(const LlcPoolParams* p, void* stream) {
   if (!p || !p->x || !p->out) return setError(LLC_ERR_ARGUMENT, "llc argument: maxpool null pointer");
   if (p->in_dtype != p->out_dtype) return setError(LLC_ERR_ARGUMENT, "llc argument: maxpool input and output types differ");
@@ -413,7 +439,10 @@ extern "C" int llc_cuda_maxpool2d(const LlcPoolParams* p, void* stream) {
     if (v4) maxpool_nhwc_kernel<float, 4><<<blocks, 256, 0, st>>>((const float*)p->x, (float*)p->out, *p);
     else maxpool_nhwc_kernel<float, 1><<<blocks, 256, 0, st>>>((const float*)p->x, (float*)p->out, *p);
   } else if (p->in_dtype == LLC_BFLOAT16) {
-    if (v4) maxpool_nhwc_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
+    if (p->c % 8 == 0 && ((reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->out)) & 15) == 0) {
+      const long long total8 = p->n * p->oh * p->ow * (p->c / 8);
+      maxpool_nhwc_bf16x8_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
+    } else if (v4) maxpool_nhwc_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
     else maxpool_nhwc_kernel<__nv_bfloat16, 1><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
   } else return setError(LLC_ERR_UNSUPPORTED, "llc argument: maxpool type must be f32 or bf16");
   LLC_LAUNCH_CHECK("maxpool_nhwc_kernel");
