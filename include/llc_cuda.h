@@ -106,6 +106,10 @@ typedef struct LlcConvParams {
    * which turns a filter row of a narrow-channel convolution into the channels of a 1-wide kernel.  Tensor-core precisions
    * only (bf16, tf32, tf32x3); c * element size must then be a multiple of 16 bytes and so must the strides. */
   int64_t x_sn, x_sh, x_sw;
+  /* Optional scratch for split-K (few output tiles, long K), as in LlcGemmParams: device memory, 16-byte aligned, first
+   * 4096 bytes zero before the first use (left zero).  NULL disables split-K. */
+  void* workspace;
+  int64_t workspace_bytes;
 } LlcConvParams;
 int llc_cuda_conv2d(const LlcConvParams* p, void* stream);
 

@@ -106,7 +106,7 @@ class LlcConvParams(Structure):
                 ("res", c_void_p), ("in_dtype", c_int32), ("out_dtype", c_int32), ("res_dtype", c_int32),
                 ("precision", c_int32)] + [(n, c_int64) for n in ("n", "h", "w_in", "c", "f", "kh", "kw", "oh", "ow")] + \
                [(n, c_int32) for n in ("stride_h", "stride_w", "pad_h", "pad_w", "dil_h", "dil_w")] + \
-               [("alpha", c_float), ("act", c_int32), ("w_lo", c_void_p), ("x_sn", c_int64), ("x_sh", c_int64), ("x_sw", c_int64)]
+               [("alpha", c_float), ("act", c_int32), ("w_lo", c_void_p), ("x_sn", c_int64), ("x_sh", c_int64), ("x_sw", c_int64), ("workspace", c_void_p), ("workspace_bytes", c_int64)]
 
 
 class LlcAttentionParams(Structure):

@@ -46,6 +46,8 @@ struct TcArgs {
   long long o_s0, o_s1, o_sm, r_s0, r_s1, r_sm, r_sn;
   int b1; int kBlocks; int vecOut;
   int resTile;              // the residual can be fetched as 32-row x 128-byte boxes with 16-byte loads
+  int splits;               // K is cut into this many slices, each a work unit of its own; partial tiles meet in `ws`
+  float* ws; int* counters; // split-K: [units][128][BN] partial accumulators; one arrival counter per tile (zero between launches)
   int hasBLo;               // tf32x3: the low-order part of B comes from memory (mapBLo) instead of the split warps
   int tmaOut;               // 0, or the bytes per row of the output box the epilogue stores through TMA (64 or 128)
   int aZ0, aZ1, bZ0, bZ1;   // 1: the operand has this batch dim, 0: it is broadcast (coordinate 0)
@@ -124,6 +126,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
   uint64_t* accEmpty = bars + 3 * kStages + 2;  // [2] accumulator drained by the epilogue
   uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 4);
   volatile int* abortWord = reinterpret_cast<volatile int*>(tmemSlot + 1);
+  volatile int* lastFlag = abortWord + 1;       // split-K: whether this CTA's unit arrived last at its tile
   uint8_t* staging = smem + kStages * S::kStageBytes + S::kBarrierBytes;   // 1024-byte aligned
   constexpr int kStagingPerWarp = 4096;
 
@@ -146,6 +149,13 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
   auto stageALo = [&](int s) { return tiles + s * S::kStageBytes + S::kABytes + S::kBBytes; };
   auto stageBLo = [&](int s) { return tiles + s * S::kStageBytes + 2 * S::kABytes + S::kBBytes; };
   const long long tilesPerBatch = (long long)p.mTiles * p.nTiles;
+  // Work units: (tile, K slice).  Without split-K a unit is a tile and its slice the whole K loop.
+  const long long units = p.tiles * p.splits;
+  const int kPer = (p.kBlocks + p.splits - 1) / p.splits;
+  auto sliceOf = [&](long long u, long long& t, int& kb0, int& kb1) {
+    t = u / p.splits; const int sidx = (int)(u - t * p.splits);
+    kb0 = sidx * kPer; kb1 = kb0 + kPer < p.kBlocks ? kb0 + kPer : p.kBlocks;
+  };
 
   if (warp == 0) {
     // ---------------------------------------------------------------- TMA producer
@@ -155,16 +165,18 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       prefetchTensorMap(&mapB);
       uint32_t it = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
+      for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
+        long long t; int kb0, kb1; sliceOf(u, t, kb0, kb1);
         const int z = (int)(t / tilesPerBatch); const int rem = (int)(t - z * tilesPerBatch);
         const int tileM = rem / p.nTiles, tileN = rem - tileM * p.nTiles;
         const int zb0 = z / p.b1, zb1 = z - zb0 * p.b1;
         int tapR = 0, tapS = 0, cc = 0;                      // im2col: filter tap and first channel of the K block
+        if (IM2COL && kb0 > 0) { const long long k0 = (long long)kb0 * BK; const int tap = (int)(k0 / p.C); cc = (int)(k0 - (long long)tap * p.C); tapR = tap / p.KW; tapS = tap - tapR * p.KW; }
         if (IM2COL) {
           const long long m0 = (long long)tileM * BM;          // first output pixel of the tile
           ow0 = (int)(m0 % p.OW); const long long t2 = m0 / p.OW; oh0 = (int)(t2 % p.OH); img0 = (int)(t2 / p.OH);
         }
-        for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
           if (!mbarWait(&empty[s], ph ^ 1, abortWord)) { atomicExch(&g_tcStatus, 1); ok = false; break; }
           mbarExpectTx(&full[s], (CONV ? S::kBBytes : S::kABytes + S::kBBytes) + ((X3 && p.hasBLo) ? S::kBBytes : 0));
@@ -192,18 +204,19 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     if (lane == 0) {
       uint32_t it = 0, tcount = 0;
       bool ok = true;
-      for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++tcount) {
+      for (long long u = blockIdx.x; u < units && ok; u += gridDim.x, ++tcount) {
+        long long t; int kb0, kb1; sliceOf(u, t, kb0, kb1);
         const int ab = tcount & 1; const uint32_t aph = (tcount >> 1) & 1;
         if (!mbarWait(&accEmpty[ab], aph ^ 1, abortWord)) { atomicExch(&g_tcStatus, 2); ok = false; break; }
         tcFenceAfter();
         const uint32_t accSet = tmemBase + (uint32_t)(ab * kSetCols);
-        for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
+        for (int kb = kb0; kb < kb1; ++kb, ++it) {
           const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
           if (!mbarWait(X3 ? &split[s] : &full[s], ph, abortWord)) { atomicExch(&g_tcStatus, 2); ok = false; break; }
           if (CONV && !X3) fenceProxyAsync();               // the gathered A tile was written through the generic proxy
           tcFenceAfter();
-          const uint32_t acc = accSet + (uint32_t)((kb % kChains) * BN);
-          const bool fresh = kb < kChains;                 // first K block of this chain: overwrite
+          const uint32_t acc = accSet + (uint32_t)(((kb - kb0) % kChains) * BN);
+          const bool fresh = kb - kb0 < kChains;           // first K block of this chain: overwrite
           const uint64_t dA = smemDescKMajorSw128(smemAddr(stageA(s)));
           const uint64_t dB = BMN ? smemDescMnMajorSw128(smemAddr(stageB(s)), kSlabBytes) : smemDescKMajorSw128(smemAddr(stageB(s)));
           constexpr uint64_t kAdvA = (UMMA_K * kElemBytes) >> 4;                      // 32 bytes of K inside the swizzle atom
@@ -241,7 +254,8 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       return r;
     };
     uint32_t tcount = 0;
-    for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++tcount) {
+    for (long long u = blockIdx.x; u < units; u += gridDim.x, ++tcount) {
+      long long t; int kb0, kb1; sliceOf(u, t, kb0, kb1);
       const int z = (int)(t / tilesPerBatch); const int rem = (int)(t - z * tilesPerBatch);
       const int tileM = rem / p.nTiles, tileN = rem - tileM * p.nTiles;
       const int zb0 = z / p.b1, zb1 = z - zb0 * p.b1;
@@ -272,15 +286,64 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
           rA[j] = (gr < p.M && colOk) ? __ldg(reinterpret_cast<const uint4*>(base + gr * p.r_sm * esz)) : make_uint4(0u, 0u, 0u, 0u);
         }
       };
-      if (resTile) issueRes(0);
-      if (!mbarWait(&accFull[ab], aph, abortWord)) { atomicExch(&g_tcStatus, 4); break; }
+      const bool splitK = p.splits > 1;
+      if (resTile && !splitK) issueRes(0);
+      if (!mbarWait(&accFull[ab], aph, abortWord)) atomicExch(&g_tcStatus, 4);   // carry on with whatever is there: every warp must still reach the barriers below
       tcFenceAfter();
       const uint32_t acc = tmemBase + (uint32_t)(ab * kSetCols) + ((uint32_t)(q * 32) << 16);
-      const int usedChains = p.kBlocks < kChains ? p.kBlocks : kChains;
+      const int usedChains = kb1 - kb0 < kChains ? kb1 - kb0 : kChains;
+      // Split-K: every unit parks its partial tile (fp32, this lane's row) in the workspace; the unit that arrives last
+      // at the tile's counter adds the slices up and runs the epilogue.  Units of one tile run on different CTAs at the
+      // same time (the grid holds every unit), so nobody waits for anybody.
+      const float* wsRow = nullptr;
+      if (splitK) {
+        float* mine = p.ws + ((size_t)u * BM + (size_t)(q * 32 + lane)) * BN;
+#pragma unroll 1
+        for (int ci = 0; ci < kColsPerWarp / 32; ++ci) {
+          const int c0 = half * kColsPerWarp + ci * 32;
+          float v[32];
+          __syncwarp();
+          tmemLoad32x32(acc + (uint32_t)c0, v);
+          if (kChains > 1) {
+            for (int ch = 1; ch < usedChains; ++ch) {
+              float w[32];
+              tmemLoad32x32(acc + (uint32_t)(ch * BN + c0), w);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += w[j];
+            }
+          }
+#pragma unroll
+          for (int j = 0; j < 8; ++j) __stcg(reinterpret_cast<float4*>(mine + c0) + j, make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]));
+        }
+        tcFenceBefore();
+        __syncwarp();
+        if (lane == 0) mbarArrive(&accEmpty[ab]);
+        __threadfence();                                 // the partial tile is visible before the arrival is counted
+        asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * 32) : "memory");
+        if (warp == 2 && lane == 0) {
+          const int old = atomicAdd(&p.counters[t], 1);
+          const int last = old == p.splits - 1;
+          if (last) p.counters[t] = 0;                   // everyone has arrived: the counter is zero again for the next launch
+          *lastFlag = last;
+        }
+        asm volatile("bar.sync 2, %0;" ::"n"(kEpiWarps * 32) : "memory");
+        if (!*lastFlag) continue;
+        __threadfence();
+        wsRow = p.ws + ((size_t)(t * p.splits) * BM + (size_t)(q * 32 + lane)) * BN;
+        if (resTile) issueRes(0);
+      }
 #pragma unroll 1
       for (int ci = 0; ci < kColsPerWarp / 32; ++ci) {
         const int c0 = half * kColsPerWarp + ci * 32;
         float v[32];
+        if (splitK) {                                   // the slices' partial sums, from the workspace (L2)
+#pragma unroll
+          for (int j = 0; j < 8; ++j) { const float4 f = __ldcg(reinterpret_cast<const float4*>(wsRow + c0) + j); v[4 * j] = f.x; v[4 * j + 1] = f.y; v[4 * j + 2] = f.z; v[4 * j + 3] = f.w; }
+          for (int sl = 1; sl < p.splits; ++sl) {
+#pragma unroll
+            for (int j = 0; j < 8; ++j) { const float4 f = __ldcg(reinterpret_cast<const float4*>(wsRow + (size_t)sl * BM * BN + c0) + j); v[4 * j] += f.x; v[4 * j + 1] += f.y; v[4 * j + 2] += f.z; v[4 * j + 3] += f.w; }
+          }
+        } else {
         __syncwarp();                                   // the load is warp-collective
         tmemLoad32x32(acc + (uint32_t)c0, v);
         if (kChains > 1) {
@@ -291,7 +354,8 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
             for (int j = 0; j < 32; ++j) v[j] += w[j];
           }
         }
-        if (c0 + 32 >= (half + 1) * kColsPerWarp) {     // this warp's share is in registers: hand the accumulator back
+        }
+        if (!splitK && c0 + 32 >= (half + 1) * kColsPerWarp) {     // this warp's share is in registers: hand the accumulator back
           tcFenceBefore();
           __syncwarp();
           if (lane == 0) mbarArrive(&accEmpty[ab]);
@@ -517,7 +581,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     const int tapsPerBlock = (p.C <= BK && BK % p.C == 0) ? BK / p.C : 0;          // whole taps per K block
     uint32_t it = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
+    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {      // (the gathered form is never split along K)
       const int rem = (int)(t % tilesPerBatch);
       const int tileM = rem / p.nTiles;
       long long rowBase[4]; int ih0[4], iw0[4];
@@ -558,8 +622,9 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     const int et = threadIdx.x - kSplitWarp0 * 32;
     uint32_t it = 0;
     bool ok = true;
-    for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x) {
-      for (int kb = 0; kb < p.kBlocks; ++kb, ++it) {
+    for (long long u = blockIdx.x; u < units && ok; u += gridDim.x) {
+      long long t; int kb0, kb1; sliceOf(u, t, kb0, kb1);
+      for (int kb = kb0; kb < kb1; ++kb, ++it) {
         const int s = it % kStages; const uint32_t ph = (it / kStages) & 1;
         if (!mbarWait(&full[s], ph, abortWord)) { atomicExch(&g_tcStatus, 3); ok = false; break; }
         const float4* srcA = reinterpret_cast<const float4*>(stageA(s)); float4* dstA = reinterpret_cast<float4*>(stageALo(s));
@@ -711,6 +776,12 @@ int numSMs() {
   return n;
 }
 
+// LLC_TC_SPLITK=0 keeps every K loop in one piece.
+bool splitKEnabled() {
+  const char* e = getenv("LLC_TC_SPLITK");
+  return !(e && e[0] == '0');
+}
+
 // LLC_TC_DIRECT_STORES=1 keeps the epilogue on direct global stores (used to compare the two paths).
 bool tmaEpilogueEnabled() {
   static const bool on = []() { const char* e = getenv("LLC_TC_DIRECT_STORES"); return !(e && e[0] == '1'); }();
@@ -728,8 +799,10 @@ int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, 
   }
   a.mTiles = (int)((a.M + BM - 1) / BM); a.nTiles = (int)((a.N + BN - 1) / BN);
   a.tiles = (long long)a.mTiles * a.nTiles * batch;
+  if (a.splits < 1) a.splits = 1;
   const int threads = tcThreads(KIND, MODE);
-  const unsigned grid = (unsigned)(a.tiles < numSMs() ? a.tiles : numSMs());
+  const long long units = a.tiles * a.splits;
+  const unsigned grid = (unsigned)(units < numSMs() ? units : numSMs());
   tc_kernel<BN, KIND, MODE, BMN><<<grid, threads, S::kTotal, st>>>(ma, mb, mo, mbl, a);
   LLC_LAUNCH_CHECK("tc_kernel");
   return LLC_OK;
@@ -747,20 +820,30 @@ int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, con
 // Tile width by a cost model: a persistent CTA works through ceil(tiles / SMs) tiles, and a tile costs the longer of its
 // main loop (K blocks x a per-block time that grows slowly with the width, because narrow tiles are bound by operand
 // traffic and latency rather than by the tensor pipe) and its epilogue.  Times in microseconds, measured on B200.
-int chooseBN(long long M, long long N, long long batch, bool allow256, int kind, int kBlocks) {
+struct TilePlan { int bn; int splits; };
+// `wsBytes` > 0 allows split-K: when the tiles of a width leave at least half of the SMs idle and the K loop is long, K
+// is cut into slices that run side by side (every unit resident at once) and meet in the workspace.
+TilePlan chooseTile(long long M, long long N, long long batch, bool allow256, int kind, int kBlocks, long long wsBytes) {
   static const float kBlockUs[3][3] = {{0.22f, 0.25f, 0.40f}, {0.28f, 0.33f, 0.50f}, {0.60f, 0.75f, 0.f}};   // [kind][width]
   static const float epilogueUs[3] = {0.8f, 1.2f, 2.0f};
   const long long mT = (M + BM - 1) / BM;
-  int best = 64; float bestCost = 0.f;
+  TilePlan best{64, 1}; float bestCost = 0.f;
   for (int i = 0; i < 3; ++i) {
     const int bn = 64 << i;
     if (bn == 256 && (!allow256 || kind == 2)) continue;
     if (i > 0 && N <= bn / 2) continue;                    // at least half of the tile's columns exist
     const long long tiles = mT * ((N + bn - 1) / bn) * batch;
-    const long long rounds = (tiles + numSMs() - 1) / numSMs();
-    const float loop = kBlocks * kBlockUs[kind][i];
-    const float cost = (float)rounds * ((loop > epilogueUs[i] ? loop : epilogueUs[i]) + 0.3f);
-    if (i == 0 || cost <= bestCost) { best = bn; bestCost = cost; }
+    int splits = 1;
+    if (wsBytes > 0 && tiles * 2 <= numSMs() && kBlocks >= 32) {
+      splits = (int)(numSMs() / tiles);
+      if (splits > 4) splits = 4;
+      // a slice must stay long (>= 20 us of main loop): meeting in the workspace costs about 10 us per tile (measured)
+      while (splits > 1 && ((kBlocks / splits) * kBlockUs[kind][i] < 20.f || 4096 + tiles * splits * (long long)BM * bn * 4 > wsBytes)) --splits;
+    }
+    const long long rounds = (tiles * splits + numSMs() - 1) / numSMs();
+    const float loop = ((kBlocks + splits - 1) / splits) * kBlockUs[kind][i];
+    const float cost = (float)rounds * ((loop > epilogueUs[i] ? loop : epilogueUs[i]) + 0.3f) + (splits > 1 ? 10.0f : 0.f);
+    if (i == 0 || cost <= bestCost) { best = TilePlan{bn, splits}; bestCost = cost; }
   }
   return best;
 }
@@ -794,7 +877,9 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   const long long batch = p->b0 * p->b1;
   const bool bmn = p->b_sk != 1;
   const int kind = !f32 ? 0 : (p->precision == LLC_PREC_TF32X3 ? 2 : 1);
-  const int bn = chooseBN(p->m, p->n, batch, !bmn, kind, (int)((p->k + bk - 1) / bk));
+  const bool wsOk = p->workspace && (reinterpret_cast<uintptr_t>(p->workspace) & 15) == 0 && !bmn && splitKEnabled();
+  const TilePlan plan = chooseTile(p->m, p->n, batch, !bmn, kind, (int)((p->k + bk - 1) / bk), wsOk ? p->workspace_bytes : 0);
+  const int bn = plan.bn;
   CUtensorMap ma, mb;
   bool okMaps = makeMap(&ma, p->a, f32, p->k, p->m, p->b1, p->b0, p->a_sm, p->a_s1, p->a_s0, BM);
   okMaps = okMaps && (bmn ? makeMapMn(&mb, p->b, f32, p->n, p->k, p->b1, p->b0, p->b_sk, p->b_s1, p->b_s0, bk)
@@ -806,6 +891,7 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   a.M = p->m; a.N = p->n; a.K = p->k;
   a.o_s0 = p->o_s0; a.o_s1 = p->o_s1; a.o_sm = p->o_sm; a.r_s0 = p->r_s0; a.r_s1 = p->r_s1; a.r_sm = p->r_sm; a.r_sn = p->r_sn;
   a.b1 = (int)p->b1; a.kBlocks = (int)((p->k + bk - 1) / bk);
+  a.splits = plan.splits; a.counters = reinterpret_cast<int*>(p->workspace); a.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(p->workspace) + 4096);
   a.aZ0 = p->b0 > 1 && p->a_s0 > 0; a.aZ1 = p->b1 > 1 && p->a_s1 > 0; a.bZ0 = p->b0 > 1 && p->b_s0 > 0; a.bZ1 = p->b1 > 1 && p->b_s1 > 0;
   const int ob = p->out_dtype == LLC_FLOAT32 ? 4 : 2;
   a.vecOut = (reinterpret_cast<uintptr_t>(p->out) % (ob * 4)) == 0 && p->o_sm % 4 == 0 && p->o_s0 % 4 == 0 && p->o_s1 % 4 == 0 &&
@@ -842,7 +928,9 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
   const int bk = kTileKBytes / eb;
   const long long M = p->n * p->oh * p->ow, K = p->kh * p->kw * p->c;
   const int kind = !f32 ? 0 : (p->precision == LLC_PREC_TF32X3 ? 2 : 1);
-  const int bn = chooseBN(M, p->f, 1, true, kind, (int)((K + bk - 1) / bk));
+  const bool wsOk = p->workspace && (reinterpret_cast<uintptr_t>(p->workspace) & 15) == 0 && im2colEligible(p, f32) && splitKEnabled();
+  const TilePlan plan = chooseTile(M, p->f, 1, true, kind, (int)((K + bk - 1) / bk), wsOk ? p->workspace_bytes : 0);
+  const int bn = plan.bn;
   CUtensorMap mb;
   if (!makeMap(&mb, p->w, f32, K, p->f, 1, 1, K, 0, 0, bn))
     return setError(LLC_ERR_CUDA, "llc cuda: cuTensorMapEncodeTiled rejected the convolution weights");
@@ -851,6 +939,7 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
   a.out_dtype = p->out_dtype; a.res_dtype = p->res_dtype; a.act = p->act; a.alpha = p->alpha;
   a.M = M; a.N = p->f; a.K = K; a.o_sm = p->f; a.r_sm = p->f; a.r_sn = 1; a.b1 = 1;
   a.kBlocks = (int)((K + bk - 1) / bk);
+  a.splits = plan.splits; a.counters = reinterpret_cast<int*>(p->workspace); a.ws = reinterpret_cast<float*>(reinterpret_cast<char*>(p->workspace) + 4096);
   const int ob = p->out_dtype == LLC_FLOAT32 ? 4 : 2;
   a.vecOut = (reinterpret_cast<uintptr_t>(p->out) % (ob * 4)) == 0 && p->f % 4 == 0 &&
              ((reinterpret_cast<uintptr_t>(p->scale) | reinterpret_cast<uintptr_t>(p->shift)) & 15) == 0;
@@ -870,6 +959,7 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
     CUtensorMap ma;
     if (makeIm2colMap(&ma, p, f32)) return dispatch<2, false>(bn, kind, ma, mb, mo, mbl, a, 1, st);
   }
+  a.splits = 1;                                          // the gathered form walks whole tiles
   return dispatch<1, false>(bn, kind, mb, mb, mo, mbl, a, 1, st);
 }
 

@@ -231,6 +231,7 @@ void LlcExec::prepare(RStep& rs) {
     if (const RView* v = rs.view("shift")) patch(&p.shift, *v);
     if (const RView* v = rs.view("res")) { patch(&p.res, *v); p.res_dtype = v->dtype; }
     if (const RView* v = rs.view("w_lo")) patch(&p.w_lo, *v);
+    p.workspace = workspace; p.workspace_bytes = (int64_t)kWorkspaceBytes;
     // x is the logical [N, C, H, W] view of channel-last storage: anything but the dense strides is passed on
     if (x.strides[1] != 1 && x.shape[1] != 1) failArg("conv input must have unit stride along the channels");
     if (!(x.strides[3] == p.c && x.strides[2] == p.w_in * p.c && (x.strides[0] == p.h * p.w_in * p.c || p.n == 1))) {

@@ -60,7 +60,7 @@ def attention(q, k, v, out, mask=None, scale=1.0):
 
 
 def conv2d(x_nhwc, w_fhwc, out_nhwc, stride, pad, dil=(1, 1), scale=None, shift=None, res=None, alpha=1.0,
-           act="none", prec="fp32", w_lo=None, x_strides=None, x_shape=None):
+           act="none", prec="fp32", w_lo=None, x_strides=None, x_shape=None, workspace=None):
     p = C.LlcConvParams()
     p.x, p.w, p.out, p.scale, p.shift, p.res = _p(x_nhwc), _p(w_fhwc), _p(out_nhwc), _p(scale), _p(shift), _p(res)
     p.in_dtype, p.out_dtype = _DT[x_nhwc.dtype], _DT[out_nhwc.dtype]
@@ -72,6 +72,8 @@ def conv2d(x_nhwc, w_fhwc, out_nhwc, stride, pad, dil=(1, 1), scale=None, shift=
     p.stride_h, p.stride_w, p.pad_h, p.pad_w, p.dil_h, p.dil_w = stride[0], stride[1], pad[0], pad[1], dil[0], dil[1]
     p.alpha, p.act = alpha, C.ACT[act]
     p.w_lo = _p(w_lo)
+    if workspace is not None:
+        p.workspace, p.workspace_bytes = _p(workspace), workspace.numel() * workspace.element_size()
     if x_strides is not None:        # (n, h, w) element strides of an explicit, possibly overlapping, view; x_shape = (n, h, w, c)
         p.x_sn, p.x_sh, p.x_sw = x_strides
         p.n, p.h, p.w_in, p.c = x_shape

@@ -199,3 +199,27 @@ def test_stem_rows_as_channels_over_a_widened_copy(dtype, prec, c_pad, tol, n, h
              x_strides=(h * w_total * c_pad, w_total * c_pad, c_pad), x_shape=(n, h, merged_w, 8 * c_pad))
     assert max_rel_err(out.permute(0, 3, 1, 2), want) < tol
     _healthy()
+
+
+@pytest.mark.parametrize("dtype,prec,tol", [(torch.bfloat16, "bf16", 1e-4), (torch.float32, "tf32x3", 5e-5), (torch.float32, "tf32", 2e-3)])
+def test_split_k_meets_in_the_workspace(dtype, prec, tol):
+    # few output tiles and a long K loop: with a workspace the K loop is cut into slices that run on otherwise idle SMs
+    ws = torch.zeros(16 << 20, dtype=torch.uint8, device=DEV)
+    m, n, k = 300, 256, 4096
+    a, w = _rand(m, k, dtype=dtype).to(DEV), _rand(n, k, seed=1, dtype=dtype).to(DEV)
+    shift = _rand(n, seed=2).to(DEV)
+    res = _rand(m, n, seed=3).to(DEV)
+    want = torch.relu((a.double() @ w.double().t()).float().cpu() + shift.cpu() + res.cpu())
+    for _ in range(2):                                  # twice: the counters must be back at zero after a launch
+        out = torch.full((1, 1, m, n), float("nan"), device=DEV)
+        G.gemm(a[None, None], w.t()[None, None], out, shift=shift, res=res[None, None], act="relu", prec=prec, workspace=ws)
+        assert max_rel_err(out[0, 0], want) < tol
+    assert int(ws[:4096].max()) == 0
+    # ResNet layer4 at a small batch: 13 x 4 tiles of 128 x 128, 144 K blocks
+    x = _rand(32, 7, 7, 512, dtype=dtype).to(DEV); wt = (_rand(512, 3, 3, 512, seed=1) * 0.05).to(dtype).to(DEV)
+    y = F.conv2d(x.permute(0, 3, 1, 2).double().cpu(), wt.permute(0, 3, 1, 2).double().cpu(), None, 1, 1).float()
+    out = torch.full((32, 7, 7, 512), float("nan"), device=DEV)
+    G.conv2d(x, wt, out, (1, 1), (1, 1), prec=prec, workspace=ws)
+    assert max_rel_err(out.permute(0, 3, 1, 2), y) < tol
+    assert int(ws[:4096].max()) == 0
+    _healthy()
