@@ -776,11 +776,12 @@ int numSMs() {
   return n;
 }
 
-// LLC_TC_SPLITK=0 keeps every K loop in one piece.
-bool splitKEnabled() {
+// LLC_TC_SPLITK=0 keeps every K loop in one piece; =2 splits wherever the SMs and the workspace allow (for tests).
+int splitKMode() {
   const char* e = getenv("LLC_TC_SPLITK");
-  return !(e && e[0] == '0');
+  return e && *e ? atoi(e) : 1;
 }
+bool splitKEnabled() { return splitKMode() != 0; }
 
 // LLC_TC_DIRECT_STORES=1 keeps the epilogue on direct global stores (used to compare the two paths).
 bool tmaEpilogueEnabled() {
@@ -834,11 +835,12 @@ TilePlan chooseTile(long long M, long long N, long long batch, bool allow256, in
     if (i > 0 && N <= bn / 2) continue;                    // at least half of the tile's columns exist
     const long long tiles = mT * ((N + bn - 1) / bn) * batch;
     int splits = 1;
-    if (wsBytes > 0 && tiles * 2 <= numSMs() && kBlocks >= 32) {
+    if (wsBytes > 0 && tiles * 2 <= numSMs() && kBlocks >= (splitKMode() == 2 ? 8 : 32)) {
       splits = (int)(numSMs() / tiles);
       if (splits > 4) splits = 4;
       // a slice must stay long (>= 20 us of main loop): meeting in the workspace costs about 10 us per tile (measured)
-      while (splits > 1 && ((kBlocks / splits) * kBlockUs[kind][i] < 20.f || 4096 + tiles * splits * (long long)BM * bn * 4 > wsBytes)) --splits;
+      const float minSliceUs = splitKMode() == 2 ? 0.f : 20.f;
+      while (splits > 1 && (kBlocks / splits < 4 || (kBlocks / splits) * kBlockUs[kind][i] < minSliceUs || 4096 + tiles * splits * (long long)BM * bn * 4 > wsBytes)) --splits;
     }
     const long long rounds = (tiles * splits + numSMs() - 1) / numSMs();
     const float loop = ((kBlocks + splits - 1) / splits) * kBlockUs[kind][i];

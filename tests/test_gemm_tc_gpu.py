@@ -202,8 +202,10 @@ def test_stem_rows_as_channels_over_a_widened_copy(dtype, prec, c_pad, tol, n, h
 
 
 @pytest.mark.parametrize("dtype,prec,tol", [(torch.bfloat16, "bf16", 1e-4), (torch.float32, "tf32x3", 5e-5), (torch.float32, "tf32", 2e-3)])
-def test_split_k_meets_in_the_workspace(dtype, prec, tol):
+def test_split_k_meets_in_the_workspace(dtype, prec, tol, monkeypatch):
     # few output tiles and a long K loop: with a workspace the K loop is cut into slices that run on otherwise idle SMs
+    # (forced here; left to itself the library splits only where a slice stays long enough to pay for the meeting)
+    monkeypatch.setenv("LLC_TC_SPLITK", "2")
     ws = torch.zeros(16 << 20, dtype=torch.uint8, device=DEV)
     m, n, k = 300, 256, 4096
     a, w = _rand(m, k, dtype=dtype).to(DEV), _rand(n, k, seed=1, dtype=dtype).to(DEV)
