@@ -59,6 +59,7 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   float* sMax = reinterpret_cast<float*>(misc + 128);           // [kGroups][128]
   float* sSum = sMax + kGroups * 128;                           // [kGroups][128]
   float* sMask = sSum + kGroups * 128;                          // [384] mask row * log2(e); -inf past the last key
+  volatile int* sMaskSet = reinterpret_cast<volatile int*>(misc + 72);   // whether the current mask row has any non-zero entry
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   constexpr int kIssuerWarp = kSoftmaxThreads / 32;
@@ -133,6 +134,7 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
     const uint32_t trow = tmemBase + ((uint32_t)(q * 32) << 16);
     const int nChunks = p.nBlocks * 4;
     int maskZ = -1;
+    bool plain = false;                                // the mask row is all zeros and covers every column: logits are scale * score
     uint32_t it = 0;
     bool ok = true;                                    // after a wait gave up the loop still runs (every thread must reach every barrier)
     for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++it) {
@@ -141,10 +143,19 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       const long long gm = (long long)tileM * kBM + row;
       const int z = zb0 * p.b1 + zb1;
       if (rowMask && z != maskZ) {                     // mask row (times log2 e); columns past the last key get -inf
+        if (threadIdx.x == 0) *sMaskSet = 0;
+        softmaxBarrier();
         const long long mBase = zb0 * p.m_s0 + zb1 * p.m_s1;
-        for (int c = threadIdx.x; c < kMaxN; c += kSoftmaxThreads)
-          sMask[c] = c < p.N ? (p.mask ? loadAs(p.mask, mBase + c, p.mask_dtype) * kLog2e : 0.f) : -INFINITY;
+        bool any = false;
+        for (int c = threadIdx.x; c < kMaxN; c += kSoftmaxThreads) {
+          const float mv = c < p.N ? (p.mask ? loadAs(p.mask, mBase + c, p.mask_dtype) * kLog2e : 0.f) : -INFINITY;
+          sMask[c] = mv;
+          any = any || (c < nChunks * 32 && mv != 0.f);
+        }
+        if (any) *sMaskSet = 1;
         maskZ = z;
+        softmaxBarrier();
+        plain = *sMaskSet == 0 && p.scaleLog2e > 0.f;
       }
       softmaxBarrier();
       const long long mRow = zb0 * p.m_s0 + zb1 * p.m_s1 + gm * p.m_sm;
@@ -160,7 +171,10 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         float v[32];
         __syncwarp();
         tmemLoad32x32(trow + (uint32_t)(c * 32), v);
-        if (rowMask) {                                   // the common case: the mask row sits in shared memory, four columns per load
+        if (plain) {                                     // no mask at all: the maximum of the raw scores, scaled afterwards
+#pragma unroll
+          for (int j = 0; j < 32; j += 2) mx = fmaxf(mx, fmaxf(v[j], v[j + 1]));
+        } else if (rowMask) {                            // the mask row sits in shared memory, four columns per load
           const float4* m4 = reinterpret_cast<const float4*>(sMask + c * 32);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
@@ -172,6 +186,7 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           for (int j = 0; j < 32; ++j) mx = fmaxf(mx, logit(v[j], c * 32 + j));
         }
       }
+      if (plain) mx *= p.scaleLog2e;
       sMax[h * 128 + row] = mx;
       softmaxBarrier();
 #pragma unroll
@@ -187,7 +202,10 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
         for (int j = 0; j < 4; ++j) {
           __nv_bfloat162 pk[4];
           float e8[8];
-          if (rowMask) {
+          if (plain) {
+#pragma unroll
+            for (int e = 0; e < 8; ++e) e8[e] = v[j * 8 + e] * p.scaleLog2e;
+          } else if (rowMask) {
             const float4 ma = reinterpret_cast<const float4*>(sMask + c * 32 + j * 8)[0], mb = reinterpret_cast<const float4*>(sMask + c * 32 + j * 8)[1];
             e8[0] = fmaf(v[j * 8], p.scaleLog2e, ma.x); e8[1] = fmaf(v[j * 8 + 1], p.scaleLog2e, ma.y); e8[2] = fmaf(v[j * 8 + 2], p.scaleLog2e, ma.z); e8[3] = fmaf(v[j * 8 + 3], p.scaleLog2e, ma.w);
             e8[4] = fmaf(v[j * 8 + 4], p.scaleLog2e, mb.x); e8[5] = fmaf(v[j * 8 + 5], p.scaleLog2e, mb.y); e8[6] = fmaf(v[j * 8 + 6], p.scaleLog2e, mb.z); e8[7] = fmaf(v[j * 8 + 7], p.scaleLog2e, mb.w);
