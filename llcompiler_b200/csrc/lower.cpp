@@ -412,7 +412,7 @@ struct Lowering {
     DType dt = res->type.elt;
     if (res->users.size() == 1 && res->users[0]->name == "llh.convert_to" && isFloat(dt)) {
       DType to = res->users[0]->results[0]->type.elt;
-      if (isFloat(to)) return to;
+      if (isFloat(to) && dtypeSize(to) < dtypeSize(dt)) return to;   // a narrowing convert is done by the producer; a widening one changes nothing (readers compute in fp32)
     }
     return dt;
   }
