@@ -1,11 +1,13 @@
-// Fused attention for sm_100a: out = softmax(scale * Q K^T + mask) V for one (batch, head, 128-query block)
-// per CTA, bf16 operands, head size 64, up to 384 keys.  The score tile never leaves the SM:
-//   warp 8, lane 0   TMA loads of Q, K and V (128-byte swizzle), then tcgen05.mma S = Q K^T into tensor memory
-//                    (128 lanes x up to 384 fp32 columns); after the softmax warps have written P, O = P V into 64
-//                    further columns.
-//   warps 0-7        softmax straight out of tensor memory: thread = one query row and every other 32-column chunk;
-//                    pass 1 row maximum, pass 2 exp2 and row sum, P written as bf16 into shared memory in the K-major
-//                    swizzled layout the second MMA reads; then the epilogue O / rowsum -> bf16 -> global.
+// Fused attention for sm_100a: out = softmax(scale * Q K^T + mask) V, bf16 operands, head size 64, up to 384 keys.
+// Persistent CTAs (one per SM) walk (batch, head, 128-query block) tiles; the score tile never leaves the SM:
+//   last warp, lane 0  TMA loads of Q, K and V (128-byte swizzle) and the MMAs: S = Q K^T into tensor memory (128 lanes x
+//                      up to 384 fp32 columns); once that MMA is complete the next tile's Q, K and this tile's V are
+//                      requested, so their flight hides behind the softmax; O = P V into 64 further columns when P is
+//                      written.
+//   16 softmax warps   straight out of tensor memory: thread = one query row and every fourth 32-column chunk; pass 1 row
+//                      maximum, pass 2 exp2 and row sum, P written as bf16 into shared memory in the K-major swizzled
+//                      layout the second MMA reads; then the epilogue O / rowsum -> bf16 -> global.  A mask row that is
+//                      all zeros (the usual full-length batch) takes a path without mask loads.
 // Replaces batch_matmul -> (scale, mask add) -> softmax -> batch_matmul of the reference's decomposed attention
 // (llcompiler/compiler/torch_compile_config.py:24 decomposes aten._softmax; the matmuls lower through
 // src/Conversion/LLHToHLO/LLHToHLO.cpp:363-382).  Algorithmic HBM bytes: Q + K + V + out (+ mask); the S x S

@@ -154,3 +154,34 @@ def test_host_results_are_page_locked_and_never_aliased():
     assert d.data_ptr() in (ptr_a, ptr_b) or d.is_pinned()
     with torch.no_grad():
         assert max_rel_err(d, m(x)) < 1e-5
+
+
+@pytest.mark.parametrize("name,batch,precision,bf16,tol", [("resnet18", 32, "tf32x3", False, 1e-4), ("resnet50", 256, "auto", True, 2e-2),
+                                                            ("bert", 256, "auto", True, 2e-2)])
+def test_full_size_batch_sharding_is_invisible(name, batch, precision, bf16, tol):
+    # At the benchmark's own sizes the CPU oracle takes minutes, so the check is a property that holds at any size: every
+    # sample is independent (inference-mode batch norm, per-sequence attention), so the full batch must equal its two halves
+    # run separately - which is also what batch-sharding over GPUs relies on.  Tile widths and split-K differ between the
+    # two batch sizes, so equality is to the configuration's tolerance, not bitwise.
+    kw = {"n_layers": 12} if name == "bert" else {}
+    m = build_model(name, **kw)
+    if bf16:
+        m = m.to(torch.bfloat16)
+    inputs = CONFIGS[name].make_inputs(batch=batch) if name != "bert" else CONFIGS[name].make_inputs(batch=batch, seq=384)
+    if bf16:
+        inputs = [i.to(torch.bfloat16) if i.is_floating_point() else i for i in inputs]
+    comp = LLCompiler(precision=precision)
+    fn = compile_with(comp, copy.deepcopy(m).cuda(), False)         # static shapes: the half batch compiles to a plan of its own
+    with torch.no_grad():
+        full = fn(*[i.cuda() for i in inputs]).float()
+        half = batch // 2
+        parts = [fn(*[i[k * half:(k + 1) * half].cuda() for i in inputs]).float() for k in range(2)]
+    torch.cuda.synchronize()
+    assert full.shape[0] == batch and torch.isfinite(full).all()
+    assert max_rel_err(torch.cat(parts), full) < tol
+    # and a quarter of the samples against the CPU oracle at a size it finishes in seconds would repeat the small-batch
+    # tests above; here one sample of the full batch is checked against the oracle instead
+    ref = round_to_bf16_(build_model(name, **kw)) if bf16 else build_model(name, **kw)
+    with torch.no_grad():
+        want = ref(*[(i[:1].float() if i.is_floating_point() else i[:1]) for i in inputs])
+    assert max_rel_err(full[:1].cpu(), want) < tol
