@@ -142,6 +142,18 @@ class LLCompiler(Importer):
         self.compiled.append(fn)
         return fn
 
+    def compile_onnx(self, model):
+        """An ONNX model (onnx.ModelProto, the bytes of a .onnx file, or its path) -> a callable that takes the graph's
+        inputs in order and returns its outputs.  The reference names this entry (llcompiler/importer/importer.py:52-54)
+        but stops at a stub; weights are the model's initialisers, written out as .npy at import."""
+        weight_dir = tempfile.mkdtemp(prefix="LLcompiler_weight_")
+        imported = self.importer(model, (), weight_dir)
+        self._mlir_module = imported.text
+        plan_path = self._compile_text(imported.text)
+        fn = CompiledFunction(imported, plan_path, self._make_engine)
+        self.compiled.append(fn)
+        return lambda *tensors: fn(tensors)
+
     # -- reference: compiler.py:140-168
     def __call__(self, model, inputs: List[torch.Tensor]) -> Any:
         if not isinstance(model, torch.fx.GraphModule):

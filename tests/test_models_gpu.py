@@ -185,3 +185,18 @@ def test_full_size_batch_sharding_is_invisible(name, batch, precision, bf16, tol
     with torch.no_grad():
         want = ref(*[(i[:1].float() if i.is_floating_point() else i[:1]) for i in inputs])
     assert max_rel_err(full[:1].cpu(), want) < tol
+
+
+def test_onnx_entry_on_the_gpu():
+    import numpy as np
+    from llcompiler_b200.importer import onnx_wire as W
+    rng = np.random.default_rng(0)
+    w1, b1 = (rng.standard_normal((512, 784)) * 0.05).astype(np.float32), rng.standard_normal(512).astype(np.float32)
+    w2, b2 = (rng.standard_normal((10, 512)) * 0.05).astype(np.float32), rng.standard_normal(10).astype(np.float32)
+    data = W.build_model([("Gemm", ["x", "w1", "b1"], ["h"], {"transB": 1}), ("Relu", ["h"], ["r"], {}), ("Gemm", ["r", "w2", "b2"], ["y"], {"transB": 1})],
+                         {"w1": w1, "b1": b1, "w2": w2, "b2": b2}, [("x", [64, 784])], [("y", [64, 10])])
+    fn = LLCompiler().compile_onnx(data)
+    x = torch.randn(64, 784)
+    t = torch.from_numpy
+    want = torch.nn.functional.linear(torch.relu(torch.nn.functional.linear(x, t(w1), t(b1))), t(w2), t(b2))
+    assert max_rel_err(fn(x.cuda()).cpu(), want) < 1e-4
