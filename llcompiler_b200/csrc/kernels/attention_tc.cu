@@ -302,7 +302,9 @@ int attnStatus() {
 using namespace llc;
 
 extern "C" int llc_cuda_attention(const LlcAttentionParams* p, void* stream) {
-  if (!p || !p->q || !p->k || !p->v || !p->out) return setError(LLC_ERR_ARGUMENT, "llc_cuda_attention: null operand");
+  if (!p) return setError(LLC_ERR_ARGUMENT, "llc_cuda_attention: null parameter block");
+  if (p->m == 0 || p->b0 == 0 || p->b1 == 0) return LLC_OK;     // no queries: nothing to write
+  if (!p->q || !p->k || !p->v || !p->out) return setError(LLC_ERR_ARGUMENT, "llc_cuda_attention: null operand");
   if (p->dtype != LLC_BFLOAT16) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: operands must be bf16");
   if (p->d != kD) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: head size must be 64");
   if (p->n < 1 || p->n > kMaxN) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: 1 to 384 keys");

@@ -341,7 +341,13 @@ extern "C" int llc_cuda_nchw_to_nhwc(const void* x, void* out, int32_t dtype, in
 }
 
 extern "C" int llc_cuda_eltwise(const LlcEltwiseParams* q, void* stream) {
-  if (!q || !q->out) return setError(LLC_ERR_ARGUMENT, "llc argument: eltwise null pointer");
+  if (!q) return setError(LLC_ERR_ARGUMENT, "llc argument: eltwise null pointer");
+  if (q->rank >= 1 && q->rank <= kMaxRank) {             // an empty tensor: nothing to do, whatever the pointers are
+    bool none = false;
+    for (int d = 0; d < q->rank; ++d) none = none || q->shape[d] == 0;
+    if (none) return LLC_OK;
+  }
+  if (!q->out) return setError(LLC_ERR_ARGUMENT, "llc argument: eltwise null pointer");
   if (q->rank < 1 || q->rank > kMaxRank) return setError(LLC_ERR_ARGUMENT, "llc argument: eltwise rank must be 1..6");
   if (q->n_in < 0 || q->n_in > kMaxIn) return setError(LLC_ERR_ARGUMENT, "llc argument: eltwise takes at most 8 inputs");
   EltArgs a{};
@@ -427,10 +433,11 @@ __global__ void __launch_bounds__(256) maxpool_nhwc_bf16x8_kernel(const __nv_bfl
 }
 
 extern "C" int llc_cuda_maxpool2d(const LlcPoolParams* p, void* stream) {
-  if (!p || !p->x || !p->out) return setError(LLC_ERR_ARGUMENT, "llc argument: maxpool null pointer");
-  if (p->in_dtype != p->out_dtype) return setError(LLC_ERR_ARGUMENT, "llc argument: maxpool input and output types differ");
+  if (!p) return setError(LLC_ERR_ARGUMENT, "llc argument: maxpool null parameter block");
   long long total = p->n * p->oh * p->ow * p->c;
-  if (total <= 0) return LLC_OK;
+  if (total <= 0) return LLC_OK;                        // an empty batch: nothing to do, whatever the pointers are
+  if (!p->x || !p->out) return setError(LLC_ERR_ARGUMENT, "llc argument: maxpool null pointer");
+  if (p->in_dtype != p->out_dtype) return setError(LLC_ERR_ARGUMENT, "llc argument: maxpool input and output types differ");
   cudaStream_t st = (cudaStream_t)stream;
   bool v4 = p->c % 4 == 0 && (reinterpret_cast<uintptr_t>(p->x) % 16) == 0 && (reinterpret_cast<uintptr_t>(p->out) % 16) == 0;
   long long threads = v4 ? total / 4 : total;

@@ -248,3 +248,20 @@ def test_nchw_to_nhwc_bit_exact_with_zero_padding(n, c, h, w, cp, dtype):
     want = torch.zeros(n, h, w, cp, dtype=dtype)
     want[..., :c] = x.permute(0, 2, 3, 1)
     assert torch.equal(out.cpu(), want)
+
+
+def test_empty_problems_launch_nothing_and_succeed():
+    # extents of zero (an empty batch) are legal everywhere: the entry points return 0 without touching memory
+    f32, bf = torch.float32, torch.bfloat16
+    e = lambda *s, dtype=f32: torch.empty(*s, device=DEV, dtype=dtype)
+    G.gemm(e(1, 1, 0, 64), e(1, 1, 64, 32), e(1, 1, 0, 32))
+    G.gemm(e(0, 2, 8, 64, dtype=bf), e(0, 2, 64, 32, dtype=bf), e(0, 2, 8, 32, dtype=bf), prec="bf16")
+    G.conv2d(e(0, 8, 8, 16), e(4, 3, 3, 16), e(0, 8, 8, 4), (1, 1), (1, 1))
+    G.maxpool2d(e(0, 8, 8, 4), e(0, 4, 4, 4), (2, 2), (2, 2), (0, 0))
+    G.softmax(e(0, 128), e(0, 128))
+    G.layernorm(e(0, 64), e(64), e(64), e(0, 64), 1e-5)
+    G.reduce(e(0, 7, 3), e(0, 3), "sum")
+    G.attention(e(1, 2, 0, 64, dtype=bf), e(1, 2, 16, 64, dtype=bf), e(1, 2, 16, 64, dtype=bf), e(1, 2, 0, 64, dtype=bf))
+    torch.cuda.synchronize()
+    from llcompiler_b200 import _capi as C
+    assert C.lib().llc_cuda_status() == 0

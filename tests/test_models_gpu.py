@@ -200,3 +200,17 @@ def test_onnx_entry_on_the_gpu():
     t = torch.from_numpy
     want = torch.nn.functional.linear(torch.relu(torch.nn.functional.linear(x, t(w1), t(b1))), t(w2), t(b2))
     assert max_rel_err(fn(x.cuda()).cpu(), want) < 1e-4
+
+
+def test_empty_and_single_sample_batches_through_the_engine():
+    # the symbolic batch may be 0 (an empty shard when a batch does not divide over the ranks) or 1
+    m = build_model("mlp")
+    comp, fn, out = _gpu_run(m, (torch.randn(8, 784),), dynamic=True)
+    eng = comp.compiled[0].engine
+    got0 = eng.run(0, torch.empty(0, 784).cuda())[0]
+    assert tuple(got0.shape) == (0, 10)
+    x1 = torch.randn(1, 784)
+    with torch.no_grad():
+        assert max_rel_err(eng.run(1, x1.cuda())[0], m(x1)) < 1e-4
+    host0 = eng.run(0, torch.empty(0, 784))[0]            # host tensors too
+    assert tuple(host0.shape) == (0, 10) and not host0.is_cuda
