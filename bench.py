@@ -51,7 +51,7 @@ DESCRIPTION = {
 
 
 # DRAM bytes per launch of the dominant kernel family (dram__bytes_read.sum + dram__bytes_write.sum averaged over the
-# launches of one forward), from the ncu capture summarised in profiles/launch_list_resnet18_fp32_b32.md.
+# launches of one forward), from an ncu capture of this command (20 tensor-core launches of one forward).
 NCU_TRAFFIC = {("resnet18", "conv", 32): 23.0e6}
 # Share of the measured bf16 peak a precision can reach at best: tf32 MMAs run at half the bf16 rate, tf32x3 issues
 # three of them per algorithmic multiply-add.
