@@ -113,6 +113,14 @@ struct Binding {
   size_t arenaBytes = 0;
   std::vector<std::unique_ptr<RStep>> steps;
   std::vector<std::vector<int64_t>> inShapes, outShapes;
+  // CUDA-graph replay of the step list for callers that come back with the same device pointers (a serving loop):
+  // the third call with one set of pointers is captured, later ones are a single graph launch.
+  struct GraphSlot { std::vector<const void*> key; cudaGraphExec_t exec = nullptr; int64_t launches = 0; };
+  std::vector<GraphSlot> graphs;
+  std::vector<std::pair<std::vector<const void*>, int>> seen;   // pointer sets met lately, with how often
+  bool graphsBroken = false;
+  int captures = 0;                         // bounded, so that a caller with ever-new addresses stops paying for captures
+  ~Binding() { for (auto& g : graphs) if (g.exec) cudaGraphExecDestroy(g.exec); }
 };
 
 std::vector<int64_t> ints(const std::string& s) {
@@ -137,6 +145,7 @@ struct LlcExec {
   int* badIds = nullptr;
   char* workspace = nullptr;                  // split-K scratch (counters at the head stay zero between launches)
   static constexpr size_t kWorkspaceBytes = 16u << 20;
+  cudaStream_t capStream = nullptr;         // capture happens here, so that the legacy default stream can replay too
   std::map<std::vector<int64_t>, std::unique_ptr<Binding>> bindings;
   int64_t lastLaunches = 0;
   std::vector<char*> base;                    // per-buffer device base pointers for the current call
@@ -149,6 +158,8 @@ struct LlcExec {
     if (stageOut) cudaFree(stageOut);
     if (badIds) cudaFree(badIds);
     if (workspace) cudaFree(workspace);
+    bindings.clear();                       // graph executables go before the stream they were captured on
+    if (capStream) cudaStreamDestroy(capStream);
   }
 
   RView resolve(const View& v, const std::map<std::string, int64_t>& env) const {
@@ -564,6 +575,55 @@ static void finishCall(LlcExec* ex, Binding& b, LlcTensor* outs, int nout, cudaS
   cudaOk(cudaStreamSynchronize(st), "cudaStreamSynchronize");
 }
 
+// Replays (or, on the third identical call, captures) the binding's steps as one CUDA graph.  Only for calls whose
+// tensors all live on the device, short plans (where launch gaps matter) and streams that are not being captured by the
+// caller.  Returns false when the steps still have to be launched one by one.  LLC_CUDA_GRAPHS=0 switches it off.
+static bool runThroughGraph(LlcExec* ex, Binding& b, const LlcTensor* in, int nin, LlcTensor* outs, int nout, cudaStream_t st) {
+  static const bool enabled = []() { const char* e = getenv("LLC_CUDA_GRAPHS"); return !(e && e[0] == '0'); }();
+  if (!enabled || b.graphsBroken || b.steps.size() < 2 || b.steps.size() > 256) return false;
+  for (int k = 0; k < nin; ++k) if (in[k].device < 0) return false;
+  for (int k = 0; k < nout; ++k) if (outs[k].device < 0) return false;
+  cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+  if (cudaStreamIsCapturing(st, &cs) != cudaSuccess || cs != cudaStreamCaptureStatusNone) { cudaGetLastError(); return false; }
+  std::vector<const void*> key;
+  key.push_back(ex->arena); key.push_back(st);
+  for (int k = 0; k < nin; ++k) key.push_back(in[k].data);
+  for (int k = 0; k < nout; ++k) key.push_back(outs[k].data);
+  for (auto& g : b.graphs)
+    if (g.key == key) {
+      if (cudaGraphLaunch(g.exec, st) != cudaSuccess) { cudaGetLastError(); b.graphsBroken = true; return false; }
+      ex->lastLaunches = g.launches;
+      return true;
+    }
+  // a caller that allocates its outputs per call still cycles through a few addresses: count each set on its own
+  auto it = std::find_if(b.seen.begin(), b.seen.end(), [&](const std::pair<std::vector<const void*>, int>& e) { return e.first == key; });
+  if (it == b.seen.end()) {
+    if (b.seen.size() >= 8) b.seen.erase(b.seen.begin());
+    b.seen.emplace_back(key, 1);
+    return false;
+  }
+  if (++it->second < 3 || b.captures >= 16) return false;
+  b.seen.erase(it);
+  ++b.captures;
+  // capture: every first-use initialisation (function attributes, driver entry points) happened in the earlier runs
+  if (!ex->capStream && cudaStreamCreateWithFlags(&ex->capStream, cudaStreamNonBlocking) != cudaSuccess) { cudaGetLastError(); b.graphsBroken = true; return false; }
+  cudaStream_t cap = ex->capStream;
+  if (cudaStreamBeginCapture(cap, cudaStreamCaptureModeThreadLocal) != cudaSuccess) { cudaGetLastError(); b.graphsBroken = true; return false; }
+  bool ok = true;
+  try { ex->lastLaunches = 0; ex->runSteps(b.steps, cap); } catch (const std::exception&) { ok = false; }
+  cudaGraph_t graph = nullptr;
+  if (cudaStreamEndCapture(cap, &graph) != cudaSuccess || !graph) ok = false;
+  cudaGraphExec_t exec = nullptr;
+  if (ok && cudaGraphInstantiate(&exec, graph, 0) != cudaSuccess) ok = false;
+  if (graph) cudaGraphDestroy(graph);
+  if (!ok) { cudaGetLastError(); if (exec) cudaGraphExecDestroy(exec); b.graphsBroken = true; ex->lastLaunches = 0; return false; }
+  if (b.graphs.size() >= 4) { cudaGraphExecDestroy(b.graphs.front().exec); b.graphs.erase(b.graphs.begin()); }
+  Binding::GraphSlot slot; slot.key = key; slot.exec = exec; slot.launches = ex->lastLaunches;
+  b.graphs.push_back(slot);
+  if (cudaGraphLaunch(exec, st) != cudaSuccess) { cudaGetLastError(); b.graphsBroken = true; b.graphs.pop_back(); cudaGraphExecDestroy(exec); ex->lastLaunches = 0; return false; }
+  return true;
+}
+
 extern "C" int llc_run(LlcExec* ex, const int64_t* symbols, int nsym, const LlcTensor* in, int nin, LlcTensor* outs, int nout, void* stream) {
   if (!ex || (nin > 0 && !in) || (nout > 0 && !outs)) return setError(LLC_ERR_ARGUMENT, "null argument");
   try {
@@ -571,7 +631,7 @@ extern "C" int llc_run(LlcExec* ex, const int64_t* symbols, int nsym, const LlcT
     bool anyHostOut = false;
     Binding& b = prepareCall(ex, symbols, nsym, in, nin, outs, nout, st, anyHostOut);
     ex->lastLaunches = 0;
-    ex->runSteps(b.steps, st);
+    if (!runThroughGraph(ex, b, in, nin, outs, nout, st)) ex->runSteps(b.steps, st);
     finishCall(ex, b, outs, nout, st, anyHostOut);
     return LLC_OK;
   } catch (const std::exception& e) { return setError(statusFor(e), e.what()); }
