@@ -2,8 +2,10 @@
 
 The reference names ONNX as an entry (llcompiler/importer/importer.py:52-54) but only maps element types and dumps
 initialisers (llcompiler/importer/onnx_translate.py:32-92).  This translator covers the operators of the MLP and ResNet
-configurations with static shapes: Gemm, MatMul, Add, Sub, Mul, Div, Relu, Conv, BatchNormalization, MaxPool,
-GlobalAveragePool, Flatten, Reshape, Identity.  Initialisers become `llh.weight` ops backed by .npy files, exactly like
+configurations: Gemm, MatMul, Add, Sub, Mul, Div, Relu, Conv, BatchNormalization, MaxPool, GlobalAveragePool, Flatten,
+Reshape, Identity.  An input extent given as a `dim_param` (or left unknown) becomes a symbol: the argument carries
+`func.input_symbol_<d>` like the arguments of the FX route (llcompiler/importer/fx_translate.py:60-75), result types
+show `?` there and the compiler's shape inference fills in the expressions.  Initialisers become `llh.weight` ops backed by .npy files, exactly like
 the parameters of the FX route; the result is the same ImportedFunction the FX importer returns.
 """
 from __future__ import annotations
@@ -15,7 +17,7 @@ from typing import Dict, List, Optional
 import numpy as np
 import torch
 
-from ..dialect.llh import Block, TensorType, Value, array_i64, bool_attr, enum_attr, f64_attr, i64_attr, print_module, str_attr
+from ..dialect.llh import DYNAMIC, Block, TensorType, Value, array_i64, bool_attr, enum_attr, f64_attr, i64_attr, print_module, str_attr
 from .fx_translate import ImportedFunction
 from .onnx_wire import FLOAT, INT64, OnnxGraph, OnnxNode, parse_model
 
@@ -55,13 +57,35 @@ def _bcast(a: List[int], b: List[int]) -> List[int]:
     for i in range(max(len(a), len(b))):
         x = a[len(a) - 1 - i] if i < len(a) else 1
         y = b[len(b) - 1 - i] if i < len(b) else 1
+        if DYNAMIC in (x, y):           # a symbolic extent meets 1, itself or a static extent it must equal at run time
+            out.append(max(x, y) if max(x, y) > 1 else DYNAMIC)
+            continue
         if x != y and 1 not in (x, y):
             raise ValueError(f"shapes {a} and {b} do not broadcast")
         out.append(max(x, y))
     return out[::-1]
 
 
+def _prod(dims) -> int:
+    return DYNAMIC if DYNAMIC in dims else int(np.prod(dims, dtype=np.int64))
+
+
+def _extent_value(block: Block, x: Value, dims: range):
+    """i64 value of the product of x's extents over `dims` (llh.dim for the symbolic ones)."""
+    static = int(np.prod([x.type.shape[d] for d in dims if x.type.shape[d] != DYNAMIC], dtype=np.int64))
+    acc = None
+    for d in dims:
+        if x.type.shape[d] == DYNAMIC:
+            v = block.dim(x, d)
+            acc = v if acc is None else block.op("llh.mul", [acc, v], ["i64"]).result
+    if acc is None:
+        return block.constant_i64(static)
+    return acc if static == 1 else block.op("llh.mul", [acc, block.constant_i64(static)], ["i64"]).result
+
+
 def _window(n: int, k: int, s: int, pl: int, ph: int, d: int = 1, ceil: bool = False) -> int:
+    if n == DYNAMIC:
+        return DYNAMIC
     num = n + pl + ph - d * (k - 1) - 1
     return (-(-num // s) if ceil else num // s) + 1
 
@@ -138,16 +162,29 @@ def _translate(ctx: _Ctx, n: OnnxNode) -> None:
     elif op == "GlobalAveragePool":
         emit("llh.adaptive_average_pool", [x], x.type.shape[:2] + [1, 1], {"out_size": array_i64([1, 1])})
     elif op in ("Flatten", "Reshape"):
+        rank = x.type.rank
         if op == "Flatten":
-            axis = int(a.get("axis", 1))
-            shape = [int(np.prod(x.type.shape[:axis], dtype=np.int64)), int(np.prod(x.type.shape[axis:], dtype=np.int64))]
+            axis = int(a.get("axis", 1)) % (rank + 1)
+            shape = [_prod(x.type.shape[:axis]), _prod(x.type.shape[axis:])]
+            dims = [_extent_value(b, x, range(0, axis)), _extent_value(b, x, range(axis, rank))]
         else:
-            shape = ctx.const_ints(n.inputs[1])
-            total = int(np.prod(x.type.shape, dtype=np.int64))
-            shape = [x.type.shape[i] if d == 0 else d for i, d in enumerate(shape)]
-            if -1 in shape:
-                shape[shape.index(-1)] = total // int(-np.prod(shape, dtype=np.int64))
-        emit("llh.reshape", [x] + [b.constant_i64(d) for d in shape], shape)
+            want = ctx.const_ints(n.inputs[1])
+            shape = [x.type.shape[i] if d == 0 else (DYNAMIC if d == -1 else d) for i, d in enumerate(want)]
+            dims = [b.dim(x, i) if d == 0 and x.type.shape[i] == DYNAMIC else (None if d == -1 else b.constant_i64(shape[i]))
+                    for i, d in enumerate(want)]
+            if -1 in want:
+                at, known = want.index(-1), [s for i, s in enumerate(shape) if want[i] != -1]
+                if DYNAMIC not in x.type.shape and DYNAMIC not in known:
+                    shape[at] = _prod(x.type.shape) // max(1, _prod(known))
+                    dims[at] = b.constant_i64(shape[at])
+                else:                       # total extent / product of the named extents, as i64 arithmetic
+                    num = _extent_value(b, x, range(rank))
+                    den = None
+                    for i, v in enumerate(dims):
+                        if i != at:
+                            den = v if den is None else b.op("llh.mul", [den, v], ["i64"]).result
+                    dims[at] = num if den is None else b.op("llh.div", [num, den], ["i64"]).result
+        emit("llh.reshape", [x] + dims, shape)
     else:
         raise NotImplementedError(f"no LLH translation for ONNX operator {op}")
 
@@ -163,11 +200,19 @@ def onnx_translate_to_mlir_text(model, weight_dir: Optional[str] = None) -> Impo
     os.makedirs(ctx.weight_dir, exist_ok=True)
     res = ImportedFunction()
     for pos, v in enumerate(graph.inputs):
-        if any(not isinstance(d, int) or d <= 0 for d in v.dims):
-            raise NotImplementedError(f"ONNX input '{v.name}' has symbolic extents {v.dims}; only static shapes are imported")
         if v.elem_type not in _ELT:
             raise NotImplementedError(f"ONNX input element type {v.elem_type}")
-        ctx.values[v.name] = ctx.block.add_arg(TensorType(list(v.dims), _ELT[v.elem_type]), {})
+        shape, attrs = [], {}
+        for d, ext in enumerate(v.dims or [1]):
+            if isinstance(ext, int) and ext > 0:
+                shape.append(ext)
+                attrs[f"func.input_symbol_{d}"] = str_attr(f"c{ext}")
+            else:                           # dim_param, or an extent the exporter left open: one symbol per distinct name
+                name = ext if isinstance(ext, str) and ext not in ("", "?") else f"{v.name}_{d}"
+                name = "".join(ch if ch.isalnum() else "_" for ch in name)
+                shape.append(DYNAMIC)
+                attrs[f"func.input_symbol_{d}"] = str_attr(("s_" + name) if name[0].isdigit() or name[0] == "c" else name)
+        ctx.values[v.name] = ctx.block.add_arg(TensorType(shape, _ELT[v.elem_type]), attrs)
         res.tensor_positions.append(pos)
     res.num_placeholders = len(graph.inputs)
     for n in graph.nodes:

@@ -200,6 +200,14 @@ def test_onnx_entry_on_the_gpu():
     t = torch.from_numpy
     want = torch.nn.functional.linear(torch.relu(torch.nn.functional.linear(x, t(w1), t(b1))), t(w2), t(b2))
     assert max_rel_err(fn(x.cuda()).cpu(), want) < 1e-4
+    # the same graph with a named batch extent: one plan, any batch
+    data = W.build_model([("Gemm", ["x", "w1", "b1"], ["h"], {"transB": 1}), ("Relu", ["h"], ["r"], {}), ("Gemm", ["r", "w2", "b2"], ["y"], {"transB": 1})],
+                         {"w1": w1, "b1": b1, "w2": w2, "b2": b2}, [("x", ["N", 784])], [("y", ["N", 10])])
+    comp = LLCompiler()
+    fn = comp.compile_onnx(data)
+    for rows in (64, 3, 257):
+        assert max_rel_err(fn(x[:rows].cuda() if rows <= 64 else x.repeat(5, 1)[:rows].cuda()).cpu(), (want if rows <= 64 else want.repeat(5, 1))[:rows]) < 1e-4
+    assert len(comp.compiled) == 1
 
 
 def test_empty_and_single_sample_batches_through_the_engine():

@@ -57,9 +57,25 @@ def test_onnx_residual_cnn():
 
 
 def test_onnx_refuses_what_it_does_not_cover():
-    data = W.build_model([("Relu", ["x"], ["y"], {})], {}, [("x", ["B", 8])], [("y", ["B", 8])])
-    with pytest.raises(NotImplementedError, match="symbolic"):
-        InterpreterCompiler().compile_onnx(data)
     data = W.build_model([("LSTM", ["x"], ["y"], {})], {}, [("x", [2, 8])], [("y", [2, 8])])
     with pytest.raises(NotImplementedError, match="LSTM"):
         InterpreterCompiler().compile_onnx(data)
+
+
+def test_onnx_symbolic_batch():
+    """`dim_param` extents become symbols bound from the input at run time: one plan serves every batch size."""
+    c1, fc, fb = _np(8, 3, 3, 3, scale=0.2), _np(10, 8 * 4 * 4, seed=2, scale=0.1), _np(10, seed=3)
+    nodes = [("Conv", ["x", "c1"], ["a"], {"kernel_shape": [3, 3], "pads": [1, 1, 1, 1], "strides": [2, 2]}), ("Relu", ["a"], ["b"], {}),
+             ("MaxPool", ["b"], ["c"], {"kernel_shape": [2, 2], "strides": [2, 2]}), ("Flatten", ["c"], ["d"], {"axis": 1}),
+             ("Gemm", ["d", "fc", "fb"], ["e"], {"transB": 1}), ("Reshape", ["e", "s"], ["y"], {})]
+    data = W.build_model(nodes, {"c1": c1, "fc": fc, "fb": fb, "s": np.array([-1, 2, 5], dtype=np.int64)}, [("x", ["batch", 3, 16, 16])], [("y", ["batch", 2, 5])])
+    comp = InterpreterCompiler()
+    fn = comp.compile_onnx(data)
+    assert 'func.input_symbol_0 = "batch"' in comp._mlir_module and "tensor<?x3x16x16xf32>" in comp._mlir_module
+    t = torch.from_numpy
+    for batch in (1, 5, 16):
+        x = torch.randn(batch, 3, 16, 16, generator=torch.Generator().manual_seed(batch))
+        want = F.linear(F.max_pool2d(F.relu(F.conv2d(x, t(c1), None, 2, 1)), 2, 2).flatten(1), t(fc), t(fb)).reshape(-1, 2, 5)
+        got = fn(x)
+        assert tuple(got.shape) == (batch, 2, 5) and max_rel_err(got, want) < 1e-4
+    assert len(comp.compiled) == 1
