@@ -31,6 +31,6 @@ class Importer:
 
     def _importer_onnx(self, model, weight_dir=None) -> ImportedFunction:
         # the reference's ONNX entry is a stub (llcompiler/importer/importer.py:52-54); here a ModelProto, the bytes of a
-        # .onnx file or its path are decoded without the onnx package (static or named extents, the MLP / ResNet operator set)
+        # .onnx file or its path are decoded without the onnx package (static or named extents, the MLP, ResNet and encoder-layer operator set)
         from .onnx_translate import onnx_translate_to_mlir_text
         return onnx_translate_to_mlir_text(model, weight_dir)

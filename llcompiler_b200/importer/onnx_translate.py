@@ -2,8 +2,9 @@
 
 The reference names ONNX as an entry (llcompiler/importer/importer.py:52-54) but only maps element types and dumps
 initialisers (llcompiler/importer/onnx_translate.py:32-92).  This translator covers the operators of the MLP and ResNet
-configurations: Gemm, MatMul, Add, Sub, Mul, Div, Relu, Conv, BatchNormalization, MaxPool, GlobalAveragePool, Flatten,
-Reshape, Identity.  An input extent given as a `dim_param` (or left unknown) becomes a symbol: the argument carries
+configurations and of a transformer encoder: Gemm, MatMul (plain, rows-folded and batched), Add, Sub, Mul, Div, Relu,
+Gelu, Sqrt, Exp, Tanh, Erf, Sigmoid, Neg, Abs, Softmax, LayerNormalization, Transpose, Gather (embedding rows), Conv,
+BatchNormalization, MaxPool, GlobalAveragePool, Flatten, Reshape, Identity.  An input extent given as a `dim_param` (or left unknown) becomes a symbol: the argument carries
 `func.input_symbol_<d>` like the arguments of the FX route (llcompiler/importer/fx_translate.py:60-75), result types
 show `?` there and the compiler's shape inference fills in the expressions.  Initialisers become `llh.weight` ops backed by .npy files, exactly like
 the parameters of the FX route; the result is the same ImportedFunction the FX importer returns.
@@ -23,6 +24,7 @@ from .onnx_wire import FLOAT, INT64, OnnxGraph, OnnxNode, parse_model
 
 _ELT = {FLOAT: "f32", INT64: "i64"}
 _TORCH = {"f32": torch.float32, "i64": torch.int64}
+_UNARY = {"Sqrt": "sqrt", "Exp": "exp", "Tanh": "tanh", "Erf": "erf", "Sigmoid": "sigmoid", "Neg": "neg", "Abs": "abs"}
 
 
 class _Ctx:
@@ -114,11 +116,54 @@ def _translate(ctx: _Ctx, n: OnnxNode) -> None:
     elif op in ("Add", "Sub", "Mul", "Div"):
         y = ctx.get(n.inputs[1])
         emit("llh." + op.lower(), [x, y], _bcast(x.type.shape, y.type.shape))
+    elif op in _UNARY:
+        emit("llh." + _UNARY[op], [x], x.type.shape)
+    elif op == "Gelu":
+        emit("llh.gelu", [x], x.type.shape, {"approximate": str_attr(a.get("approximate", "none") or "none")})
+    elif op == "Softmax":
+        emit("llh.softmax", [x], x.type.shape, {"axis": i64_attr(int(a.get("axis", -1)) % x.type.rank)})
+    elif op == "LayerNormalization":
+        if len(n.inputs) < 3 or not n.inputs[2]:
+            raise NotImplementedError("LayerNormalization without a bias")
+        emit("llh.layer_norm", [x, ctx.get(n.inputs[1]), ctx.get(n.inputs[2])], x.type.shape,
+             {"epsilon": f64_attr(float(a.get("epsilon", 1e-5))), "axis": i64_attr(int(a.get("axis", -1)) % x.type.rank)})
+    elif op == "Transpose":
+        perm = [int(p) for p in (a.get("perm") or range(x.type.rank - 1, -1, -1))]
+        emit("llh.transpose", [x], [x.type.shape[p] for p in perm], {"perms": array_i64(perm)})
+    elif op == "Gather":
+        ids = ctx.get(n.inputs[1])
+        if int(a.get("axis", 0)) != 0 or x.type.rank != 2 or ids.type.elt != "i64":
+            raise NotImplementedError("Gather other than rows of a table by int64 indices")
+        emit("llh.embedding", [x, ids], ids.type.shape + [x.type.shape[1]], elt=x.type.elt)
     elif op == "MatMul":
         y = ctx.get(n.inputs[1])
-        if x.type.rank != 2 or y.type.rank != 2:
-            raise NotImplementedError("MatMul of rank other than 2")
-        emit("llh.matmul", [x, y], [x.type.shape[0], y.type.shape[1]])
+        rx, ry = x.type.rank, y.type.rank
+        if rx == 2 and ry == 2:
+            emit("llh.matmul", [x, y], [x.type.shape[0], y.type.shape[1]])
+        elif rx > 2 and ry == 2:              # [..., M, K] x [K, N]: the leading extents fold into the rows
+            rows = b.op("llh.reshape", [x, _extent_value(b, x, range(rx - 1)), b.constant_i64(x.type.shape[-1])],
+                        [TensorType([_prod(x.type.shape[:-1]), x.type.shape[-1]], x.type.elt)]).result
+            mm = b.op("llh.matmul", [rows, y], [TensorType([rows.type.shape[0], y.type.shape[1]], x.type.elt)]).result
+            shape = x.type.shape[:-1] + [y.type.shape[1]]
+            emit("llh.reshape", [mm] + [b.dim(x, d) if shape[d] == DYNAMIC else b.constant_i64(shape[d]) for d in range(rx - 1)]
+                 + [b.constant_i64(shape[-1])], shape)
+        elif rx == ry and rx >= 3:            # batched on both sides: fold the leading extents into one batch
+            def fold(v):
+                if v.type.rank == 3:
+                    return v
+                return b.op("llh.reshape", [v, _extent_value(b, v, range(v.type.rank - 2)), b.constant_i64(v.type.shape[-2]), b.constant_i64(v.type.shape[-1])],
+                            [TensorType([_prod(v.type.shape[:-2])] + v.type.shape[-2:], v.type.elt)]).result
+            if DYNAMIC in x.type.shape[-2:] or DYNAMIC in y.type.shape[-2:]:
+                raise NotImplementedError("batched MatMul with a symbolic matrix extent")
+            fx, fy = fold(x), fold(y)
+            bm = b.op("llh.batch_matmul", [fx, fy], [TensorType([fx.type.shape[0], fx.type.shape[1], fy.type.shape[2]], x.type.elt)]).result
+            shape = x.type.shape[:-1] + [y.type.shape[-1]]
+            if rx == 3:
+                ctx.values[n.outputs[0]] = bm
+            else:
+                emit("llh.reshape", [bm] + [b.dim(x, d) if shape[d] == DYNAMIC else b.constant_i64(shape[d]) for d in range(rx)], shape)
+        else:
+            raise NotImplementedError(f"MatMul of ranks {rx} and {ry}")
     elif op == "Gemm":
         if a.get("transA", 0) or float(a.get("alpha", 1.0)) != 1.0 or float(a.get("beta", 1.0)) != 1.0:
             raise NotImplementedError("Gemm with transA, alpha or beta")

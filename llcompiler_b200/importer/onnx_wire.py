@@ -242,7 +242,8 @@ def _enc_attr(name: str, v) -> bytes:
 
 
 def build_model(nodes, initializers: Dict[str, np.ndarray], inputs, outputs) -> bytes:
-    """nodes: (op_type, [inputs], [outputs], {attrs}); inputs / outputs: (name, [dims]).  Returns ModelProto bytes."""
+    """nodes: (op_type, [inputs], [outputs], {attrs}); inputs / outputs: (name, [dims]) or (name, [dims], element type code).
+    Returns ModelProto bytes."""
     g = b""
     for op, ins, outs, attrs in nodes:
         n = b"".join(_ld(1, i.encode()) for i in ins) + b"".join(_ld(2, o.encode()) for o in outs) + _ld(4, op.encode())
@@ -250,7 +251,7 @@ def build_model(nodes, initializers: Dict[str, np.ndarray], inputs, outputs) -> 
         g += _ld(1, n)
     g += _ld(2, b"graph")
     g += b"".join(_ld(5, _enc_tensor(k, v)) for k, v in initializers.items())
-    g += b"".join(_ld(11, _enc_value(n, d)) for n, d in inputs)
-    g += b"".join(_ld(12, _enc_value(n, d)) for n, d in outputs)
+    g += b"".join(_ld(11, _enc_value(*v)) for v in inputs)
+    g += b"".join(_ld(12, _enc_value(*v)) for v in outputs)
     opset = _ld(1, b"") + _vi(2, 17)
     return _vi(1, 8) + _ld(8, opset) + _ld(7, g)

@@ -79,3 +79,42 @@ def test_onnx_symbolic_batch():
         got = fn(x)
         assert tuple(got.shape) == (batch, 2, 5) and max_rel_err(got, want) < 1e-4
     assert len(comp.compiled) == 1
+
+
+def test_onnx_transformer_encoder_layer():
+    """Embedding rows, layer norm, attention with folded and batched MatMul, GELU feed-forward, residuals - with a named batch."""
+    d, heads, seq, vocab = 32, 4, 8, 50
+    dh = d // heads
+    p = {k: _np(*shape, seed=i, scale=sc) for i, (k, shape, sc) in enumerate([
+        ("emb", (vocab, d), 1.0), ("g1", (d,), 0.2), ("b1", (d,), 0.1), ("wq", (d, d), 0.2), ("bq", (d,), 0.1), ("wk", (d, d), 0.2), ("bk", (d,), 0.1),
+        ("wv", (d, d), 0.2), ("bv", (d,), 0.1), ("wo", (d, d), 0.2), ("bo", (d,), 0.1), ("g2", (d,), 0.2), ("b2", (d,), 0.1),
+        ("w1", (d, 4 * d), 0.2), ("c1", (4 * d,), 0.1), ("w2", (4 * d, d), 0.1), ("c2", (d,), 0.1)])}
+    p["g1"] += 1.0
+    p["g2"] += 1.0
+    init = dict(p, split=np.array([0, 0, heads, dh], dtype=np.int64), merge=np.array([0, 0, d], dtype=np.int64), scale=np.array(dh ** -0.5, dtype=np.float32))
+    nodes = [("Gather", ["emb", "ids"], ["x"], {"axis": 0}),
+             ("LayerNormalization", ["x", "g1", "b1"], ["n1"], {"axis": -1, "epsilon": 1e-5})]
+    for t in "qkv":
+        nodes += [("MatMul", ["n1", "w" + t], [t + "0"], {}), ("Add", [t + "0", "b" + t], [t + "1"], {}), ("Reshape", [t + "1", "split"], [t + "2"], {}),
+                  ("Transpose", [t + "2"], [t + "3"], {"perm": [0, 2, 3, 1] if t == "k" else [0, 2, 1, 3]})]
+    nodes += [("MatMul", ["q3", "k3"], ["s0"], {}), ("Mul", ["s0", "scale"], ["s1"], {}), ("Softmax", ["s1"], ["pr"], {"axis": -1}),
+              ("MatMul", ["pr", "v3"], ["o0"], {}), ("Transpose", ["o0"], ["o1"], {"perm": [0, 2, 1, 3]}), ("Reshape", ["o1", "merge"], ["o2"], {}),
+              ("MatMul", ["o2", "wo"], ["o3"], {}), ("Add", ["o3", "bo"], ["o4"], {}), ("Add", ["x", "o4"], ["r1"], {}),
+              ("LayerNormalization", ["r1", "g2", "b2"], ["n2"], {"axis": -1, "epsilon": 1e-5}),
+              ("MatMul", ["n2", "w1"], ["f0"], {}), ("Add", ["f0", "c1"], ["f1"], {}), ("Gelu", ["f1"], ["f2"], {}),
+              ("MatMul", ["f2", "w2"], ["f3"], {}), ("Add", ["f3", "c2"], ["f4"], {}), ("Add", ["r1", "f4"], ["y"], {})]
+    data = W.build_model(nodes, init, [("ids", ["N", seq], W.INT64)], [("y", ["N", seq, d])])
+    comp = InterpreterCompiler()
+    fn = comp.compile_onnx(data)
+    t = {k: torch.from_numpy(v) for k, v in p.items()}
+    for batch in (2, 5):
+        ids = torch.randint(0, vocab, (batch, seq), generator=torch.Generator().manual_seed(batch))
+        x = t["emb"][ids]
+        n1 = F.layer_norm(x, (d,), t["g1"], t["b1"])
+        q, k, v = [(n1 @ t["w" + c] + t["b" + c]).reshape(batch, seq, heads, dh).transpose(1, 2) for c in "qkv"]
+        o = (torch.softmax(q @ k.transpose(-1, -2) * dh ** -0.5, -1) @ v).transpose(1, 2).reshape(batch, seq, d)
+        r1 = x + o @ t["wo"] + t["bo"]
+        want = r1 + F.gelu(F.layer_norm(r1, (d,), t["g2"], t["b2"]) @ t["w1"] + t["c1"]) @ t["w2"] + t["c2"]
+        got = fn(ids)
+        assert tuple(got.shape) == (batch, seq, d) and max_rel_err(got, want) < 1e-4
+    assert len(comp.compiled) == 1
