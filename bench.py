@@ -228,7 +228,7 @@ def main():
             dist.all_gather_into_tensor(gathered, o)
         return o
 
-    for _ in range(args.warmup):
+    for _ in range(args.warmup):                # the executor captures its CUDA graph on the second of these calls
         step()
     torch.cuda.synchronize()
     if world > 1:

@@ -114,7 +114,7 @@ struct Binding {
   std::vector<std::unique_ptr<RStep>> steps;
   std::vector<std::vector<int64_t>> inShapes, outShapes;
   // CUDA-graph replay of the step list for callers that come back with the same device pointers (a serving loop):
-  // the third call with one set of pointers is captured, later ones are a single graph launch.
+  // the second call with one set of pointers is captured, later ones are a single graph launch.
   struct GraphSlot { std::vector<const void*> key; cudaGraphExec_t exec = nullptr; int64_t launches = 0; };
   std::vector<GraphSlot> graphs;
   std::vector<std::pair<std::vector<const void*>, int>> seen;   // pointer sets met lately, with how often
@@ -575,7 +575,7 @@ static void finishCall(LlcExec* ex, Binding& b, LlcTensor* outs, int nout, cudaS
   cudaOk(cudaStreamSynchronize(st), "cudaStreamSynchronize");
 }
 
-// Replays (or, on the third identical call, captures) the binding's steps as one CUDA graph.  Only for calls whose
+// Replays (or, on the second call with the same pointers, captures) the binding's steps as one CUDA graph.  Only for calls whose
 // tensors all live on the device, short plans (where launch gaps matter) and streams that are not being captured by the
 // caller.  Returns false when the steps still have to be launched one by one.  LLC_CUDA_GRAPHS=0 switches it off.
 static bool runThroughGraph(LlcExec* ex, Binding& b, const LlcTensor* in, int nin, LlcTensor* outs, int nout, cudaStream_t st) {
@@ -602,7 +602,7 @@ static bool runThroughGraph(LlcExec* ex, Binding& b, const LlcTensor* in, int ni
     b.seen.emplace_back(key, 1);
     return false;
   }
-  if (++it->second < 3 || b.captures >= 16) return false;
+  if (++it->second < 2 || b.captures >= 16) return false;
   b.seen.erase(it);
   ++b.captures;
   // capture: every first-use initialisation (function attributes, driver entry points) happened in the earlier runs

@@ -226,7 +226,7 @@ def test_empty_and_single_sample_batches_through_the_engine():
 
 @pytest.mark.parametrize("name,precision,tol", [("mlp", "auto", 1e-4), ("encoder", "auto", 1e-4), ("resnet18", "tf32x3", 1e-4)])
 def test_repeated_device_calls_replay_a_graph_with_identical_results(name, precision, tol):
-    """A caller that keeps coming back with the same device pointers is served by one graph launch from its third
+    """A caller that keeps coming back with the same device pointers is served by one graph launch from its second
     call on; every replay has to give the bits of the first, step-by-step, run - also on a side stream, with
     other inputs in the same buffer, and after a call of another batch size in between."""
     m = build_model(name)
