@@ -872,7 +872,13 @@ bool tcGemmSupported(const LlcGemmParams* p) {
   if ((reinterpret_cast<uintptr_t>(p->a) | reinterpret_cast<uintptr_t>(p->b)) & 15) return false;
   if (p->m < 1 || p->n < 1 || p->k < 1) return false;
   if (p->b0 > (1 << 30) || p->b1 > (1 << 30) || p->m > (1LL << 31) * 64 || p->n > (1LL << 31)) return false;
-  if (p->m * p->n * p->k < (1LL << 18)) return false;   // tiny problems: the FMA kernel has less fixed cost
+  // tiny problems: the FMA kernel has less fixed cost.  For 32-bit operands the break-even measured near 2^25
+  // multiply-adds (64x512x784 took 20 us on either kernel, 64x10x512 19 us against 27 us); LLC_TC_MIN_MACS_LOG2 moves it.
+  const char* minEnv = getenv("LLC_TC_MIN_MACS_LOG2");
+  int minLog2F32 = minEnv && *minEnv ? atoi(minEnv) : 25;
+  minLog2F32 = minLog2F32 < 0 ? 0 : (minLog2F32 > 40 ? 40 : minLog2F32);
+  const long long macs = p->m * p->n * p->k * (p->b0 > 0 ? p->b0 : 1) * (p->b1 > 0 ? p->b1 : 1);
+  if (p->m * p->n * p->k < (1LL << 18) || (f32 && macs < (1LL << minLog2F32))) return false;
   return encodeTiled() != nullptr;
 }
 

@@ -14,6 +14,12 @@ import gpu_ops as G  # noqa: E402
 from llcompiler_b200 import _capi as C  # noqa: E402
 from oracle.models import max_rel_err  # noqa: E402
 
+
+@pytest.fixture(autouse=True)
+def _small_problems_stay_on_the_tensor_cores(monkeypatch):
+    # by default fp32 problems below 2^25 multiply-adds go to the FMA kernel; these tests are about the tensor-core one
+    monkeypatch.setenv("LLC_TC_MIN_MACS_LOG2", "18")
+
 DEV = "cuda"
 
 
@@ -225,3 +231,20 @@ def test_split_k_meets_in_the_workspace(dtype, prec, tol, monkeypatch):
     assert max_rel_err(out.permute(0, 3, 1, 2), y) < tol
     assert int(ws[:4096].max()) == 0
     _healthy()
+
+
+def test_small_fp32_problems_take_the_fma_kernel_by_default(monkeypatch):
+    """Below 2^25 multiply-adds the tensor-core kernel's fixed cost loses: the call is served with plain fp32 FMAs, so its
+    result carries no TF32 rounding at all, whatever precision was asked for."""
+    monkeypatch.delenv("LLC_TC_MIN_MACS_LOG2")
+    torch.manual_seed(0)
+    a, b = torch.randn(1, 1, 32, 512, device="cuda"), torch.randn(1, 1, 1000, 512, device="cuda")
+    want = (a.double() @ b.double().transpose(2, 3)).float()
+    out = torch.empty(1, 1, 32, 1000, device="cuda")
+    G.gemm(a, b.transpose(2, 3), out, prec="tf32")
+    torch.cuda.synchronize()
+    assert max_rel_err(out, want) < 2e-6                  # a single-pass TF32 product of K=512 is off by about 1e-4
+    monkeypatch.setenv("LLC_TC_MIN_MACS_LOG2", "18")
+    G.gemm(a, b.transpose(2, 3), out, prec="tf32")
+    torch.cuda.synchronize()
+    assert 2e-6 < max_rel_err(out, want) < 2e-3

@@ -262,3 +262,14 @@ def test_repeated_device_calls_replay_a_graph_with_identical_results(name, preci
         for _ in range(4):
             out2 = fn(*args)
         assert max_rel_err(out2, want2) < tol
+
+
+def test_mlp_fp32_on_tensor_cores_tf32x3():
+    m = build_model("mlp")
+    for batch in (64, 1000):
+        x = CONFIGS["mlp"].make_inputs(batch=batch)[0]
+        with torch.no_grad():
+            want = m(x)
+        comp, fn, out = _gpu_run(m, (x,), dynamic=True, precision="tf32x3")
+        assert max_rel_err(out, want) < 1e-4
+        assert comp.compiled[0].engine.executor.last_launch_count() == 2
