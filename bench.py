@@ -1,18 +1,20 @@
 #!/usr/bin/env python
 """Benchmark of the compiled-model inference path.
 
-  python bench.py --gpus N --steps K --warmup W [--config resnet18] [--impl reference]
+  python bench.py --gpus N --steps K --warmup W [--config bert] [--impl reference]
 
-A step is one forward of the configured model over one batch of seeded synthetic input.  At
-N > 1 (one rank per GPU, launched with torch.distributed.run) every rank runs its own batch
-shard with replicated weights and the outputs are all-gathered over NCCL inside the timed step
-(weak scaling: the per-GPU batch is fixed).  The line printed by rank 0 carries:
+A step is one forward of the configured model over one GLOBAL batch of seeded synthetic input.  The default workload
+is the largest single-GPU configuration, BERT-base x12 bf16 on ids[256,384].  At N > 1 (one rank per GPU, launched with
+torch.distributed.run) the global batch is split evenly over the ranks (strong scaling: 256 -> 256/N per GPU) by
+llcompiler_b200.executor.BatchShardedRunner: weights replicated, every rank runs its slice, the outputs are
+all-gathered over NCCL inside the timed step.  The line printed by rank 0 carries:
   value      samples/s with inputs resident in HBM, device-timed with CUDA events, max over ranks
-  e2e        the same metric through Torch_ExecutionEngine.run with pinned HOST tensors, the
-             host->device and device->host copies inside the timed region
-  roofline   the dominant kernel (convolution / GEMM): algorithmic FLOPs / event-timed duration
-  cpu_baseline  the CPU oracle (PyTorch CPU eager fp32, what the reference pins itself to) on a
-             bounded sample of the same workload, on this box's host cores
+  e2e        the same metric with page-locked HOST tensors in and out, the host->device and device->host copies
+             inside the timed region (N = 1: Torch_ExecutionEngine.run on host tensors, i.e. the C ABI's host path;
+             N > 1: the sharded runner's host path, every rank uploads its slice, rank 0 reads the gathered batch back)
+  roofline   the dominant kernel family (GEMM / convolution): algorithmic FLOPs / CUDA-event duration of its launches
+  cpu_baseline  the CPU oracle (PyTorch CPU eager fp32, what the reference pins itself to) on a bounded sample of
+             the same workload, on this box's host cores; N = 1 only
 `--impl reference` times that CPU path alone with all host threads.
 """
 from __future__ import annotations
@@ -32,7 +34,7 @@ if ROOT not in sys.path:
 import torch  # noqa: E402
 
 WORKLOADS = {
-    # name: (oracle config, per-GPU batch, extra make_inputs kwargs, dtype label, precision option)
+    # name: (oracle config, global batch, extra make_inputs kwargs, dtype label, precision option)
     "mlp": ("mlp", 64, {}, "f32", "auto"),
     "resnet18": ("resnet18", 32, {}, "f32", "tf32x3"),      # fp32 storage, three-pass TF32 on tensor cores (1e-4)
     "encoder128": ("encoder", 8, {"seq": 128}, "f32", "tf32"),  # the configuration names TF32 matmuls (2e-2)
@@ -40,6 +42,7 @@ WORKLOADS = {
     "resnet50": ("resnet50", 256, {}, "bf16", "auto"),
     "bert": ("bert", 256, {}, "bf16", "auto"),
 }
+DEFAULT_WORKLOAD = "bert"      # the largest configuration that fits one GPU
 DESCRIPTION = {
     "resnet18": "ResNet-18 fp32 NCHW [32,3,224,224] (configs[1])",
     "mlp": "MLP 784-512-10 fp32 B=64 (configs[0])",
@@ -53,6 +56,13 @@ DESCRIPTION = {
 # DRAM bytes per launch of the dominant kernel family (dram__bytes_read.sum + dram__bytes_write.sum averaged over the
 # launches of one forward), from an ncu capture of this command (20 tensor-core launches of one forward).
 NCU_TRAFFIC = {("resnet18", "conv", 32): 23.0e6}
+
+
+def config_dict(name: str, batch: int, world: int, prec: str) -> dict:
+    """The `config` object of the JSON line; both arms print the same one."""
+    return {"workload": DESCRIPTION[name], "global_batch": batch, "per_gpu_batch": batch // world,
+            "parallelism": f"batch split over {world} GPU(s), weights replicated, outputs all-gathered",
+            "l2": "flushed between timed iterations (256 MB write)", "precision": prec}
 # Share of the measured bf16 peak a precision can reach at best: tf32 MMAs run at half the bf16 rate, tf32x3 issues
 # three of them per algorithmic multiply-add.
 PRECISION_CEILING = {"bf16": 1.0, "auto": 1.0, "tf32": 0.5, "tf32x3": 1.0 / 6.0, "fp32": None}
@@ -135,7 +145,7 @@ def cpu_oracle_rate(model, inputs, batch: int, budget_s: float, threads: int, sa
 def run_reference(args, rank: int, world: int):
     if rank != 0:
         return
-    oname, batch, kw, dtype, _ = WORKLOADS[args.config]
+    oname, batch, kw, dtype, prec = WORKLOADS[args.config]
     cfg, model, inputs = build_workload(oname, batch, kw)
     threads = os.cpu_count() or 1
     sample_batch = min(batch, 8 if oname in ("resnet50", "bert") else batch)
@@ -156,9 +166,9 @@ def run_reference(args, rank: int, world: int):
     sample = f"{args.steps} forwards of a {sample_batch}-sample slice of the batch, PyTorch CPU eager fp32 (the reference's own parity pin; its CPU lowering cannot be built offline)"
     line = {
         "impl": "reference", "metric": "inferences_per_sec", "value": value, "unit": "samples/s", "n_gpus": args.gpus,
-        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps * (batch / sample_batch),
-        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-        "config": {"workload": DESCRIPTION[args.config], "per_gpu_batch": batch},
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": 1e3 * total / args.steps,      # one step = one forward of the sample, see cpu_baseline.sample
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "f32", "data": "synthetic",
+        "config": config_dict(args.config, batch, max(args.gpus, 1), args.precision or prec),
         "cpu_baseline": {"value": value, "unit": "samples/s", "cores": threads, "kind": "port", "sample": sample},
         "e2e": {"value": value, "unit": "samples/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -172,7 +182,7 @@ def main():
     ap.add_argument("--steps", type=int, default=20)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours")
-    ap.add_argument("--config", default="resnet18", choices=sorted(WORKLOADS))
+    ap.add_argument("--config", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--precision", default=None)
     ap.add_argument("--steps-out", default=None, help="write the per-plan-step CUDA-event table here")
@@ -189,47 +199,42 @@ def main():
     if rank == 0:
         build()
     import torch.distributed as dist
+    dev = torch.device("cuda", local if world > 1 else 0)
+    torch.cuda.set_device(dev)
     if world > 1:
-        torch.cuda.set_device(local)
-        dist.init_process_group("nccl", device_id=torch.device("cuda", local))
+        dist.init_process_group("nccl", device_id=dev)
         dist.barrier()
-    else:
-        torch.cuda.set_device(0)
     from llcompiler_b200.compiler import LLCompiler
+    from llcompiler_b200.executor import BatchShardedRunner, shard_bounds
 
     oname, batch, kw, dtype, prec = WORKLOADS[args.config]
     prec = args.precision or prec
+    if batch % world:
+        raise SystemExit(f"the global batch of {batch} does not split evenly over {world} GPUs")
     cfg, model, inputs = build_workload(oname, batch, kw)
-    dev = torch.device("cuda", local if world > 1 else 0)
+    lo, hi = shard_bounds(batch, world, rank)
     import copy
     gmodel = copy.deepcopy(model)
     if dtype == "bf16":
         gmodel = gmodel.to(torch.bfloat16)
     gmodel = gmodel.to(dev)
     cast = (lambda t: t.to(torch.bfloat16)) if dtype == "bf16" else (lambda t: t)
-    host_inputs = tuple((cast(i) if i.is_floating_point() else i).contiguous().pin_memory() for i in inputs)
+    host_inputs = tuple((cast(i) if i.is_floating_point() else i).contiguous().pin_memory() for i in inputs)   # the global batch
     dev_inputs = tuple(i.to(dev) for i in host_inputs)
 
     comp = LLCompiler(precision=prec, device=dev.index)
     torch._dynamo.reset()
     fn = torch.compile(gmodel, backend=comp, dynamic=False, fullgraph=True)
     with torch.no_grad():
-        out = fn(*dev_inputs)
+        out = fn(*(i[lo:hi] for i in dev_inputs))          # compiled for this rank's slice
     torch.cuda.synchronize()
     eng = comp.compiled[0].engine
     launches_per_step = eng.executor.last_launch_count()
-
-    gathered = torch.empty((world,) + tuple(out.shape), dtype=out.dtype, device=dev) if world > 1 else None
+    runner = BatchShardedRunner(lambda *a: eng.run(*a), device=dev, host_result_ranks=(0,))
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
 
-    def step():
-        o = eng.run(*dev_inputs)[0]
-        if world > 1:
-            dist.all_gather_into_tensor(gathered, o)
-        return o
-
     for _ in range(args.warmup):                # the executor captures its CUDA graph on the second of these calls
-        step()
+        full = runner(*dev_inputs)
     torch.cuda.synchronize()
     if world > 1:
         dist.barrier()
@@ -240,28 +245,33 @@ def main():
         for i in range(args.steps):
             flush.zero_()                       # evict L2 between timed iterations (outside the timed span)
             starts[i].record()
-            step()
+            full = runner(*dev_inputs)          # this rank's slice + the all-gather of every rank's outputs
             ends[i].record()
         torch.cuda.synchronize()
         if world > 1:
             dist.barrier()
         total_ms = sum(s.elapsed_time(e) for s, e in zip(starts, ends))
-        # end to end: pinned host inputs, host outputs, copies inside the timed region
+        # end to end: page-locked host inputs, host outputs, copies inside the timed region
         for _ in range(2):
-            eng.run(*host_inputs)
+            runner(*host_inputs)
         torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
         t0 = time.perf_counter()
         for _ in range(args.steps):
-            o_host = eng.run(*host_inputs)[0]
+            o_host = runner(*host_inputs)
         torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
+    eng.status()                                # raises if any kernel of the run reported a failure
+    assert tuple(full.shape)[0] == batch and not o_host.is_cuda
     t = torch.tensor([total_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     total_ms, e2e_ms = float(t[0]), float(t[1])
 
     # dominant kernel: event-timed per kernel family over a profiled pass (events around every launch)
-    prof = eng.profile(*dev_inputs, reps=5)
+    local_dev_inputs = tuple(i[lo:hi] for i in dev_inputs)
+    prof = eng.profile(*local_dev_inputs, reps=5)
     if args.steps_out and rank == 0:
         with open(args.steps_out, "w") as f:
             f.write("# step kernel ms GFLOP MB  TFLOP/s GB/s\n")
@@ -271,37 +281,44 @@ def main():
     roof = None
     pk = peaks()
     if prof:
+        pass_ms = max(sum(r["ms"] for r in prof), 1e-9)
         top = max(prof, key=lambda r: r["ms"])
-        if top["flops"] > 0 and top["kernel"] in ("conv", "gemm"):
+        common = {"kernel": top["kernel"], "peak_source": pk["source"], "launches": top["launches"],
+                  "ms_per_launch": top["ms"] / max(top["launches"], 1),
+                  # both figures come from the same pass: events around every launch of one forward, 5 repetitions
+                  "share_of_profiled_pass": top["ms"] / pass_ms, "profiled_pass_ms": pass_ms,
+                  "traffic": NCU_TRAFFIC.get((args.config, top["kernel"], batch // world))}
+        if top["flops"] > 0 and top["kernel"] in ("conv", "gemm", "attention"):
             achieved = top["flops"] / (top["ms"] * 1e-3) / 1e12
-            roof = {"bound": "tensor", "kernel": top["kernel"], "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s",
-                    "frac": achieved / pk["tflops"], "traffic": NCU_TRAFFIC.get((args.config, top["kernel"], batch)),
-                    "peak_source": pk["source"], "launches": top["launches"],
-                    "share_of_step": top["ms"] / max(sum(r["ms"] for r in prof), 1e-9),
-                    "precision_ceiling_frac": PRECISION_CEILING.get(prec)}
+            roof = {"bound": "tensor", "achieved": achieved, "peak": pk["tflops"], "unit": "TFLOP/s", "frac": achieved / pk["tflops"],
+                    "frac_of_sustained_peak": achieved / pk["tflops_sustained"] if pk.get("tflops_sustained") else None,
+                    "precision_ceiling_frac": PRECISION_CEILING.get(prec), **common}
         else:
             achieved = top["bytes"] / (top["ms"] * 1e-3) / 1e9
-            roof = {"bound": "hbm", "kernel": top["kernel"], "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s",
-                    "frac": achieved / pk["hbm_gbs"], "traffic": None, "peak_source": pk["source"], "launches": top["launches"],
-                    "share_of_step": top["ms"] / max(sum(r["ms"] for r in prof), 1e-9)}
+            roof = {"bound": "hbm", "achieved": achieved, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": achieved / pk["hbm_gbs"], **common}
+        roof["families"] = {r["kernel"]: {"launches": r["launches"], "ms": round(r["ms"], 4),
+                                          "tflops": round(r["flops"] / max(r["ms"], 1e-9) / 1e9, 1), "gbs": round(r["bytes"] / max(r["ms"], 1e-9) / 1e6, 1)}
+                            for r in prof}
 
     if rank == 0:
-        cpu_val, cpu_n, cpu_dt = cpu_oracle_rate(model, inputs, batch, args.cpu_budget, os.cpu_count() or 1,
-                                                 2 if oname == "bert" else (8 if oname == "resnet50" else batch))
-        h2d = sum(i.numel() * i.element_size() for i in host_inputs)
-        d2h = out.numel() * out.element_size()
+        cpu = None
+        if world == 1:          # the other ranks of a multi-GPU run would spin in a barrier meanwhile: N = 1 only
+            cpu_val, cpu_n, cpu_dt = cpu_oracle_rate(model, inputs, batch, args.cpu_budget, os.cpu_count() or 1,
+                                                     2 if oname == "bert" else (8 if oname == "resnet50" else batch))
+            cpu = {"value": cpu_val, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "port",
+                   "sample": f"{cpu_n} forwards in {cpu_dt:.1f} s, PyTorch CPU eager fp32 (CPU oracle)"}
+        h2d = sum(i.numel() * i.element_size() for i in host_inputs)           # every rank uploads its slice: the whole batch
+        d2h = full.numel() * full.element_size()                               # rank 0 reads the gathered batch back
         line = {
-            "metric": "inferences_per_sec", "value": batch * world * args.steps / (total_ms * 1e-3), "unit": "samples/s",
+            "metric": "inferences_per_sec", "value": batch * args.steps / (total_ms * 1e-3), "unit": "samples/s",
             "n_gpus": world, "steps": args.steps, "warmup": args.warmup, "ms_per_step": total_ms / args.steps,
-            "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
-            "config": {"workload": DESCRIPTION[args.config], "per_gpu_batch": batch, "parallelism": f"batch-sharded x{world}",
-                       "l2": "flushed between timed iterations (256 MB write)", "precision": prec},
+            "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
+            "config": config_dict(args.config, batch, world, prec),
             "clocks": clocks.summary(),
-            "e2e": {"value": batch * world * args.steps / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": {"value": batch * args.steps / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
             "gpu_launches": int(launches_per_step * args.steps),
             "roofline": roof,
-            "cpu_baseline": {"value": cpu_val, "unit": "samples/s", "cores": os.cpu_count() or 1, "kind": "port",
-                             "sample": f"{cpu_n} forwards in {cpu_dt:.1f} s, PyTorch CPU eager fp32 (CPU oracle)"},
+            "cpu_baseline": cpu,
         }
         print(json.dumps(line), flush=True)
     if world > 1:

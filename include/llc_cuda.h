@@ -57,7 +57,7 @@ int llc_cuda_gemm(const LlcGemmParams* p, void* stream);
  * is ignored.  A shape whose split needs more than 1 MiB is refused with LLC_ERR_ARGUMENT.  The
  * first call on a device looks up the array's device address (cudaGetSymbolAddress); make that
  * first call before starting any stream capture.  All calls share the one array: launches that
- * overlap on the GPU (different streams, threads or processes' contexts on one device) race.
+ * overlap on the GPU (different streams or threads of one process on one device) race.
  * Calls no cudaMalloc / cudaFree. */
 int llc_cuda_gemm_static_scratch(const LlcGemmParams* p, void* stream);
 

@@ -102,6 +102,20 @@ int llc_output_shape(LlcExec* exec, const int64_t* symbols, int n_symbols, const
 int llc_run(LlcExec* exec, const int64_t* symbols, int n_symbols, const LlcTensor* inputs, int n_inputs,
             LlcTensor* outputs, int n_outputs, void* stream);
 
+/* Reads and clears the failure words the kernels of this executor's device write when they cannot raise an error
+ * themselves: a bounded wait of a tensor-core kernel that gave up (words[0] GEMM / convolution, words[1] attention; see
+ * llc_cuda_status for the codes) and the number of embedding indices that lay outside their table (words[2]; such rows
+ * are written as zeros).  Returns LLC_OK when all three are zero, LLC_ERR_ARGUMENT for bad indices, LLC_ERR_CUDA for a
+ * wait that gave up.  `words` may be NULL.  Synchronises the device.  llc_run and llc_profile make the same check
+ * themselves whenever they wait for their results (host tensors); a caller that passes device tensors gets control
+ * back before the kernels have run and calls this after its own synchronisation.  The reference has no counterpart: its
+ * CHECK macros log and carry on (include/llcompiler/Support/Logger.h:126-134). */
+int llc_status(LlcExec* exec, int32_t* words);
+
+/* Threading: calls on one LlcExec are serialised by a lock inside it (bindings, arena and staging buffers are shared
+ * state), so two threads may share a handle but do not overlap; different handles are independent.  Every entry point
+ * leaves the calling thread's current CUDA device as it found it. */
+
 /* Same arguments as llc_run; runs the plan `reps` times (after one warm-up pass) with CUDA events
  * around every kernel and writes a text report: one "step <i> <kernel> <ms> <flops> <bytes>" line per
  * plan step and one "kernel <name> <launches> <ms> <flops> <bytes>" line per kernel family (ms and

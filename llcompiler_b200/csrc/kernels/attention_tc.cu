@@ -289,6 +289,11 @@ bool makeHeadMap(CUtensorMap* map, const void* base, long long rows, long long b
 
 }  // namespace
 
+int* attnStatusAddress() {
+  void* p = nullptr;
+  return cudaGetSymbolAddress(&p, g_attnStatus) == cudaSuccess ? static_cast<int*>(p) : nullptr;
+}
+
 // Reads and clears the attention kernel's status word.
 int attnStatus() {
   int v = 0, zero = 0;
@@ -330,15 +335,15 @@ extern "C" int llc_cuda_attention(const LlcAttentionParams* p, void* stream) {
   a.qZ0 = p->b0 > 1 && p->q_s0 > 0; a.qZ1 = p->b1 > 1 && p->q_s1 > 0; a.kZ0 = p->b0 > 1 && p->k_s0 > 0; a.kZ1 = p->b1 > 1 && p->k_s1 > 0;
   a.vZ0 = p->b0 > 1 && p->v_s0 > 0; a.vZ1 = p->b1 > 1 && p->v_s1 > 0;
   a.scaleLog2e = p->scale * kLog2e;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;                          // the shared-memory opt-in is kept per device
+  const int dev = currentDevice();
+  if (!configured.test(dev)) {
     cudaError_t e = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return cudaFail(e, "cudaFuncSetAttribute(attention_kernel)");
-    configured = true;
+    configured.set(dev);
   }
   a.tiles = batch * mTiles;
-  int dev = 0, sms = kNumSMs;
-  if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+  const int sms = deviceSMs();
   const unsigned grid = (unsigned)(a.tiles < sms ? a.tiles : sms);
   attention_kernel<<<grid, kSoftmaxThreads + 32, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, a);
   LLC_LAUNCH_CHECK("attention_kernel");

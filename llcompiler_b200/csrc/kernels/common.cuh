@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <stdint.h>
 
+#include <atomic>
 #include <string>
 
 #include "../../../include/llc_cuda.h"
@@ -26,6 +27,27 @@ inline int cudaFail(cudaError_t e, const char* what) {
     cudaError_t e__ = cudaGetLastError();                          \
     if (e__ != cudaSuccess) return llc::cudaFail(e__, name);       \
   } while (0)
+
+// One-time set-up that CUDA keeps per device (function attributes such as the dynamic shared-memory opt-in): a bit
+// per device ordinal.  Two threads that meet on a fresh device both run the set-up, which is idempotent.
+struct DeviceOnce {
+  std::atomic<unsigned long long> done{0};
+  bool test(int dev) const { return dev >= 0 && dev < 64 && ((done.load(std::memory_order_acquire) >> dev) & 1ull); }
+  void set(int dev) { if (dev >= 0 && dev < 64) done.fetch_or(1ull << dev, std::memory_order_release); }
+};
+inline int currentDevice() { int d = 0; return cudaGetDevice(&d) == cudaSuccess ? d : 0; }
+// SM count of the current device (cached per ordinal).
+inline int deviceSMs() {
+  static std::atomic<int> cache[64];
+  const int dev = currentDevice();
+  if (dev < 0 || dev >= 64) return kNumSMs;
+  int v = cache[dev].load(std::memory_order_relaxed);
+  if (v > 0) return v;
+  v = kNumSMs;
+  if (cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || v <= 0) v = kNumSMs;
+  cache[dev].store(v, std::memory_order_relaxed);
+  return v;
+}
 
 inline int dtypeBytes(int32_t dt) {
   switch (dt) {

@@ -774,10 +774,7 @@ bool makeOutMap(CUtensorMap* map, void* base, bool f32, long long N, long long M
 // Bytes per row of the output box: a 32-column chunk of fp32, or as much of a warp's share of bf16 columns as fits 128 bytes.
 int outBoxBytes(int bn, bool outF32) { return outF32 ? 128 : (bn / 2 >= 64 ? 128 : 64); }
 
-int numSMs() {
-  static int n = []() { int dev = 0, v = kNumSMs; if (cudaGetDevice(&dev) == cudaSuccess) cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev); return v > 0 ? v : kNumSMs; }();
-  return n;
-}
+int numSMs() { return deviceSMs(); }
 
 // LLC_TC_SPLITK=0 keeps every K loop in one piece (2 is accepted and means the default: split wherever SMs would idle).
 int splitKMode() {
@@ -795,11 +792,12 @@ bool tmaEpilogueEnabled() {
 template <int BN, int KIND, int MODE, bool BMN>
 int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mbl, TcArgs a, long long batch, cudaStream_t st) {
   using S = Smem<BN, KIND == 2>;
-  static bool configured = false;
-  if (!configured) {
+  static DeviceOnce configured;                          // the shared-memory opt-in is kept per device
+  const int dev = currentDevice();
+  if (!configured.test(dev)) {
     cudaError_t e = cudaFuncSetAttribute(tc_kernel<BN, KIND, MODE, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return cudaFail(e, "cudaFuncSetAttribute(tc_kernel)");
-    configured = true;
+    configured.set(dev);
   }
   a.mTiles = (int)((a.M + BM - 1) / BM); a.nTiles = (int)((a.N + BN - 1) / BN);
   a.tiles = (long long)a.mTiles * a.nTiles * batch;
@@ -973,6 +971,12 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
   }
   a.splits = 1;                                          // the gathered form walks whole tiles
   return dispatch<1, false>(bn, kind, mb, mb, mo, mbl, a, 1, st);
+}
+
+// Device address of the status word on the current device (for callers that copy it back on their own stream).
+int* tcStatusAddress() {
+  void* p = nullptr;
+  return cudaGetSymbolAddress(&p, g_tcStatus) == cudaSuccess ? static_cast<int*>(p) : nullptr;
 }
 
 // Reads and clears the status word the bounded waits write (0 = no wait ever gave up).

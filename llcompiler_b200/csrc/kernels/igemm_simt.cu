@@ -263,24 +263,37 @@ __global__ void __launch_bounds__(256) igemm_simt_kernel(IgemmArgs p) {
 
 constexpr size_t kCounterBytes = 4096;   // head of the workspace: one counter per output tile
 
+// The split-K decision, in one place for the launcher and for the entry point that has to refuse a shape whose
+// split does not fit its fixed scratch.  Few 64 x 64 output tiles and a long reduction: K is cut over the idle SMs.
+// `split` == 1 means no split; `need` is the scratch a split takes (tile counters + fp32 partial tiles).
+struct SplitKChoice { long long split = 1, kPer = 0; size_t need = 0; };
+SplitKChoice chooseSplitK(long long M, long long N, long long K, long long batch) {
+  SplitKChoice c;
+  const long long t64 = ((M + 63) / 64) * ((N + 63) / 64) * batch;
+  if (t64 <= 0 || t64 * 2 > kNumSMs || K < 512 || t64 > (long long)(kCounterBytes / 4)) return c;
+  long long want = kNumSMs / t64; if (want > 32) want = 32; if (want > K / 128) want = K / 128;
+  if (want < 1) return c;
+  const long long kPer = ((K + want - 1) / want + BK - 1) / BK * BK;
+  const long long split = (K + kPer - 1) / kPer;
+  if (split <= 1 || batch * split > 65535) return c;
+  c.split = split; c.kPer = kPer;
+  c.need = kCounterBytes + (size_t)t64 * split * 64 * 64 * sizeof(float);
+  return c;
+}
+
 template <typename T, bool CONV, bool VEC>
 int launchTiles(IgemmArgs a, long long batch, cudaStream_t st, void* workspace, long long workspaceBytes) {
   auto tiles = [&](long long bm, long long bn) { return ((a.M + bm - 1) / bm) * ((a.N + bn - 1) / bn) * batch; };
   if (a.M <= 0 || a.N <= 0 || batch <= 0) return LLC_OK;
   if (batch > 65535) return setError(LLC_ERR_ARGUMENT, "llc argument: gemm batch count above 65535");
   a.splitK = 1;
-  // few output tiles and a long reduction: split K over the idle SMs (needs caller scratch)
-  const long long t64 = tiles(64, 64);
-  if (workspace && t64 * 2 <= kNumSMs && a.K >= 512 && t64 <= (long long)(kCounterBytes / 4)) {
-    long long want = kNumSMs / t64; if (want > 32) want = 32; if (want > a.K / 128) want = a.K / 128;
-    long long kPer = ((a.K + want - 1) / want + BK - 1) / BK * BK;
-    long long split = (a.K + kPer - 1) / kPer;
-    size_t need = kCounterBytes + (size_t)t64 * split * 64 * 64 * sizeof(float);
-    if (split > 1 && need <= (size_t)workspaceBytes && batch * split <= 65535) {
-      a.splitK = (int)split; a.kPer = kPer;
+  if (workspace) {                      // splitting needs caller scratch
+    const SplitKChoice c = chooseSplitK(a.M, a.N, a.K, batch);
+    if (c.split > 1 && c.need <= (size_t)workspaceBytes) {
+      a.splitK = (int)c.split; a.kPer = c.kPer;
       a.counters = reinterpret_cast<unsigned*>(workspace);
       a.partial = reinterpret_cast<float*>(reinterpret_cast<char*>(workspace) + kCounterBytes);
-      dim3 g((unsigned)((a.M + 63) / 64), (unsigned)((a.N + 63) / 64), (unsigned)(batch * split));
+      dim3 g((unsigned)((a.M + 63) / 64), (unsigned)((a.N + 63) / 64), (unsigned)(batch * c.split));
       igemm_simt_kernel<T, 64, 64, CONV, VEC><<<g, 256, 0, st>>>(a);
       LLC_LAUNCH_CHECK("igemm_simt_kernel(split-K)");
       return LLC_OK;
@@ -394,18 +407,11 @@ extern "C" int llc_cuda_gemm_static_scratch(const LlcGemmParams* p, void* stream
   auto floatIo = [](int32_t dt) { return dt == LLC_FLOAT32 || dt == LLC_BFLOAT16; };
   if (!floatIo(p->in_dtype) || !floatIo(p->out_dtype) || (p->res && !floatIo(p->res_dtype)))
     return setError(LLC_ERR_UNSUPPORTED, "llc argument: gemm operands must be f32 or bf16");
-  // the same split the workspace path would choose; a shape whose split does not fit is refused
-  const long long batch = p->b0 * p->b1;
-  const long long t64 = ((p->m + 63) / 64) * ((p->n + 63) / 64) * batch;
-  if (t64 * 2 <= kNumSMs && p->k >= 512) {
-    long long want = kNumSMs / t64; if (want > 32) want = 32; if (want > p->k / 128) want = p->k / 128;
-    const long long kPer = ((p->k + want - 1) / want + BK - 1) / BK * BK;
-    const long long split = (p->k + kPer - 1) / kPer;
-    const size_t need = kCounterBytes + (size_t)t64 * split * 64 * 64 * sizeof(float);
-    if (split > 1 && need > kStaticScratchBytes)
-      return setError(LLC_ERR_ARGUMENT, "llc argument: this GEMM needs " + std::to_string(need) + " bytes of split-K scratch, the built-in array holds " +
-                                            std::to_string(kStaticScratchBytes));
-  }
+  // the split the launcher would choose with scratch at hand; a shape whose split does not fit is refused
+  const SplitKChoice c = chooseSplitK(p->m, p->n, p->k, p->b0 * p->b1);
+  if (c.split > 1 && c.need > kStaticScratchBytes)
+    return setError(LLC_ERR_ARGUMENT, "llc argument: this GEMM needs " + std::to_string(c.need) + " bytes of split-K scratch, the built-in array holds " +
+                                          std::to_string(kStaticScratchBytes));
   void* scratch = nullptr;
   int rc = staticScratchAddress(&scratch);
   if (rc != LLC_OK) return rc;

@@ -867,6 +867,8 @@ struct Lowering {
     P.step.params.emplace_back("pad", rowMerge ? arr({pad[0], 0, pad[2], 0}) : arr(pad));   // the copy holds the left and right padding
     P.step.params.emplace_back("dil", arr(dil));
     P.step.params.emplace_back("prec", gemmPrecision(x.dtype));
+    // the contraction length of the convolution as written (the views above may carry padded channels or a zero tap)
+    if (Cin.isConst()) P.step.params.emplace_back("kalg", std::to_string(KH * KW * Cin.constant()));
     std::vector<Expr> ost = nhwcStrides(oshape);
     P.nativeOut = freshView(dt, oshape, false, &ost);
     P.buf = P.nativeOut.buf;

@@ -3,6 +3,7 @@
 // (tensor, compiler, executor), same class and method names, same argument order.  A non-zero
 // status from the C ABI becomes a Python RuntimeError (the reference logs and carries on,
 // include/llcompiler/Support/Logger.h:126-134).
+#include <pybind11/numpy.h>
 #include <pybind11/pybind11.h>
 #include <pybind11/stl.h>
 
@@ -36,6 +37,42 @@ struct Tensor {
     py::print(s + "])");
   }
 };
+
+// Element size and struct-module format of a dtype code (the reference's get_itemsize / get_format,
+// src/Pybind/Entrance.cpp:27-58, plus the two 16-bit floats).
+py::ssize_t itemSize(int type) {
+  switch (type) {
+    case LLC_INT8: case LLC_INT1: return 1;
+    case LLC_INT16: case LLC_FLOAT16: case LLC_BFLOAT16: return 2;
+    case LLC_INT32: case LLC_FLOAT32: return 4;
+    default: return 8;
+  }
+}
+std::string formatOf(int type) {
+  switch (type) {
+    case LLC_INT8: return "b"; case LLC_INT1: return "?"; case LLC_INT16: return "h"; case LLC_INT32: return "i"; case LLC_INT64: return "q";
+    case LLC_FLOAT32: return "f"; case LLC_FLOAT64: return "d"; case LLC_FLOAT16: return "e";
+    case LLC_BFLOAT16: return "H";      // no struct code for bf16: exposed as its 16-bit pattern
+  }
+  throw std::runtime_error("Tensor: unknown element type code " + std::to_string(type));
+}
+// Buffer view of a HOST tensor (the reference's tensors are always host memory, src/Pybind/Entrance.cpp:80-91);
+// device memory cannot be read through the buffer protocol.
+py::buffer_info bufferOf(Tensor& t) {
+  if (t.device >= 0) throw std::runtime_error("Tensor: device memory has no buffer view; copy the torch tensor to the host first");
+  std::vector<py::ssize_t> shape(t.size.begin(), t.size.end()), strides;
+  for (auto s : t.stride) strides.push_back((py::ssize_t)s * itemSize(t.type));
+  return py::buffer_info(reinterpret_cast<void*>(t.data), itemSize(t.type), formatOf(t.type), (py::ssize_t)shape.size(), shape, strides);
+}
+
+// The reference's executor.get_tool (src/Compiler/Command.cpp:13-15 over ToolPath.h.in:19-24) names the external
+// programs its pipeline shells out to.  This backend runs no subprocess: "llc-opt" is the text-IR driver module, "cxx"
+// the host compiler the build used; the LLVM tools have no counterpart and raise, as an unknown name does there.
+std::string getTool(const std::string& name) {
+  if (name == "llc-opt") return "python -m llcompiler_b200.llc_opt";
+  if (name == "cxx") return "g++";
+  throw py::index_error("no tool '" + name + "': the CUDA pipeline runs in-process and has no LLVM tool chain (opt, llc, llc-translate)");
+}
 
 // llc::compiler::CompileOptions (include/llcompiler/Compiler/CompileOption.h:39-71)
 struct CompileOptions {
@@ -105,6 +142,18 @@ struct Execution {
     report.resize(strlen(report.c_str()));
     return report;
   }
+  // Raises when a kernel of an earlier call recorded a failure (see llc_status); returns the three words otherwise.
+  std::vector<int> status() {
+    need();
+    int32_t w[3] = {0, 0, 0};
+    int rc;
+    {
+      py::gil_scoped_release release;
+      rc = llc_status(exec, w);
+    }
+    check(rc);
+    return {w[0], w[1], w[2]};
+  }
   int num_inputs() const { need(); return llc_num_inputs(exec); }
   int num_outputs() const { need(); return llc_num_outputs(exec); }
   int num_symbols() const { need(); return llc_num_symbols(exec); }
@@ -117,8 +166,10 @@ struct Execution {
 PYBIND11_MODULE(llcompiler_, m) {
   m.doc() = "B200 execution backend with the llcompiler_ module surface";
   auto tensor = m.def_submodule("tensor");
-  py::class_<Tensor>(tensor, "Tensor")
+  py::class_<Tensor>(tensor, "Tensor", py::buffer_protocol())
       .def(py::init<>())
+      .def_buffer(&bufferOf)
+      .def("to_numpy", [](Tensor& t) { return py::array(bufferOf(t)); })
       .def(py::init<uintptr_t, uintptr_t, int, int64_t, std::vector<int64_t>, std::vector<int64_t>, int>(), py::arg("data_ptr"), py::arg("base_ptr"),
            py::arg("type"), py::arg("offset"), py::arg("size"), py::arg("stride"), py::arg("device") = -1)
       .def_readwrite("data", &Tensor::data).def_readwrite("base", &Tensor::base).def_readwrite("offset", &Tensor::offset)
@@ -149,6 +200,7 @@ PYBIND11_MODULE(llcompiler_, m) {
       .def("display_mlir_passes", [](CompileOptions& o, bool v) { o.mlir_passes = v; });
 
   auto executor = m.def_submodule("executor");
+  executor.def("get_tool", &getTool);
   py::class_<Execution>(executor, "Execution")
       .def(py::init<>())
       .def("load", &Execution::load, py::arg("path"), py::arg("device") = 0)
@@ -156,6 +208,7 @@ PYBIND11_MODULE(llcompiler_, m) {
       .def("run_with_symbols", &Execution::run_with_symbols, py::arg("symbols"), py::arg("inputs"), py::arg("outs"), py::arg("stream") = 0)
       .def("output_shapes", &Execution::output_shapes)
       .def("profile", &Execution::profile, py::arg("symbols"), py::arg("inputs"), py::arg("outs"), py::arg("reps") = 5, py::arg("stream") = 0)
+      .def("status", &Execution::status)
       .def("num_inputs", &Execution::num_inputs).def("num_outputs", &Execution::num_outputs).def("num_symbols", &Execution::num_symbols)
       .def("last_launch_count", &Execution::last_launch_count).def("arena_bytes", &Execution::arena_bytes);
   m.def("version", []() { return std::string(llc_version()); });

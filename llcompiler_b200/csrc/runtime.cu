@@ -14,6 +14,7 @@
 #include <fstream>
 #include <map>
 #include <memory>
+#include <mutex>
 #include <sstream>
 
 #include "../../include/llc_cuda.h"
@@ -23,7 +24,20 @@
 
 namespace llc {
 
+int* tcStatusAddress();     // device addresses of the status words the bounded waits of the tensor-core kernels write
+int* attnStatusAddress();
+
 namespace {
+
+// Makes `device` current for the duration of a call and puts the caller's device back afterwards.
+struct DeviceGuard {
+  int prev = -1; bool switched = false;
+  explicit DeviceGuard(int device) {
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
+    if (prev != device) { if (cudaSetDevice(device) != cudaSuccess) throw std::runtime_error("llc cuda: cudaSetDevice failed"); switched = true; }
+  }
+  ~DeviceGuard() { if (switched && prev >= 0) cudaSetDevice(prev); }
+};
 
 [[noreturn]] void failArg(const std::string& m) { throw std::runtime_error("llc argument: " + m); }
 [[noreturn]] void failIo(const std::string& m) { throw std::runtime_error("llc io: " + m); }
@@ -143,6 +157,10 @@ struct LlcExec {
   char* stageIn = nullptr; size_t stageInCap = 0;
   char* stageOut = nullptr; size_t stageOutCap = 0;
   int* badIds = nullptr;
+  int* tcWord = nullptr; int* attnWord = nullptr;   // device addresses of the kernels' status words on `device`
+  int* hostStatus = nullptr;                  // page-locked mirror: [tensor-core word, attention word, bad embedding ids]
+  bool usesTc = false, usesGather = false;    // which of the words this plan's kernels can write
+  std::mutex mutex;                           // one call at a time per executor (bindings, arena and staging are shared state)
   char* workspace = nullptr;                  // split-K scratch (counters at the head stay zero between launches)
   static constexpr size_t kWorkspaceBytes = 16u << 20;
   cudaStream_t capStream = nullptr;         // capture happens here, so that the legacy default stream can replay too
@@ -151,15 +169,19 @@ struct LlcExec {
   std::vector<char*> base;                    // per-buffer device base pointers for the current call
 
   ~LlcExec() {
+    int prev = -1;
+    if (cudaGetDevice(&prev) != cudaSuccess) prev = -1;
     cudaSetDevice(device);
     if (staticPool) cudaFree(staticPool);
     if (arena) cudaFree(arena);
     if (stageIn) cudaFree(stageIn);
     if (stageOut) cudaFree(stageOut);
     if (badIds) cudaFree(badIds);
+    if (hostStatus) cudaFreeHost(hostStatus);
     if (workspace) cudaFree(workspace);
     bindings.clear();                       // graph executables go before the stream they were captured on
     if (capStream) cudaStreamDestroy(capStream);
+    if (prev >= 0 && prev != device) cudaSetDevice(prev);
   }
 
   RView resolve(const View& v, const std::map<std::string, int64_t>& env) const {
@@ -174,6 +196,8 @@ struct LlcExec {
   void prepare(RStep& rs);
   int launch(RStep& rs, cudaStream_t st);
   Binding& bind(const int64_t* symbols, int nsym, const LlcTensor* in, int nin);
+  void queueStatusRead(cudaStream_t st);
+  void raiseOnStatus(cudaStream_t st);
   void runSteps(std::vector<std::unique_ptr<RStep>>& steps, cudaStream_t st);
 };
 
@@ -344,6 +368,30 @@ void LlcExec::runSteps(std::vector<std::unique_ptr<RStep>>& steps, cudaStream_t 
   }
 }
 
+// The kernels report failures they cannot raise themselves through three device words: the tensor-core GEMM /
+// convolution and the attention kernel record a bounded wait that gave up, the embedding gather counts ids outside
+// its table (those rows are written as zeros).  queueStatusRead copies the words this plan can write into page-locked
+// host memory behind the work already on `st`; raiseOnStatus, called once the stream has been synchronised, clears
+// whatever is set and throws, so a broken launch or a bad id is an error of the call instead of a wrong result.
+void LlcExec::queueStatusRead(cudaStream_t st) {
+  hostStatus[0] = hostStatus[1] = hostStatus[2] = 0;
+  if (usesTc && tcWord) cudaOk(cudaMemcpyAsync(&hostStatus[0], tcWord, sizeof(int), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(status)");
+  if (usesTc && attnWord) cudaOk(cudaMemcpyAsync(&hostStatus[1], attnWord, sizeof(int), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(status)");
+  if (usesGather) cudaOk(cudaMemcpyAsync(&hostStatus[2], badIds, sizeof(int), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(status)");
+}
+void LlcExec::raiseOnStatus(cudaStream_t st) {
+  const int tc = hostStatus[0], at = hostStatus[1], bad = hostStatus[2];
+  if (!tc && !at && !bad) return;
+  if (tc) cudaMemsetAsync(tcWord, 0, sizeof(int), st);
+  if (at) cudaMemsetAsync(attnWord, 0, sizeof(int), st);
+  if (bad) cudaMemsetAsync(badIds, 0, sizeof(int), st);
+  cudaStreamSynchronize(st);
+  hostStatus[0] = hostStatus[1] = hostStatus[2] = 0;
+  if (bad) failArg(std::to_string(bad) + " embedding indices lie outside their table (those rows were written as zeros)");
+  throw std::runtime_error("llc cuda: a tensor-core kernel gave up on a bounded wait (status " + std::to_string(tc ? tc : at) +
+                           (tc ? ", GEMM / convolution" : ", attention") + "); the results of this call are invalid");
+}
+
 Binding& LlcExec::bind(const int64_t* symbols, int nsym, const LlcTensor* in, int nin) {
   if (nin != (int)plan.inputs.size()) failArg("expected " + std::to_string(plan.inputs.size()) + " input tensors, got " + std::to_string(nin));
   if (nsym != plan.numSymbolArgs && nsym != 0) failArg("expected " + std::to_string(plan.numSymbolArgs) + " symbol values, got " + std::to_string(nsym));
@@ -429,7 +477,7 @@ extern "C" int llc_load(const char* path, int device, LlcExec** out) {
     if (e != cudaSuccess || count == 0) throw std::runtime_error("llc cuda: no CUDA device is available (the B200 backend has no CPU fallback)");
     if (device < 0 || device >= count) failArg("device ordinal " + std::to_string(device) + " out of range");
     ex->device = device;
-    cudaOk(cudaSetDevice(device), "cudaSetDevice");
+    DeviceGuard guard(device);
     size_t nb = ex->plan.buffers.size();
     ex->staticOffset.assign(nb, 0);
     ex->base.assign(nb, nullptr);
@@ -445,6 +493,12 @@ extern "C" int llc_load(const char* path, int device, LlcExec** out) {
     cudaOk(cudaMalloc(&ex->staticPool, std::max<size_t>(total, 256)), "cudaMalloc(weights)");
     cudaOk(cudaMalloc(&ex->badIds, sizeof(int)), "cudaMalloc(status)");
     cudaOk(cudaMemset(ex->badIds, 0, sizeof(int)), "cudaMemset(status)");
+    cudaOk(cudaHostAlloc(reinterpret_cast<void**>(&ex->hostStatus), 4 * sizeof(int), cudaHostAllocDefault), "cudaHostAlloc(status)");
+    ex->tcWord = tcStatusAddress(); ex->attnWord = attnStatusAddress();
+    for (auto& s : ex->plan.steps) {
+      if (s.kernel == "gemm" || s.kernel == "conv" || s.kernel == "attention") ex->usesTc = true;
+      if (s.kernel == "gather") ex->usesGather = true;
+    }
     cudaOk(cudaMalloc(&ex->workspace, LlcExec::kWorkspaceBytes), "cudaMalloc(workspace)");
     cudaOk(cudaMemset(ex->workspace, 0, 4096), "cudaMemset(workspace)");
     for (size_t i = 0; i < nb; ++i) {
@@ -481,7 +535,9 @@ extern "C" int llc_load(const char* path, int device, LlcExec** out) {
       init.push_back(std::move(rs));
     }
     ex->runSteps(init, 0);
+    ex->queueStatusRead(0);
     cudaOk(cudaDeviceSynchronize(), "load-time kernels");
+    ex->raiseOnStatus(0);
     ex->lastLaunches = 0;
     *out = ex.release();
     return LLC_OK;
@@ -498,6 +554,7 @@ extern "C" void llc_free(LlcExec* e) { delete e; }
 extern "C" int llc_output_shape(LlcExec* ex, const int64_t* symbols, int nsym, const LlcTensor* in, int nin, int index, int64_t* sizes, int32_t* rank, int32_t* dtype) {
   if (!ex || !sizes || !rank) return setError(LLC_ERR_ARGUMENT, "null argument");
   try {
+    std::lock_guard<std::mutex> lock(ex->mutex);
     Binding& b = ex->bind(symbols, nsym, in, nin);
     if (index < 0 || index >= (int)b.outShapes.size()) failArg("output index out of range");
     auto& s = b.outShapes[index];
@@ -512,7 +569,6 @@ extern "C" int llc_output_shape(LlcExec* ex, const int64_t* symbols, int nsym, c
 // Binds symbols, sizes the arena, points every input/output buffer at caller memory (staging host
 // tensors through the device) and returns the binding to launch.
 static Binding& prepareCall(LlcExec* ex, const int64_t* symbols, int nsym, const LlcTensor* in, int nin, LlcTensor* outs, int nout, cudaStream_t st, bool& anyHostOut) {
-  cudaOk(cudaSetDevice(ex->device), "cudaSetDevice");
   Binding& b = ex->bind(symbols, nsym, in, nin);
   if (nout != (int)ex->plan.outputs.size()) failArg("expected " + std::to_string(ex->plan.outputs.size()) + " output tensors, got " + std::to_string(nout));
   if (b.arenaBytes > ex->arenaCap) {
@@ -572,7 +628,9 @@ static void finishCall(LlcExec* ex, Binding& b, LlcTensor* outs, int nout, cudaS
     int buf = ex->plan.outputs[k].buf;
     if (outs[k].device < 0 && b.bufBytes[buf]) cudaOk(cudaMemcpyAsync(outs[k].data, ex->base[buf], b.bufBytes[buf], cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(D2H)");
   }
+  ex->queueStatusRead(st);                    // the call waits for its results anyway: look at the failure words too
   cudaOk(cudaStreamSynchronize(st), "cudaStreamSynchronize");
+  ex->raiseOnStatus(st);
 }
 
 // Replays (or, on the second call with the same pointers, captures) the binding's steps as one CUDA graph.  Only for calls whose
@@ -629,10 +687,26 @@ extern "C" int llc_run(LlcExec* ex, const int64_t* symbols, int nsym, const LlcT
   try {
     cudaStream_t st = (cudaStream_t)stream;
     bool anyHostOut = false;
+    std::lock_guard<std::mutex> lock(ex->mutex);
+    DeviceGuard guard(ex->device);
     Binding& b = prepareCall(ex, symbols, nsym, in, nin, outs, nout, st, anyHostOut);
     ex->lastLaunches = 0;
     if (!runThroughGraph(ex, b, in, nin, outs, nout, st)) ex->runSteps(b.steps, st);
     finishCall(ex, b, outs, nout, st, anyHostOut);
+    return LLC_OK;
+  } catch (const std::exception& e) { return setError(statusFor(e), e.what()); }
+}
+
+extern "C" int llc_status(LlcExec* ex, int32_t* words) {
+  if (!ex) return setError(LLC_ERR_ARGUMENT, "null argument");
+  try {
+    std::lock_guard<std::mutex> lock(ex->mutex);
+    DeviceGuard guard(ex->device);
+    cudaOk(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
+    ex->queueStatusRead(0);
+    cudaOk(cudaStreamSynchronize(0), "cudaStreamSynchronize");
+    if (words) { words[0] = ex->hostStatus[0]; words[1] = ex->hostStatus[1]; words[2] = ex->hostStatus[2]; }
+    ex->raiseOnStatus(0);
     return LLC_OK;
   } catch (const std::exception& e) { return setError(statusFor(e), e.what()); }
 }
@@ -650,7 +724,13 @@ static void stepWork(const RStep& rs, double& flops, double& bytes) {
   const std::string& k = rs.step->kernel;
   if (k == "gemm") { const RView* a = rs.view("a"); const RView* o = rs.view("out"); flops = 2.0 * o->shape[0] * o->shape[1] * o->shape[2] * o->shape[3] * a->shape[3]; }
   if (k == "attention") { const RView* kk = rs.view("k"); const RView* o = rs.view("out"); flops = 4.0 * o->shape[0] * o->shape[1] * o->shape[2] * o->shape[3] * kk->shape[3]; }
-  if (k == "conv") { const RView* w = rs.view("w"); const RView* o = rs.view("out"); flops = 2.0 * o->shape[0] * o->shape[2] * o->shape[3] * w->shape[0] * w->shape[1] * w->shape[2] * w->shape[3]; }
+  if (k == "conv") {
+    // the contraction length as the model wrote it ("kalg"), not the packed weight view, which may hold padded channels
+    const RView* w = rs.view("w"); const RView* o = rs.view("out");
+    const std::string kalg = rs.step->param("kalg", "");
+    const double kLen = kalg.empty() ? (double)w->shape[1] * w->shape[2] * w->shape[3] : std::stod(kalg);
+    flops = 2.0 * o->shape[0] * o->shape[2] * o->shape[3] * w->shape[0] * kLen;
+  }
 }
 
 extern "C" int llc_profile(LlcExec* ex, const int64_t* symbols, int nsym, const LlcTensor* in, int nin, LlcTensor* outs, int nout, int reps, void* stream,
@@ -659,6 +739,8 @@ extern "C" int llc_profile(LlcExec* ex, const int64_t* symbols, int nsym, const 
   try {
     cudaStream_t st = (cudaStream_t)stream;
     bool anyHostOut = false;
+    std::lock_guard<std::mutex> lock(ex->mutex);
+    DeviceGuard guard(ex->device);
     Binding& b = prepareCall(ex, symbols, nsym, in, nin, outs, nout, st, anyHostOut);
     size_t n = b.steps.size();
     std::vector<cudaEvent_t> ev(2 * n);
@@ -677,6 +759,7 @@ extern "C" int llc_profile(LlcExec* ex, const int64_t* symbols, int nsym, const 
     }
     for (auto& e : ev) cudaEventDestroy(e);
     finishCall(ex, b, outs, nout, st, anyHostOut);
+    if (!anyHostOut) { ex->queueStatusRead(st); cudaOk(cudaStreamSynchronize(st), "cudaStreamSynchronize"); ex->raiseOnStatus(st); }
     struct Agg { int launches = 0; double ms = 0, flops = 0, bytes = 0; };
     std::map<std::string, Agg> agg;
     std::ostringstream o;

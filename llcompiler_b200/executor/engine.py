@@ -99,6 +99,13 @@ class Torch_ExecutionEngine(ExecutionEngine):
             self.executor.run(inputs, outputs_, stream)
         return outputs
 
+    def status(self):
+        """Waits for the device and raises if a kernel of an earlier call recorded a failure: a tensor-core kernel whose
+        bounded wait gave up, or embedding indices outside their table (those rows are zeros).  ``run`` makes this check
+        itself when its tensors live on the host; with device tensors the call returns before the kernels have run, so
+        the caller asks here after its own synchronisation.  Returns the three status words (all zero when healthy)."""
+        return self.executor.status()
+
     def profile(self, *args, reps: int = 5):
         """Per-kernel CUDA-event timing of one call: list of dicts with kernel, launches, ms, flops, bytes."""
         symbols = [int(a) for a in args if isinstance(a, int) and not isinstance(a, bool)]

@@ -5,7 +5,7 @@ distributed code; the batch symbol of its symbolic-shape machinery is what makes
 plan serve the per-rank slice."""
 from __future__ import annotations
 
-from typing import Callable, List, Sequence, Tuple
+from typing import Callable, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -20,12 +20,18 @@ def shard_bounds(total: int, world: int, rank: int) -> Tuple[int, int]:
     return start, start + base + (1 if rank < extra else 0)
 
 
+def _world_and_rank(group=None) -> Tuple[int, int]:
+    """Size and rank of the group; a process without a process group is a group of one."""
+    if not dist.is_available() or not dist.is_initialized():
+        return 1, 0
+    return dist.get_world_size(group), dist.get_rank(group)
+
+
 def gather_batch(local: torch.Tensor, total: int, group=None) -> torch.Tensor:
     """All-gathers per-rank output slices (dim 0) into the full batch on every rank."""
-    world = dist.get_world_size(group)
+    world, rank = _world_and_rank(group)
     if world == 1:
         return local
-    rank = dist.get_rank(group)
     sizes = [shard_bounds(total, world, r)[1] - shard_bounds(total, world, r)[0] for r in range(world)]
     if len(set(sizes)) == 1 and local.is_cuda:
         out = local.new_empty((total,) + tuple(local.shape[1:]))
@@ -41,17 +47,40 @@ def gather_batch(local: torch.Tensor, total: int, group=None) -> torch.Tensor:
 
 class BatchShardedRunner:
     """Wraps a compiled callable: ``runner(*full_batch_inputs)`` runs this rank's slice and returns the
-    gathered full-batch output.  Inputs whose leading extent is not the batch are passed whole."""
+    gathered full-batch output.  Inputs whose leading extent is not the batch are passed whole.
 
-    def __init__(self, fn: Callable, group=None):
-        self.fn, self.group = fn, group
+    With ``device`` set (GPU ranks over NCCL) host inputs are accepted too: the rank's slice is copied to the
+    device (asynchronously when the host tensor is page-locked), the gather runs over the device tensors, and the
+    gathered batch is copied back to page-locked host memory on the ranks listed in ``host_result_ranks``
+    (default: every rank); the other ranks copy back their own slice only."""
+
+    def __init__(self, fn: Callable, group=None, device: Optional[torch.device] = None, host_result_ranks: Optional[Sequence[int]] = None):
+        self.fn, self.group, self.device = fn, group, device
+        self.host_result_ranks = None if host_result_ranks is None else set(host_result_ranks)
+        self._host_out = {}
+
+    def _to_host(self, t: torch.Tensor) -> torch.Tensor:
+        key = (tuple(t.shape), t.dtype)
+        buf = self._host_out.get(key)
+        if buf is None:
+            buf = self._host_out[key] = torch.empty(t.shape, dtype=t.dtype, pin_memory=True)
+        buf.copy_(t, non_blocking=True)
+        torch.cuda.current_stream(t.device).synchronize()
+        return buf
 
     def __call__(self, *inputs: torch.Tensor) -> torch.Tensor:
-        world, rank = dist.get_world_size(self.group), dist.get_rank(self.group)
+        world, rank = _world_and_rank(self.group)
         total = inputs[0].shape[0]
         lo, hi = shard_bounds(total, world, rank)
         local = [i[lo:hi] if i.dim() > 0 and i.shape[0] == total else i for i in inputs]
+        from_host = self.device is not None and world > 1 and not any(i.is_cuda for i in inputs)
+        if from_host:
+            local = [i.to(self.device, non_blocking=True) for i in local]
         out = self.fn(*local)
         if isinstance(out, (list, tuple)):
             out = out[0]
-        return gather_batch(out, total, self.group)
+        full = gather_batch(out, total, self.group)
+        if from_host:
+            wants_full = self.host_result_ranks is None or rank in self.host_result_ranks
+            return self._to_host(full if wants_full else out)
+        return full

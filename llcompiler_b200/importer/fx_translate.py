@@ -183,6 +183,13 @@ def _binary(name: str):
                 c = ctx.block.op("llh.scalar_cast", [v], [TensorType([1], v.type)]).result
                 v = ctx.block.op("llh.convert_to", [c], [TensorType([1], rt.elt)]).result
             ops.append(v)
+        # aten::add / aten::sub carry `alpha`: out = a +- alpha * b.  (The reference's translators drop it,
+        # fx_op_translate/binary ops; eager parity needs it.)
+        alpha = node.kwargs.get("alpha", 1) if name in ("llh.add", "llh.sub") else 1
+        if not isinstance(alpha, (int, float)):
+            raise NotImplementedError(f"{node.target}: alpha must be a python number, got {alpha!r}")
+        if alpha != 1:
+            ops[1] = ctx.block.op("llh.mul", [ops[1], ctx.block.scalar_tensor(alpha, rt.elt)], [TensorType(ops[1].type.shape, rt.elt)]).result
         return ctx.block.op(name, ops, [rt])
     return build
 
@@ -242,7 +249,16 @@ def _bmm(ctx, node):
 def _addmm(ctx, node):
     rt = _result_type(node)
     mm = ctx.block.op("llh.matmul", [_arg(ctx, node.args[1]), _arg(ctx, node.args[2])], [rt]).result
-    return ctx.block.op("llh.add", [mm, _arg(ctx, node.args[0])], [rt])
+    # out = beta * input + alpha * (mat1 @ mat2)
+    beta, alpha = node.kwargs.get("beta", 1), node.kwargs.get("alpha", 1)
+    if not isinstance(beta, (int, float)) or not isinstance(alpha, (int, float)):
+        raise NotImplementedError("aten::addmm: beta and alpha must be python numbers")
+    bias = _arg(ctx, node.args[0])
+    if alpha != 1:
+        mm = ctx.block.op("llh.mul", [mm, ctx.block.scalar_tensor(alpha, rt.elt)], [rt]).result
+    if beta != 1:
+        bias = ctx.block.op("llh.mul", [bias, ctx.block.scalar_tensor(beta, rt.elt)], [TensorType(bias.type.shape, rt.elt)]).result
+    return ctx.block.op("llh.add", [mm, bias], [rt])
 
 
 def _transpose(ctx, x: Value, perms: Sequence[int], rt: Optional[TensorType] = None) -> Op:
@@ -388,6 +404,11 @@ translator("aten::mean.dim")(_reduce("llh.reduce_mean"))
 @translator("aten::_softmax", "aten::softmax.int")
 def _softmax(ctx, node):
     x = _arg(ctx, node.args[0])
+    # aten::_softmax(x, dim, half_to_float) / aten::softmax.int(x, dim, dtype): a result type other than the input's
+    # would need a cast in front, which this translator does not insert
+    extra = node.args[2] if len(node.args) > 2 else node.kwargs.get("dtype", node.kwargs.get("half_to_float"))
+    if extra not in (None, False) and _result_type(node).elt != x.type.elt:
+        raise NotImplementedError(f"{node.target}: softmax with a result type different from its input's")
     return ctx.block.op("llh.softmax", [x], [_result_type(node)],
                         {"axis": i64_attr(node.args[1] % x.type.rank)})
 
@@ -415,6 +436,14 @@ def _slice(ctx, node):
     start = node.args[2] if len(node.args) > 2 and node.args[2] is not None else 0
     end = node.args[3] if len(node.args) > 3 and node.args[3] is not None else INT64_MAX
     step = node.args[4] if len(node.args) > 4 else 1
+    extent = x.type.shape[dim]
+    if extent != DYNAMIC:                # a static extent: python's own normalisation (negative = from the end, clamped)
+        if isinstance(start, int):
+            start = min(max(start + extent if start < 0 else start, 0), extent)
+        if isinstance(end, int) and end < INT64_MAX:
+            end = min(max(end + extent if end < 0 else end, 0), extent)
+    elif (isinstance(start, int) and start < 0) or (isinstance(end, int) and end < 0):
+        raise NotImplementedError("aten::slice.Tensor: negative bounds on a symbolic extent")
     b = ctx.block
     starts, ends, steps = [], [], []
     for i in range(rank):

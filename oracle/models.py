@@ -252,3 +252,30 @@ def max_rel_err(got: torch.Tensor, want: torch.Tensor) -> float:
     want = want.detach().double().cpu()
     denom = want.abs().max().clamp_min(1e-30)
     return float((got - want).abs().max() / denom)
+
+
+ELEMENTWISE_K = 0.5
+
+
+def parity_figures(got: torch.Tensor, want: torch.Tensor, tol: float, k: float = ELEMENTWISE_K):
+    """(global relative error, worst element-wise ratio).
+
+    The element-wise ratio is max_i |got_i - want_i| / (tol * |want_i| + k * tol * max|want|): at most 1 exactly when
+    ``torch.allclose(got, want, rtol=tol, atol=k * tol * max|want|)`` holds.  The absolute term is there because an
+    output element that is a sum of cancelling terms carries the rounding error of the terms, not of the sum; with
+    k = 0.5 an element far below the tensor's maximum may be off by half of what the global figure allows, no more.
+    """
+    got = got.detach().double().cpu()
+    want = want.detach().double().cpu()
+    top = want.abs().max().clamp_min(1e-30)
+    diff = (got - want).abs()
+    return float(diff.max() / top), float((diff / (tol * want.abs() + k * tol * top)).max())
+
+
+def assert_parity(got: torch.Tensor, want: torch.Tensor, tol: float, what: str = "") -> None:
+    """Both gates of a configuration's tolerance: the global relative error below `tol` and every element inside
+    rtol = tol, atol = ELEMENTWISE_K * tol * max|want|.  Prints both figures (visible with pytest -s / on failure)."""
+    glob, elem = parity_figures(got, want, tol)
+    print(f"parity {what}: max|d|/max|want| = {glob:.3e} (tol {tol:g}); worst element at {elem:.3f} of rtol={tol:g}, atol={ELEMENTWISE_K}*tol*max|want|")
+    assert glob < tol, f"{what}: relative error {glob} above {tol}"
+    assert elem <= 1.0, f"{what}: an element is {elem:.2f}x outside rtol={tol}, atol={ELEMENTWISE_K}*tol*max|want|"

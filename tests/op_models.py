@@ -170,6 +170,26 @@ class LayerNormGelu(nn.Module):
         return torch.nn.functional.gelu(self.ln(x))
 
 
+class AddAlpha(nn.Module):
+    def forward(self, x):
+        return torch.sub(torch.add(x, x * x, alpha=2), x, alpha=0.5)
+
+
+class AddmmBetaAlpha(nn.Module):
+    def __init__(self):
+        super().__init__()
+        self.w = nn.Parameter(torch.randn(24, 16))
+        self.b = nn.Parameter(torch.randn(16))
+
+    def forward(self, x):
+        return torch.addmm(self.b, x, self.w, beta=0.5, alpha=2.0)
+
+
+class SliceClamped(nn.Module):
+    def forward(self, x):
+        return x[:, 2:100] + x[:, -3:]           # an end past the extent is clamped, a negative start counts from the end
+
+
 def _g(seed):
     return torch.Generator().manual_seed(seed)
 
@@ -200,8 +220,53 @@ OP_CASES = {
     "reduce_max": (ReduceMax, lambda: (torch.randn(3, 3, 24, 20, generator=_g(23)),), True),
     "reduce_sum": (ReduceSum, lambda: (torch.randn(3, 3, 24, 20, generator=_g(24)),), False),
     "softmax": (Softmax, lambda: (torch.randn(4, 6, 40, generator=_g(25)),), False),
+    "add_sub_alpha": (AddAlpha, lambda: (torch.randn(3, 3, 24, 20, generator=_g(27)),), False),
+    "addmm_beta_alpha": (AddmmBetaAlpha, lambda: (torch.randn(10, 24, generator=_g(28)),), False),
+    "slice_clamped": (SliceClamped, lambda: (torch.randn(6, 5, 7, generator=_g(29)),), True),
     "layer_norm_gelu": (LayerNormGelu, lambda: (torch.randn(4, 6, 48, generator=_g(26)),), False),
 }
+
+
+# The same op families at the reference's own input shapes (test/python/ops/*.py: 3x3x224x224 images,
+# batch_matmul 3x224x112, broadcast 224x112, linear 10 x 100000 through three bias-free layers, where 1000x224 with an
+# all-true predicate).  Their outputs are too large to commit whole: the golden file keeps a strided sample and a sum.
+REFERENCE_SHAPE_CASES = {
+    "abs": (Abs, lambda: (torch.randn(3, 3, 224, 224, generator=_g(101)),), True),
+    "add": (Add, lambda: (torch.randn(3, 3, 224, 224, generator=_g(102)),), True),
+    "sub": (Sub, lambda: (torch.randn(3, 3, 224, 224, generator=_g(103)),), False),
+    "mul": (Mul, lambda: (torch.randn(3, 3, 224, 224, generator=_g(104)),), True),
+    "div": (Div, lambda: (torch.randn(3, 3, 100, generator=_g(105)),), False),
+    "relu": (Relu, lambda: (torch.randn(3, 3, 224, 224, generator=_g(106)),), True),
+    "sqrt": (Sqrt, lambda: (torch.randn(3, 3, 224, 224, generator=_g(107)),), False),
+    "conv2d_nchw_fchw": (Conv2D, lambda: (torch.randn(3, 3, 224, 224, generator=_g(109)),), False),
+    "max_pool_2d": (MaxPool2D, lambda: (torch.randn(3, 3, 224, 224, generator=_g(110)),), True),
+    "batch_norm_2d_inference": (BatchNorm2DInference, lambda: (torch.randn(3, 3, 224, 224, generator=_g(111)),), False),
+    "batch_norm_1d_inference": (BatchNorm1DInference, lambda: (torch.randn(3, 3, 224, generator=_g(112)),), False),
+    "linear": (lambda: Linear(100000), lambda: (torch.randn(10, 100000, generator=_g(113)),), False),
+    "matmul": (Matmul, lambda: (torch.randn(3, 3, generator=_g(114)),), False),
+    "batch_matmul": (BatchMatmul, lambda: (torch.randn(3, 224, 112, generator=_g(115)),), False),
+    "broadcast": (Broadcast, lambda: (torch.randn(224, 112, generator=_g(116)),), False),
+    "extract": (Extract, lambda: (torch.randn(3, 3, 224, 224, generator=_g(117)),), False),
+    "unsqueeze": (Unsqueeze, lambda: (torch.randn(3, 3, 224, 224, generator=_g(119)),), True),
+    "where": (Where, lambda: (torch.ones(1000, 224, dtype=torch.bool), torch.randn(1000, 224, generator=_g(121)),
+                              torch.randn(1000, 224, generator=_g(122))), True),
+    "reduce_max": (ReduceMax, lambda: (torch.randn(3, 3, 224, 224, generator=_g(123)),), True),
+    "reduce_sum": (ReduceSum, lambda: (torch.randn(3, 3, 224, 224, generator=_g(124)),), False),
+}
+SAMPLE_LIMIT = 2048
+
+
+def sample_of(t):
+    """The strided sample of an output that the golden file keeps for the reference-shape cases."""
+    flat = t.reshape(-1)
+    step = max(1, flat.numel() // SAMPLE_LIMIT)
+    return flat[::step][:SAMPLE_LIMIT].clone()
+
+
+def build_reference_shape_case(name):
+    torch.manual_seed(0)
+    factory, inputs, exact = REFERENCE_SHAPE_CASES[name]
+    return factory().eval(), inputs(), exact
 
 
 def build_case(name):

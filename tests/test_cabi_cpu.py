@@ -56,9 +56,32 @@ def test_load_without_a_gpu_fails_loudly():
 
 def test_plan_text_round_trips_through_the_reference_lit_inputs():
     # every LLH module of the reference's own symbol-inference lit file parses and re-prints
-    ref = "/root/reference/test/Dialect/LLH/symbol_infer/infer_symbol_shape.mlir"
-    if not os.path.exists(ref):
+    from reference_tree import reference_path
+    ref = reference_path("test", "Dialect", "LLH", "symbol_infer", "infer_symbol_shape.mlir")
+    if not ref or not os.path.exists(ref):
         pytest.skip("reference tree not present")
     out = _capi.run_pass(open(ref).read(), "parse")
     assert out.count("func.func") >= 20
     assert _capi.run_pass(out, "parse") == out
+
+
+def test_tensor_buffer_view_get_tool_and_the_package_alias():
+    """The rest of the reference's module surface (src/Pybind/Entrance.cpp:71-91, :113): a host Tensor exposes the
+    buffer protocol and to_numpy(), executor.get_tool names the in-process tools, and the package imports under the
+    reference's name."""
+    import numpy as np
+    import torch
+    from llcompiler_.executor import get_tool
+    from llcompiler_.tensor import Tensor
+    t = torch.arange(24, dtype=torch.float32).reshape(2, 3, 4)[:, ::2]           # a strided host view
+    T = Tensor(t.data_ptr(), t.data_ptr(), 4, t.storage_offset(), list(t.shape), list(t.stride()))
+    assert np.array_equal(T.to_numpy(), t.numpy()) and np.array_equal(np.asarray(memoryview(T)), t.numpy())
+    with pytest.raises(RuntimeError):
+        Tensor(0, 0, 4, 0, [1], [1], 0).to_numpy()                               # device memory has no buffer view
+    assert "llc_opt" in get_tool("llc-opt")
+    with pytest.raises(IndexError):
+        get_tool("opt")
+    import llcompiler
+    from llcompiler.compiler import LLCompiler
+    from llcompiler_b200.compiler import LLCompiler as Impl
+    assert LLCompiler is Impl and llcompiler.LLCompiler is Impl

@@ -248,3 +248,26 @@ def test_small_fp32_problems_take_the_fma_kernel_by_default(monkeypatch):
     G.gemm(a, b.transpose(2, 3), out, prec="tf32")
     torch.cuda.synchronize()
     assert 2e-6 < max_rel_err(out, want) < 2e-3
+
+
+@pytest.mark.parametrize("prec,in_dtype", [("tf32", torch.float32), ("bf16", torch.bfloat16)])
+def test_fp32_output_gelu_epilogue_is_erf_gelu_to_1e6(prec, in_dtype):
+    """With fp32 output the tensor-core epilogue computes GELU with a polynomial erf (one exp, one reciprocal, five
+    FMAs).  The activation is isolated here: the same GEMM runs once without and once with the activation, and the
+    activated result is compared with the erf GELU (float64) of the kernel's own un-activated result, so that what is
+    measured is the activation's error alone: 1e-6 relative to the largest value, and 2e-6 absolute on every element."""
+    m, n, k = 512, 384, 256
+    a, w = (_rand(m, k) * 0.25).to(in_dtype), _rand(n, k, seed=1).to(in_dtype)
+    bias = _rand(n, seed=2)
+    A, B = a.to(DEV)[None, None], w.to(DEV).t()[None, None]
+    pre = torch.empty(1, 1, m, n, device=DEV)
+    act = torch.empty(1, 1, m, n, device=DEV)
+    G.gemm(A, B, pre, shift=bias.to(DEV), prec=prec)
+    G.gemm(A, B, act, shift=bias.to(DEV), act="gelu", prec=prec)
+    torch.cuda.synchronize()
+    x = pre[0, 0].double().cpu()
+    want = 0.5 * x * (1.0 + torch.erf(x / 2.0 ** 0.5))
+    assert x.abs().max() > 4                              # both tails of the activation are exercised
+    assert max_rel_err(act[0, 0], want) < 1e-6
+    assert float((act[0, 0].double().cpu() - want).abs().max()) < 2e-6
+    _healthy()

@@ -12,7 +12,7 @@ pytestmark = pytest.mark.gpu
 
 from helpers import compile_with  # noqa: E402
 from llcompiler_b200.compiler import LLCompiler  # noqa: E402
-from oracle.models import CONFIGS, build_model, max_rel_err, round_to_bf16_  # noqa: E402
+from oracle.models import CONFIGS, assert_parity, build_model, max_rel_err, round_to_bf16_  # noqa: E402
 
 
 def _gpu_run(model, inputs, dynamic=False, precision="auto", device_inputs=True):
@@ -33,7 +33,8 @@ def test_mlp_symbolic_batch_device_and_host_tensors():
     with torch.no_grad():
         want = m(x)
     comp, fn, out = _gpu_run(m, (x,), dynamic=True)
-    assert out.is_cuda and max_rel_err(out, want) < 1e-4
+    assert out.is_cuda
+    assert_parity(out, want, 1e-4, "mlp fp32")
     eng = comp.compiled[0].engine
     assert eng.executor.last_launch_count() == 2          # two fused GEMM launches, nothing else
     for b in (1, 7, 65, 1024):                             # same plan, other batch sizes
@@ -53,7 +54,7 @@ def test_resnet18_fp32():
     with torch.no_grad():
         want = m(x)
     comp, fn, out = _gpu_run(m, (x,))
-    assert max_rel_err(out, want) < 1e-4
+    assert_parity(out, want, 1e-4, "resnet18 fp32")
     assert comp.compiled[0].engine.executor.last_launch_count() == 24
 
 
@@ -64,7 +65,7 @@ def test_encoder_layer_symbolic_seq(seq):
     with torch.no_grad():
         want = m(x)
     comp, fn, out = _gpu_run(m, (x,), dynamic=True)
-    assert max_rel_err(out, want) < 1e-4                  # fp32 FMA path; the TF32 path states 2e-2
+    assert_parity(out, want, 1e-4, f"encoder fp32 S={seq}")   # fp32 FMA path; the TF32 path states 2e-2
 
 
 def test_resnet50_bf16():
@@ -75,7 +76,7 @@ def test_resnet50_bf16():
     mb = build_model("resnet50").to(torch.bfloat16)
     comp, fn, out = _gpu_run(mb, (x,))
     assert out.dtype == torch.bfloat16
-    assert max_rel_err(out.float(), want) < 2e-2
+    assert_parity(out.float(), want, 2e-2, "resnet50 bf16")
 
 
 def test_bert_bf16_two_layers_with_mask():
@@ -87,7 +88,7 @@ def test_bert_bf16_two_layers_with_mask():
         want = m(ids, mask)
     mb = build_model("bert", n_layers=2).to(torch.bfloat16)
     comp, fn, out = _gpu_run(mb, (ids, mask))
-    assert max_rel_err(out.float(), want) < 2e-2
+    assert_parity(out.float(), want, 2e-2, "bert bf16, 2 layers, masked")
 
 
 def test_bert_fp32_two_layers():
@@ -96,7 +97,7 @@ def test_bert_fp32_two_layers():
     with torch.no_grad():
         want = m(ids, mask)
     comp, fn, out = _gpu_run(m, (ids, mask))
-    assert max_rel_err(out, want) < 1e-4
+    assert_parity(out, want, 1e-4, "bert fp32, 2 layers")
 
 
 def test_wrong_inputs_raise():
@@ -120,7 +121,7 @@ def test_resnet18_fp32_on_tensor_cores_tf32x3():
     with torch.no_grad():
         want = m(x)
     comp, fn, out = _gpu_run(m, (x,), precision="tf32x3")
-    assert max_rel_err(out, want) < 1e-4
+    assert_parity(out, want, 1e-4, "resnet18 tf32x3")
 
 
 @pytest.mark.parametrize("seq", [128, 512])
@@ -130,7 +131,7 @@ def test_encoder_layer_tf32(seq):
     with torch.no_grad():
         want = m(x)
     comp, fn, out = _gpu_run(m, (x,), dynamic=True, precision="tf32")
-    assert max_rel_err(out, want) < 2e-2                  # the tolerance stated for TF32 paths
+    assert_parity(out, want, 2e-2, f"encoder tf32 S={seq}")   # the tolerance stated for TF32 paths
 
 
 def test_host_results_are_page_locked_and_never_aliased():
@@ -179,12 +180,14 @@ def test_full_size_batch_sharding_is_invisible(name, batch, precision, bf16, tol
     torch.cuda.synchronize()
     assert full.shape[0] == batch and torch.isfinite(full).all()
     assert max_rel_err(torch.cat(parts), full) < tol
-    # and a quarter of the samples against the CPU oracle at a size it finishes in seconds would repeat the small-batch
-    # tests above; here one sample of the full batch is checked against the oracle instead
+    comp.compiled[0].engine.status()
+    # eight samples spread over the full batch (first, last, one in every eighth) against the CPU oracle: they were
+    # computed with the tile plan of the full batch, which the small-batch tests above never see
     ref = round_to_bf16_(build_model(name, **kw)) if bf16 else build_model(name, **kw)
+    pick = torch.tensor(sorted({0, batch - 1} | {(k * batch) // 8 + k for k in range(1, 7)}))
     with torch.no_grad():
-        want = ref(*[(i[:1].float() if i.is_floating_point() else i[:1]) for i in inputs])
-    assert max_rel_err(full[:1].cpu(), want) < tol
+        want = ref(*[(i[pick].float() if i.is_floating_point() else i[pick]) for i in inputs])
+    assert_parity(full[pick.cuda()].cpu(), want, tol, f"{name} full batch {batch}, samples {pick.tolist()}")
 
 
 def test_onnx_entry_on_the_gpu():
@@ -273,3 +276,47 @@ def test_mlp_fp32_on_tensor_cores_tf32x3():
         comp, fn, out = _gpu_run(m, (x,), dynamic=True, precision="tf32x3")
         assert max_rel_err(out, want) < 1e-4
         assert comp.compiled[0].engine.executor.last_launch_count() == 2
+
+
+def test_out_of_range_embedding_ids_are_an_error_of_the_call():
+    """The gather kernel writes zeros for an id outside its table and counts it; the executor reads that count
+    wherever it waits for its results, so the call fails instead of returning a wrong batch, and the handle stays usable."""
+    m = build_model("bert", n_layers=1)
+    ids, mask = CONFIGS["bert"].make_inputs(batch=2, seq=64)
+    with torch.no_grad():
+        want = m(ids, mask)
+    comp, fn, out = _gpu_run(m, (ids, mask))
+    eng = comp.compiled[0].engine
+    assert eng.status() == [0, 0, 0]
+    bad = ids.clone()
+    bad[1, 7] = 30522                                     # one past the last row of the table
+    with pytest.raises(RuntimeError, match="embedding indices"):
+        eng.run(bad, mask)                                # host tensors: the call waits and checks
+    eng.run(bad.cuda(), mask.cuda())                      # device tensors: the call only enqueues ...
+    with pytest.raises(RuntimeError, match="embedding indices"):
+        eng.status()                                      # ... and the caller asks after its synchronisation
+    assert eng.status() == [0, 0, 0]                      # reading clears
+    assert_parity(eng.run(ids, mask)[0], want, 1e-4, "bert after a refused call")
+
+
+def test_one_plan_on_two_devices_in_one_process():
+    """The dynamic shared-memory opt-in of the tensor-core kernels is kept per device: a second executor on another GPU
+    of the same process must launch them too, and the caller's current device must be left alone."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    m = round_to_bf16_(build_model("bert", n_layers=1))
+    ids, mask = CONFIGS["bert"].make_inputs(batch=2, seq=128)
+    with torch.no_grad():
+        want = m(ids, mask)
+    mb = build_model("bert", n_layers=1).to(torch.bfloat16)
+    outs = []
+    for d in (0, 1):
+        comp = LLCompiler(device=d)
+        fn = compile_with(comp, copy.deepcopy(mb).to(f"cuda:{d}"), False)
+        with torch.no_grad():
+            outs.append(fn(ids.to(f"cuda:{d}"), mask.to(f"cuda:{d}")))
+        torch.cuda.synchronize(d)
+        comp.compiled[0].engine.status()
+        assert torch.cuda.current_device() == 0
+        assert_parity(outs[-1].float(), want, 2e-2, f"bert bf16 on cuda:{d}")
+    assert torch.equal(outs[0].cpu(), outs[1].cpu())

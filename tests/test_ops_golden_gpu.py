@@ -13,10 +13,11 @@ pytestmark = pytest.mark.gpu
 
 from helpers import compile_with  # noqa: E402
 from llcompiler_b200.compiler import LLCompiler  # noqa: E402
-from op_models import OP_CASES, build_case  # noqa: E402
+from op_models import OP_CASES, REFERENCE_SHAPE_CASES, build_case, build_reference_shape_case, sample_of  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
 GOLDEN = torch.load(os.path.join(HERE, "golden", "op_vectors.pt"))
+GOLDEN_REF_SHAPES = torch.load(os.path.join(HERE, "golden", "op_vectors_reference_shapes.pt"))
 
 
 @pytest.mark.parametrize("dynamic", [False, True])
@@ -35,6 +36,29 @@ def test_op_on_gpu_matches_golden(name, dynamic):
         assert torch.equal(got, want)
     else:
         assert torch.allclose(got, want, rtol=1e-5, atol=1e-5, equal_nan=True)
+
+
+@pytest.mark.parametrize("name", sorted(REFERENCE_SHAPE_CASES))
+def test_op_on_gpu_at_the_reference_shapes(name):
+    """The reference's op scripts at their own sizes (3x3x224x224 images, a 10 x 100000 linear layer, ...) through
+    importer, lowering and the CUDA kernels: the whole output against PyTorch CPU eager computed here, and its strided
+    sample against the committed golden vector; the reference's tolerance rtol = atol = 1e-5, bit-exact where it applies."""
+    model, inputs, exact = build_reference_shape_case(name)
+    comp = LLCompiler()
+    with torch.no_grad():
+        want = model(*inputs)
+        got = compile_with(comp, copy.deepcopy(model).cuda(), False)(*[i.cuda() for i in inputs])
+    torch.cuda.synchronize()
+    comp.compiled[0].engine.status()
+    assert comp.compiled[0].engine.executor.last_launch_count() > 0
+    got = got.cpu()
+    g = GOLDEN_REF_SHAPES["cases"][name]
+    assert list(got.shape) == g["shape"]
+    if exact:
+        assert torch.equal(got, want) and torch.equal(sample_of(got), g["sample"])
+    else:
+        assert torch.allclose(got, want, rtol=1e-5, atol=1e-5, equal_nan=True)
+        assert torch.allclose(sample_of(got), g["sample"], rtol=1e-5, atol=1e-5, equal_nan=True)
 
 
 def test_known_answers_on_gpu():

@@ -9,8 +9,9 @@ import pytest
 
 import filecheck_lite as F
 from llcompiler_b200 import _capi
+from reference_tree import reference_path
 
-REF = "/root/reference/test/Dialect/LLH"
+REF = reference_path("test", "Dialect", "LLH") or ""
 PASSES = {"--infer-symbol-shape": "infer-symbol-shape", "--operation-legalization": "operation-legalization",
           "--remove-redundant-ops": "remove-redundant-ops"}
 # functions of each file whose CHECK lines hold on this implementation's output; the others need parts of the
