@@ -146,6 +146,113 @@ __global__ void __launch_bounds__(256) eltwise_vec_kernel(const __grid_constant_
   VecIo::store(p.out, oOff, p.odt, make_float4(regs[r][0], regs[r][1], regs[r][2], regs[r][3]));
 }
 
+// Short programs (at most four instructions: a copy, a cast, one unary or binary op on loaded operands, ...) on rows that
+// are dense or broadcast along the innermost dim: eight elements per thread with 16-byte accesses, the registers of the
+// program in real registers (the general kernels above index their register file dynamically, which puts it in local
+// memory).  This is the path of the big memory-bound steps: layout copies, embedding sums, residual adds, casts.
+constexpr int kSmallProg = 4;
+template <typename T> __device__ __forceinline__ void load8(const T* p, float* v);
+template <> __device__ __forceinline__ void load8<float>(const float* p, float* v) {
+  const float4 a = __ldg(reinterpret_cast<const float4*>(p)), b = __ldg(reinterpret_cast<const float4*>(p) + 1);
+  v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w; v[4] = b.x; v[5] = b.y; v[6] = b.z; v[7] = b.w;
+}
+template <> __device__ __forceinline__ void load8<__nv_bfloat16>(const __nv_bfloat16* p, float* v) {
+  const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p));
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+}
+__device__ __forceinline__ float pick4(const float (*r)[8], int which, int v) {
+  const float lo = which & 1 ? r[1][v] : r[0][v], hi = which & 1 ? r[3][v] : r[2][v];
+  return which & 2 ? hi : lo;
+}
+template <typename IDX>
+__global__ void __launch_bounds__(256) eltwise_small_kernel(const __grid_constant__ EltArgs p) {
+  const IDX t = (IDX)blockIdx.x * blockDim.x + threadIdx.x;
+  if ((long long)t * 8 >= p.total) return;
+  IDX rem = t * 8;
+  long long oOff = 0, iOff[kSmallProg] = {0, 0, 0, 0};
+  for (int d = p.rank - 1; d >= 0; --d) {
+    const IDX ext = (IDX)p.shape[d];
+    const IDX c = rem % ext; rem /= ext;
+    oOff += (long long)c * p.ostr[d];
+#pragma unroll
+    for (int k = 0; k < kSmallProg; ++k) if (k < p.nin) iOff[k] += (long long)c * p.istr[k][d];
+  }
+  const int last = p.rank - 1;
+  auto loadOperand = [&](int k, float* dst) {
+    const void* base = k == 0 ? p.in[0] : k == 1 ? p.in[1] : k == 2 ? p.in[2] : p.in[3];
+    const int dt = k == 0 ? p.idt[0] : k == 1 ? p.idt[1] : k == 2 ? p.idt[2] : p.idt[3];
+    const long long off = k == 0 ? iOff[0] : k == 1 ? iOff[1] : k == 2 ? iOff[2] : iOff[3];
+    const long long str = k == 0 ? p.istr[0][last] : k == 1 ? p.istr[1][last] : k == 2 ? p.istr[2][last] : p.istr[3][last];
+    if (str == 0) {
+      const float x = loadAs(base, off, dt);
+#pragma unroll
+      for (int v = 0; v < 8; ++v) dst[v] = x;
+    } else if (dt == LLC_FLOAT32) load8<float>(reinterpret_cast<const float*>(base) + off, dst);
+    else load8<__nv_bfloat16>(reinterpret_cast<const __nv_bfloat16*>(base) + off, dst);
+  };
+  float o[8];
+  // the two shapes almost every large step has: one operand (a copy, a cast, one unary op) or two operands and one
+  // binary op; the op is decoded once, outside the element loop
+  const int n = p.prog.n;
+  const bool unary = (n == 1 || (n == 2 && p.prog.op[1] != E_LD && p.prog.op[1] != E_IMM && p.prog.a[1] == 0)) && p.prog.op[0] == E_LD;
+  const bool binary = n == 3 && p.prog.op[0] == E_LD && p.prog.op[1] == E_LD && p.prog.op[2] >= E_ADD && p.prog.op[2] <= E_MIN && p.prog.a[2] + p.prog.b[2] == 1;
+  if (unary) {
+    loadOperand(p.prog.a[0], o);
+    if (n == 2) {
+      const int op = p.prog.op[1];
+      if (op == E_RELU) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v) o[v] = fmaxf(o[v], 0.f);
+      } else if (op != E_CAST) {
+#pragma unroll
+        for (int v = 0; v < 8; ++v) o[v] = evalOp(op, o[v], o[v], o[v], 0.f);
+      }
+    }
+  } else if (binary) {
+    float x[8], y[8];
+    loadOperand(p.prog.a[p.prog.a[2]], x); loadOperand(p.prog.a[p.prog.b[2]], y);
+    switch (p.prog.op[2]) {
+#define LLC_BIN(OP, EXPR) case OP: _Pragma("unroll") for (int v = 0; v < 8; ++v) o[v] = EXPR; break;
+      LLC_BIN(E_ADD, x[v] + y[v]) LLC_BIN(E_SUB, x[v] - y[v]) LLC_BIN(E_MUL, x[v] * y[v]) LLC_BIN(E_DIV, x[v] / y[v])
+      LLC_BIN(E_MAX, fmaxf(x[v], y[v])) LLC_BIN(E_MIN, fminf(x[v], y[v]))
+#undef LLC_BIN
+    }
+  } else {
+  float r[kSmallProg][8];
+#pragma unroll
+  for (int i = 0; i < kSmallProg; ++i) {
+    if (i < p.prog.n) {
+      const int op = p.prog.op[i];
+      if (op == E_LD) {
+        loadOperand(p.prog.a[i], r[i]);
+      } else {
+        const int a = p.prog.a[i], b = p.prog.b[i], c = p.prog.c[i];
+        const float imm = p.prog.imm[i];
+#pragma unroll
+        for (int v = 0; v < 8; ++v) r[i][v] = evalOp(op, pick4(r, a, v), pick4(r, b, v), pick4(r, c, v), imm);
+      }
+    } else {
+#pragma unroll
+      for (int v = 0; v < 8; ++v) r[i][v] = 0.f;
+    }
+  }
+#pragma unroll
+  for (int v = 0; v < 8; ++v) o[v] = pick4(r, p.prog.n - 1, v);
+  }
+
+  if (p.odt == LLC_FLOAT32) {
+    float4* dst = reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + oOff);
+    dst[0] = make_float4(o[0], o[1], o[2], o[3]); dst[1] = make_float4(o[4], o[5], o[6], o[7]);
+  } else {
+    uint4 q; __nv_bfloat162 h;
+    h = __floats2bfloat162_rn(o[0], o[1]); q.x = *reinterpret_cast<unsigned*>(&h); h = __floats2bfloat162_rn(o[2], o[3]); q.y = *reinterpret_cast<unsigned*>(&h);
+    h = __floats2bfloat162_rn(o[4], o[5]); q.z = *reinterpret_cast<unsigned*>(&h); h = __floats2bfloat162_rn(o[6], o[7]); q.w = *reinterpret_cast<unsigned*>(&h);
+    *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + oOff) = q;
+  }
+}
+
 int parseProgram(const char* text, EltProgram& prog, int nin) {
   static const struct { const char* name; int op; int arity; } table[] = {
       {"add", E_ADD, 2}, {"sub", E_SUB, 2}, {"mul", E_MUL, 2}, {"div", E_DIV, 2}, {"max", E_MAX, 2}, {"min", E_MIN, 2}, {"pow", E_POW, 2},
@@ -391,7 +498,21 @@ extern "C" int llc_cuda_eltwise(const LlcEltwiseParams* q, void* stream) {
     if (s != 1 || !isVecType(a.idt[k]) || !alignedFor(a.in[k], a.idt[k])) vec = false;
     for (int d = 0; d + 1 < r && vec; ++d) if (a.istr[k][d] % 4) vec = false;
   }
-  if (vec) {
+  // eight elements per thread: every access 16 bytes wide (fp32: two of them) and aligned, whatever the outer coordinates
+  bool small = vec && a.prog.n <= kSmallProg && a.nin <= kSmallProg && inner % 8 == 0 && (reinterpret_cast<uintptr_t>(a.out) & 15) == 0;
+  for (int d = 0; d + 1 < r && small; ++d) if (a.ostr[d] % 8) small = false;
+  for (int k = 0; k < a.nin && small; ++k) {
+    if (a.istr[k][r - 1] == 0) continue;
+    if (reinterpret_cast<uintptr_t>(a.in[k]) & 15) small = false;
+    for (int d = 0; d + 1 < r && small; ++d) if (a.istr[k][d] % 8) small = false;
+  }
+  if (small) {
+    const long long threads = total / 8;
+    const unsigned blocks = (unsigned)((threads + 255) / 256);
+    if (total < (1LL << 32)) eltwise_small_kernel<unsigned><<<blocks, 256, 0, st>>>(a);
+    else eltwise_small_kernel<unsigned long long><<<blocks, 256, 0, st>>>(a);
+    LLC_LAUNCH_CHECK("eltwise_small_kernel");
+  } else if (vec) {
     long long threads = total / 4;
     eltwise_vec_kernel<<<(unsigned)((threads + 255) / 256), 256, 0, st>>>(a);
     LLC_LAUNCH_CHECK("eltwise_vec_kernel");

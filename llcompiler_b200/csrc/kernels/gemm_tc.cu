@@ -12,10 +12,11 @@
 //               accumulation into one of two TMEM accumulators), commits the stage back to the
 //               producer; after the last K block commits the accumulator to the epilogue.
 //               Allocates and frees tensor memory.
-//   warps 2-9   epilogue: tcgen05.ld (32 lanes x 32 columns per warp and step; a warp owns one lane
-//               quarter and one column half), alpha*scale[n]*acc + shift[n] + res, activation,
-//               16-byte stores; releases the accumulator as soon as it is in registers so that the
-//               next tile's MMAs overlap the stores.
+//   warps 2-9   epilogue: tcgen05.ld (32 lanes x 32 columns per warp and step, the next step's load in
+//               flight; a warp owns one lane quarter and one column half), alpha*scale[n]*acc + shift[n]
+//               + res, activation, rows staged in one of two swizzled slots and written by TMA stores;
+//               releases the accumulator as soon as it is in registers so that the next tile's MMAs
+//               overlap the stores.
 //   next 8      convolution only: im2col gather of the A tile (NHWC activations) with 16-byte
 //               cp.async into the swizzled layout, zero-filling padding taps.
 //   next 4      tf32x3 only: split each landed fp32 tile into its low-order part x - tf32(x)
@@ -45,22 +46,26 @@ struct TcArgs {
   long long M, N, K;
   long long o_s0, o_s1, o_sm, r_s0, r_s1, r_sm, r_sn;
   int b1; int kBlocks; int vecOut;
-  int resTile;              // the residual can be fetched as 32-row x 128-byte boxes with 16-byte loads
+  int resTile;              // the residual can be fetched as 32-row x 64-byte units with 16-byte loads
   int splits;               // K is cut into this many slices, each a work unit of its own; partial tiles meet in `ws`
   float* ws; int* counters; // split-K: [units][128][BN] partial accumulators; one arrival counter per tile (zero between launches)
   int hasBLo;               // tf32x3: the low-order part of B comes from memory (mapBLo) instead of the split warps
-  int tmaOut;               // 0, or the bytes per row of the output box the epilogue stores through TMA (64 or 128)
+  int tmaOut;               // 0, or the bytes per row of the output box the epilogue stores through TMA (64)
   int aZ0, aZ1, bZ0, bZ1;   // 1: the operand has this batch dim, 0: it is broadcast (coordinate 0)
+  int rZ0, rZ1;             // the same for the residual (RES kernels: it is loaded through a tensor map)
   int mTiles, nTiles; long long tiles;
   // convolution (A gathered from NHWC activations)
   const void* x; int H, W, C, KH, KW, OH, OW, sh, sw, ph, pw, dh, dw;
   long long xs_n, xs_h, xs_w;   // element strides of x along image, row and pixel (dense NHWC: H*W*C, W*C, C)
 };
 
-template <int BN, bool X3> struct Smem {
+// RES: the epilogue adds a residual tile that TMA loads fetch ahead of time into a ring of four units per epilogue warp
+// (the ring also stages the output); without it a warp has two output slots.
+template <int BN, bool X3, bool RES> struct Smem {
   static constexpr int kABytes = BM * kTileKBytes, kBBytes = BN * kTileKBytes;
   static constexpr int kStageBytes = (kABytes + kBBytes) * (X3 ? 2 : 1);
-  static constexpr int kStagingBytes = 8 * 4096;   // one 32-row x 128-byte output box per epilogue warp
+  static constexpr int kStagingPerWarp = RES ? 8192 : 4096;   // units of 32 rows x 64 bytes: a ring of four, or two output slots
+  static constexpr int kStagingBytes = 8 * kStagingPerWarp;
   static constexpr int kStageBudget = 224 * 1024 - kStagingBytes;
   static constexpr int kStages = kStageBudget / kStageBytes > 8 ? 8 : kStageBudget / kStageBytes;
   static constexpr int kBarrierBytes = 1024;
@@ -87,15 +92,16 @@ __host__ __device__ constexpr int tcThreads(int kind, int mode) { return (2 + 8 
 // 16-byte chunk inside one filter tap), 2 convolution with A loaded by TMA in im2col mode (a K block of 128
 // bytes lies inside one filter tap: channels * element size is a multiple of 128).  (A variant with sixteen epilogue
 // warps and one pipeline stage less was measured 1.2 to 1.9 times slower on every shape tried and is not kept.)
-template <int BN, int KIND, int MODE, bool BMN>
+template <int BN, int KIND, int MODE, bool BMN, bool RES>
 __global__ void __launch_bounds__(tcThreads(KIND, MODE), 1)
 tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUtensorMap mapB, const __grid_constant__ CUtensorMap mapO,
-          const __grid_constant__ CUtensorMap mapBLo, const TcArgs p) {
+          const __grid_constant__ CUtensorMap mapBLo, const __grid_constant__ CUtensorMap mapR, const TcArgs p) {
   constexpr bool X3 = KIND == 2;
   constexpr bool TF32 = KIND != 0;
   constexpr bool CONV = MODE == 1;      // the gather warps exist
   constexpr bool IM2COL = MODE == 2;
-  using S = Smem<BN, X3>;
+  using S = Smem<BN, X3, RES>;
+  static_assert(!RES || (KIND != 2 && MODE != 1 && !BMN), "the residual ring exists for bf16 / tf32 kernels with TMA-fed operands");
   constexpr int kStages = S::kStages;
   constexpr int kElemBytes = TF32 ? 4 : 2;
   constexpr int BK = kTileKBytes / kElemBytes;          // 64 bf16 / 32 tf32
@@ -127,14 +133,16 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
   uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(bars + 3 * kStages + 4);
   volatile int* abortWord = reinterpret_cast<volatile int*>(tmemSlot + 1);
   volatile int* lastFlag = abortWord + 1;       // split-K: whether this CTA's unit arrived last at its tile
+  uint64_t* resFull = bars + 64;                // [8 epilogue warps][4]: a unit of the residual has landed (RES)
   uint8_t* staging = smem + kStages * S::kStageBytes + S::kBarrierBytes;   // 1024-byte aligned
-  constexpr int kStagingPerWarp = 4096;
+  constexpr int kStagingPerWarp = S::kStagingPerWarp;
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbarInit(&full[s], kFullCount); mbarInit(&empty[s], 1); mbarInit(&split[s], 4); }
     for (int a = 0; a < 2; ++a) { mbarInit(&accFull[a], 1); mbarInit(&accEmpty[a], kEpiWarps); }
+    if (RES) for (int i = 0; i < kEpiWarps * 4; ++i) mbarInit(&resFull[i], 1);
     *abortWord = 0;
     fenceBarrierInit();
   }
@@ -240,19 +248,46 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
     }
   } else if (warp < 2 + kEpiWarps) {
     // ---------------------------------------------------------------- epilogue
-    // Warp w reads TMEM lanes 32*(w%4)..+31 (a hardware rule) and the column share (w-2)/4 of the tile.
+    // Warp w reads TMEM lanes 32*(w%4)..+31 (a hardware rule) and the column share (w-2)/4 of the tile, in chunks of 32
+    // columns; the accumulator load of chunk i+1 is in flight while chunk i is worked on.  Results leave as units of
+    // 32 rows x 64 bytes (32 bf16 or 16 fp32 columns, 64-byte swizzle), each staged in shared memory and written by one
+    // TMA store, so that the store of a unit overlaps the arithmetic of the next.
+    //   RES kernels: a warp owns a ring of four unit buffers.  The residual of a unit is loaded into its buffer by TMA
+    //   three units ahead (across tile boundaries: it depends on nothing the MMAs produce), the lane adds its row,
+    //   writes the result back into the same buffer and the store takes it from there.
+    //   Other kernels: two output slots used in turn; a residual, if any, comes through registers (below).
     const int q = warp & 3, half = (warp - 2) >> 2;
     constexpr int kColsPerWarp = BN / (kEpiWarps / 4);
+    constexpr int kChunks = kColsPerWarp / 32;
+    constexpr bool kPrefetch = kChains == 1 && !CONV;           // tf32x3 adds several accumulators per chunk, and the gather form has no registers to spare
+    constexpr uint32_t kRing = RES ? 4u : 2u;
     char* outBase = reinterpret_cast<char*>(p.out);
     const bool outF32 = p.out_dtype == LLC_FLOAT32;
-    const int tmaW = p.tmaOut;                                  // bytes per staged row; 0: direct stores
-    uint8_t* outStage = staging + (warp - 2) * kStagingPerWarp;
-    auto stagedRow = [&](int c) -> uint4 {                       // 16-byte piece c of this lane's row of the staged box
-      uint4 r;
-      asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(r.x), "=r"(r.y), "=r"(r.z), "=r"(r.w)
-                   : "r"(smemAddr(outStage) + (uint32_t)lane * 128u + ((((uint32_t)c) ^ ((uint32_t)lane & 7u)) << 4)) : "memory");
-      return r;
+    const bool tma = RES || p.tmaOut != 0;
+    const int esz = outF32 ? 4 : 2;
+    const int unitCols = 64 / esz;                              // columns of one staged unit
+    const int nUnits = kColsPerWarp / unitCols;                 // units of this warp per tile
+    uint8_t* const warpStaging = staging + (warp - 2) * kStagingPerWarp;
+    const uint32_t slotBase = smemAddr(warpStaging);
+    uint64_t* const myResFull = resFull + (warp - 2) * 4;
+    uint32_t slotIt = 0;                                        // units this warp has staged so far; the buffer in use is slotIt % kRing
+    // 16-byte piece c of row r of a unit buffer (64-byte swizzle: the piece index is XORed with bits 1-2 of the row)
+    auto pieceAddr = [&](uint32_t slot, uint32_t r, uint32_t c) { return slotBase + (slot << 11) + r * 64u + ((c ^ ((r >> 1) & 3u)) << 4); };
+    auto acquireSlot = [&]() { if (lane == 0) bulkWaitRead1(); __syncwarp(); };   // the store before the last has read its slot
+    // RES: starts the TMA load of the residual of this warp's unit number m (counted over all its tiles) into buffer m % 4
+    auto loadResUnit = [&](uint32_t m) {
+      const long long um = blockIdx.x + (long long)(m / (uint32_t)nUnits) * gridDim.x;
+      if (um >= units) return;                                   // past this CTA's last tile: nobody will wait for it
+      const int g = (int)(m % (uint32_t)nUnits);
+      const int z = (int)(um / tilesPerBatch); const int rem = (int)(um - z * tilesPerBatch);
+      const int tM = rem / p.nTiles, tN = rem - tM * p.nTiles;
+      const int z0 = z / p.b1, z1 = z - z0 * p.b1;
+      uint64_t* bar = &myResFull[m & 3u];
+      mbarExpectTx(bar, 2048);
+      tmaLoad4d(warpStaging + ((m & 3u) << 11), &mapR, bar, tN * BN + half * kColsPerWarp + g * unitCols, tM * BM + q * 32, z1 * p.rZ1, z0 * p.rZ0);
     };
+    if (RES && lane == 0) { prefetchTensorMap(&mapR); loadResUnit(0); loadResUnit(1); loadResUnit(2); }
+    if (tma && lane == 0) prefetchTensorMap(&mapO);
     uint32_t tcount = 0;
     for (long long u = blockIdx.x; u < units; u += gridDim.x, ++tcount) {
       long long t; int kb0, kb1; sliceOf(u, t, kb0, kb1);
@@ -262,31 +297,85 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
       const int ab = tcount & 1; const uint32_t aph = (tcount >> 1) & 1;
       const long long gm = (long long)tileM * BM + q * 32 + lane;
       const bool rowOk = gm < p.M;
+      const bool rowsInside = (long long)tileM * BM + q * 32 < p.M;          // this warp's 32 rows are not all past the edge
       const long long oRow = zb0 * p.o_s0 + zb1 * p.o_s1 + gm * p.o_sm;
       const long long rRow = zb0 * p.r_s0 + zb1 * p.r_s1 + gm * p.r_sm;
-      // Residual tile.  A box of the residual (32 rows x 128 bytes, the same box the output store writes) is fetched with
-      // coalesced 16-byte loads (eight lanes per row), passed through this warp's staging buffer and read back one row
-      // per lane: lane = row is how the accumulator arrives, but loading global memory that way touches 32 lines per
-      // instruction.  The loads of the first box are issued here, while the tile's MMAs still run, those of box b + 1
-      // when box b is taken over.
-      const bool resTile = !CONV && p.resTile && tmaW == 128;   // (the gather kernel has no registers to spare and its layers no residual)
-      // One box is in flight per warp (two were measured no faster and cost 32 registers).
-      const int boxCols = outF32 ? 32 : 64;
-      const int esz = outF32 ? 4 : 2;
-      const int nBoxes = kColsPerWarp / boxCols;
-      uint4 rA[8];
-      auto issueRes = [&](int b) {
-        const int chunk = lane & 7, r0 = lane >> 3;
-        const long long gcol = (long long)tileN * BN + half * kColsPerWarp + b * boxCols + chunk * (16 / esz);
+      // Residual through registers (kernels without the ring).  A unit of the residual (32 rows x 64 bytes, the box
+      // the output store writes) is fetched with coalesced 16-byte loads (four lanes per row, eight rows per
+      // instruction), passed through the staging slot and read back one row per lane: lane = row is how the
+      // accumulator arrives, but loading global memory that way touches 32 lines per instruction.  The loads of unit
+      // g + 1 are issued when unit g is taken over, those of unit 0 while the MMAs still run.
+      const bool resTile = !RES && !CONV && p.resTile && tma;    // (the gather kernel has no registers to spare and its layers no residual)
+      uint4 rA[4];
+      auto issueRes = [&](int g) {
+        const int piece = lane & 3, r0 = lane >> 2;
+        const long long gcol = (long long)tileN * BN + half * kColsPerWarp + (long long)g * unitCols + piece * (16 / esz);
         const char* base = reinterpret_cast<const char*>(p.res) + (zb0 * p.r_s0 + zb1 * p.r_s1 + gcol) * esz;
         const bool colOk = gcol < p.N;
 #pragma unroll
-        for (int j = 0; j < 8; ++j) {
-          const long long gr = (long long)tileM * BM + q * 32 + j * 4 + r0;
+        for (int j = 0; j < 4; ++j) {
+          const long long gr = (long long)tileM * BM + q * 32 + j * 8 + r0;
           rA[j] = (gr < p.M && colOk) ? __ldg(reinterpret_cast<const uint4*>(base + gr * p.r_sm * esz)) : make_uint4(0u, 0u, 0u, 0u);
         }
       };
-      const bool splitK = p.splits > 1;
+      // The lane's own row of the residual of the unit in buffer `slot`, as four 16-byte pieces.
+      auto ownRow = [&](uint32_t slot, uint4* own) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          asm volatile("ld.shared.v4.b32 {%0, %1, %2, %3}, [%4];" : "=r"(own[c].x), "=r"(own[c].y), "=r"(own[c].z), "=r"(own[c].w)
+                       : "r"(pieceAddr(slot, (uint32_t)lane, (uint32_t)c)) : "memory");
+      };
+      // Takes unit g over (register path): the residual rows go through the acquired slot, the next unit's loads start.
+      auto residualRow = [&](int g, uint4* own) {
+        const uint32_t slot = slotIt % kRing;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          const uint4 r = rA[j];
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(pieceAddr(slot, (uint32_t)(j * 8 + (lane >> 2)), (uint32_t)(lane & 3))), "r"(r.x), "r"(r.y),
+                       "r"(r.z), "r"(r.w) : "memory");
+        }
+        __syncwarp();                                            // from here on every lane touches only its own row
+        if (g + 1 < nUnits) issueRes(g + 1);
+        ownRow(slot, own);
+      };
+      // Ring path: waits for the residual of the current unit to land and reads the lane's row.
+      auto ringRow = [&](uint4* own) {
+        if (!mbarWait(&myResFull[slotIt & 3u], (slotIt >> 2) & 1u, abortWord)) atomicExch(&g_tcStatus, 4);
+        ownRow(slotIt & 3u, own);
+      };
+      // Hands the staged unit to the TMA store (columns from x0 on; rows past M and columns past N are clipped by the
+      // store).  A group is committed even when nothing is stored, so that "all but the latest group" always means
+      // "every unit before this one".  RES: the buffer of the unit before this one is then free for the residual of
+      // the unit three ahead.
+      auto storeUnit = [&](long long x0) {
+        fenceProxyAsync();
+        __syncwarp();
+        if (lane == 0) {
+          if (rowsInside && x0 < p.N) tmaStore4d(&mapO, warpStaging + ((slotIt % kRing) << 11), (int)x0, tileM * BM + q * 32, zb1, zb0);
+          bulkCommit();
+          if (RES) { bulkWaitRead1(); loadResUnit(slotIt + 3u); }
+        }
+        ++slotIt;
+      };
+      auto stageF32 = [&](const float* w) {                      // 16 fp32 values -> the lane's row of the current buffer
+        const uint32_t slot = slotIt % kRing;
+#pragma unroll
+        for (int c = 0; c < 4; ++c)
+          asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(pieceAddr(slot, (uint32_t)lane, (uint32_t)c)), "f"(w[4 * c]), "f"(w[4 * c + 1]),
+                       "f"(w[4 * c + 2]), "f"(w[4 * c + 3]) : "memory");
+      };
+      auto stageBf16 = [&](const float* w) {                     // 32 fp32 values, rounded to bf16
+        const uint32_t slot = slotIt % kRing;
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          const __nv_bfloat162 a0 = __floats2bfloat162_rn(w[8 * c], w[8 * c + 1]), a1 = __floats2bfloat162_rn(w[8 * c + 2], w[8 * c + 3]);
+          const __nv_bfloat162 a2 = __floats2bfloat162_rn(w[8 * c + 4], w[8 * c + 5]), a3 = __floats2bfloat162_rn(w[8 * c + 6], w[8 * c + 7]);
+          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(pieceAddr(slot, (uint32_t)lane, (uint32_t)c)),
+                       "r"(*reinterpret_cast<const unsigned*>(&a0)), "r"(*reinterpret_cast<const unsigned*>(&a1)), "r"(*reinterpret_cast<const unsigned*>(&a2)),
+                       "r"(*reinterpret_cast<const unsigned*>(&a3)) : "memory");
+        }
+      };
+      const bool splitK = !RES && p.splits > 1;
       if (resTile && !splitK) issueRes(0);
       if (!mbarWait(&accFull[ab], aph, abortWord)) atomicExch(&g_tcStatus, 4);   // carry on with whatever is there: every warp must still reach the barriers below
       tcFenceAfter();
@@ -302,7 +391,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         // (warp, lane) position of their CTAs, so the layout needs to make sense to nobody else.
         float4* mine = reinterpret_cast<float4*>(p.ws + (size_t)u * BM * BN) + (size_t)((half * 4 + q) * (kColsPerWarp / 4)) * 32 + lane;
 #pragma unroll 1
-        for (int ci = 0; ci < kColsPerWarp / 32; ++ci) {
+        for (int ci = 0; ci < kChunks; ++ci) {
           const int c0 = half * kColsPerWarp + ci * 32;
           float v[32];
           __syncwarp();
@@ -335,8 +424,11 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         wsRow = reinterpret_cast<const float4*>(p.ws + (size_t)(t * p.splits) * BM * BN) + (size_t)((half * 4 + q) * (kColsPerWarp / 4)) * 32 + lane;
         if (resTile) issueRes(0);
       }
+      const bool pipelined = kPrefetch && !splitK;
+      uint32_t raw[32];
+      if (pipelined) { __syncwarp(); tmemIssue32(acc + (uint32_t)(half * kColsPerWarp), raw); }
 #pragma unroll 1
-      for (int ci = 0; ci < kColsPerWarp / 32; ++ci) {
+      for (int ci = 0; ci < kChunks; ++ci) {
         const int c0 = half * kColsPerWarp + ci * 32;
         float v[32];
         if (splitK) {                                   // the slices' partial sums, from the workspace (L2)
@@ -346,19 +438,24 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
 #pragma unroll
             for (int j = 0; j < 8; ++j) { const float4 f = __ldcg(wsRow + (size_t)sl * (BM * BN / 4) + (ci * 8 + j) * 32); v[4 * j] += f.x; v[4 * j + 1] += f.y; v[4 * j + 2] += f.z; v[4 * j + 3] += f.w; }
           }
-        } else {
-        __syncwarp();                                   // the load is warp-collective
-        tmemLoad32x32(acc + (uint32_t)c0, v);
-        if (kChains > 1) {
-          for (int ch = 1; ch < usedChains; ++ch) {
-            float w[32];
-            tmemLoad32x32(acc + (uint32_t)(ch * BN + c0), w);
+        } else if (pipelined) {
+          tmemWait32(raw);
 #pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] += w[j];
+          for (int j = 0; j < 32; ++j) v[j] = __uint_as_float(raw[j]);
+          if (ci + 1 < kChunks) { __syncwarp(); tmemIssue32(acc + (uint32_t)(c0 + 32), raw); }
+        } else {
+          __syncwarp();                                 // the load is warp-collective
+          tmemLoad32x32(acc + (uint32_t)c0, v);
+          if (kChains > 1) {
+            for (int ch = 1; ch < usedChains; ++ch) {
+              float w[32];
+              tmemLoad32x32(acc + (uint32_t)(ch * BN + c0), w);
+#pragma unroll
+              for (int j = 0; j < 32; ++j) v[j] += w[j];
+            }
           }
         }
-        }
-        if (!splitK && c0 + 32 >= (half + 1) * kColsPerWarp) {     // this warp's share is in registers: hand the accumulator back
+        if (!splitK && ci == kChunks - 1) {             // this warp's share is in registers: hand the accumulator back
           tcFenceBefore();
           __syncwarp();
           if (lane == 0) mbarArrive(&accEmpty[ab]);
@@ -366,99 +463,92 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         const long long gn0 = (long long)tileN * BN + c0;
         const bool inside = gn0 < p.N;
         const bool whole = p.vecOut && gn0 + 32 <= p.N;
-        bool packed = false;
-        __nv_bfloat162 pk[16];
-        const int sub = (tmaW == 128 && !outF32) ? (ci & 1) : 0;          // bf16: two chunks fill a 128-byte row of the box
-        const long long x0 = gn0 - sub * 32;
-        if (tmaW && sub == 0 && x0 < p.N) {
-          if (lane == 0) bulkWaitRead();                                  // the previous store has read the staging buffer
-          __syncwarp();
-          if (resTile) {
-            const uint32_t st = smemAddr(outStage);
-            const int b = (ci * 32) / boxCols;
+        const int g0 = (ci * 32) / unitCols;              // first unit of this chunk
+        // v = alpha * scale[n] * v + shift[n]: one multiply-add per element with the folded per-column factors
+        if (whole) {
+          const float4* sc = p.scale ? reinterpret_cast<const float4*>(p.scale + gn0) : nullptr;
+          const float4* sh = p.shift ? reinterpret_cast<const float4*>(p.shift + gn0) : nullptr;
+          if (sc || sh || p.alpha != 1.f) {
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
-              const uint32_t row = (uint32_t)(j * 4 + (lane >> 3));
-              const uint4 r = rA[j];
-              asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(st + row * 128u + ((((uint32_t)lane & 7u) ^ (row & 7u)) << 4)), "r"(r.x), "r"(r.y),
-                           "r"(r.z), "r"(r.w) : "memory");
+              float4 s4 = sc ? __ldg(sc + j) : make_float4(1.f, 1.f, 1.f, 1.f);
+              const float4 b4 = sh ? __ldg(sh + j) : make_float4(0.f, 0.f, 0.f, 0.f);
+              s4.x *= p.alpha; s4.y *= p.alpha; s4.z *= p.alpha; s4.w *= p.alpha;
+              v[4 * j] = fmaf(v[4 * j], s4.x, b4.x); v[4 * j + 1] = fmaf(v[4 * j + 1], s4.y, b4.y);
+              v[4 * j + 2] = fmaf(v[4 * j + 2], s4.z, b4.z); v[4 * j + 3] = fmaf(v[4 * j + 3], s4.w, b4.w);
             }
-            __syncwarp();                                                 // from here on every lane touches only its own row
-            if (b + 1 < nBoxes) issueRes(b + 1);
+          }
+        } else if (inside) {
+          // ragged edge (the last column tile, or vectors that are not 16-byte aligned): element by element
+#pragma unroll
+          for (int j = 0; j < 32; ++j) {
+            const long long n = gn0 + j;
+            if (n < p.N) {
+              float x = v[j] * p.alpha;
+              if (p.scale) x *= __ldg(p.scale + n);
+              if (p.shift) x += __ldg(p.shift + n);
+              v[j] = x;
+            }
           }
         }
-        if (whole) {
-          // whole chunk inside the matrix: flag tests hoisted out of the element loops
-          if (p.scale) {
-            const float4* sc = reinterpret_cast<const float4*>(p.scale + gn0);
-            if (p.shift) {                                // the folded batch norm: one fused multiply-add per element
-              const float4* sh = reinterpret_cast<const float4*>(p.shift + gn0);
+        auto activate = [&](float* w, int count) {
+          if (p.act == LLC_ACT_RELU) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                float4 s4 = __ldg(sc + j); const float4 b4 = __ldg(sh + j);
-                if (p.alpha != 1.f) { s4.x *= p.alpha; s4.y *= p.alpha; s4.z *= p.alpha; s4.w *= p.alpha; }
-                v[4 * j] = fmaf(v[4 * j], s4.x, b4.x); v[4 * j + 1] = fmaf(v[4 * j + 1], s4.y, b4.y);
-                v[4 * j + 2] = fmaf(v[4 * j + 2], s4.z, b4.z); v[4 * j + 3] = fmaf(v[4 * j + 3], s4.w, b4.w);
-              }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) { float4 s4 = __ldg(sc + j); v[4 * j] *= p.alpha * s4.x; v[4 * j + 1] *= p.alpha * s4.y; v[4 * j + 2] *= p.alpha * s4.z; v[4 * j + 3] *= p.alpha * s4.w; }
-            }
-          } else if (p.shift) {
-            const float4* sh = reinterpret_cast<const float4*>(p.shift + gn0);
-            if (p.alpha != 1.f) {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) { const float4 b4 = __ldg(sh + j); v[4 * j] = fmaf(v[4 * j], p.alpha, b4.x); v[4 * j + 1] = fmaf(v[4 * j + 1], p.alpha, b4.y); v[4 * j + 2] = fmaf(v[4 * j + 2], p.alpha, b4.z); v[4 * j + 3] = fmaf(v[4 * j + 3], p.alpha, b4.w); }
-            } else {
-#pragma unroll
-              for (int j = 0; j < 8; ++j) { const float4 b4 = __ldg(sh + j); v[4 * j] += b4.x; v[4 * j + 1] += b4.y; v[4 * j + 2] += b4.z; v[4 * j + 3] += b4.w; }
-            }
-          } else if (p.alpha != 1.f) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] *= p.alpha;
-          }
-          // bf16 output through the staging buffer: residual add and ReLU on packed pairs after the conversion (the
-          // rounding order of a bf16 graph: the producer's result is rounded, then added to the bf16 residual)
-          packed = !TF32 && !outF32 && tmaW != 0 && (!p.res || resTile) && !(p.act == LLC_ACT_GELU && p.res);
-          if (packed) {
-            if (p.act == LLC_ACT_GELU) {
-#pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = geluTanhBf16(v[j]);
-            }
-#pragma unroll
-            for (int j = 0; j < 16; ++j) pk[j] = __floats2bfloat162_rn(v[2 * j], v[2 * j + 1]);
-            if (resTile) {
-#pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint4 r = stagedRow((ci & 1) * 4 + j);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) pk[4 * j + e] = __hadd2(pk[4 * j + e], h[e]);
-              }
-            }
-            if (p.act == LLC_ACT_RELU) {
-              const __nv_bfloat162 zero2 = __floats2bfloat162_rn(0.f, 0.f);
-#pragma unroll
-              for (int j = 0; j < 16; ++j) pk[j] = __hmax2(pk[j], zero2);
-            }
-          } else {
-          if (resTile) {
+            for (int j = 0; j < 32; ++j) if (j < count) w[j] = fmaxf(w[j], 0.f);
+          } else if (p.act == LLC_ACT_GELU) {
             if (outF32) {
 #pragma unroll
-              for (int j = 0; j < 8; ++j) {
-                const uint4 r = stagedRow(j);
-                v[4 * j] += __uint_as_float(r.x); v[4 * j + 1] += __uint_as_float(r.y);
-                v[4 * j + 2] += __uint_as_float(r.z); v[4 * j + 3] += __uint_as_float(r.w);
-              }
+              for (int j = 0; j < 32; ++j) if (j < count) w[j] = geluFast(w[j]);
             } else {
 #pragma unroll
-              for (int j = 0; j < 4; ++j) {
-                const uint4 r = stagedRow((ci & 1) * 4 + j);
-                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&r);
-#pragma unroll
-                for (int e = 0; e < 4; ++e) { float2 f = __bfloat1622float2(h[e]); v[8 * j + 2 * e] += f.x; v[8 * j + 2 * e + 1] += f.y; }
-              }
+              for (int j = 0; j < 32; ++j) if (j < count) w[j] = geluTanhBf16(w[j]);
             }
+          }
+        };
+        if constexpr (RES) {
+          // every unit of every tile goes through the ring, inside the matrix or not (loads past the edge read zeros,
+          // stores past the edge write nothing), so that buffers and barrier phases advance uniformly
+          if (outF32) {
+#pragma unroll
+            for (int un = 0; un < 2; ++un) {
+              uint4 own[4];
+              ringRow(own);
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                v[un * 16 + 4 * c] += __uint_as_float(own[c].x); v[un * 16 + 4 * c + 1] += __uint_as_float(own[c].y);
+                v[un * 16 + 4 * c + 2] += __uint_as_float(own[c].z); v[un * 16 + 4 * c + 3] += __uint_as_float(own[c].w);
+              }
+              activate(v + un * 16, 16);
+              stageF32(v + un * 16);
+              storeUnit(gn0 + un * 16);
+            }
+          } else {
+            uint4 own[4];
+            ringRow(own);
+#pragma unroll
+            for (int c = 0; c < 4; ++c) {
+              const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&own[c]);
+#pragma unroll
+              for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); v[8 * c + 2 * e] += f.x; v[8 * c + 2 * e + 1] += f.y; }
+            }
+            activate(v, 32);
+            stageBf16(v);
+            storeUnit(gn0);
+          }
+        } else if (whole) {
+          // residual, in fp32 (one rounding for the sum, whatever the storage type)
+          bool slotHeld = false;                            // bf16: the unit's slot was acquired for the residual already
+          if (resTile) {
+            if (!outF32) {
+              uint4 own[4];
+              acquireSlot(); residualRow(g0, own); slotHeld = true;
+#pragma unroll
+              for (int c = 0; c < 4; ++c) {
+                const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&own[c]);
+#pragma unroll
+                for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); v[8 * c + 2 * e] += f.x; v[8 * c + 2 * e + 1] += f.y; }
+              }
+            }                                               // fp32: two units per chunk, each takes its residual below
           } else if (p.res && rowOk) {
             if (p.r_sn == 1 && p.res_dtype == LLC_BFLOAT16 && ((rRow + gn0) & 3) == 0) {
               const __nv_bfloat16* rp = reinterpret_cast<const __nv_bfloat16*>(p.res) + rRow + gn0;
@@ -473,73 +563,32 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
               for (int j = 0; j < 32; ++j) v[j] += loadAs(p.res, rRow + (gn0 + j) * p.r_sn, p.res_dtype);
             }
           }
-          if (p.act == LLC_ACT_RELU) {
-#pragma unroll
-            for (int j = 0; j < 32; ++j) v[j] = fmaxf(v[j], 0.f);
-          } else if (p.act == LLC_ACT_GELU) {
+          // (with fp32 output and a residual tile the activation follows the residual, unit by unit, below)
+          if (!(resTile && outF32)) activate(v, 32);
+          if (tma) {
             if (outF32) {
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = geluFast(v[j]);
-            } else {
+              for (int un = 0; un < 2; ++un) {
+                acquireSlot();
+                if (resTile) {
+                  uint4 own[4];
+                  residualRow(g0 + un, own);
 #pragma unroll
-              for (int j = 0; j < 32; ++j) v[j] = geluTanhBf16(v[j]);
-            }
-          }
-          }
-        } else if (inside && rowOk) {
-          // ragged edge: element by element
-#pragma unroll
-          for (int j = 0; j < 32; ++j) {
-            const long long n = gn0 + j;
-            if (n < p.N) {
-              float x = v[j] * p.alpha;
-              if (p.scale) x *= __ldg(p.scale + n);
-              if (p.shift) x += __ldg(p.shift + n);
-              if (p.res) x += loadAs(p.res, rRow + n * p.r_sn, p.res_dtype);
-              v[j] = applyAct(x, p.act);
-            }
-          }
-        }
-        if (tmaW) {
-          // Stage the rows in shared memory (swizzled: conflict-free 16-byte writes) and let one TMA
-          // store write them out as whole lines; rows >= M and columns >= N are clipped by the store.
-          const bool closes = outF32 || tmaW == 64 || sub == 1;
-          if (x0 < p.N) {
-            if (inside) {
-              const uint32_t rowOff = (uint32_t)lane * (uint32_t)tmaW;
-              const uint32_t swz = (rowOff >> 7) & (uint32_t)(tmaW / 16 - 1);
-              const uint32_t rowAddr = smemAddr(outStage) + rowOff;
-              if (outF32) {
-#pragma unroll
-                for (int j = 0; j < 8; ++j)
-                  asm volatile("st.shared.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + (((uint32_t)j ^ swz) << 4)), "f"(v[4 * j]), "f"(v[4 * j + 1]),
-                               "f"(v[4 * j + 2]), "f"(v[4 * j + 3]) : "memory");
-              } else {
-#pragma unroll
-                for (int j = 0; j < 4; ++j) {
-                  __nv_bfloat162 a0, a1, a2, a3;
-                  if (packed) { a0 = pk[4 * j]; a1 = pk[4 * j + 1]; a2 = pk[4 * j + 2]; a3 = pk[4 * j + 3]; }
-                  else {
-                    a0 = __floats2bfloat162_rn(v[8 * j], v[8 * j + 1]); a1 = __floats2bfloat162_rn(v[8 * j + 2], v[8 * j + 3]);
-                    a2 = __floats2bfloat162_rn(v[8 * j + 4], v[8 * j + 5]); a3 = __floats2bfloat162_rn(v[8 * j + 6], v[8 * j + 7]);
+                  for (int c = 0; c < 4; ++c) {
+                    v[un * 16 + 4 * c] += __uint_as_float(own[c].x); v[un * 16 + 4 * c + 1] += __uint_as_float(own[c].y);
+                    v[un * 16 + 4 * c + 2] += __uint_as_float(own[c].z); v[un * 16 + 4 * c + 3] += __uint_as_float(own[c].w);
                   }
-                  asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + (((uint32_t)(sub * 4 + j) ^ swz) << 4)),
-                               "r"(*reinterpret_cast<unsigned*>(&a0)), "r"(*reinterpret_cast<unsigned*>(&a1)), "r"(*reinterpret_cast<unsigned*>(&a2)),
-                               "r"(*reinterpret_cast<unsigned*>(&a3)) : "memory");
+                  activate(v + un * 16, 16);
                 }
+                stageF32(v + un * 16);
+                storeUnit(gn0 + un * 16);
               }
+            } else {
+              if (!slotHeld) acquireSlot();
+              stageBf16(v);
+              storeUnit(gn0);
             }
-            if (closes) {
-              fenceProxyAsync();
-              __syncwarp();
-              if (lane == 0 && (long long)tileM * BM + q * 32 < p.M) {
-                tmaStore4d(&mapO, outStage, (int)x0, tileM * BM + q * 32, zb1, zb0);
-                bulkCommit();
-              }
-            }
-          }
-        } else if (inside && rowOk) {
-          if (whole) {
+          } else if (rowOk) {
             if (outF32) {
               float* dst = reinterpret_cast<float*>(outBase) + oRow + gn0;
 #pragma unroll
@@ -561,7 +610,30 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
                 for (int j = 0; j < 32; j += 4) Vec4<__nv_bfloat16>::store(d2 + j, make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]));
               }
             }
-          } else {
+          }
+        } else if (inside) {
+          // ragged edge, continued: residual and activation element by element, then staged units or scalar stores
+          if (rowOk) {
+#pragma unroll
+            for (int j = 0; j < 32; ++j) {
+              const long long n = gn0 + j;
+              if (n < p.N) {
+                float x = v[j];
+                if (p.res) x += loadAs(p.res, rRow + n * p.r_sn, p.res_dtype);
+                v[j] = applyAct(x, p.act);
+              }
+            }
+          }
+          if (tma) {
+            if (outF32) {
+#pragma unroll
+              for (int un = 0; un < 2; ++un) {
+                if (gn0 + un * 16 < p.N) { acquireSlot(); stageF32(v + un * 16); storeUnit(gn0 + un * 16); }
+              }
+            } else {
+              acquireSlot(); stageBf16(v); storeUnit(gn0);
+            }
+          } else if (rowOk) {
 #pragma unroll
             for (int j = 0; j < 32; ++j)
               if (gn0 + j < p.N) storeAs(p.out, oRow + gn0 + j, p.out_dtype, v[j]);
@@ -569,7 +641,7 @@ tc_kernel(const __grid_constant__ CUtensorMap mapA, const __grid_constant__ CUte
         }
       }
     }
-    if (tmaW && lane == 0) bulkWaitRead();   // shared memory stays valid until the last store has read it
+    if (tma && lane == 0) bulkWaitRead();   // shared memory stays valid until the last store has read it
   } else if (CONV && warp < kGatherWarp0 + kGatherWarps) {
     // ---------------------------------------------------------------- im2col gather of A (convolution)
     // 256 threads; thread g owns 16-byte chunk (g & 7) of tile rows (g >> 3) + 32*j, j = 0..3, so that
@@ -771,8 +843,33 @@ bool makeOutMap(CUtensorMap* map, void* base, bool f32, long long N, long long M
                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
-// Bytes per row of the output box: a 32-column chunk of fp32, or as much of a warp's share of bf16 columns as fits 128 bytes.
-int outBoxBytes(int bn, bool outF32) { return outF32 ? 128 : (bn / 2 >= 64 ? 128 : 64); }
+// Residual [b0, b1, M, N] (unit stride along N, batch dims possibly broadcast) -> the same 64-byte x 32-row boxes as the
+// output map, for the ring of TMA loads in the RES kernels.  `has1` / `has0` tell whether the batch coordinates apply.
+bool makeResMap(CUtensorMap* map, const void* base, bool f32, long long N, long long M, long long b1, long long b0, long long sRow, long long s1,
+                long long s0, bool* has1Out, bool* has0Out) {
+  EncodeTiledFn enc = encodeTiled();
+  if (!enc) return false;
+  const int eb = f32 ? 4 : 2;
+  const bool has1 = b1 > 1 && s1 > 0, has0 = b0 > 1 && s0 > 0;
+  auto ok16 = [&](long long s) { return s > 0 && (s * eb) % 16 == 0; };
+  if ((reinterpret_cast<uintptr_t>(base) & 15) || !ok16(sRow) || sRow < N || (has1 && !ok16(s1)) || (has0 && !ok16(s0))) return false;
+  if ((b1 > 1 && s1 < 0) || (b0 > 1 && s0 < 0) || N > (1LL << 31) || M > (1LL << 31)) return false;
+  const long long dense = sRow * M;
+  cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)(has1 ? b1 : 1), (cuuint64_t)(has0 ? b0 : 1)};
+  cuuint64_t strides[3] = {(cuuint64_t)(sRow * eb), (cuuint64_t)((has1 ? s1 : dense) * eb), (cuuint64_t)((has0 ? s0 : dense) * eb)};
+  cuuint32_t box[4] = {(cuuint32_t)(64 / eb), 32, 1, 1};
+  cuuint32_t estr[4] = {1, 1, 1, 1};
+  *has1Out = has1; *has0Out = has0;
+  return enc(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 4, const_cast<void*>(base), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+// LLC_TC_RES_RING=0 keeps residuals on the register path (used to compare the two).
+bool resRingEnabled() {
+  static const bool on = []() { const char* e = getenv("LLC_TC_RES_RING"); return !(e && e[0] == '0'); }();
+  return on;
+}
+// Bytes per row of the output box the epilogue stages and stores: 32 bf16 or 16 fp32 columns.
+constexpr int kOutBoxBytes = 64;
 
 int numSMs() { return deviceSMs(); }
 
@@ -789,33 +886,39 @@ bool tmaEpilogueEnabled() {
   return on;
 }
 
-template <int BN, int KIND, int MODE, bool BMN>
-int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mbl, TcArgs a, long long batch, cudaStream_t st) {
-  using S = Smem<BN, KIND == 2>;
+template <int BN, int KIND, int MODE, bool BMN, bool RES>
+int launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mbl, const CUtensorMap& mr, TcArgs a, long long batch, cudaStream_t st) {
+  using S = Smem<BN, KIND == 2, RES>;
+  static_assert(S::kStages >= 2, "at least two pipeline stages");
   static DeviceOnce configured;                          // the shared-memory opt-in is kept per device
   const int dev = currentDevice();
   if (!configured.test(dev)) {
-    cudaError_t e = cudaFuncSetAttribute(tc_kernel<BN, KIND, MODE, BMN>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
+    cudaError_t e = cudaFuncSetAttribute(tc_kernel<BN, KIND, MODE, BMN, RES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal);
     if (e != cudaSuccess) return cudaFail(e, "cudaFuncSetAttribute(tc_kernel)");
     configured.set(dev);
   }
   a.mTiles = (int)((a.M + BM - 1) / BM); a.nTiles = (int)((a.N + BN - 1) / BN);
   a.tiles = (long long)a.mTiles * a.nTiles * batch;
-  if (a.splits < 1) a.splits = 1;
+  if (a.splits < 1 || RES) a.splits = 1;
   const int threads = tcThreads(KIND, MODE);
   const long long units = a.tiles * a.splits;
   const unsigned grid = (unsigned)(units < numSMs() ? units : numSMs());
-  tc_kernel<BN, KIND, MODE, BMN><<<grid, threads, S::kTotal, st>>>(ma, mb, mo, mbl, a);
+  tc_kernel<BN, KIND, MODE, BMN, RES><<<grid, threads, S::kTotal, st>>>(ma, mb, mo, mbl, mr, a);
   LLC_LAUNCH_CHECK("tc_kernel");
   return LLC_OK;
 }
 
+// `res`: the kernel variant whose epilogue fetches the residual through a ring of TMA loads (bf16 / tf32, TMA-fed operands).
 template <int MODE, bool BMN>
-int dispatch(int bn, int kind, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mbl, const TcArgs& a, long long batch, cudaStream_t st) {
-#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_) return launch<BN_, K_, MODE, BMN>(ma, mb, mo, mbl, a, batch, st);
+int dispatch(int bn, int kind, bool res, const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mo, const CUtensorMap& mbl, const CUtensorMap& mr,
+             const TcArgs& a, long long batch, cudaStream_t st) {
+#define TC_CASE(BN_, K_) if (bn == BN_ && kind == K_ && !res) return launch<BN_, K_, MODE, BMN, false>(ma, mb, mo, mbl, mr, a, batch, st);
+#define TC_CASE_RES(BN_, K_) if (bn == BN_ && kind == K_ && res) return launch<BN_, K_, MODE, BMN, true>(ma, mb, mo, mbl, mr, a, batch, st);
   TC_CASE(64, 0) TC_CASE(128, 0)
   if constexpr (!BMN) { TC_CASE(64, 1) TC_CASE(64, 2) TC_CASE(128, 1) TC_CASE(128, 2) TC_CASE(256, 0) TC_CASE(256, 1) }
+  if constexpr (!BMN && MODE != 1) { TC_CASE_RES(64, 0) TC_CASE_RES(128, 0) TC_CASE_RES(256, 0) TC_CASE_RES(64, 1) TC_CASE_RES(128, 1) TC_CASE_RES(256, 1) }
 #undef TC_CASE
+#undef TC_CASE_RES
   return setError(LLC_ERR_INTERNAL, "llc internal: no tensor-core kernel for this tile");
 }
 
@@ -907,8 +1010,7 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   a.vecOut = (reinterpret_cast<uintptr_t>(p->out) % (ob * 4)) == 0 && p->o_sm % 4 == 0 && p->o_s0 % 4 == 0 && p->o_s1 % 4 == 0 &&
              ((reinterpret_cast<uintptr_t>(p->scale) | reinterpret_cast<uintptr_t>(p->shift)) & 15) == 0;
   CUtensorMap mo = ma;   // a valid map even when unused
-  const int boxBytes = outBoxBytes(bn, ob == 4);
-  if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->n, p->m, p->b1, p->b0, p->o_sm, p->o_s1, p->o_s0, boxBytes)) a.tmaOut = boxBytes;
+  if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->n, p->m, p->b1, p->b0, p->o_sm, p->o_s1, p->o_s0, kOutBoxBytes)) a.tmaOut = kOutBoxBytes;
   auto r16 = [&](long long st) { return st >= 0 && (st * ob) % 16 == 0; };
   a.resTile = p->res && p->r_sn == 1 && p->res_dtype == p->out_dtype && (reinterpret_cast<uintptr_t>(p->res) & 15) == 0 && r16(p->r_sm) && r16(p->r_s0) &&
               r16(p->r_s1) && p->n % (16 / ob) == 0;
@@ -916,7 +1018,14 @@ int tcGemm(const LlcGemmParams* p, cudaStream_t st) {
   if (kind == 2 && !bmn && p->b_lo && (reinterpret_cast<uintptr_t>(p->b_lo) & 15) == 0 &&
       makeMap(&mbl, p->b_lo, f32, p->k, p->n, p->b1, p->b0, p->b_sn, p->b_s1, p->b_s0, bn))
     a.hasBLo = 1;
-  return bmn ? dispatch<0, true>(bn, kind, ma, mb, mo, mbl, a, batch, st) : dispatch<0, false>(bn, kind, ma, mb, mo, mbl, a, batch, st);
+  // the residual through a ring of TMA loads: whole tiles only (no split-K), same element type as the output
+  CUtensorMap mr = mo;
+  bool resRing = false;
+  if (a.resTile && a.tmaOut && plan.splits == 1 && kind != 2 && !bmn && resRingEnabled()) {
+    bool h1 = false, h0 = false;
+    if (makeResMap(&mr, p->res, ob == 4, p->n, p->m, p->b1, p->b0, p->r_sm, p->r_s1, p->r_s0, &h1, &h0)) { resRing = true; a.rZ1 = h1; a.rZ0 = h0; }
+  }
+  return bmn ? dispatch<0, true>(bn, kind, false, ma, mb, mo, mbl, mr, a, batch, st) : dispatch<0, false>(bn, kind, resRing, ma, mb, mo, mbl, mr, a, batch, st);
 }
 
 bool tcConvSupported(const LlcConvParams* p) {
@@ -960,17 +1069,24 @@ int tcConv(const LlcConvParams* p, cudaStream_t st) {
     a.xs_w = dense ? p->c : p->x_sw; a.xs_h = dense ? p->w_in * p->c : p->x_sh; a.xs_n = dense ? p->h * p->w_in * p->c : p->x_sn;
   }
   CUtensorMap mo = mb;
-  const int boxBytes = outBoxBytes(bn, ob == 4);
-  if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->f, M, 1, 1, p->f, 0, 0, boxBytes)) a.tmaOut = boxBytes;
+  if (tmaEpilogueEnabled() && makeOutMap(&mo, p->out, ob == 4, p->f, M, 1, 1, p->f, 0, 0, kOutBoxBytes)) a.tmaOut = kOutBoxBytes;
   a.resTile = p->res && p->res_dtype == p->out_dtype && (reinterpret_cast<uintptr_t>(p->res) & 15) == 0 && (p->f * ob) % 16 == 0;
   CUtensorMap mbl = mb;
   if (kind == 2 && p->w_lo && (reinterpret_cast<uintptr_t>(p->w_lo) & 15) == 0 && makeMap(&mbl, p->w_lo, f32, K, p->f, 1, 1, K, 0, 0, bn)) a.hasBLo = 1;
   if (im2colEligible(p, f32)) {
     CUtensorMap ma;
-    if (makeIm2colMap(&ma, p, f32)) return dispatch<2, false>(bn, kind, ma, mb, mo, mbl, a, 1, st);
+    if (makeIm2colMap(&ma, p, f32)) {
+      CUtensorMap mr = mo;
+      bool resRing = false;
+      if (a.resTile && a.tmaOut && plan.splits == 1 && kind != 2 && resRingEnabled()) {
+        bool h1 = false, h0 = false;
+        if (makeResMap(&mr, p->res, ob == 4, p->f, M, 1, 1, p->f, 0, 0, &h1, &h0)) resRing = true;
+      }
+      return dispatch<2, false>(bn, kind, resRing, ma, mb, mo, mbl, mr, a, 1, st);
+    }
   }
   a.splits = 1;                                          // the gathered form walks whole tiles
-  return dispatch<1, false>(bn, kind, mb, mb, mo, mbl, a, 1, st);
+  return dispatch<1, false>(bn, kind, false, mb, mb, mo, mbl, mo, a, 1, st);
 }
 
 // Device address of the status word on the current device (for callers that copy it back on their own stream).

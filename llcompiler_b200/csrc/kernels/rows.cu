@@ -85,35 +85,89 @@ int launchSoftmaxWarp(const void* x, void* out, long long rows, int len, cudaStr
 }
 
 // ---- LayerNorm -------------------------------------------------------------------------------
+// 16 bytes of a row per lane and load: E = 8 bf16 or 4 fp32 elements.
+template <typename T, int E> __device__ __forceinline__ void unpackVec(const uint4& raw, float* v);
+template <> __device__ __forceinline__ void unpackVec<float, 4>(const uint4& raw, float* v) {
+  v[0] = __uint_as_float(raw.x); v[1] = __uint_as_float(raw.y); v[2] = __uint_as_float(raw.z); v[3] = __uint_as_float(raw.w);
+}
+template <> __device__ __forceinline__ void unpackVec<__nv_bfloat16, 8>(const uint4& raw, float* v) {
+  const __nv_bfloat162* h = reinterpret_cast<const __nv_bfloat162*>(&raw);
+#pragma unroll
+  for (int e = 0; e < 4; ++e) { const float2 f = __bfloat1622float2(h[e]); v[2 * e] = f.x; v[2 * e + 1] = f.y; }
+}
+// E consecutive elements of type T as floats (E * sizeof(T) is 8, 16 or 32 bytes, aligned to min(16, that))
+template <typename T, int E> __device__ __forceinline__ void loadElems(const T* p, float* v) {
+  if constexpr (sizeof(T) * E == 16) { const uint4 raw = __ldg(reinterpret_cast<const uint4*>(p)); unpackVec<T, E>(raw, v); }
+  else if constexpr (sizeof(T) == 4) { unpackVec<float, 4>(__ldg(reinterpret_cast<const uint4*>(p)), v); unpackVec<float, 4>(__ldg(reinterpret_cast<const uint4*>(p) + 1), v + 4); }
+  else { const float4 f = Vec4<T>::load(p); v[0] = f.x; v[1] = f.y; v[2] = f.z; v[3] = f.w; }
+}
+template <typename T, int E> __device__ __forceinline__ void storeElems(T* p, const float* v) {
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int e = 0; e < E; e += 4) *reinterpret_cast<float4*>(p + e) = make_float4(v[e], v[e + 1], v[e + 2], v[e + 3]);
+  } else if constexpr (E == 8) {
+    uint4 o; __nv_bfloat162 h;
+    h = __floats2bfloat162_rn(v[0], v[1]); o.x = *reinterpret_cast<unsigned*>(&h); h = __floats2bfloat162_rn(v[2], v[3]); o.y = *reinterpret_cast<unsigned*>(&h);
+    h = __floats2bfloat162_rn(v[4], v[5]); o.z = *reinterpret_cast<unsigned*>(&h); h = __floats2bfloat162_rn(v[6], v[7]); o.w = *reinterpret_cast<unsigned*>(&h);
+    *reinterpret_cast<uint4*>(p) = o;
+  } else {
+    Vec4<T>::store(p, make_float4(v[0], v[1], v[2], v[3]));
+  }
+}
+
+// One warp per row, rows taken grid-stride; a lane holds NV vectors of 16 bytes of the row.  The next row's loads are
+// issued before the current row's two reductions, so that the statistics of one row hide the memory latency of the next.
 template <typename TI, typename TP, typename TO, int NV>
 __global__ void __launch_bounds__(kWarpsPerBlock * 32) layernorm_warp_kernel(const TI* __restrict__ x, const TP* __restrict__ gamma, const TP* __restrict__ beta,
                                                                               TO* __restrict__ out, long long rows, int d, float eps) {
+  constexpr int E = 16 / sizeof(TI);
+  const int lane = threadIdx.x & 31;
+  const long long warpsTotal = (long long)gridDim.x * kWarpsPerBlock;
   long long row = (long long)blockIdx.x * kWarpsPerBlock + (threadIdx.x >> 5);
   if (row >= rows) return;
-  const int lane = threadIdx.x & 31;
-  const TI* xr = x + row * d;
-  float4 v[NV];
-  float s = 0.f;
+  uint4 nxt[NV];
+  auto fetch = [&](long long r) {
+    const TI* xr = x + r * d;
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    int c = (i * 32 + lane) * 4;
-    if (c < d) { v[i] = ldg4(xr + c); s += (v[i].x + v[i].y) + (v[i].z + v[i].w); }
-  }
-  const float mean = warpSum(s) / (float)d;
-  float q = 0.f;
+    for (int i = 0; i < NV; ++i) { const int c = (i * 32 + lane) * E; if (c < d) nxt[i] = __ldg(reinterpret_cast<const uint4*>(xr + c)); }
+  };
+  fetch(row);
+  const float invD = 1.f / (float)d;
+  for (; row < rows; row += warpsTotal) {
+    float v[NV][E];
+    float s = 0.f;
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    int c = (i * 32 + lane) * 4;
-    if (c < d) { float a = v[i].x - mean, b = v[i].y - mean, e = v[i].z - mean, f = v[i].w - mean; q += (a * a + b * b) + (e * e + f * f); }
-  }
-  const float rstd = rsqrtf(warpSum(q) / (float)d + eps);
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * E;
+      if (c < d) {
+        unpackVec<TI, E>(nxt[i], v[i]);
 #pragma unroll
-  for (int i = 0; i < NV; ++i) {
-    int c = (i * 32 + lane) * 4;
-    if (c < d) {
-      float4 g = ldg4(gamma + c), b = ldg4(beta + c);
-      Vec4<TO>::store(out + row * d + c, make_float4((v[i].x - mean) * rstd * g.x + b.x, (v[i].y - mean) * rstd * g.y + b.y,
-                                                     (v[i].z - mean) * rstd * g.z + b.z, (v[i].w - mean) * rstd * g.w + b.w));
+        for (int e = 0; e < E; ++e) s += v[i][e];
+      }
+    }
+    if (row + warpsTotal < rows) fetch(row + warpsTotal);
+    const float mean = warpSum(s) * invD;
+    float q = 0.f;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * E;
+      if (c < d) {
+#pragma unroll
+        for (int e = 0; e < E; ++e) { const float a = v[i][e] - mean; q = fmaf(a, a, q); }
+      }
+    }
+    const float rstd = rsqrtf(warpSum(q) * invD + eps);
+    TO* orow = out + row * d;
+#pragma unroll
+    for (int i = 0; i < NV; ++i) {
+      const int c = (i * 32 + lane) * E;
+      if (c < d) {
+        float g[E], b[E], o[E];
+        loadElems<TP, E>(gamma + c, g); loadElems<TP, E>(beta + c, b);
+#pragma unroll
+        for (int e = 0; e < E; ++e) o[e] = fmaf((v[i][e] - mean) * rstd, g[e], b[e]);
+        storeElems<TO, E>(orow + c, o);
+      }
     }
   }
 }
@@ -145,11 +199,16 @@ __global__ void __launch_bounds__(256) layernorm_block_kernel(const void* x, con
 
 template <typename TI, typename TP, typename TO>
 int launchLayerNormWarp(const void* x, const void* g, const void* b, void* out, long long rows, int d, float eps, cudaStream_t st) {
-  unsigned blocks = (unsigned)((rows + kWarpsPerBlock - 1) / kWarpsPerBlock);
-  int nv = (d + 127) / 128;
+  constexpr int E = 16 / (int)sizeof(TI);
+  // enough warps to keep every SM full (8 blocks of 8 warps each), each taking its rows grid-stride
+  const long long wantBlocks = (rows + kWarpsPerBlock - 1) / kWarpsPerBlock, cap = (long long)deviceSMs() * 8;
+  const unsigned blocks = (unsigned)(wantBlocks < cap ? wantBlocks : cap);
+  const int nv = (d + 32 * E - 1) / (32 * E);
   const TI* xi = reinterpret_cast<const TI*>(x); const TP* gi = reinterpret_cast<const TP*>(g); const TP* bi = reinterpret_cast<const TP*>(b);
   TO* oo = reinterpret_cast<TO*>(out);
-  if (nv <= 2) layernorm_warp_kernel<TI, TP, TO, 2><<<blocks, kWarpsPerBlock * 32, 0, st>>>(xi, gi, bi, oo, rows, d, eps);
+  if (nv <= 1) layernorm_warp_kernel<TI, TP, TO, 1><<<blocks, kWarpsPerBlock * 32, 0, st>>>(xi, gi, bi, oo, rows, d, eps);
+  else if (nv <= 2) layernorm_warp_kernel<TI, TP, TO, 2><<<blocks, kWarpsPerBlock * 32, 0, st>>>(xi, gi, bi, oo, rows, d, eps);
+  else if (nv <= 3) layernorm_warp_kernel<TI, TP, TO, 3><<<blocks, kWarpsPerBlock * 32, 0, st>>>(xi, gi, bi, oo, rows, d, eps);
   else if (nv <= 4) layernorm_warp_kernel<TI, TP, TO, 4><<<blocks, kWarpsPerBlock * 32, 0, st>>>(xi, gi, bi, oo, rows, d, eps);
   else if (nv <= 6) layernorm_warp_kernel<TI, TP, TO, 6><<<blocks, kWarpsPerBlock * 32, 0, st>>>(xi, gi, bi, oo, rows, d, eps);
   else layernorm_warp_kernel<TI, TP, TO, 8><<<blocks, kWarpsPerBlock * 32, 0, st>>>(xi, gi, bi, oo, rows, d, eps);
@@ -210,7 +269,9 @@ extern "C" int llc_cuda_layernorm(const void* x, const void* gamma, const void* 
   if (rows <= 0 || d <= 0) return LLC_OK;
   if (!x || !out || !gamma || !beta) return setError(LLC_ERR_ARGUMENT, "llc argument: layernorm null pointer");
   cudaStream_t st = (cudaStream_t)stream;
-  bool fast = d % 4 == 0 && d <= 1024 && aligned16(x) && aligned16(out) && aligned16(gamma) && aligned16(beta);
+  // rows of whole 16-byte vectors of the input type, at most 8 of them per lane
+  const int e = idt == LLC_BFLOAT16 ? 8 : 4;
+  bool fast = d % e == 0 && d <= 32 * e * 8 && aligned16(x) && aligned16(out) && aligned16(gamma) && aligned16(beta);
 #define LN_CASE(I, P, O, TI, TP, TO) if (fast && idt == I && pdt == P && odt == O) return launchLayerNormWarp<TI, TP, TO>(x, gamma, beta, out, rows, (int)d, eps, st);
   LN_CASE(LLC_FLOAT32, LLC_FLOAT32, LLC_FLOAT32, float, float, float)
   LN_CASE(LLC_BFLOAT16, LLC_BFLOAT16, LLC_BFLOAT16, __nv_bfloat16, __nv_bfloat16, __nv_bfloat16)

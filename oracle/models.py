@@ -272,10 +272,21 @@ def parity_figures(got: torch.Tensor, want: torch.Tensor, tol: float, k: float =
     return float(diff.max() / top), float((diff / (tol * want.abs() + k * tol * top)).max())
 
 
-def assert_parity(got: torch.Tensor, want: torch.Tensor, tol: float, what: str = "") -> None:
+def assert_parity(got: torch.Tensor, want: torch.Tensor, tol: float, what: str = "", lowp_eager: torch.Tensor | None = None) -> None:
     """Both gates of a configuration's tolerance: the global relative error below `tol` and every element inside
-    rtol = tol, atol = ELEMENTWISE_K * tol * max|want|.  Prints both figures (visible with pytest -s / on failure)."""
+    rtol = tol, atol = ELEMENTWISE_K * tol * max|want|.  Prints both figures (visible with pytest -s / on failure).
+
+    `lowp_eager` is for deep bf16 networks: the output of PyTorch's own bf16 eager run of the same model on the same
+    inputs.  Twelve layers of bf16 storage rounding put some elements outside the element-wise bound whatever kernels
+    compute them (PyTorch's bf16 BERT x12 reads 1.24 on it, this backend 1.05, measured on 8 sequences), so the
+    element-wise figure is then required to stay within 1.1 times that of the bf16 eager run instead of below 1.
+    """
     glob, elem = parity_figures(got, want, tol)
     print(f"parity {what}: max|d|/max|want| = {glob:.3e} (tol {tol:g}); worst element at {elem:.3f} of rtol={tol:g}, atol={ELEMENTWISE_K}*tol*max|want|")
     assert glob < tol, f"{what}: relative error {glob} above {tol}"
-    assert elem <= 1.0, f"{what}: an element is {elem:.2f}x outside rtol={tol}, atol={ELEMENTWISE_K}*tol*max|want|"
+    bound = 1.0
+    if lowp_eager is not None:
+        eg, ee = parity_figures(lowp_eager, want, tol)
+        print(f"parity {what}: the bf16 eager run of the same model reads {eg:.3e} and {ee:.3f}")
+        bound = max(1.0, 1.1 * ee)
+    assert elem <= bound, f"{what}: an element is {elem:.2f}x outside rtol={tol}, atol={ELEMENTWISE_K}*tol*max|want| (bound {bound:.2f})"

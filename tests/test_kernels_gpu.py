@@ -143,7 +143,8 @@ def test_softmax(rows, length, dtype):
     assert torch.allclose(out.float().sum(-1).cpu(), torch.ones(rows), atol=2e-2 if dtype == torch.bfloat16 else 1e-5)
 
 
-@pytest.mark.parametrize("rows,d", [(1024, 768), (33, 768), (7, 100), (3, 3000), (1, 4)])
+# (20011 rows: more rows than resident warps, so every warp walks several rows; 2048 and 1024: the widest register-held rows)
+@pytest.mark.parametrize("rows,d", [(1024, 768), (33, 768), (7, 100), (3, 3000), (1, 4), (20011, 768), (300, 2048), (64, 1024), (50, 8)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_layernorm(rows, d, dtype):
     x, g, b = (_rand(rows, d) * 2 + 0.3).to(dtype), (_rand(d, seed=1) + 1).to(dtype), _rand(d, seed=2).to(dtype)
@@ -202,6 +203,34 @@ def test_eltwise_broadcast_and_layout_copy():
     f = torch.empty(2, 12, device=DEV)
     G.eltwise(f, [ids.to(DEV)], "#1;ld0;cast,1;sub,0,2")
     assert torch.equal(f.cpu(), 1.0 - ids.float())
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_eltwise_short_programs_on_wide_rows(dtype):
+    """Short programs on rows of whole 16-byte vectors take the eight-elements-per-thread kernel: a row broadcast over the
+    batch (the embedding sum), a residual add with a strided operand, a cast, a copy between layouts whose inner dim stays
+    dense, a scalar broadcast along the rows, a where.  Bit-exact against the same arithmetic in torch."""
+    x = _rand(6, 40, 64).to(dtype)
+    row = _rand(40, 64, seed=1).to(dtype)
+    X, R = x.to(DEV), row.to(DEV)
+    out = torch.empty_like(X)
+    G.eltwise(out, [X, R.unsqueeze(0).expand(6, 40, 64)], "ld0;ld1;add,0,1")
+    assert torch.equal(out.cpu(), (x.float() + row.float()).to(dtype))
+    big = _rand(6, 40, 128, seed=2).to(dtype).to(DEV)
+    G.eltwise(out, [X, big[:, :, 64:]], "ld0;ld1;sub,0,1")                 # second operand: every other 64-wide half
+    assert torch.equal(out.cpu(), (x.float() - big[:, :, 64:].float().cpu()).to(dtype))
+    other = torch.bfloat16 if dtype == torch.float32 else torch.float32
+    cast = torch.empty(6, 40, 64, device=DEV, dtype=other)
+    G.eltwise(cast, [X], "ld0")
+    assert torch.equal(cast.cpu(), x.to(other))
+    swapped = torch.empty(40, 6, 64, device=DEV, dtype=dtype)
+    G.eltwise(swapped.permute(1, 0, 2), [X], "ld0;relu,0")
+    assert torch.equal(swapped.cpu(), torch.relu(x).permute(1, 0, 2).contiguous())
+    col = _rand(6, 40, 1, seed=3).to(dtype).to(DEV)
+    G.eltwise(out, [X, col.expand(6, 40, 64)], "ld0;ld1;mul,0,1")
+    assert torch.equal(out.cpu(), (x.float() * col.float().cpu()).to(dtype))
+    G.eltwise(out, [X, R.unsqueeze(0).expand(6, 40, 64)], "ld0;ld1;gt,0,1;where,2,0,1")
+    assert torch.equal(out.cpu(), torch.where(x > row, x, row.expand(6, 40, 64)))
 
 
 def test_argument_errors_are_reported():
