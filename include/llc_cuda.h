@@ -62,10 +62,10 @@ int llc_cuda_gemm(const LlcGemmParams* p, void* stream);
 int llc_cuda_gemm_static_scratch(const LlcGemmParams* p, void* stream);
 
 /* out[b0,b1,m,:] = softmax_n(scale * sum_d Q[b0,b1,m,d] K[b0,b1,n,d] + mask[b0,b1,m,n]) V[b0,b1,n,:] in one kernel: the
- * scores stay in tensor memory, the probabilities in shared memory.  Replaces the chain llh.batch_matmul -> llh.div /
+ * scores stay in tensor memory, the probabilities in shared memory (keys in blocks of 128, running softmax).  Replaces the chain llh.batch_matmul -> llh.div /
  * llh.add (scale, mask) -> softmax (decomposed by llcompiler/compiler/torch_compile_config.py:24) -> llh.batch_matmul that
  * the reference lowers op by op (src/Conversion/LLHToHLO/LLHToHLO.cpp:363-382).  bf16 operands and output with unit
- * stride along d, d == 64, 1 <= n <= 384; every other stride a non-negative multiple of 8 elements (0 = broadcast for
+ * stride along d, d == 64, 1 <= n <= 512; every other stride a non-negative multiple of 8 elements (0 = broadcast for
  * batch strides), pointers 16-byte aligned.  mask may be NULL; it has unit stride along n and may broadcast over
  * b0, b1 and m (stride 0).  Anything else returns LLC_ERR_UNSUPPORTED. */
 typedef struct LlcAttentionParams {

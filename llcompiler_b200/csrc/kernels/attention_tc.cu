@@ -1,4 +1,6 @@
-// Fused attention for sm_100a: out = softmax(scale * Q K^T + mask) V, bf16 operands, head size 64, up to 384 keys.
+// Fused attention for sm_100a: out = softmax(scale * Q K^T + mask) V, bf16 operands, head size 64.  This file: the
+// two-pass kernel for up to 384 keys (the whole score tile in tensor memory) and the entry point; 385 to 512 keys go
+// to the blockwise kernel of attention_blocks_tc.cu.
 // Persistent CTAs (one per SM) walk (batch, head, 128-query block) tiles; the score tile never leaves the SM:
 //   last warp, lane 0  TMA loads of Q, K and V (128-byte swizzle) and the MMAs: S = Q K^T into tensor memory (128 lanes x
 //                      up to 384 fp32 columns); once that MMA is complete the next tile's Q, K and this tile's V are
@@ -294,12 +296,17 @@ int* attnStatusAddress() {
   return cudaGetSymbolAddress(&p, g_attnStatus) == cudaSuccess ? static_cast<int*>(p) : nullptr;
 }
 
-// Reads and clears the attention kernel's status word.
+int attentionBlocks(const LlcAttentionParams* p, cudaStream_t stream);   // attention_blocks_tc.cu: up to 512 keys
+int attnBlocksStatus();
+int* attnBlocksStatusAddress();
+
+// Reads and clears the status words of the two attention kernels.
 int attnStatus() {
   int v = 0, zero = 0;
   if (cudaMemcpyFromSymbol(&v, g_attnStatus, sizeof(int)) != cudaSuccess) return -1;
   if (v) cudaMemcpyToSymbol(g_attnStatus, &zero, sizeof(int));
-  return v;
+  const int w = attnBlocksStatus();
+  return v ? v : w;
 }
 
 }  // namespace llc
@@ -312,7 +319,7 @@ extern "C" int llc_cuda_attention(const LlcAttentionParams* p, void* stream) {
   if (!p->q || !p->k || !p->v || !p->out) return setError(LLC_ERR_ARGUMENT, "llc_cuda_attention: null operand");
   if (p->dtype != LLC_BFLOAT16) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: operands must be bf16");
   if (p->d != kD) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: head size must be 64");
-  if (p->n < 1 || p->n > kMaxN) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: 1 to 384 keys");
+  if (p->n < 1 || p->n > 512) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: 1 to 512 keys");
   if (p->m < 1 || p->b0 < 1 || p->b1 < 1) return setError(LLC_ERR_ARGUMENT, "llc_cuda_attention: empty problem");
   if (p->mask && p->mask_dtype != LLC_FLOAT32 && p->mask_dtype != LLC_BFLOAT16) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: mask must be f32 or bf16");
   auto ok8 = [](long long s) { return s >= 0 && s % 8 == 0; };    // 16-byte multiples of bf16
@@ -321,6 +328,10 @@ extern "C" int llc_cuda_attention(const LlcAttentionParams* p, void* stream) {
     return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: strides must be non-negative multiples of 8 elements and rows must not overlap");
   if ((reinterpret_cast<uintptr_t>(p->q) | reinterpret_cast<uintptr_t>(p->k) | reinterpret_cast<uintptr_t>(p->v) | reinterpret_cast<uintptr_t>(p->out)) & 15)
     return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: operands must be 16-byte aligned");
+  // more keys than the score tile of the two-pass kernel holds (384 columns of tensor memory): the blockwise kernel
+  // (LLC_ATTENTION_BLOCKS=1 sends every shape there: the tests use it to run that kernel on the small shapes too)
+  const char* forceBlocks = getenv("LLC_ATTENTION_BLOCKS");
+  if (p->n > kMaxN || (forceBlocks && forceBlocks[0] == '1')) return attentionBlocks(p, static_cast<cudaStream_t>(stream));
   const long long batch = p->b0 * p->b1, mTiles = (p->m + kBM - 1) / kBM;
   if (batch * mTiles > 0x7FFFFFFFLL) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: too many tiles");
   CUtensorMap mq, mk, mv;

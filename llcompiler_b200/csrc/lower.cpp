@@ -633,7 +633,7 @@ struct Lowering {
     return x;
   }
   // Whether a pending GEMM is the score matrix the fused attention kernel can produce itself: bf16 Q and K with a
-  // head size of 64 read along their unit-stride dim, at most 384 keys (a compile-time constant), nothing absorbed but
+  // head size of 64 read along their unit-stride dim, at most 512 keys (a compile-time constant), nothing absorbed but
   // a constant scale and an additive mask with unit stride along the keys, and the logical view still the plain
   // [.., M, N] matrix.
   bool attentionScores(const TV& t) {
@@ -646,7 +646,7 @@ struct Lowering {
     if (!a || !b || a->dtype != DType::BF16 || b->dtype != DType::BF16) return false;
     if (!a->shape[3].isConst(64) || !a->strides[3].isConst(1) || !b->strides[2].isConst(1)) return false;
     const Expr& N = b->shape[3];
-    if (!N.isConst() || N.constant() < 1 || N.constant() > 384) return false;
+    if (!N.isConst() || N.constant() < 1 || N.constant() > 512) return false;
     auto mult8 = [](const Expr& e) { return e.isConst() && e.constant() >= 0 && e.constant() % 8 == 0; };
     if (!mult8(a->strides[0]) || !mult8(a->strides[1]) || !mult8(a->strides[2]) || !mult8(b->strides[0]) || !mult8(b->strides[1]) || !mult8(b->strides[3]) ||
         !mult8(a->offset) || !mult8(b->offset)) return false;

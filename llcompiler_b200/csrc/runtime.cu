@@ -26,6 +26,7 @@ namespace llc {
 
 int* tcStatusAddress();     // device addresses of the status words the bounded waits of the tensor-core kernels write
 int* attnStatusAddress();
+int* attnBlocksStatusAddress();
 
 namespace {
 
@@ -157,8 +158,8 @@ struct LlcExec {
   char* stageIn = nullptr; size_t stageInCap = 0;
   char* stageOut = nullptr; size_t stageOutCap = 0;
   int* badIds = nullptr;
-  int* tcWord = nullptr; int* attnWord = nullptr;   // device addresses of the kernels' status words on `device`
-  int* hostStatus = nullptr;                  // page-locked mirror: [tensor-core word, attention word, bad embedding ids]
+  int* tcWord = nullptr; int* attnWord = nullptr; int* attnBlocksWord = nullptr;   // device addresses of the kernels' status words on `device`
+  int* hostStatus = nullptr;                  // page-locked mirror: [tensor-core word, attention word, bad embedding ids, blockwise attention word]
   bool usesTc = false, usesGather = false;    // which of the words this plan's kernels can write
   std::mutex mutex;                           // one call at a time per executor (bindings, arena and staging are shared state)
   char* workspace = nullptr;                  // split-K scratch (counters at the head stay zero between launches)
@@ -374,19 +375,21 @@ void LlcExec::runSteps(std::vector<std::unique_ptr<RStep>>& steps, cudaStream_t 
 // host memory behind the work already on `st`; raiseOnStatus, called once the stream has been synchronised, clears
 // whatever is set and throws, so a broken launch or a bad id is an error of the call instead of a wrong result.
 void LlcExec::queueStatusRead(cudaStream_t st) {
-  hostStatus[0] = hostStatus[1] = hostStatus[2] = 0;
+  hostStatus[0] = hostStatus[1] = hostStatus[2] = hostStatus[3] = 0;
+  if (usesTc && attnBlocksWord) cudaOk(cudaMemcpyAsync(&hostStatus[3], attnBlocksWord, sizeof(int), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(status)");
   if (usesTc && tcWord) cudaOk(cudaMemcpyAsync(&hostStatus[0], tcWord, sizeof(int), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(status)");
   if (usesTc && attnWord) cudaOk(cudaMemcpyAsync(&hostStatus[1], attnWord, sizeof(int), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(status)");
   if (usesGather) cudaOk(cudaMemcpyAsync(&hostStatus[2], badIds, sizeof(int), cudaMemcpyDeviceToHost, st), "cudaMemcpyAsync(status)");
 }
 void LlcExec::raiseOnStatus(cudaStream_t st) {
-  const int tc = hostStatus[0], at = hostStatus[1], bad = hostStatus[2];
+  const int tc = hostStatus[0], at = hostStatus[1] ? hostStatus[1] : hostStatus[3], bad = hostStatus[2];
   if (!tc && !at && !bad) return;
   if (tc) cudaMemsetAsync(tcWord, 0, sizeof(int), st);
-  if (at) cudaMemsetAsync(attnWord, 0, sizeof(int), st);
+  if (hostStatus[1]) cudaMemsetAsync(attnWord, 0, sizeof(int), st);
+  if (hostStatus[3]) cudaMemsetAsync(attnBlocksWord, 0, sizeof(int), st);
   if (bad) cudaMemsetAsync(badIds, 0, sizeof(int), st);
   cudaStreamSynchronize(st);
-  hostStatus[0] = hostStatus[1] = hostStatus[2] = 0;
+  hostStatus[0] = hostStatus[1] = hostStatus[2] = hostStatus[3] = 0;
   if (bad) failArg(std::to_string(bad) + " embedding indices lie outside their table (those rows were written as zeros)");
   throw std::runtime_error("llc cuda: a tensor-core kernel gave up on a bounded wait (status " + std::to_string(tc ? tc : at) +
                            (tc ? ", GEMM / convolution" : ", attention") + "); the results of this call are invalid");
@@ -494,7 +497,7 @@ extern "C" int llc_load(const char* path, int device, LlcExec** out) {
     cudaOk(cudaMalloc(&ex->badIds, sizeof(int)), "cudaMalloc(status)");
     cudaOk(cudaMemset(ex->badIds, 0, sizeof(int)), "cudaMemset(status)");
     cudaOk(cudaHostAlloc(reinterpret_cast<void**>(&ex->hostStatus), 4 * sizeof(int), cudaHostAllocDefault), "cudaHostAlloc(status)");
-    ex->tcWord = tcStatusAddress(); ex->attnWord = attnStatusAddress();
+    ex->tcWord = tcStatusAddress(); ex->attnWord = attnStatusAddress(); ex->attnBlocksWord = attnBlocksStatusAddress();
     for (auto& s : ex->plan.steps) {
       if (s.kernel == "gemm" || s.kernel == "conv" || s.kernel == "attention") ex->usesTc = true;
       if (s.kernel == "gather") ex->usesGather = true;
@@ -705,7 +708,7 @@ extern "C" int llc_status(LlcExec* ex, int32_t* words) {
     cudaOk(cudaDeviceSynchronize(), "cudaDeviceSynchronize");
     ex->queueStatusRead(0);
     cudaOk(cudaStreamSynchronize(0), "cudaStreamSynchronize");
-    if (words) { words[0] = ex->hostStatus[0]; words[1] = ex->hostStatus[1]; words[2] = ex->hostStatus[2]; }
+    if (words) { words[0] = ex->hostStatus[0]; words[1] = ex->hostStatus[1] ? ex->hostStatus[1] : ex->hostStatus[3]; words[2] = ex->hostStatus[2]; }
     ex->raiseOnStatus(0);
     return LLC_OK;
   } catch (const std::exception& e) { return setError(statusFor(e), e.what()); }
