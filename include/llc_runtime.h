@@ -84,6 +84,16 @@ int llc_run_pass(const char* mlir_text, const char* pass, const LlcOptions* opti
  * (weight re-layout, folded batch-norm vectors).  Allocates device memory. */
 int llc_load(const char* plan_path, int device, LlcExec** out_exec);
 
+/* llc_load with a weight directory (NULL or "" = llc_load): the .npy files the plan names are looked up in
+ * `weight_dir` by file name first, and the uploaded, re-laid-out weight pool is kept there as `pool.bin` (tied to the
+ * plan text, the pool size and the library build): a later load of the same plan from the same directory reads that
+ * one file, uploads it and runs no load-time kernel.  This is the run side of the plan and weight cache; the
+ * reference names its artefact after a hash of the module text (src/Compiler/Compiler.cpp:305-309) but rebuilds it
+ * and re-dumps the weights on every compile (llcompiler/importer/fx_translate.py:416-436).
+ * llc_loaded_from_pool tells which way a handle was loaded (1 = from pool.bin). */
+int llc_load_from(const char* plan_path, const char* weight_dir, int device, LlcExec** out_exec);
+int llc_loaded_from_pool(const LlcExec* exec);
+
 int llc_num_inputs(const LlcExec* exec);
 int llc_num_outputs(const LlcExec* exec);
 int llc_num_symbols(const LlcExec* exec);

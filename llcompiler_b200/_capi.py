@@ -132,7 +132,7 @@ class LlcEltwiseParams(Structure):
 
 
 EXPORTED_SYMBOLS = [
-    "llc_compile", "llc_run_pass", "llc_load", "llc_num_inputs", "llc_num_outputs", "llc_num_symbols",
+    "llc_compile", "llc_run_pass", "llc_load", "llc_load_from", "llc_loaded_from_pool", "llc_num_inputs", "llc_num_outputs", "llc_num_symbols",
     "llc_output_shape", "llc_run", "llc_profile", "llc_status", "llc_last_launch_count", "llc_arena_bytes", "llc_free", "llc_last_error",
     "llc_version", "llc_cuda_gemm", "llc_cuda_conv2d", "llc_cuda_maxpool2d", "llc_cuda_reduce",
     "llc_cuda_softmax", "llc_cuda_layernorm", "llc_cuda_gather", "llc_cuda_eltwise", "llc_cuda_status", "llc_cuda_nchw_to_nhwc", "llc_cuda_gemm_static_scratch", "llc_cuda_attention", "llc_cuda_nchw_to_nhwc_wide",

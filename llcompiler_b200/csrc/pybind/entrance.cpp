@@ -100,10 +100,11 @@ struct Compiler {
 struct Execution {
   LlcExec* exec = nullptr;
   ~Execution() { if (exec) llc_free(exec); }
-  void load(const std::string& path, int device) {
+  void load(const std::string& path, int device, const std::string& weight_dir) {
     if (exec) throw std::runtime_error("Execution.load may be called once per object");
-    check(llc_load(path.c_str(), device, &exec));
+    check(llc_load_from(path.c_str(), weight_dir.empty() ? nullptr : weight_dir.c_str(), device, &exec));
   }
+  bool loaded_from_pool() const { need(); return llc_loaded_from_pool(exec) == 1; }
   void need() const { if (!exec) throw std::runtime_error("Execution.load has not been called"); }
   void run_impl(const std::vector<int64_t>& symbols, std::vector<Tensor*>& in, std::vector<Tensor*>& out, uintptr_t stream) {
     need();
@@ -203,7 +204,8 @@ PYBIND11_MODULE(llcompiler_, m) {
   executor.def("get_tool", &getTool);
   py::class_<Execution>(executor, "Execution")
       .def(py::init<>())
-      .def("load", &Execution::load, py::arg("path"), py::arg("device") = 0)
+      .def("load", &Execution::load, py::arg("path"), py::arg("device") = 0, py::arg("weight_dir") = "")
+      .def("loaded_from_pool", &Execution::loaded_from_pool)
       .def("run", &Execution::run, py::arg("inputs"), py::arg("outs"), py::arg("stream") = 0)
       .def("run_with_symbols", &Execution::run_with_symbols, py::arg("symbols"), py::arg("inputs"), py::arg("outs"), py::arg("stream") = 0)
       .def("output_shapes", &Execution::output_shapes)

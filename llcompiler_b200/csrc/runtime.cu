@@ -16,6 +16,8 @@
 #include <memory>
 #include <mutex>
 #include <sstream>
+#include <sys/stat.h>
+#include <unistd.h>
 
 #include "../../include/llc_cuda.h"
 #include "../../include/llc_runtime.h"
@@ -167,6 +169,7 @@ struct LlcExec {
   cudaStream_t capStream = nullptr;         // capture happens here, so that the legacy default stream can replay too
   std::map<std::vector<int64_t>, std::unique_ptr<Binding>> bindings;
   int64_t lastLaunches = 0;
+  bool loadedFromPool = false;                // the static pool came from a saved file (no weight files read, no load-time kernels)
   std::vector<char*> base;                    // per-buffer device base pointers for the current call
 
   ~LlcExec() {
@@ -467,14 +470,30 @@ static bool isDenseRowMajor(const LlcTensor& t) {
   return true;
 }
 
-extern "C" int llc_load(const char* path, int device, LlcExec** out) {
+namespace {
+// The static pool (weights as uploaded plus everything the load-time kernels derive from them: re-laid-out filters,
+// folded batch-norm vectors, the low-order parts of tf32x3 weights) saved beside the weights, so that a later load of
+// the same plan with the same weights is one file read and one copy.  The header ties the file to the plan text, the
+// pool size and the library build.
+struct PoolHeader { char magic[8]; uint64_t planHash, bytes, buildHash; };
+const char kPoolMagic[8] = {'L', 'L', 'C', 'P', 'O', 'O', 'L', '1'};
+uint64_t buildHash() { return std::hash<std::string>()(std::string(llc_version()) + __DATE__ + __TIME__); }
+bool fileExists(const std::string& p) { struct stat st; return ::stat(p.c_str(), &st) == 0; }
+std::string baseName(const std::string& p) { size_t k = p.find_last_of('/'); return k == std::string::npos ? p : p.substr(k + 1); }
+}  // namespace
+
+extern "C" int llc_load(const char* path, int device, LlcExec** out) { return llc_load_from(path, nullptr, device, out); }
+
+extern "C" int llc_load_from(const char* path, const char* weightDirC, int device, LlcExec** out) {
+  const std::string weightDir = weightDirC ? weightDirC : "";
   if (!path || !out) return setError(LLC_ERR_ARGUMENT, "null argument");
   std::unique_ptr<LlcExec> ex(new LlcExec());
   try {
     std::ifstream f(path);
     if (!f) failIo(std::string("cannot open plan ") + path);
     std::stringstream ss; ss << f.rdbuf();
-    ex->plan = parsePlan(ss.str());
+    const std::string planText = ss.str();
+    ex->plan = parsePlan(planText);
     int count = 0;
     cudaError_t e = cudaGetDeviceCount(&count);
     if (e != cudaSuccess || count == 0) throw std::runtime_error("llc cuda: no CUDA device is available (the B200 backend has no CPU fallback)");
@@ -504,13 +523,32 @@ extern "C" int llc_load(const char* path, int device, LlcExec** out) {
     }
     cudaOk(cudaMalloc(&ex->workspace, LlcExec::kWorkspaceBytes), "cudaMalloc(workspace)");
     cudaOk(cudaMemset(ex->workspace, 0, 4096), "cudaMemset(workspace)");
+    // a saved pool for this plan, these weights and this build: one read, one copy, no load-time kernels
+    const std::string poolPath = weightDir.empty() ? "" : weightDir + "/pool.bin";
+    const PoolHeader wantHeader = [&]() { PoolHeader h{}; memcpy(h.magic, kPoolMagic, 8); h.planHash = std::hash<std::string>()(planText); h.bytes = total; h.buildHash = buildHash(); return h; }();
+    bool fromPool = false;
+    if (!poolPath.empty() && total > 0) {
+      std::ifstream pf(poolPath, std::ios::binary);
+      PoolHeader got{};
+      if (pf && pf.read(reinterpret_cast<char*>(&got), sizeof got) && memcmp(&got, &wantHeader, sizeof got) == 0) {
+        std::vector<char> host(total);
+        if (pf.read(host.data(), (std::streamsize)total)) {
+          cudaOk(cudaMemcpy(ex->staticPool, host.data(), total, cudaMemcpyHostToDevice), "cudaMemcpy(pool)");
+          fromPool = true;
+        }
+      }
+    }
     for (size_t i = 0; i < nb; ++i) {
       auto& b = ex->plan.buffers[i];
       if (b.kind != BufferDecl::Weight && b.kind != BufferDecl::Const) continue;
       ex->base[i] = ex->staticPool + ex->staticOffset[i];
+      if (fromPool) continue;
       size_t n = bytes[i] / dtypeSize(b.dtype);
       if (b.kind == BufferDecl::Weight) {
-        std::vector<char> host = readNpy(b.file, b.dtype, n);
+        // with a weight directory the files are looked up there by name (the plan records where the importer put them)
+        std::string file = b.file;
+        if (!weightDir.empty() && fileExists(weightDir + "/" + baseName(b.file))) file = weightDir + "/" + baseName(b.file);
+        std::vector<char> host = readNpy(file, b.dtype, n);
         cudaOk(cudaMemcpy(ex->base[i], host.data(), bytes[i], cudaMemcpyHostToDevice), "cudaMemcpy(weight)");
       } else if (!b.values.empty()) {
         if (b.values.size() != n) failArg("constant buffer value count mismatch");
@@ -537,10 +575,23 @@ extern "C" int llc_load(const char* path, int device, LlcExec** out) {
       for (auto& v : s.views) rs->views.emplace_back(v.first, ex->resolve(v.second, empty));
       init.push_back(std::move(rs));
     }
-    ex->runSteps(init, 0);
-    ex->queueStatusRead(0);
-    cudaOk(cudaDeviceSynchronize(), "load-time kernels");
-    ex->raiseOnStatus(0);
+    if (!fromPool) {
+      ex->runSteps(init, 0);
+      ex->queueStatusRead(0);
+      cudaOk(cudaDeviceSynchronize(), "load-time kernels");
+      ex->raiseOnStatus(0);
+      if (!poolPath.empty() && total > 0) {            // save the pool for the next load (written whole, then renamed)
+        std::vector<char> host(total);
+        cudaOk(cudaMemcpy(host.data(), ex->staticPool, total, cudaMemcpyDeviceToHost), "cudaMemcpy(pool)");
+        const std::string tmp = poolPath + ".tmp" + std::to_string((long long)getpid());
+        std::ofstream pf(tmp, std::ios::binary);
+        if (pf && pf.write(reinterpret_cast<const char*>(&wantHeader), sizeof wantHeader) && pf.write(host.data(), (std::streamsize)total)) {
+          pf.close();
+          if (::rename(tmp.c_str(), poolPath.c_str()) != 0) ::unlink(tmp.c_str());
+        } else { pf.close(); ::unlink(tmp.c_str()); }
+      }
+    }
+    ex->loadedFromPool = fromPool;
     ex->lastLaunches = 0;
     *out = ex.release();
     return LLC_OK;
@@ -552,6 +603,7 @@ extern "C" int llc_num_outputs(const LlcExec* e) { return e ? (int)e->plan.outpu
 extern "C" int llc_num_symbols(const LlcExec* e) { return e ? e->plan.numSymbolArgs : -1; }
 extern "C" int64_t llc_last_launch_count(const LlcExec* e) { return e ? e->lastLaunches : -1; }
 extern "C" int64_t llc_arena_bytes(const LlcExec* e) { return e ? (int64_t)e->arenaCap : -1; }
+extern "C" int llc_loaded_from_pool(const LlcExec* e) { return e ? (e->loadedFromPool ? 1 : 0) : -1; }
 extern "C" void llc_free(LlcExec* e) { delete e; }
 
 extern "C" int llc_output_shape(LlcExec* ex, const int64_t* symbols, int nsym, const LlcTensor* in, int nin, int index, int64_t* sizes, int32_t* rank, int32_t* dtype) {

@@ -28,12 +28,13 @@ TYPE_TO_TORCH_DTYPE = {v: k for k, v in TORCH_DTYPE_TO_TYPE.items()}
 
 
 class ExecutionEngine:
-    def __init__(self, so_file: str, device: Optional[int] = None):
+    def __init__(self, so_file: str, device: Optional[int] = None, weight_dir: Optional[str] = None):
         if not torch.cuda.is_available():
             raise RuntimeError("the B200 backend needs a CUDA device; there is no CPU fallback")
         self.device = torch.cuda.current_device() if device is None else int(device)
         self.executor = Execution()
-        self.executor.load(so_file, self.device)
+        # `weight_dir`: where the plan's .npy files live (looked up by name) and where the uploaded weight pool is kept
+        self.executor.load(so_file, self.device, weight_dir or "")
         self.gen_outs_call = None
         self._out_meta = {}
         self._pinned = {}

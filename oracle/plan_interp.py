@@ -42,7 +42,8 @@ def load_npy(path: str, dtype: str) -> torch.Tensor:
 
 
 class PlanInterpreter:
-    def __init__(self, text: str):
+    def __init__(self, text: str, weight_dir: str = ""):
+        self.weight_dir = weight_dir       # when set, weight files are looked up there by name first (as llc_load_from does)
         self.options: Dict[str, str] = {}
         self.symbols: List[tuple] = []
         self.buffers: List[dict] = []
@@ -107,7 +108,12 @@ class PlanInterpreter:
                 mem[i] = inputs[b["index"]].contiguous().reshape(-1).to(dt)
             elif b["kind"] == "weight":
                 if i not in self._weights:
-                    self._weights[i] = load_npy(b["file"], b["dtype"]).to(dt)
+                    path = b["file"]
+                    if self.weight_dir:
+                        import os
+                        cand = os.path.join(self.weight_dir, os.path.basename(path))
+                        path = cand if os.path.exists(cand) else path
+                    self._weights[i] = load_npy(path, b["dtype"]).to(dt)
                 mem[i] = self._weights[i]
             elif b["values"] is not None:
                 mem[i] = torch.tensor(b["values"], dtype=torch.float64).to(dt)

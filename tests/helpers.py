@@ -17,9 +17,9 @@ from oracle.plan_interp import PlanInterpreter  # noqa: E402
 
 
 class _InterpEngine:
-    def __init__(self, plan_path: str):
+    def __init__(self, plan_path: str, weight_dir: str = ""):
         self.text = open(plan_path).read()
-        self.interp = PlanInterpreter(self.text)
+        self.interp = PlanInterpreter(self.text, weight_dir or "")
 
     def run(self, *args):
         symbols = [a for a in args if isinstance(a, int)]
@@ -36,8 +36,8 @@ class InterpreterCompiler(LLCompiler):
                                   global_layout=self.target_layout, precision=self.precision,
                                   log_root=self.log_root or None)
 
-    def _make_engine(self, plan_path: str):
-        return _InterpEngine(plan_path)
+    def _make_engine(self, plan_path: str, weight_dir=None):
+        return _InterpEngine(plan_path, weight_dir)
 
 
 def compile_with(compiler: LLCompiler, model: torch.nn.Module, dynamic: bool = False):

@@ -324,3 +324,25 @@ def test_one_plan_on_two_devices_in_one_process():
         assert torch.cuda.current_device() == 0
         assert_parity(outs[-1].float(), want, 2e-2, f"bert bf16 on cuda:{d}")
     assert torch.equal(outs[0].cpu(), outs[1].cpu())
+
+
+def test_cached_plan_and_weight_pool_give_identical_results(tmp_path, monkeypatch):
+    """Second compilation of the same model with the same weights: the plan comes from the cache (no import, no lowering)
+    and the executor uploads the saved weight pool instead of reading the .npy files and running the load-time kernels
+    (filter re-layout, folded batch norm, the low-order parts of the tf32x3 weights); the results are the same bits."""
+    monkeypatch.setenv("LLC_CACHE_DIR", str(tmp_path))
+    m = build_model("resnet18")
+    x = torch.randn(2, 3, 64, 64, generator=torch.Generator().manual_seed(1))
+    outs, comps = [], []
+    for _ in range(2):
+        comp = LLCompiler(precision="tf32x3")
+        with torch.no_grad():
+            outs.append(compile_with(comp, copy.deepcopy(m).cuda(), False)(x.cuda()))
+        torch.cuda.synchronize()
+        comps.append(comp)
+    first, second = (c.compiled[0].engine.executor for c in comps)
+    assert comps[0].cache_hits == 0 and not first.loaded_from_pool()
+    assert comps[1].cache_hits == 1 and second.loaded_from_pool()
+    assert torch.equal(outs[0], outs[1])
+    with torch.no_grad():
+        assert_parity(outs[1], m(x), 1e-4, "resnet18 from the cache")
