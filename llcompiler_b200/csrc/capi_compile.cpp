@@ -66,13 +66,29 @@ extern "C" int llc_run_pass(const char* text, const char* pass, const LlcOptions
       if (blank) continue;
       auto m = parseModule(part);
       if (m->funcs.empty()) continue;
-      if (p == "parse") {}
-      else if (p == "operation-legalization") runOperationLegalization(*m);
-      else if (p == "remove-redundant-ops") runRemoveRedundantOps(*m);
-      else if (p == "fuse-softmax") runFuseSoftmax(*m);
-      else if (p == "infer-symbol-shape") runInferSymbolShape(*m);
-      else if (p == "lower") { checkOptions(d); result += lowerToPlan(*m, d).str(); result += "// -----\n"; continue; }
-      else return setError(LLC_ERR_ARGUMENT, "unknown pass '" + p + "'");
+      // `pass` may be a comma-separated pipeline, applied in order (the reference's RUN lines chain several)
+      bool printedPlan = false;
+      size_t at = 0;
+      while (at <= p.size()) {
+        size_t comma = p.find(',', at);
+        if (comma == std::string::npos) comma = p.size();
+        const std::string one = p.substr(at, comma - at);
+        at = comma + 1;
+        if (one.empty() || one == "parse") {}
+        else if (one == "operation-legalization") runOperationLegalization(*m);
+        else if (one == "remove-redundant-ops") runRemoveRedundantOps(*m);
+        else if (one == "fuse-softmax") runFuseSoftmax(*m);
+        else if (one == "infer-symbol-shape") runInferSymbolShape(*m);
+        else if (one == "decompose-ops") runDecomposeOps(*m);
+        else if (one == "transform-layout") runTransformLayout(*m);
+        else if (one == "canonicalize") runCanonicalize(*m);
+        else if (one == "inline") runFold(*m);
+        else if (one == "cse") runCse(*m);
+        else if (one == "unload-and-bind-encoding") runUnloadAndBindEncoding(*m);
+        else if (one == "lower") { checkOptions(d); result += lowerToPlan(*m, d).str(); result += "// -----\n"; printedPlan = true; break; }
+        else return setError(LLC_ERR_ARGUMENT, "unknown pass '" + one + "'");
+      }
+      if (printedPlan) continue;
       result += m->str();
       result += "// -----\n";
     }

@@ -561,8 +561,15 @@ struct Parser {
         balanced('{', '}');
         continue;
       }
-      if (peek("\"llh.symbolic_int\"") || peek("\"llh.")) {  // module-level symbol declarations
-        Func dummy; operation(dummy); continue;
+      if (peek("\"llh.symbolic_int\"") || peek("\"llh.")) {  // module-level symbol declarations: kept, in order, for printing
+        Func dummy; operation(dummy);
+        if (!dummy.ops.empty() && dummy.ops.back()->name == "llh.symbolic_int")
+          if (const Attr* n = dummy.ops.back()->attr("sym_name")) {
+            bool known = false;
+            for (auto& d : m->symbolDecls) known = known || d == n->s;
+            if (!known) m->symbolDecls.push_back(n->s);
+          }
+        continue;
       }
       fail("unexpected text at module level");
     }

@@ -81,5 +81,12 @@ void runOperationLegalization(Module& m);
 void runRemoveRedundantOps(Module& m);
 void runFuseSoftmax(Module& m);
 void runInferSymbolShape(Module& m);   // writes #llh.encoding onto every tensor type
+// llh_transforms.cpp: the reference's LLH-level rewrites that its lit files exercise
+void runDecomposeOps(Module& m);
+void runTransformLayout(Module& m);
+void runCanonicalize(Module& m);
+void runFold(Module& m);
+void runCse(Module& m);
+void runUnloadAndBindEncoding(Module& m);
 
 }  // namespace llc

@@ -1,11 +1,11 @@
 """A small FileCheck: enough of the directive language to run the CHECK lines of LLVM-lit style
-test files (CHECK, CHECK-SAME, CHECK-LABEL, CHECK-NEXT, CHECK-NOT, {{regex}} blocks) against text."""
+test files (CHECK, CHECK-SAME, CHECK-LABEL, CHECK-NEXT, CHECK-NOT, CHECK-COUNT-<n>, {{regex}} blocks) against text."""
 from __future__ import annotations
 
 import re
 from typing import List, Tuple
 
-_DIRECTIVE = re.compile(r"//\s*(CHECK(?:-[A-Z]+)?):\s?(.*)$")
+_DIRECTIVE = re.compile(r"//\s*(CHECK(?:-[A-Z]+)*(?:-\d+)?):\s?(.*)$")
 
 
 def directives(source: str, prefix: str = "CHECK") -> List[Tuple[str, str]]:
@@ -15,8 +15,11 @@ def directives(source: str, prefix: str = "CHECK") -> List[Tuple[str, str]]:
         if not m:
             continue
         kind, pat = m.group(1), m.group(2).strip()
-        if kind == prefix or kind.startswith(prefix + "-") and kind[len(prefix) + 1:] in ("SAME", "LABEL", "NEXT", "NOT"):
+        rest = kind[len(prefix) + 1:] if kind.startswith(prefix + "-") else None
+        if kind == prefix or rest in ("SAME", "LABEL", "NEXT", "NOT"):
             out.append((kind[len(prefix):].lstrip("-") or "PLAIN", pat))
+        elif rest is not None and re.fullmatch(r"COUNT-\d+", rest):
+            out.extend([("PLAIN", pat)] * int(rest.split("-")[1]))     # n matches one after the other
     return out
 
 

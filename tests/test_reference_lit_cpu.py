@@ -12,8 +12,10 @@ from llcompiler_b200 import _capi
 from reference_tree import reference_path
 
 REF = reference_path("test", "Dialect", "LLH") or ""
-PASSES = {"--infer-symbol-shape": "infer-symbol-shape", "--operation-legalization": "operation-legalization",
-          "--remove-redundant-ops": "remove-redundant-ops"}
+PASSES = {"--infer-symbol-shape": "infer-symbol-shape", "-infer-symbol-shape": "infer-symbol-shape", "--operation-legalization": "operation-legalization",
+          "--remove-redundant-ops": "remove-redundant-ops", "--decompose-ops": "decompose-ops", "--transform-layout": "transform-layout",
+          "--canonicalize": "canonicalize", "-canonicalize": "canonicalize", "--inline": "inline", "--cse": "cse",
+          "--unload-and-bind-encoding": "unload-and-bind-encoding"}
 # functions of each file whose CHECK lines hold on this implementation's output; the others need parts of the
 # reference that are out of scope here (affine-map symbol relations, training-mode batch norm, scalar
 # results)
@@ -22,6 +24,15 @@ EXPECTED = {
                                 "conv_static", "broadcast_to", "batch_matmul", "extract", "where", "reduce", "checkIsReturnOperand"},
     "remove_redundant_ops.mlir": None,      # all of them
     "operation-legalization.mlir": None,
+    "decompose_ops.mlir": None,
+    "transform_layout.mlir": None,
+    "canonicalize.mlir": None,
+    "fold.mlir": None,
+    "insert_braodcast.mlir": None,
+    "reshape_before_braodcast.mlir": None,
+    "layout_canonicalize.mlir": None,
+    "unload_and_bind_encoding.mlir": None,
+    "ops.mlir": None,
 }
 
 
@@ -38,8 +49,15 @@ def test_filecheck_directives():
 
 def _run_file(path):
     src = open(path).read()
-    run = re.findall(r"RUN: llc-opt (.*?) %s", src)
-    name = next((v for k, v in PASSES.items() if run and k in run[0]), None)
+    # the passes of the first RUN line, in order (flags that only steer the driver or that MLIR itself provides for
+    # printing are left out; a file whose RUN line names no pass is parsed and printed back)
+    run = re.findall(r"RUN: llc-opt (.*?)\|", src)
+    flags = re.findall(r"(--?[\w-]+)(?:=\"[^\"]*\")?", run[0]) if run else []
+    chain = [PASSES[f] for f in flags if f in PASSES]
+    unknown = [f for f in flags if f not in PASSES and f not in ("--split-input-file", "--mlir-print-op-generic")]
+    name = ",".join(chain) if chain else ("parse" if run and not unknown else None)
+    if unknown:
+        name = None
     results = {}
     for piece in src.split("// -----"):
         fn = re.search(r"func\.func @(\w+)", piece)
