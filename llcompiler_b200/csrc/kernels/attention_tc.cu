@@ -3,13 +3,19 @@
 // to the blockwise kernel of attention_blocks_tc.cu.
 // Persistent CTAs (one per SM) walk (batch, head, 128-query block) tiles; the score tile never leaves the SM:
 //   last warp, lane 0  TMA loads of Q, K and V (128-byte swizzle) and the MMAs: S = Q K^T into tensor memory (128 lanes x
-//                      up to 384 fp32 columns); once that MMA is complete the next tile's Q, K and this tile's V are
-//                      requested, so their flight hides behind the softmax; O = P V into 64 further columns when P is
-//                      written.
-//   16 softmax warps   straight out of tensor memory: thread = one query row and every fourth 32-column chunk; pass 1 row
-//                      maximum, pass 2 exp2 and row sum, P written as bf16 into shared memory in the K-major swizzled
-//                      layout the second MMA reads; then the epilogue O / rowsum -> bf16 -> global.  A mask row that is
-//                      all zeros (the usual full-length batch) takes a path without mask loads.
+//                      up to 384 fp32 columns), one commit per 128-key block; once that MMA is complete the next tile's
+//                      Q, K and this tile's V are requested, so their flight hides behind the softmax; O = P V into 64
+//                      further columns, issued round by round as P is written (two 64-key atoms per round, last block first); then at
+//                      once the NEXT tile's S = Q K^T (the score columns are free as soon as the last round of P is
+//                      written), which so runs under this tile's second MMA and epilogue.
+//   16 softmax warps   straight out of tensor memory: thread = one query row and every fourth 32-column chunk, so that
+//                      round r of either pass touches key block r only; pass 1 row maximum (block r as soon as its
+//                      MMAs are complete), pass 2 exp2 and row sum, P written as bf16 into shared memory in the K-major
+//                      swizzled layout the second MMA reads and handed over after every round; then the epilogue
+//                      O / rowsum -> bf16 -> shared memory.
+//   mask-row warp      the tile's mask row (times log2 e) into shared memory, a tile ahead
+//   store warp         one TMA store per output tile  A mask row that is all zeros (the usual full-length batch) takes a
+//                      path without mask loads.
 // Replaces batch_matmul -> (scale, mask add) -> softmax -> batch_matmul of the reference's decomposed attention
 // (llcompiler/compiler/torch_compile_config.py:24 decomposes aten._softmax; the matmuls lower through
 // src/Conversion/LLHToHLO/LLHToHLO.cpp:363-382).  Algorithmic HBM bytes: Q + K + V + out (+ mask); the S x S
@@ -18,7 +24,7 @@
 #include "tc_common.cuh"
 
 namespace llc {
-__device__ int g_attnStatus = 0;   // non-zero after a bounded wait gave up: 6 loader/issuer thread, 7 softmax warps
+__device__ int g_attnStatus = 0;   // non-zero after a bounded wait gave up: 6 loader/issuer thread, 7 softmax warps, 8 mask-row warp, 9 store warp
 
 namespace {
 using namespace tc;
@@ -29,6 +35,7 @@ constexpr int kMaxN = 384;        // keys: 384 score columns + 64 output columns
 constexpr int kTile = kBM * 128;  // bytes of a 128-row x 128-byte tile
 constexpr int kGroups = 4;              // softmax warps per lane quarter: group h takes every kGroups-th 32-column chunk
 constexpr int kSoftmaxThreads = 4 * kGroups * 32;
+constexpr int kThreads = kSoftmaxThreads + 96;   // + the loader / MMA issuer warp, the mask-row warp and the store warp
 constexpr float kLog2e = 1.4426950408889634f;
 
 struct AttnArgs {
@@ -46,9 +53,12 @@ constexpr int kSmemBytes = kTile /*Q*/ + 3 * kTile /*K*/ + 3 * kTile /*V*/ + 6 *
 __device__ __forceinline__ float fastExp2(float x) { float y; asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x)); return y; }
 __device__ __forceinline__ void softmaxBarrier() { asm volatile("bar.sync 1, %0;" ::"n"(kSoftmaxThreads) : "memory"); }
 
-__global__ void __launch_bounds__(kSoftmaxThreads + 32, 1)
+// ROWMASK: the mask (if any) does not depend on the query row.  The per-row form is a kernel of its own because its
+// per-element mask loads multiply the code size, and the common kernel is bound by instruction fetch as it is.
+template <bool ROWMASK>
+__global__ void __launch_bounds__(kThreads, 1)
 attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant__ CUtensorMap mapK, const __grid_constant__ CUtensorMap mapV,
-                 const AttnArgs p) {
+                 const __grid_constant__ CUtensorMap mapO, const AttnArgs p) {
   extern __shared__ uint8_t smemRaw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smemRaw) + 1023) & ~uintptr_t(1023));
   uint8_t* sQ = smem;
@@ -56,21 +66,27 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   uint8_t* sV = sK + 3 * kTile;
   uint8_t* sP = sV + 3 * kTile;
   uint8_t* misc = sP + 6 * kTile;
-  // One phase per tile on every barrier: [0] Q,K landed  [1] V landed  [2] S complete  [3] P written  [4] O complete  [5] O read
+  // One phase per tile on every barrier: [0] Q,K landed  [1] V landed  [2] O complete  [3] O read
+  // barS[j] key block j of S complete   barP[r] round r of P (atoms 2r, 2r+1) written
   uint64_t* bars = reinterpret_cast<uint64_t*>(misc);
-  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(misc + 64);
-  volatile int* abortWord = reinterpret_cast<volatile int*>(misc + 68);
-  float* sMax = reinterpret_cast<float*>(misc + 128);           // [kGroups][128]
+  uint64_t* barS = bars + 4;
+  uint64_t* barP = bars + 7;
+  uint64_t* barMaskFull = bars + 10;   // [2] the mask row of a tile is in buffer (tile & 1)
+  uint64_t* barMaskFree = bars + 12;   // [2] the softmax warps are done with that buffer
+  uint64_t* barOut = bars + 14;        // the output tile is staged in shared memory
+  uint64_t* barOutFree = bars + 15;    // ... and has left it again
+  uint32_t* tmemSlot = reinterpret_cast<uint32_t*>(misc + 128);
+  volatile int* abortWord = reinterpret_cast<volatile int*>(misc + 132);
+  float* sMax = reinterpret_cast<float*>(misc + 256);           // [kGroups][128]
   float* sSum = sMax + kGroups * 128;                           // [kGroups][128]
-  float* sMask = sSum + kGroups * 128;                          // [384] mask row * log2(e); -inf past the last key
-  volatile int* sMaskSet = reinterpret_cast<volatile int*>(misc + 72);   // whether the current mask row has any non-zero entry
+  float* sMask = sSum + kGroups * 128;                          // [2][384] mask row * log2(e); -inf past the last key
+  volatile int* sMaskSet = reinterpret_cast<volatile int*>(misc + 136);   // [2] whether that mask row has any non-zero entry
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int kIssuerWarp = kSoftmaxThreads / 32;
+  constexpr int kIssuerWarp = kSoftmaxThreads / 32, kMaskWarp = kIssuerWarp + 1, kStoreWarp = kIssuerWarp + 2;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 5; ++i) mbarInit(&bars[i], 1);
-    mbarInit(&bars[5], kSoftmaxThreads / 32);
+    for (int i = 0; i < 16; ++i) mbarInit(&bars[i], (i == 3 || i == 14) ? kSoftmaxThreads / 32 : 1);   // O read, output staged: one arrival per softmax warp
     *abortWord = 0;
     fenceBarrierInit();
   }
@@ -79,20 +95,31 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   __syncthreads();
   tcFenceAfter();
   const uint32_t tmemBase = *tmemSlot;
-  const bool rowMask = p.mask == nullptr || p.m_sm == 0;        // the mask does not depend on the query row
-  auto coords = [&](long long t, int& tileM, int& zb0, int& zb1) {
-    const int z = (int)(t / p.mTiles); tileM = (int)(t - (long long)z * p.mTiles);
-    zb0 = z / p.b1; zb1 = z - zb0 * p.b1;
+  constexpr bool rowMask = ROWMASK;
+  // The CTA's tiles: blockIdx.x, + gridDim.x, ...; (query block, head, batch) are stepped without a division per tile.
+  struct TileWalk {
+    int tileM, zb1, zb0, dM, d1, d0, mTiles, b1;
+    __device__ TileWalk(const AttnArgs& a, unsigned first, unsigned step) : mTiles(a.mTiles), b1(a.b1) {
+      const int z = (int)(first / (unsigned)mTiles); tileM = (int)(first - (unsigned)z * (unsigned)mTiles);
+      zb0 = z / b1; zb1 = z - zb0 * b1;
+      const int gz = (int)(step / (unsigned)mTiles); dM = (int)(step - (unsigned)gz * (unsigned)mTiles);
+      d0 = gz / b1; d1 = gz - d0 * b1;
+    }
+    __device__ void next() {
+      tileM += dM; int c = tileM >= mTiles; tileM -= c * mTiles;
+      zb1 += d1 + c; c = zb1 >= b1; zb1 -= c * b1;
+      zb0 += d0 + c;
+    }
   };
 
   if (warp == kIssuerWarp) {
     if (lane == 0) {
-      // Loader and MMA issuer.  Per tile: S = Q K^T as soon as Q and K are there; once that MMA is complete (Q, K
-      // and, from the previous tile, V and P are free again) the next tile's Q, K and this tile's V are requested,
-      // so their flight time hides behind the softmax; O = P V when the softmax warps have written P.
+      // Loader and MMA issuer.  Per tile: once S = Q K^T is complete (Q, K and, from the previous tile, V and P are
+      // free again: a commit covers every MMA issued before it) the next tile's Q, K and this tile's V are requested;
+      // O = P V round by round as the softmax warps hand P over; then the next tile's S = Q K^T.
       prefetchTensorMap(&mapQ); prefetchTensorMap(&mapK); prefetchTensorMap(&mapV);
-      auto loadQK = [&](long long t) {
-        int tileM, zb0, zb1; coords(t, tileM, zb0, zb1);
+      auto loadQK = [&](const TileWalk& w) {
+        const int tileM = w.tileM, zb0 = w.zb0, zb1 = w.zb1;
         mbarExpectTx(&bars[0], (1 + p.nBlocks) * kTile);
         tmaLoad4d(sQ, &mapQ, &bars[0], 0, tileM * kBM, zb1 * p.qZ1, zb0 * p.qZ0);
         for (int j = 0; j < p.nBlocks; ++j) tmaLoad4d(sK + j * kTile, &mapK, &bars[0], 0, j * 128, zb1 * p.kZ1, zb0 * p.kZ0);
@@ -100,35 +127,108 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       constexpr uint32_t idescS = instrDesc(1, kBM, 128, 0, 0);
       constexpr uint32_t idescO = instrDesc(1, kBM, kD, 0, 1);
       const uint64_t dQ = smemDescKMajorSw128(smemAddr(sQ));
-      if ((long long)blockIdx.x < p.tiles) loadQK(blockIdx.x);
-      uint32_t it = 0;
-      bool ok = true;
-      for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it) {
-        const uint32_t ph = it & 1;
-        int tileM, zb0, zb1; coords(t, tileM, zb0, zb1);
-        ok = mbarWait(&bars[0], ph, abortWord);
-        tcFenceAfter();
-        for (int j = 0; j < p.nBlocks; ++j) {           // one 128 x 128 block of scores per 128 keys, K = 64 in four steps of 16
+      auto issueS = [&]() {                             // one 128 x 128 block of scores per 128 keys, K = 64 in four steps of 16
+        for (int j = 0; j < p.nBlocks; ++j) {
           const uint64_t dK = smemDescKMajorSw128(smemAddr(sK + j * kTile));
 #pragma unroll
           for (int k = 0; k < 4; ++k) mmaSS<false>(tmemBase + (uint32_t)(j * 128), dQ + 2 * k, dK + 2 * k, idescS, k > 0 ? 1u : 0u);
+          mmaCommit(&barS[j]);
         }
-        mmaCommit(&bars[2]);
-        ok = ok && mbarWait(&bars[2], ph, abortWord);   // every MMA issued so far is complete
-        if (t + gridDim.x < p.tiles) loadQK(t + gridDim.x);
+      };
+      bool ok = true;
+      TileWalk cur(p, blockIdx.x, gridDim.x), nxt = cur;
+      nxt.next();
+      if ((long long)blockIdx.x < p.tiles) {
+        loadQK(cur);
+        ok = mbarWait(&bars[0], 0, abortWord);
+        tcFenceAfter();
+        issueS();
+      }
+      uint32_t it = 0;
+      for (long long t = blockIdx.x; t < p.tiles && ok; t += gridDim.x, ++it, cur.next(), nxt.next()) {
+        const uint32_t ph = it & 1;
+        const int zb0 = cur.zb0, zb1 = cur.zb1;
+        const bool more = t + gridDim.x < p.tiles;
+        ok = mbarWait(&barS[p.nBlocks - 1], ph, abortWord);   // every MMA issued so far is complete
+        if (more) loadQK(nxt);
         mbarExpectTx(&bars[1], p.nBlocks * kTile);
         for (int j = 0; j < p.nBlocks; ++j) tmaLoad4d(sV + j * kTile, &mapV, &bars[1], 0, j * 128, zb1 * p.vZ1, zb0 * p.vZ0);
-        ok = ok && mbarWait(&bars[3], ph, abortWord) && mbarWait(&bars[1], ph, abortWord);
-        if (it > 0) ok = ok && mbarWait(&bars[5], ph ^ 1, abortWord);   // the previous tile's O has been read
-        tcFenceAfter();
-        for (int a = 0; a < p.kAtoms; ++a) {            // P is K-major in atoms of 64 keys, V the MN-major operand (head dim contiguous)
-          const uint64_t dP = smemDescKMajorSw128(smemAddr(sP + a * kTile));
-          const uint64_t dV = smemDescMnMajorSw128(smemAddr(sV + a * 64 * 128), 64 * 128);
+        ok = ok && mbarWait(&bars[1], ph, abortWord);
+        if (it > 0) ok = ok && mbarWait(&bars[3], ph ^ 1, abortWord);   // the previous tile's O has been read
+        uint32_t accumulate = 0;
+        for (int r = p.nBlocks - 1; r >= 0; --r) {      // P is K-major in atoms of 64 keys, V the MN-major operand (head dim contiguous);
+          ok = ok && mbarWait(&barP[r], ph, abortWord);  // the softmax warps hand the rounds over from the last key block to the first
+          tcFenceAfter();
+          for (int a = 2 * r; a < 2 * r + 2 && a < p.kAtoms; ++a) {
+            const uint64_t dP = smemDescKMajorSw128(smemAddr(sP + a * kTile));
+            const uint64_t dV = smemDescMnMajorSw128(smemAddr(sV + a * 64 * 128), 64 * 128);
 #pragma unroll
-          for (int k = 0; k < 4; ++k) mmaSS<false>(tmemBase + kMaxN, dP + 2 * k, dV + (uint64_t)(k * ((16 * 128) >> 4)), idescO, (a > 0 || k > 0) ? 1u : 0u);
+            for (int k = 0; k < 4; ++k) { mmaSS<false>(tmemBase + kMaxN, dP + 2 * k, dV + (uint64_t)(k * ((16 * 128) >> 4)), idescO, accumulate); accumulate = 1; }
+          }
         }
-        mmaCommit(&bars[4]);                            // also reached after a failed wait, so that the other warps do not spin out
+        mmaCommit(&bars[2]);                            // also reached after a failed wait, so that the other warps do not spin out
+        if (more && ok) {                               // the score columns are free: every softmax thread has read them
+          ok = mbarWait(&bars[0], ph ^ 1, abortWord);
+          tcFenceAfter();
+          issueS();
+        }
         if (!ok) atomicExch(&g_attnStatus, 6);
+      }
+    }
+  } else if (warp == kMaskWarp) {
+    // ---------------------------------------------------------------- mask rows
+    // One mask row (times log2 e; -inf past the last key) per tile, into one of two buffers, a tile ahead of the softmax
+    // warps: a global load issued by them would stall them for as long as the TMA loads keep the memory system busy.
+    if (rowMask) {
+      const int usedCols = p.nBlocks * 128;
+      uint32_t it = 0;
+      bool ok = true;
+      TileWalk w(p, blockIdx.x, gridDim.x);
+      for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++it, w.next()) {
+        const int buf = (int)(it & 1);
+        const uint32_t use = it >> 1;                  // how often this buffer has been filled before
+        if (use > 0 && ok && !mbarWait(&barMaskFree[buf], (use - 1) & 1, abortWord)) { atomicExch(&g_attnStatus, 8); ok = false; }
+        const long long mBase = w.zb0 * p.m_s0 + w.zb1 * p.m_s1;
+        // every load of the row is issued before the first one is used (a branch per element would serialise them)
+        constexpr int kPerLane = kMaxN / 32;
+        float mv[kPerLane];
+        const int last = (int)p.N - 1;
+        if (p.mask == nullptr) {
+#pragma unroll
+          for (int i = 0; i < kPerLane; ++i) mv[i] = 0.f;
+        } else if (p.mask_dtype == LLC_FLOAT32) {
+          const float* m = static_cast<const float*>(p.mask) + mBase;
+#pragma unroll
+          for (int i = 0; i < kPerLane; ++i) mv[i] = __ldg(m + min(lane + 32 * i, last));
+        } else {
+          const __nv_bfloat16* m = static_cast<const __nv_bfloat16*>(p.mask) + mBase;
+#pragma unroll
+          for (int i = 0; i < kPerLane; ++i) mv[i] = __bfloat162float(m[min(lane + 32 * i, last)]);
+        }
+        bool any = false;
+#pragma unroll
+        for (int i = 0; i < kPerLane; ++i) {
+          const int c = lane + 32 * i;
+          const float v = c < p.N ? mv[i] * kLog2e : -INFINITY;
+          sMask[buf * kMaxN + c] = v;
+          any = any || (c < usedCols && v != 0.f);
+        }
+        any = __any_sync(0xffffffffu, any);
+        if (lane == 0) { sMaskSet[buf] = any ? 1 : 0; mbarArrive(&barMaskFull[buf]); }   // the arrive releases the warp's writes (ordered by the vote)
+      }
+    }
+  } else if (warp == kStoreWarp) {
+    // ---------------------------------------------------------------- output tiles: shared memory -> one TMA store each
+    if (lane == 0) {
+      TileWalk w(p, blockIdx.x, gridDim.x);
+      uint32_t it = 0;
+      bool ok = true;
+      for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++it, w.next()) {
+        if (ok && !mbarWait(barOut, it & 1, abortWord)) { atomicExch(&g_attnStatus, 9); ok = false; }
+        tmaStore4d(&mapO, sP, 0, w.tileM * kBM, w.zb1, w.zb0);   // also clips the rows past the last query
+        bulkCommit();
+        bulkWaitRead();                                // the store has read the staging buffer: P may overwrite it
+        mbarArrive(barOutFree);
       }
     }
   } else {
@@ -136,58 +236,60 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
     const int q = warp & 3, h = warp >> 2;             // tensor-memory lane quarter (a hardware rule) and chunk group
     const int row = q * 32 + lane;
     const uint32_t trow = tmemBase + ((uint32_t)(q * 32) << 16);
-    const int nChunks = p.nBlocks * 4;
-    int maskZ = -1;
-    bool plain = false;                                // the mask row is all zeros and covers every column: logits are scale * score
+    const int nB = p.nBlocks;                          // rounds: in round r group h owns chunk 4r + h, which lies in key block r
     uint32_t it = 0;
     bool ok = true;                                    // after a wait gave up the loop still runs (every thread must reach every barrier)
-    for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++it) {
+    TileWalk w(p, blockIdx.x, gridDim.x);
+    for (long long t = blockIdx.x; t < p.tiles; t += gridDim.x, ++it, w.next()) {
       const uint32_t ph = it & 1;
-      int tileM, zb0, zb1; coords(t, tileM, zb0, zb1);
+      const int tileM = w.tileM, zb0 = w.zb0, zb1 = w.zb1;
       const long long gm = (long long)tileM * kBM + row;
-      const int z = zb0 * p.b1 + zb1;
-      if (rowMask && z != maskZ) {                     // mask row (times log2 e); columns past the last key get -inf
-        if (threadIdx.x == 0) *sMaskSet = 0;
-        softmaxBarrier();
-        const long long mBase = zb0 * p.m_s0 + zb1 * p.m_s1;
-        bool any = false;
-        for (int c = threadIdx.x; c < kMaxN; c += kSoftmaxThreads) {
-          const float mv = c < p.N ? (p.mask ? loadAs(p.mask, mBase + c, p.mask_dtype) * kLog2e : 0.f) : -INFINITY;
-          sMask[c] = mv;
-          any = any || (c < nChunks * 32 && mv != 0.f);
-        }
-        if (any) *sMaskSet = 1;
-        maskZ = z;
-        softmaxBarrier();
-        plain = *sMaskSet == 0 && p.scaleLog2e > 0.f;
-      }
-      softmaxBarrier();
+      float* sMaskCur = sMask + (it & 1) * kMaxN;
+      if (rowMask && ok && !mbarWait(&barMaskFull[it & 1], (it >> 1) & 1, abortWord)) { atomicExch(&g_attnStatus, 7); ok = false; }
+      // the mask row is all zeros and covers every column: logits are scale * score
+      const bool plain = rowMask && sMaskSet[it & 1] == 0 && p.scaleLog2e > 0.f;
       const long long mRow = zb0 * p.m_s0 + zb1 * p.m_s1 + gm * p.m_sm;
       auto logit = [&](float s, int col) -> float {    // scaled score plus mask, in units of log2
-        if (rowMask) return fmaf(s, p.scaleLog2e, sMask[col]);
+        if constexpr (rowMask) return fmaf(s, p.scaleLog2e, sMaskCur[col]);
         if (col >= p.N || gm >= p.M) return col < p.N ? s * p.scaleLog2e : -INFINITY;
         return fmaf(s, p.scaleLog2e, loadAs(p.mask, mRow + col, p.mask_dtype) * kLog2e);
       };
-      if (ok && !mbarWait(&bars[2], ph, abortWord)) { atomicExch(&g_attnStatus, 7); ok = false; }
-      tcFenceAfter();
-      float mx = -INFINITY;
-      for (int c = h; c < nChunks; c += kGroups) {
-        float v[32];
-        __syncwarp();
-        tmemLoad32x32(trow + (uint32_t)(c * 32), v);
+      // ---- pass 1: row maximum.  Chunk r of the thread lives in sc[r & 1]; the load of the next chunk is in flight while
+      // this one is worked on.  Tensor memory delivers about 128 bytes per clock to the SM, which is what bounds this pass.
+      uint32_t sc[2][32];
+      auto chunkMax = [&](const uint32_t* v, int c, float mx) -> float {
         if (plain) {                                     // no mask at all: the maximum of the raw scores, scaled afterwards
 #pragma unroll
-          for (int j = 0; j < 32; j += 2) mx = fmaxf(mx, fmaxf(v[j], v[j + 1]));
+          for (int j = 0; j < 32; j += 2) mx = fmaxf(mx, fmaxf(__uint_as_float(v[j]), __uint_as_float(v[j + 1])));
         } else if (rowMask) {                            // the mask row sits in shared memory, four columns per load
-          const float4* m4 = reinterpret_cast<const float4*>(sMask + c * 32);
+          const float4* m4 = reinterpret_cast<const float4*>(sMaskCur + c * 32);
 #pragma unroll
           for (int j = 0; j < 8; ++j) {
             const float4 mk = m4[j];
-            mx = fmaxf(fmaxf(mx, fmaf(v[4 * j], p.scaleLog2e, mk.x)), fmaxf(fmaf(v[4 * j + 1], p.scaleLog2e, mk.y), fmaxf(fmaf(v[4 * j + 2], p.scaleLog2e, mk.z), fmaf(v[4 * j + 3], p.scaleLog2e, mk.w))));
+            mx = fmaxf(fmaxf(mx, fmaf(__uint_as_float(v[4 * j]), p.scaleLog2e, mk.x)),
+                       fmaxf(fmaf(__uint_as_float(v[4 * j + 1]), p.scaleLog2e, mk.y),
+                             fmaxf(fmaf(__uint_as_float(v[4 * j + 2]), p.scaleLog2e, mk.z), fmaf(__uint_as_float(v[4 * j + 3]), p.scaleLog2e, mk.w))));
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, logit(v[j], c * 32 + j));
+          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, logit(__uint_as_float(v[j]), c * 32 + j));
+        }
+        return mx;
+      };
+      auto waitS = [&](int r) {
+        if (ok && !mbarWait(&barS[r], ph, abortWord)) { atomicExch(&g_attnStatus, 7); ok = false; }
+        tcFenceAfter();
+        __syncwarp();
+      };
+      float mx = -INFINITY;
+      waitS(0);
+      tmemIssue32(trow + (uint32_t)(h * 32), sc[0]);
+#pragma unroll
+      for (int r = 0; r < 3; ++r) {
+        if (r < nB) {
+          tmemWait32(sc[r & 1]);
+          if (r + 1 < nB) { waitS(r + 1); tmemIssue32(trow + (uint32_t)((4 * (r + 1) + h) * 32), sc[(r + 1) & 1]); }
+          mx = chunkMax(sc[r & 1], 4 * r + h, mx);
         }
       }
       if (plain) mx *= p.scaleLog2e;
@@ -196,65 +298,79 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
 #pragma unroll
       for (int g = 0; g < kGroups; ++g) mx = fmaxf(mx, sMax[g * 128 + row]);
       if (mx == -INFINITY) mx = 0.f;                   // a fully masked row: all probabilities become 0
-      float sum = 0.f;
-      for (int c = h; c < nChunks; c += kGroups) {
-        float v[32];
-        __syncwarp();
-        tmemLoad32x32(trow + (uint32_t)(c * 32), v);
-        const uint32_t rowAddr = smemAddr(sP + (c >> 1) * kTile) + (uint32_t)row * 128u;
+      // ---- pass 2: exp2 and row sum, from the last chunk (still in registers) down to the first, each earlier chunk read
+      // again while the one after it is worked on; P is handed to the second MMA after every round
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int j = 0; j < 4; ++j) {
-          __nv_bfloat162 pk[4];
-          float e8[8];
-          if (plain) {
+      for (int r = 2; r >= 0; --r) {
+        if (r < nB) {
+          const int c = 4 * r + h;
+          const uint32_t* v = sc[r & 1];
+          // the first atoms of P double as the staging buffer of the previous tile's output
+          if (r == 0 && it > 0 && ok && !mbarWait(barOutFree, (it - 1) & 1, abortWord)) { atomicExch(&g_attnStatus, 7); ok = false; }
+          if (r < nB - 1) tmemWait32(sc[r & 1]);
+          if (r > 0) { __syncwarp(); tmemIssue32(trow + (uint32_t)((c - 4) * 32), sc[(r - 1) & 1]); }
+          else tcFenceBefore();                          // this thread's reads of S come before the next tile's MMA, which may overwrite it
+          const uint32_t rowAddr = smemAddr(sP + (c >> 1) * kTile) + (uint32_t)row * 128u;
 #pragma unroll
-            for (int e = 0; e < 8; ++e) e8[e] = v[j * 8 + e] * p.scaleLog2e;
-          } else if (rowMask) {
-            const float4 ma = reinterpret_cast<const float4*>(sMask + c * 32 + j * 8)[0], mb = reinterpret_cast<const float4*>(sMask + c * 32 + j * 8)[1];
-            e8[0] = fmaf(v[j * 8], p.scaleLog2e, ma.x); e8[1] = fmaf(v[j * 8 + 1], p.scaleLog2e, ma.y); e8[2] = fmaf(v[j * 8 + 2], p.scaleLog2e, ma.z); e8[3] = fmaf(v[j * 8 + 3], p.scaleLog2e, ma.w);
-            e8[4] = fmaf(v[j * 8 + 4], p.scaleLog2e, mb.x); e8[5] = fmaf(v[j * 8 + 5], p.scaleLog2e, mb.y); e8[6] = fmaf(v[j * 8 + 6], p.scaleLog2e, mb.z); e8[7] = fmaf(v[j * 8 + 7], p.scaleLog2e, mb.w);
-          } else {
+          for (int j = 0; j < 4; ++j) {
+            __nv_bfloat162 pk[4];
+            float e8[8];
+            if (plain) {
 #pragma unroll
-            for (int e = 0; e < 8; ++e) e8[e] = logit(v[j * 8 + e], c * 32 + j * 8 + e);
+              for (int e = 0; e < 8; ++e) e8[e] = fmaf(__uint_as_float(v[j * 8 + e]), p.scaleLog2e, -mx);
+            } else if (rowMask) {
+              const float4 ma = reinterpret_cast<const float4*>(sMaskCur + c * 32 + j * 8)[0], mb = reinterpret_cast<const float4*>(sMaskCur + c * 32 + j * 8)[1];
+              const float mk[8] = {ma.x, ma.y, ma.z, ma.w, mb.x, mb.y, mb.z, mb.w};
+#pragma unroll
+              for (int e = 0; e < 8; ++e) e8[e] = fmaf(__uint_as_float(v[j * 8 + e]), p.scaleLog2e, mk[e]) - mx;
+            } else {
+#pragma unroll
+              for (int e = 0; e < 8; ++e) e8[e] = logit(__uint_as_float(v[j * 8 + e]), c * 32 + j * 8 + e) - mx;
+            }
+#pragma unroll
+            for (int e = 0; e < 8; ++e) { e8[e] = fastExp2(e8[e]); sum4[e & 3] += e8[e]; }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) pk[e] = __floats2bfloat162_rn(e8[2 * e], e8[2 * e + 1]);
+            const uint32_t chunk = (uint32_t)((c & 1) * 4 + j);
+            asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + ((chunk ^ (uint32_t)(row & 7)) << 4)), "r"(*reinterpret_cast<unsigned*>(&pk[0])),
+                         "r"(*reinterpret_cast<unsigned*>(&pk[1])), "r"(*reinterpret_cast<unsigned*>(&pk[2])), "r"(*reinterpret_cast<unsigned*>(&pk[3])) : "memory");
           }
-#pragma unroll
-          for (int e = 0; e < 8; ++e) { e8[e] = fastExp2(e8[e] - mx); sum += e8[e]; }
-#pragma unroll
-          for (int e = 0; e < 4; ++e) pk[e] = __floats2bfloat162_rn(e8[2 * e], e8[2 * e + 1]);
-          const uint32_t chunk = (uint32_t)((c & 1) * 4 + j);
-          asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + ((chunk ^ (uint32_t)(row & 7)) << 4)), "r"(*reinterpret_cast<unsigned*>(&pk[0])),
-                       "r"(*reinterpret_cast<unsigned*>(&pk[1])), "r"(*reinterpret_cast<unsigned*>(&pk[2])), "r"(*reinterpret_cast<unsigned*>(&pk[3])) : "memory");
+          // Round done: atoms 2r and 2r+1 of P are whole once every group has written its chunk.
+          if (r == 0) sSum[h * 128 + row] = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+          fenceProxyAsync();                             // P was written through the generic proxy, the MMA reads it through the async proxy
+          softmaxBarrier();
+          if (threadIdx.x == 0) mbarArrive(&barP[r]);
         }
       }
-      sSum[h * 128 + row] = sum;
-      tcFenceBefore();                                 // this thread's reads of S are done before the next tile's MMA may overwrite it
-      fenceProxyAsync();                               // P was written through the generic proxy, the MMA reads it through the async proxy
-      softmaxBarrier();
-      if (threadIdx.x == 0) mbarArrive(&bars[3]);
+      if (rowMask && threadIdx.x == 0) mbarArrive(&barMaskFree[it & 1]);   // past the last barrier: nobody reads this tile's mask row any more
       float tot = 0.f;
 #pragma unroll
       for (int g = 0; g < kGroups; ++g) tot += sSum[g * 128 + row];
       const float inv = 1.f / tot;
-      if (ok && !mbarWait(&bars[4], ph, abortWord)) { atomicExch(&g_attnStatus, 7); ok = false; }
+      if (ok && !mbarWait(&bars[2], ph, abortWord)) { atomicExch(&g_attnStatus, 7); ok = false; }
       tcFenceAfter();
-      // epilogue: group h takes 64 / kGroups output columns of its rows
+      // ---- epilogue: group h takes 64 / kGroups output columns of its rows; the tile leaves through the first atom of the
+      // P buffer (free once the second MMA is complete) and one TMA store, which also clips the rows past the last query
       constexpr int kCols = kD / kGroups;
       float o[kCols];
       __syncwarp();
       tmemLoadCols<kCols>(trow + (uint32_t)(kMaxN + h * kCols), o);
       tcFenceBefore();
       __syncwarp();
-      if (lane == 0) mbarArrive(&bars[5]);             // O is in registers: the next tile's second MMA may overwrite it
-      if (gm < p.M) {
-        uint4* dst = reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + zb0 * p.o_s0 + zb1 * p.o_s1 + gm * p.o_sm + h * kCols);
+      if (lane == 0) mbarArrive(&bars[3]);             // O is in registers: the next tile's second MMA may overwrite it
+      const uint32_t outRow = smemAddr(sP) + (uint32_t)row * 128u;
 #pragma unroll
-        for (int j = 0; j < kCols / 8; ++j) {
-          __nv_bfloat162 a0 = __floats2bfloat162_rn(o[8 * j] * inv, o[8 * j + 1] * inv), a1 = __floats2bfloat162_rn(o[8 * j + 2] * inv, o[8 * j + 3] * inv);
-          __nv_bfloat162 a2 = __floats2bfloat162_rn(o[8 * j + 4] * inv, o[8 * j + 5] * inv), a3 = __floats2bfloat162_rn(o[8 * j + 6] * inv, o[8 * j + 7] * inv);
-          uint4 pk; pk.x = *reinterpret_cast<unsigned*>(&a0); pk.y = *reinterpret_cast<unsigned*>(&a1); pk.z = *reinterpret_cast<unsigned*>(&a2); pk.w = *reinterpret_cast<unsigned*>(&a3);
-          dst[j] = pk;
-        }
+      for (int j = 0; j < kCols / 8; ++j) {
+        __nv_bfloat162 a0 = __floats2bfloat162_rn(o[8 * j] * inv, o[8 * j + 1] * inv), a1 = __floats2bfloat162_rn(o[8 * j + 2] * inv, o[8 * j + 3] * inv);
+        __nv_bfloat162 a2 = __floats2bfloat162_rn(o[8 * j + 4] * inv, o[8 * j + 5] * inv), a3 = __floats2bfloat162_rn(o[8 * j + 6] * inv, o[8 * j + 7] * inv);
+        const uint32_t chunk = (uint32_t)(h * (kCols / 8) + j);
+        asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(outRow + ((chunk ^ (uint32_t)(row & 7)) << 4)), "r"(*reinterpret_cast<unsigned*>(&a0)),
+                     "r"(*reinterpret_cast<unsigned*>(&a1)), "r"(*reinterpret_cast<unsigned*>(&a2)), "r"(*reinterpret_cast<unsigned*>(&a3)) : "memory");
       }
+      fenceProxyAsync();
+      __syncwarp();
+      if (lane == 0) mbarArrive(barOut);               // the store warp sends the tile off
     }
   }
   tcFenceBefore();
@@ -334,9 +450,9 @@ extern "C" int llc_cuda_attention(const LlcAttentionParams* p, void* stream) {
   if (p->n > kMaxN || (forceBlocks && forceBlocks[0] == '1')) return attentionBlocks(p, static_cast<cudaStream_t>(stream));
   const long long batch = p->b0 * p->b1, mTiles = (p->m + kBM - 1) / kBM;
   if (batch * mTiles > 0x7FFFFFFFLL) return setError(LLC_ERR_UNSUPPORTED, "llc_cuda_attention: too many tiles");
-  CUtensorMap mq, mk, mv;
+  CUtensorMap mq, mk, mv, mo;
   if (!makeHeadMap(&mq, p->q, p->m, p->b1, p->b0, p->q_sm, p->q_s1, p->q_s0) || !makeHeadMap(&mk, p->k, p->n, p->b1, p->b0, p->k_sn, p->k_s1, p->k_s0) ||
-      !makeHeadMap(&mv, p->v, p->n, p->b1, p->b0, p->v_sn, p->v_s1, p->v_s0))
+      !makeHeadMap(&mv, p->v, p->n, p->b1, p->b0, p->v_sn, p->v_s1, p->v_s0) || !makeHeadMap(&mo, p->out, p->m, p->b1, p->b0, p->o_sm, p->o_s1, p->o_s0))
     return setError(LLC_ERR_CUDA, "llc cuda: cuTensorMapEncodeTiled rejected the attention operands");
   AttnArgs a{};
   a.out = p->out; a.mask = p->mask; a.mask_dtype = p->mask_dtype;
@@ -349,14 +465,16 @@ extern "C" int llc_cuda_attention(const LlcAttentionParams* p, void* stream) {
   static DeviceOnce configured;                          // the shared-memory opt-in is kept per device
   const int dev = currentDevice();
   if (!configured.test(dev)) {
-    cudaError_t e = cudaFuncSetAttribute(attention_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    cudaError_t e = cudaFuncSetAttribute(attention_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(attention_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes);
     if (e != cudaSuccess) return cudaFail(e, "cudaFuncSetAttribute(attention_kernel)");
     configured.set(dev);
   }
   a.tiles = batch * mTiles;
   const int sms = deviceSMs();
   const unsigned grid = (unsigned)(a.tiles < sms ? a.tiles : sms);
-  attention_kernel<<<grid, kSoftmaxThreads + 32, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, a);
+  if (p->mask == nullptr || p->mask_sm == 0) attention_kernel<true><<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mo, a);
+  else attention_kernel<false><<<grid, kThreads, kSmemBytes, static_cast<cudaStream_t>(stream)>>>(mq, mk, mv, mo, a);
   LLC_LAUNCH_CHECK("attention_kernel");
   return LLC_OK;
 }
