@@ -86,7 +86,7 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
   constexpr int kIssuerWarp = kSoftmaxThreads / 32, kMaskWarp = kIssuerWarp + 1, kStoreWarp = kIssuerWarp + 2;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < 16; ++i) mbarInit(&bars[i], (i == 3 || i == 14) ? kSoftmaxThreads / 32 : 1);   // O read, output staged: one arrival per softmax warp
+    for (int i = 0; i < 16; ++i) mbarInit(&bars[i], (i == 3 || (i >= 7 && i <= 9) || i == 14) ? kSoftmaxThreads / 32 : 1);   // O read, P rounds, output staged: one arrival per softmax warp
     *abortWord = 0;
     fenceBarrierInit();
   }
@@ -336,13 +336,14 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
             asm volatile("st.shared.v4.b32 [%0], {%1, %2, %3, %4};" ::"r"(rowAddr + ((chunk ^ (uint32_t)(row & 7)) << 4)), "r"(*reinterpret_cast<unsigned*>(&pk[0])),
                          "r"(*reinterpret_cast<unsigned*>(&pk[1])), "r"(*reinterpret_cast<unsigned*>(&pk[2])), "r"(*reinterpret_cast<unsigned*>(&pk[3])) : "memory");
           }
-          // Round done: atoms 2r and 2r+1 of P are whole once every group has written its chunk.
-          if (r == 0) sSum[h * 128 + row] = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+          // Round done for this warp: atoms 2r and 2r+1 of P are whole once every warp has arrived (no CTA-wide barrier).
           fenceProxyAsync();                             // P was written through the generic proxy, the MMA reads it through the async proxy
-          softmaxBarrier();
-          if (threadIdx.x == 0) mbarArrive(&barP[r]);
+          __syncwarp();
+          if (lane == 0) mbarArrive(&barP[r]);
         }
       }
+      sSum[h * 128 + row] = (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+      softmaxBarrier();
       if (rowMask && threadIdx.x == 0) mbarArrive(&barMaskFree[it & 1]);   // past the last barrier: nobody reads this tile's mask row any more
       float tot = 0.f;
 #pragma unroll
