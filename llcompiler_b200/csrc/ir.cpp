@@ -217,7 +217,11 @@ std::string Module::str() const {
     }
     o << "  }\n";
   }
-  for (auto& l : symbolRelations) o << "  " << l << "\n";
+  if (!symbolRelations.empty()) {   // the relations live in a module of their own, as in the reference's output
+    o << "  module @__symbol__ {\n";
+    for (auto& l : symbolRelations) o << "    " << l << "\n";
+    o << "  }\n";
+  }
   o << "}\n";
   return o.str();
 }
@@ -508,6 +512,21 @@ struct Parser {
         Type t = v.type;
         if (t.kind == Type::Scalar && t.elt == DType::Index) t.elt = DType::I64;
         Value* r = m->newValue(t, resultNames[0]);
+        r->def = op; op->results.push_back(r); values[resultNames[0]] = r;
+      } else if (name == "tensor.dim" || name == "arith.addi" || name == "arith.subi" || name == "arith.muli" || name == "arith.divsi" ||
+                 name == "arith.index_cast") {
+        // index arithmetic around shapes, in MLIR's custom form; read as the LLH scalar ops over i64 that say the same
+        // (`tensor.dim %t, %i : type`, `arith.subi %a, %b : index`, `arith.index_cast %a : index to i64`)
+        static const std::map<std::string, std::string> same = {{"tensor.dim", "llh.dim"}, {"arith.addi", "llh.add"}, {"arith.subi", "llh.sub"},
+                                                                {"arith.muli", "llh.mul"}, {"arith.divsi", "llh.div"}, {"arith.index_cast", "llh.scalar_cast"}};
+        op = m->newOp(same.at(name));
+        if (peek("{")) op->attrs = attrDict("{", "}");
+        for (;;) { op->operands.push_back(use(valueName())); if (!eat(",")) break; }
+        expect(":");
+        type();
+        if (name == "arith.index_cast") { if (!eatWord("to")) fail("arith.index_cast: expected 'to'"); type(); }
+        if (resultNames.size() != 1) fail(name + " needs one result");
+        Value* r = m->newValue(Type::scalar(DType::I64), resultNames[0]);
         r->def = op; op->results.push_back(r); values[resultNames[0]] = r;
       } else {
         fail("unsupported custom-form operation '" + name + "'");

@@ -163,6 +163,13 @@ struct Lowering {
   std::vector<PendingK> pend;
   std::vector<AttnCand> attn;
   bool shapesOnly = false;     // infer-symbol-shape: the plan is discarded, so results need not be materialised (scalars may be returned)
+  // How a derived extent came about, keyed by its printed form: the affine map the reference attaches to the new symbol
+  // (SymbolAnalysis::buildNewSymbol, LLHinfersymbolShape.cpp:277-292) and the extents it is a function of.
+  struct RelInfo { std::string map; std::vector<Expr> operands; };
+  std::map<std::string, RelInfo> relInfo;
+  void noteRelation(const Expr& result, const std::string& map, const std::vector<Expr>& operands) {
+    if (!result.isConst()) relInfo.emplace(result.str(), RelInfo{map, operands});
+  }
   std::map<Value*, TV> tvs;
   std::map<std::string, int> constVecCache;
 
@@ -760,8 +767,17 @@ struct Lowering {
   }
   Expr windowOut(const Expr& in, int64_t padLo, int64_t padHi, int64_t dil, int64_t k, int64_t stride, bool ceil = false) {
     // LLHinfersymbolShape.cpp:257-292: (in + pad_l + pad_h - dil*(k-1) - 1) / stride + 1
-    Expr num = in + Expr(padLo + padHi - dil * (k - 1) - 1);
-    return (ceil ? num.ceildiv(Expr(stride)) : num.floordiv(Expr(stride))) + Expr(1);
+    const int64_t c = padLo + padHi - dil * (k - 1) - 1;
+    Expr num = in + Expr(c);
+    Expr out = (ceil ? num.ceildiv(Expr(stride)) : num.floordiv(Expr(stride))) + Expr(1);
+    if (!in.isConst()) {
+      // the reference records the relation as the map (s0 + c) ceildiv stride + 1 (LLHinfersymbolShape.cpp:281-287), printed
+      // the way MLIR prints affine expressions
+      auto plus = [](const std::string& a, int64_t v) { return v == 0 ? a : a + (v < 0 ? " - " : " + ") + std::to_string(v < 0 ? -v : v); };
+      std::string body = stride == 1 ? plus("s0", c + 1) : plus((c == 0 ? std::string("s0") : "(" + plus("s0", c) + ")") + " ceildiv " + std::to_string(stride), 1);
+      noteRelation(out, "(d0)[s0] -> (" + body + ")", {in});
+    }
+    return out;
   }
   void conv(Op* op, bool hasBias) {
     Value* xv = op->operands[0];
@@ -1217,6 +1233,8 @@ struct Lowering {
       if (en.isConst() && en.constant() < 0) en = en + x.shape[d];
       o.offset = o.offset + st * x.strides[d];
       o.shape[d] = (en - st).ceildiv(sp);
+      if (!(o.shape[d] == x.shape[d]))
+        noteRelation(o.shape[d], sp.isConst(1) ? "(d0)[s0, s1] -> (s0 - s1)" : "(d0)[s0, s1, s2] -> ((s0 - s1) ceildiv s2)", sp.isConst(1) ? std::vector<Expr>{en, st} : std::vector<Expr>{en, st, sp});
       o.strides[d] = x.strides[d] * sp;
     }
     tvs[op->results[0]] = makeView(o, raw(xv).isConst);
@@ -1270,6 +1288,8 @@ struct Lowering {
     TV t; t.kind = TV::Scalar; t.dtype = DType::I64; t.isConst = true;
     if (name == "add") t.scalar = a + b; else if (name == "sub") t.scalar = a - b; else if (name == "mul") t.scalar = a * b;
     else if (name == "div") t.scalar = a.floordiv(b); else fail("unsupported scalar op llh." + name);
+    const char* sign = name == "add" ? "+" : name == "sub" ? "-" : name == "mul" ? "*" : "floordiv";
+    noteRelation(t.scalar, std::string("(d0)[s0, s1] -> (s0 ") + sign + " s1)", {a, b});
     tvs[op->results[0]] = t;
   }
 
@@ -1457,6 +1477,14 @@ struct Lowering {
       else if (s == "conv") conv(op, false);
       else if (s == "conv_bias") conv(op, true);
       else if (s == "batch_norm_inference") batchNormInference(op);
+      else if (s == "batch_norm" && shapesOnly) {       // shapes only: the result has the input's shape, the statistics keep their declared types
+        TV x = get(op->operands[0]);
+        for (size_t i = 0; i < op->results.size(); ++i) {
+          TV t; t.kind = TV::ViewK; t.dtype = op->results[i]->type.elt;
+          if (i == 0) t.shape = x.shape; else for (auto d : op->results[i]->type.dims) t.shape.push_back(Expr(d));
+          tvs[op->results[i]] = t;
+        }
+      }
       else if (s == "max_pool") maxPool(op);
       else if (s == "adaptive_average_pool") adaptiveAvgPool(op);
       else if (s == "reduce_sum") reduce(op, "sum");
@@ -1525,6 +1553,62 @@ void runInferSymbolShape(Module& m) {
       v->type.encoding.push_back(e.isConst() ? "c" + std::to_string(e.constant()) : e.str());
     }
   }
+  // A derived extent gets a symbol of its own, the lowest free "s<k>", and a relation that says how it follows from its
+  // operands (the reference: SymbolAnalysis::buildNewSymbol); equal expressions share one symbol.
+  m.leadingLines.clear();
+  std::vector<std::string> relationMaps;
+  {
+    auto isName = [](const std::string& n) { for (char c : n) if (!isalnum((unsigned char)c) && c != '_') return false; return !n.empty(); };
+    std::set<std::string> used;
+    std::vector<Value*> order;
+    Func* f0 = m.entrance();
+    if (f0) {
+      for (Value* a : f0->args) order.push_back(a);
+      for (Op* op : f0->ops) for (Value* r : op->results) order.push_back(r);
+    }
+    for (Value* v : order) if (v->type.isTensor()) for (auto& n : v->type.encoding) if (isName(n)) used.insert(n);
+    std::map<std::string, std::string> fresh;          // printed expression -> symbol
+    std::vector<std::string> created;
+    auto nameOf = [&](const std::string& expr) -> std::string {
+      if (isName(expr)) return expr;
+      auto it = fresh.find(expr);
+      if (it != fresh.end()) return it->second;
+      int k = 0;
+      while (used.count("s" + std::to_string(k))) ++k;
+      std::string n = "s" + std::to_string(k);
+      used.insert(n); fresh[expr] = n; created.push_back(expr);
+      return n;
+    };
+    for (Value* v : order) if (v->type.isTensor()) for (auto& n : v->type.encoding) n = nameOf(n);
+    // an integer scalar carries its symbol as an attribute of the op that produces it (the reference: `symbol = @c3`)
+    if (f0) for (Op* op : f0->ops) {
+      if (op->results.size() != 1 || op->results[0]->type.isTensor()) continue;
+      auto it = L.tvs.find(op->results[0]);
+      if (it == L.tvs.end() || it->second.kind != TV::Scalar || it->second.isFloatScalar) continue;
+      const Expr& e = it->second.scalar;
+      Attr a; a.kind = Attr::SymRef; a.s = e.isConst() ? "c" + std::to_string(e.constant()) : nameOf(e.str());
+      bool set = false;
+      for (auto& kv : op->props) if (kv.first == "symbol") { kv.second = a; set = true; }
+      if (!set) {
+        auto pos = op->props.begin();
+        while (pos != op->props.end() && pos->first < "symbol") ++pos;
+        op->props.insert(pos, std::make_pair(std::string("symbol"), a));
+      }
+    }
+    std::vector<std::string> maps;
+    for (size_t i = 0; i < created.size(); ++i) {      // may grow: an operand can be a derived extent that no tensor carries
+      const std::string expr = created[i];
+      auto it = L.relInfo.find(expr);
+      if (it == L.relInfo.end()) continue;
+      size_t mi = std::find(maps.begin(), maps.end(), it->second.map) - maps.begin();
+      if (mi == maps.size()) maps.push_back(it->second.map);
+      std::string rel;
+      for (auto& o : it->second.operands) rel += (rel.empty() ? "@" : ", @") + (o.isConst() ? "c" + std::to_string(o.constant()) : nameOf(o.str()));
+      relationMaps.push_back("\"llh.symbol_relation_map\"() <{express = \"" + expr + "\", relation = #map" + (mi ? std::to_string(mi) : "") + ", relations = [" + rel +
+                             "], symbol = @" + fresh[expr] + "}> : () -> ()");
+    }
+    for (size_t i = 0; i < maps.size(); ++i) m.leadingLines.push_back("#map" + (i ? std::to_string(i) : std::string()) + " = affine_map<" + maps[i] + ">");
+  }
   // every symbol an encoding names is declared once at the head of the module, arguments first, then in program order
   // (the reference's pass materialises them as llh.symbolic_int ops, SymbolAnalysis.cpp:266-330)
   m.symbolDecls.clear();
@@ -1561,6 +1645,7 @@ void runInferSymbolShape(Module& m) {
     m.symbolRelations.push_back("\"llh.symbol_relation\"() <{relation = @c1, relation_kind = #llh.SymbolRelation<GE>, symbol = @" + n + "}> : () -> ()");
   }
   if (anyDynamic && declared.insert("c1").second) m.symbolDecls.push_back("c1");
+  for (auto& l : relationMaps) m.symbolRelations.push_back(l);
   if (f) {
     f->resultTypes.clear();
     for (Op* op : f->ops) if (op->name == "func.return") for (Value* v : op->operands) f->resultTypes.push_back(v->type);
