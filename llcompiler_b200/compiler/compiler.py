@@ -174,7 +174,7 @@ class LLCompiler(Importer):
                 if isinstance(t, torch.Tensor):
                     _tensor_digest(h, t)
         opts = (tuple(static_positions), self.mode, self.target, self.pipeline, self.target_layout, self.precision, self.log_root,
-                os.environ.get("LLC_FUSE_ATTENTION", ""), os.environ.get("LLC_MERGE_STEM_ROWS", ""), type(self).__name__)
+                os.environ.get("LLC_FUSE_ATTENTION", ""), os.environ.get("LLC_MERGE_STEM_ROWS", ""), os.environ.get("LLC_FUSE_SIBLING_GEMMS", ""), type(self).__name__)
         h.update(repr(opts).encode())
         from .. import _capi
         st = os.stat(_capi.LIB_PATH)

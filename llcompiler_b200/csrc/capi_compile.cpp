@@ -31,6 +31,7 @@ static CompileOptionsData optionsFrom(const LlcOptions* o) {
   CompileOptionsData d;
   // LLC_FUSE_ATTENTION=0 keeps attention as GEMM, softmax, GEMM (the path every shape outside the fused kernel's limits takes)
   if (const char* e = getenv("LLC_FUSE_ATTENTION")) d.fuseAttention = !(e[0] == '0');
+  if (const char* e = getenv("LLC_FUSE_SIBLING_GEMMS")) d.fuseSiblingGemms = !(e[0] == '0');
   if (const char* e = getenv("LLC_MERGE_STEM_ROWS")) d.mergeStemRows = !(e[0] == '0');
   if (!o) return d;
   auto set = [](std::string& dst, const char* src) { if (src && *src) dst = src; };
@@ -116,7 +117,7 @@ extern "C" int llc_compile(const char* text, const LlcOptions* options, char* ou
     dump("02_kernel_plan.llcplan", body);
     // the artefact is named after a hash of the module text, like the reference's temp .so
     // (src/Compiler/Compiler.cpp:305-309)
-    size_t h = std::hash<std::string>()(std::string(text) + "|" + d.precision + (d.fuseAttention ? "|fa" : "") + (d.mergeStemRows ? "|ms" : ""));
+    size_t h = std::hash<std::string>()(std::string(text) + "|" + d.precision + (d.fuseAttention ? "|fa" : "") + (d.mergeStemRows ? "|ms" : "") + (d.fuseSiblingGemms ? "|sg" : ""));
     const char* tmp = getenv("TMPDIR");
     char path[512];
     snprintf(path, sizeof path, "%s/llc_%016zx_%d.llcplan", tmp && *tmp ? tmp : "/tmp", h, (int)getpid());

@@ -1511,9 +1511,140 @@ struct Lowering {
       else if (s == "drop") { TV c = get(op->operands[0]); tvs[op->results[0]] = c; }   // inference: identity
       else fail("no CUDA lowering for '" + n + "'");
     }
+    if (!shapesOnly && opts.fuseSiblingGemms) fuseSiblingGemms();
     plan.options["precision"] = opts.precision;
     plan.options["mode"] = opts.mode;
     plan.options["target"] = opts.target;
+  }
+
+  // ---- sibling GEMMs
+  // Several linear layers that read the same activation (the query, key and value projections of an attention layer)
+  // become one GEMM: the weights are stacked once at load into [G*N, K], the bias vectors into [G*N], the product is
+  // written as [M, G*N], and every later reader of one of the original outputs gets the matching column range of that
+  // buffer as a strided view.  One launch with a G times wider N keeps the tensor pipe busier than G launches do
+  // (measured on B200, bf16, M = 98304, K = 768: 1302 TFLOP/s at N = 2304 against 1144 at N = 768).
+  struct SiblingGemm {
+    View a, b, out, shift;
+    bool hasShift = false;
+    int64_t N = 0, K = 0;
+  };
+  bool siblingCandidate(const Step& s, SiblingGemm& g) const {
+    if (s.kernel != "gemm" || s.init) return false;
+    const View *a = s.view("a"), *b = s.view("b"), *o = s.view("out"), *sh = s.view("shift");
+    if (!a || !b || !o) return false;
+    for (auto& v : s.views) if (v.first != "a" && v.first != "b" && v.first != "out" && v.first != "shift") return false;
+    if (s.param("act") != "none" || s.param("prec") == "tf32x3") return false;
+    if (std::stod(s.param("alpha", "1")) != 1.0) return false;
+    if (a->rank() != 4 || b->rank() != 4 || o->rank() != 4) return false;
+    if (!a->shape[0].isConst(1) || !a->shape[1].isConst(1) || !b->shape[0].isConst(1) || !b->shape[1].isConst(1)) return false;
+    if (!b->shape[2].isConst() || !b->shape[3].isConst() || !b->offset.isConst() || !bufIsConst(b->buf)) return false;
+    g.K = b->shape[2].constant(); g.N = b->shape[3].constant();
+    if (!b->strides[2].isConst(1) || !b->strides[3].isConst(g.K)) return false;        // the weight as stored: [N][K]
+    if (g.N % 64 || g.K % 64) return false;
+    if (plan.buffers[o->buf].kind != BufferDecl::Temp || !o->offset.isConst(0) || o->strides != rowMajor(o->shape) || !o->shape[3].isConst(g.N)) return false;
+    if (sh) {
+      if (sh->rank() != 1 || !sh->shape[0].isConst(g.N) || !sh->strides[0].isConst(1) || sh->dtype != DType::F32 || !bufIsConst(sh->buf)) return false;
+      g.shift = *sh; g.hasShift = true;
+    }
+    g.a = *a; g.b = *b; g.out = *o;
+    return true;
+  }
+  // A view over one of the original [M, N] outputs, restated over the fused [M, G*N] buffer (column block j): every dim
+  // must either step through whole rows or stay inside one row.
+  bool remapIntoFused(View& v, int64_t N, int64_t G, int64_t j, int fusedBuf) const {
+    if (!v.offset.isConst()) return false;
+    const int64_t off = v.offset.constant(), col0 = off % N;
+    int64_t colSpan = col0;
+    View r = v;
+    for (size_t d = 0; d < v.rank(); ++d) {
+      if (v.shape[d].isConst(1)) { r.strides[d] = Expr(0); continue; }
+      if (!v.strides[d].isConst()) return false;
+      const int64_t st = v.strides[d].constant();
+      if (st % N == 0) { r.strides[d] = Expr(st / N * G * N); continue; }
+      if (st < 0 || !v.shape[d].isConst()) return false;
+      colSpan += (v.shape[d].constant() - 1) * st;
+    }
+    if (colSpan >= N) return false;
+    r.offset = Expr(off / N * G * N + col0 + j * N);
+    r.buf = fusedBuf;
+    v = r;
+    return true;
+  }
+  void fuseSiblingGemms() {
+    for (size_t i = 0; i < plan.steps.size(); ++i) {
+      SiblingGemm g0;
+      if (!siblingCandidate(plan.steps[i], g0)) continue;
+      std::vector<size_t> group = {i};
+      std::vector<SiblingGemm> gs = {g0};
+      for (size_t j = i + 1; j < plan.steps.size() && group.size() < 4; ++j) {
+        const Step& sj = plan.steps[j];
+        if (sj.init) continue;
+        if (const View* o = sj.view("out")) if (o->buf == g0.a.buf) break;       // the activation is overwritten: stop looking
+        SiblingGemm g;
+        if (!siblingCandidate(sj, g)) continue;
+        if (g.a.str() != g0.a.str() || g.N != g0.N || g.K != g0.K || g.b.dtype != g0.b.dtype || g.out.dtype != g0.out.dtype || g.hasShift != g0.hasShift ||
+            sj.param("prec") != plan.steps[i].param("prec") || !(g.out.shape[2] == g0.out.shape[2]))
+          continue;
+        group.push_back(j); gs.push_back(g);
+      }
+      if (group.size() < 2) continue;
+      bool isOutput = false;
+      for (auto& g : gs) for (auto& o : plan.outputs) isOutput = isOutput || o.buf == g.out.buf;
+      if (isOutput) continue;
+      // every reader of the original outputs must be expressible over the fused buffer; checked before anything changes.
+      // A group that does not work out is tried again without its last member.
+      int64_t G = 0;
+      const int64_t N = g0.N, K = g0.K;
+      int fusedBuf = -1;
+      std::vector<std::pair<View*, View>> rewrites;
+      bool ok = false;
+      for (; !ok && group.size() >= 2; ) {
+      G = (int64_t)group.size();
+      fusedBuf = newBuffer(g0.out.dtype, g0.out.shape[2] * Expr(G * N), BufferDecl::Temp);
+      rewrites.clear();
+      ok = true;
+      for (size_t k = 0; k < plan.steps.size() && ok; ++k) {
+        if (std::find(group.begin(), group.end(), k) != group.end()) continue;
+        // the fused GEMM takes the place of the last one (where the operands of all of them are ready), so nothing in
+        // between may read an output of the earlier ones
+        if (k > group.front() && k < group.back())
+          for (auto& nv : plan.steps[k].views) for (auto& g : gs) ok = ok && nv.second.buf != g.out.buf;
+        for (auto& nv : plan.steps[k].views)
+          for (int64_t j = 0; j < G && ok; ++j)
+            if (nv.second.buf == gs[j].out.buf) {
+              View r = nv.second;
+              ok = nv.first != "out" && remapIntoFused(r, N, G, j, fusedBuf);
+              rewrites.emplace_back(&nv.second, r);
+            }
+      }
+      if (!ok) { group.pop_back(); gs.pop_back(); }
+      }
+      if (!ok) continue;
+      for (auto& rw : rewrites) *rw.first = rw.second;
+      // stacked operands, built once at load (the load-time steps are placed directly in front of the fused GEMM, behind
+      // the load-time steps that make the operands of the single ones)
+      const size_t before = plan.steps.size();
+      View w = freshView(g0.b.dtype, {Expr(G * N), Expr(K)}, true), sh;
+      if (g0.hasShift) sh = freshView(DType::F32, {Expr(G * N)}, true);
+      for (int64_t j = 0; j < G; ++j) {
+        View src = gs[j].b; src.shape = {Expr(N), Expr(K)}; src.strides = {Expr(K), Expr(1)};
+        View dst = w; dst.offset = Expr(j * N * K); dst.shape = src.shape;
+        emitEltwise(leafNode(src), dst, true);
+        if (g0.hasShift) { View d = sh; d.offset = Expr(j * N); d.shape = {Expr(N)}; emitEltwise(leafNode(gs[j].shift), d, true); }
+      }
+      Step fused = plan.steps[i];
+      for (auto& nv : fused.views) {
+        if (nv.first == "b") { nv.second = w; nv.second.shape = {Expr(1), Expr(1), Expr(K), Expr(G * N)}; nv.second.strides = {Expr(G * N * K), Expr(G * N * K), Expr(1), Expr(K)}; }
+        if (nv.first == "shift") nv.second = sh;
+        if (nv.first == "out") { nv.second.buf = fusedBuf; nv.second.shape[3] = Expr(G * N); nv.second.strides = rowMajor(nv.second.shape); }
+      }
+      std::vector<Step> inits(plan.steps.begin() + (long)before, plan.steps.end());
+      plan.steps.resize(before);
+      plan.steps[group.back()] = fused;
+      plan.steps.insert(plan.steps.begin() + (long)group.back(), inits.begin(), inits.end());
+      for (size_t k = group.size() - 1; k-- > 0;) plan.steps.erase(plan.steps.begin() + (long)group[k]);
+      --i;   // position i now holds whatever followed the first GEMM: look at it again
+    }
   }
 };
 

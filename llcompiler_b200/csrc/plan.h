@@ -71,6 +71,7 @@ struct CompileOptionsData {
   bool displayMlirPasses = false, displayLlvmPasses = false;
   bool mergeStemRows = true;       // narrow-channel stem convolutions read a filter row per K block (LLC_MERGE_STEM_ROWS=0 disables)
   bool fuseAttention = true;       // batch_matmul -> softmax -> batch_matmul as one attention step where the kernel's limits allow
+  bool fuseSiblingGemms = true;    // linear layers over one activation (query, key, value) as one GEMM over stacked weights (LLC_FUSE_SIBLING_GEMMS=0 disables)
 };
 
 // Runs the GPU pipeline on parsed LLH text and returns the plan.

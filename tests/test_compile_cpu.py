@@ -87,14 +87,24 @@ def test_bert_bf16_attention_becomes_one_step(monkeypatch):
     # place from the projections' [B, S, H*D] outputs and writes [B, S, H, D] directly
     plan, got, want = _bert_bf16(monkeypatch, fuse=True)
     assert plan.count("step attention") == 2 and plan.count("step softmax") == 0
-    assert plan.count("step gemm") == 12 and plan.count("step eltwise") == 2
+    # the query, key and value projections of a layer are one GEMM over weights stacked at load time (N = 3 x 768), and
+    # the attention step reads its three operands as column ranges of that GEMM's output
+    assert plan.count("step gemm") == 8 and plan.count("step eltwise") == 2 and plan.count("[1,1,768,2304;") == 2
+    assert plan.count("init eltwise out=") >= 12 and " k=b" in plan and "@768[2,12,64,16;36864,64,1,2304]" in plan
     assert "scale:0.125" in plan and " mask=" in plan
+    assert max_rel_err(got, want) < 2e-2
+
+
+def test_bert_bf16_projections_kept_apart_are_the_same_function(monkeypatch):
+    monkeypatch.setenv("LLC_FUSE_SIBLING_GEMMS", "0")
+    plan, got, want = _bert_bf16(monkeypatch, fuse=True)
+    assert plan.count("step gemm") == 12 and plan.count("2304") == 0
     assert max_rel_err(got, want) < 2e-2
 
 
 def test_bert_bf16_unfused_attention_is_the_same_function(monkeypatch):
     plan, got, want = _bert_bf16(monkeypatch, fuse=False)
-    assert plan.count("step attention") == 0 and plan.count("step softmax") == 2 and plan.count("step gemm") == 16
+    assert plan.count("step attention") == 0 and plan.count("step softmax") == 2 and plan.count("step gemm") == 14   # query and key projections fuse; the value projection comes after the score GEMM
     assert max_rel_err(got, want) < 2e-2
 
 
