@@ -10,8 +10,10 @@ llcompiler_b200.executor.BatchShardedRunner: weights replicated, every rank runs
 all-gathered over NCCL inside the timed step.  The line printed by rank 0 carries:
   value      samples/s with inputs resident in HBM, device-timed with CUDA events, max over ranks
   e2e        the same metric with page-locked HOST tensors in and out, the host->device and device->host copies
-             inside the timed region (N = 1: Torch_ExecutionEngine.run on host tensors, i.e. the C ABI's host path;
-             N > 1: the sharded runner's host path, every rank uploads its slice, rank 0 reads the gathered batch back)
+             inside the timed region: K batches through BatchShardedRunner.pipelined (two in flight: every rank uploads
+             its slice, runs it, the gather follows, rank 0 reads the gathered batch back on a copy stream while the
+             next batch computes); `one_batch_at_a_time` is the same K batches through the plain call, each finished
+             before the next starts (N = 1: Torch_ExecutionEngine.run on host tensors, i.e. the C ABI's host path)
   roofline   the dominant kernel family (GEMM / convolution): algorithmic FLOPs / CUDA-event duration of its launches
   cpu_baseline  the CPU oracle (PyTorch CPU eager fp32, what the reference pins itself to) on a bounded sample of
              the same workload, on this box's host cores; N = 1 only
@@ -263,13 +265,25 @@ def main():
         for _ in range(args.steps):
             o_host = runner(*host_inputs)
         torch.cuda.synchronize()
+        e2e_sync_s = time.perf_counter() - t0
+        # the same K steps through the runner's pipelined call: two batches in flight, the device-to-host copy of one
+        # under the kernels of the next; every copy still lies inside the timed region
+        for o_host in runner.pipelined((host_inputs for _ in range(2)), depth=2):
+            pass
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t0 = time.perf_counter()
+        for o_host in runner.pipelined((host_inputs for _ in range(args.steps)), depth=2):
+            pass
+        torch.cuda.synchronize()
         e2e_s = time.perf_counter() - t0
     eng.status()                                # raises if any kernel of the run reported a failure
     assert tuple(full.shape)[0] == batch and not o_host.is_cuda
-    t = torch.tensor([total_ms, e2e_s * 1e3], dtype=torch.float64, device=dev)
+    t = torch.tensor([total_ms, e2e_s * 1e3, e2e_sync_s * 1e3], dtype=torch.float64, device=dev)
     if world > 1:
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-    total_ms, e2e_ms = float(t[0]), float(t[1])
+    total_ms, e2e_ms, e2e_sync_ms = float(t[0]), float(t[1]), float(t[2])
 
     # dominant kernel: event-timed per kernel family over a profiled pass (events around every launch)
     local_dev_inputs = tuple(i[lo:hi] for i in dev_inputs)
@@ -317,7 +331,9 @@ def main():
             "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": dtype, "data": "synthetic",
             "config": config_dict(args.config, batch, world, prec),
             "clocks": clocks.summary(),
-            "e2e": {"value": batch * args.steps / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
+            "e2e": {"value": batch * args.steps / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
+                    "call": "BatchShardedRunner.pipelined(depth=2): two batches in flight",
+                    "one_batch_at_a_time": batch * args.steps / (e2e_sync_ms * 1e-3)},
             "gpu_launches": int(launches_per_step * args.steps),
             "roofline": roof,
             "cpu_baseline": cpu,

@@ -5,7 +5,8 @@ distributed code; the batch symbol of its symbolic-shape machinery is what makes
 plan serve the per-rank slice."""
 from __future__ import annotations
 
-from typing import Callable, List, Optional, Sequence, Tuple
+import collections
+from typing import Callable, Iterable, Iterator, List, Optional, Sequence, Tuple
 
 import torch
 import torch.distributed as dist
@@ -58,6 +59,9 @@ class BatchShardedRunner:
         self.fn, self.group, self.device = fn, group, device
         self.host_result_ranks = None if host_result_ranks is None else set(host_result_ranks)
         self._host_out = {}
+        self._copy_stream = None
+        self._upload_stream = None
+        self._ring = {}
 
     def _to_host(self, t: torch.Tensor) -> torch.Tensor:
         key = (tuple(t.shape), t.dtype)
@@ -84,3 +88,63 @@ class BatchShardedRunner:
             wants_full = self.host_result_ranks is None or rank in self.host_result_ranks
             return self._to_host(full if wants_full else out)
         return full
+
+    def pipelined(self, batches: Iterable[Sequence[torch.Tensor]], depth: int = 2) -> Iterator[torch.Tensor]:
+        """Runs a stream of batches with up to ``depth`` of them in flight and yields their results, in order, as
+        page-locked host tensors: the device-to-host copy of one batch runs on a stream of its own under the kernels
+        of the next (and so does the upload of the next batch's inputs), so a result or an input of hundreds of megabytes
+        does not add its transfer time to every step.  Each batch is
+        what ``__call__`` takes (host or device tensors); sharding, the gather and ``host_result_ranks`` are as there.
+        A yielded tensor belongs to a ring of ``depth + 1`` buffers per result shape: it stays valid until ``depth``
+        more results have been taken."""
+        if self.device is None:
+            raise ValueError("pipelined() needs the runner's device")
+        if depth < 1:
+            raise ValueError("depth must be at least 1")
+        world, rank = _world_and_rank(self.group)
+        if self._copy_stream is None:
+            self._copy_stream = torch.cuda.Stream(device=self.device)
+            self._upload_stream = torch.cuda.Stream(device=self.device)
+        copy, up = self._copy_stream, self._upload_stream
+        main = torch.cuda.current_stream(self.device)
+        pending = collections.deque()
+        for inputs in batches:
+            total = inputs[0].shape[0]
+            lo, hi = shard_bounds(total, world, rank)
+            local = [i[lo:hi] if i.dim() > 0 and i.shape[0] == total else i for i in inputs]
+            if any(not i.is_cuda for i in local):    # uploads have a stream of their own too: they run under the previous batch's kernels
+                with torch.cuda.stream(up):
+                    local = [i if i.is_cuda else i.to(self.device, non_blocking=True) for i in local]
+                    uploaded = torch.cuda.Event()
+                    uploaded.record(up)
+                main.wait_event(uploaded)
+                for i in local:
+                    i.record_stream(main)
+            out = self.fn(*local)
+            if isinstance(out, (list, tuple)):
+                out = out[0]
+            full = gather_batch(out, total, self.group)
+            wants_full = self.host_result_ranks is None or rank in self.host_result_ranks
+            src = full if wants_full else out
+            key = (tuple(src.shape), src.dtype)
+            ring = self._ring.setdefault(key, {"bufs": [], "next": 0})
+            while len(ring["bufs"]) < depth + 1:
+                ring["bufs"].append(torch.empty(src.shape, dtype=src.dtype, pin_memory=True))
+            host = ring["bufs"][ring["next"] % (depth + 1)]
+            ring["next"] += 1
+            ready, done = torch.cuda.Event(), torch.cuda.Event()
+            ready.record(main)
+            copy.wait_event(ready)
+            with torch.cuda.stream(copy):
+                host.copy_(src, non_blocking=True)
+                done.record(copy)
+            src.record_stream(copy)          # the allocator must not hand the result's memory out again before the copy has read it
+            pending.append((done, host))
+            if len(pending) >= depth:
+                d, h = pending.popleft()
+                d.synchronize()
+                yield h
+        while pending:
+            d, h = pending.popleft()
+            d.synchronize()
+            yield h
