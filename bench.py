@@ -58,8 +58,9 @@ DESCRIPTION = {
 # DRAM bytes per launch of the dominant kernel family (dram__bytes_read.sum + dram__bytes_write.sum averaged over the
 # launches of one forward), from an ncu capture of this command (20 tensor-core launches of one forward).
 NCU_TRAFFIC = {("resnet18", "conv", 32): 23.0e6,
-               # the six GEMMs of a BERT layer at 98304 rows: four 768x768 (258.8 MB), 3072x768 (708.0 MB), 768x3072 (743.1 MB)
-               ("bert", "gemm", 256): 414.4e6}
+               # the four GEMMs of a BERT layer at 98304 rows: 2304x768 (557.2 MB), 768x768 (258.8 MB), 3072x768 (708.0 MB),
+               # 768x3072 (743.1 MB)
+               ("bert", "gemm", 256): 566.8e6}
 
 
 def config_dict(name: str, batch: int, world: int, prec: str) -> dict:
