@@ -388,22 +388,82 @@ using namespace llc;
 
 // Same with the rows widened: output pixel (img, h, wq) of a [n, h, w_total, CP] buffer is input pixel wq - w_left, or
 // zeros in the halo columns left and right of the image.
-template <typename T, int CP>
+// A thread block takes kRows output rows; thread t takes the pixels t, t + 256, ... of each of them, so that kRows * c
+// loads are in flight per thread, neighbouring threads read neighbouring elements, and no thread divides.
+template <typename T, int CP, int kRows>
 __global__ void __launch_bounds__(256) nchw_to_nhwc_wide_kernel(const T* __restrict__ x, T* __restrict__ out, long long n, int c, int h, int w, int w_left,
                                                                  int w_total) {
+  const long long row0 = (long long)blockIdx.x * kRows, rows = n * h;
+  const long long hw = (long long)h * w;
+  const T* src[kRows];
+  T* dst[kRows];
+#pragma unroll
+  for (int i = 0; i < kRows; ++i) {
+    const long long r = min(row0 + i, rows - 1);
+    const long long img = r / h;
+    src[i] = x + img * c * hw + (r - img * h) * w;
+    dst[i] = out + r * (long long)w_total * CP;
+  }
+  for (int wq = threadIdx.x; wq < w_total; wq += 256) {
+    const int wi = wq - w_left;
+    const bool inside = wi >= 0 && wi < w;
+    __align__(16) T v[kRows][CP];
+#pragma unroll
+    for (int i = 0; i < kRows; ++i)
+#pragma unroll
+      for (int k = 0; k < CP; ++k) v[i][k] = (inside && k < c) ? src[i][k * hw + wi] : T(0.f);
+    constexpr int kVec = CP * sizeof(T) / 16;
+#pragma unroll
+    for (int i = 0; i < kRows; ++i)
+      if (row0 + i < rows) {
+        uint4* d = reinterpret_cast<uint4*>(dst[i] + (long long)wq * CP);
+#pragma unroll
+        for (int k = 0; k < kVec; ++k) d[k] = reinterpret_cast<const uint4*>(v[i])[k];
+      }
+  }
+}
+
+// The same for image rows that start on a 4-element boundary: a thread reads four neighbouring pixels of every channel
+// with one vector load each and writes their four padded pixels (64 contiguous bytes); the zero columns left and right of
+// the image are written by a few extra threads per row.
+template <typename T, int CP>
+__global__ void __launch_bounds__(256) nchw_to_nhwc_wide_quad_kernel(const T* __restrict__ x, T* __restrict__ out, long long rows, int c, int h, int w,
+                                                                      int w_left, int w_total) {
+  struct alignas(4 * sizeof(T)) Quad { T v[4]; };
+  const int quads = w / 4, halo = w_total - w, perRow = quads + (halo + 3) / 4;
   const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
-  if (idx >= n * h * w_total) return;
-  const int wq = (int)(idx % w_total); const long long t = idx / w_total; const int row = (int)(t % h); const long long img = t / h;
-  const int wi = wq - w_left;
-  const bool inside = wi >= 0 && wi < w;
-  const long long hw = (long long)h * w, px = (long long)row * w + wi;
-  __align__(16) T v[CP];
-#pragma unroll
-  for (int k = 0; k < CP; ++k) v[k] = (inside && k < c) ? x[(img * c + k) * hw + px] : T(0.f);
+  const long long r = idx / perRow;
+  if (r >= rows) return;
+  const int j = (int)(idx - r * perRow);
+  T* dstRow = out + r * (long long)w_total * CP;
   constexpr int kVec = CP * sizeof(T) / 16;
-  uint4* dst = reinterpret_cast<uint4*>(out + idx * CP);
+  if (j < quads) {
+    const long long img = r / h, hw = (long long)h * w;
+    const T* src = x + img * c * hw + (r - img * h) * w + 4 * j;
+    Quad q[CP];
 #pragma unroll
-  for (int k = 0; k < kVec; ++k) dst[k] = reinterpret_cast<const uint4*>(v)[k];
+    for (int k = 0; k < CP; ++k)
+      if (k < c) q[k] = *reinterpret_cast<const Quad*>(src + k * hw);
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      __align__(16) T v[CP];
+#pragma unroll
+      for (int k = 0; k < CP; ++k) v[k] = k < c ? q[k].v[i] : T(0.f);
+      uint4* d = reinterpret_cast<uint4*>(dstRow + (long long)(w_left + 4 * j + i) * CP);
+#pragma unroll
+      for (int k = 0; k < kVec; ++k) d[k] = reinterpret_cast<const uint4*>(v)[k];
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const int hq = (j - quads) * 4 + i;
+      if (hq < halo) {
+        uint4* d = reinterpret_cast<uint4*>(dstRow + (long long)(hq < w_left ? hq : w + hq) * CP);
+#pragma unroll
+        for (int k = 0; k < kVec; ++k) d[k] = make_uint4(0u, 0u, 0u, 0u);
+      }
+    }
+  }
 }
 
 extern "C" int llc_cuda_nchw_to_nhwc_wide(const void* x, void* out, int32_t dtype, int64_t n, int64_t c, int64_t h, int64_t w, int64_t c_pad, int64_t w_left,
@@ -415,11 +475,21 @@ extern "C" int llc_cuda_nchw_to_nhwc_wide(const void* x, void* out, int32_t dtyp
   const bool f32 = dtype == LLC_FLOAT32;
   if (!((f32 && c_pad == 4) || (dtype == LLC_BFLOAT16 && c_pad == 8)))
     return setError(LLC_ERR_UNSUPPORTED, "llc argument: nchw_to_nhwc_wide takes f32 padded to 4 channels or bf16 padded to 8");
-  const long long total = n * h * w_total;
-  const unsigned blocks = (unsigned)((total + 255) / 256);
+  if (n * h > 0x7FFFFFFFLL) return setError(LLC_ERR_UNSUPPORTED, "llc argument: nchw_to_nhwc_wide takes at most 2^31 - 1 image rows");
+  constexpr int kRows = 4;
+  const unsigned blocks = (unsigned)((n * h + kRows - 1) / kRows);
   cudaStream_t st = static_cast<cudaStream_t>(stream);
-  if (f32) nchw_to_nhwc_wide_kernel<float, 4><<<blocks, 256, 0, st>>>((const float*)x, (float*)out, n, (int)c, (int)h, (int)w, (int)w_left, (int)w_total);
-  else nchw_to_nhwc_wide_kernel<__nv_bfloat16, 8><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, (int)c, (int)h, (int)w, (int)w_left, (int)w_total);
+  const size_t elt = f32 ? 4 : 2;
+  if (w % 4 == 0 && reinterpret_cast<uintptr_t>(x) % (4 * elt) == 0) {       // every image row starts on a 4-element boundary
+    const long long perRow = w / 4 + (w_total - w + 3) / 4, threads = n * h * perRow;
+    const unsigned qb = (unsigned)((threads + 255) / 256);
+    if (f32) nchw_to_nhwc_wide_quad_kernel<float, 4><<<qb, 256, 0, st>>>((const float*)x, (float*)out, n * h, (int)c, (int)h, (int)w, (int)w_left, (int)w_total);
+    else nchw_to_nhwc_wide_quad_kernel<__nv_bfloat16, 8><<<qb, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n * h, (int)c, (int)h, (int)w, (int)w_left, (int)w_total);
+    LLC_LAUNCH_CHECK("nchw_to_nhwc_wide_quad_kernel");
+    return LLC_OK;
+  }
+  if (f32) nchw_to_nhwc_wide_kernel<float, 4, kRows><<<blocks, 256, 0, st>>>((const float*)x, (float*)out, n, (int)c, (int)h, (int)w, (int)w_left, (int)w_total);
+  else nchw_to_nhwc_wide_kernel<__nv_bfloat16, 8, kRows><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)x, (__nv_bfloat16*)out, n, (int)c, (int)h, (int)w, (int)w_left, (int)w_total);
   LLC_LAUNCH_CHECK("nchw_to_nhwc_wide_kernel");
   return LLC_OK;
 }
@@ -553,6 +623,45 @@ __global__ void __launch_bounds__(256) maxpool_nhwc_bf16x8_kernel(const __nv_bfl
   *reinterpret_cast<uint4*>(out + ((n * p.oh + oh) * p.ow + ow) * p.c + c) = o;
 }
 
+// The same for a window and stride known at compile time (3x3 / stride 2 is what the ResNets use): every load of the window
+// is issued before the first maximum is taken (out-of-range taps read a clamped address and are masked afterwards), so a
+// thread has KH*KW 16-byte loads in flight instead of one.
+template <int KH, int KW, int S>
+__global__ void __launch_bounds__(256) maxpool_nhwc_bf16x8_window_kernel(const __nv_bfloat16* __restrict__ x, __nv_bfloat16* __restrict__ out, LlcPoolParams p) {
+  const int cv = (int)(p.c / 8);
+  const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+  if (idx >= p.n * p.oh * p.ow * cv) return;
+  const unsigned pix = (unsigned)(idx / cv);
+  const int c = (int)(idx - (long long)pix * cv) * 8;
+  const unsigned ohow = (unsigned)(p.oh * p.ow);
+  const unsigned n = pix / ohow, rem = pix - n * ohow;
+  const int oh = (int)(rem / (unsigned)p.ow), ow = (int)(rem - (unsigned)oh * (unsigned)p.ow);
+  const int ih0 = oh * S - (int)p.pad_h, iw0 = ow * S - (int)p.pad_w;
+  const __nv_bfloat16* img = x + (long long)n * p.h * p.w * p.c + c;
+  uint4 q[KH * KW];
+#pragma unroll
+  for (int r = 0; r < KH; ++r)
+#pragma unroll
+    for (int t = 0; t < KW; ++t) {
+      const int ih = min(max(ih0 + r, 0), (int)p.h - 1), iw = min(max(iw0 + t, 0), (int)p.w - 1);
+      q[r * KW + t] = __ldg(reinterpret_cast<const uint4*>(img + ((long long)ih * p.w + iw) * p.c));
+    }
+  const __nv_bfloat162 lowest = __floats2bfloat162_rn(-INFINITY, -INFINITY);
+  __nv_bfloat162 m[4] = {lowest, lowest, lowest, lowest};
+#pragma unroll
+  for (int r = 0; r < KH; ++r)
+#pragma unroll
+    for (int t = 0; t < KW; ++t) {
+      const bool in = ih0 + r >= 0 && ih0 + r < p.h && iw0 + t >= 0 && iw0 + t < p.w;
+      const __nv_bfloat162* hq = reinterpret_cast<const __nv_bfloat162*>(&q[r * KW + t]);
+#pragma unroll
+      for (int e = 0; e < 4; ++e) m[e] = in ? __hmax2(m[e], hq[e]) : m[e];
+    }
+  uint4 o;
+  o.x = *reinterpret_cast<unsigned*>(&m[0]); o.y = *reinterpret_cast<unsigned*>(&m[1]); o.z = *reinterpret_cast<unsigned*>(&m[2]); o.w = *reinterpret_cast<unsigned*>(&m[3]);
+  *reinterpret_cast<uint4*>(out + (long long)pix * p.c + c) = o;
+}
+
 extern "C" int llc_cuda_maxpool2d(const LlcPoolParams* p, void* stream) {
   if (!p) return setError(LLC_ERR_ARGUMENT, "llc argument: maxpool null parameter block");
   long long total = p->n * p->oh * p->ow * p->c;
@@ -569,7 +678,9 @@ extern "C" int llc_cuda_maxpool2d(const LlcPoolParams* p, void* stream) {
   } else if (p->in_dtype == LLC_BFLOAT16) {
     if (p->c % 8 == 0 && ((reinterpret_cast<uintptr_t>(p->x) | reinterpret_cast<uintptr_t>(p->out)) & 15) == 0) {
       const long long total8 = p->n * p->oh * p->ow * (p->c / 8);
-      maxpool_nhwc_bf16x8_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
+      if (p->kh == 3 && p->kw == 3 && p->stride_h == 2 && p->stride_w == 2 && p->dil_h == 1 && p->dil_w == 1 && p->n * p->oh * p->ow < (1LL << 31))
+        maxpool_nhwc_bf16x8_window_kernel<3, 3, 2><<<(unsigned)((total8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
+      else maxpool_nhwc_bf16x8_kernel<<<(unsigned)((total8 + 255) / 256), 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
     } else if (v4) maxpool_nhwc_kernel<__nv_bfloat16, 4><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
     else maxpool_nhwc_kernel<__nv_bfloat16, 1><<<blocks, 256, 0, st>>>((const __nv_bfloat16*)p->x, (__nv_bfloat16*)p->out, *p);
   } else return setError(LLC_ERR_UNSUPPORTED, "llc argument: maxpool type must be f32 or bf16");

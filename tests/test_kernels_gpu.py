@@ -108,7 +108,8 @@ def test_conv2d(case, dtype):
 
 
 @pytest.mark.parametrize("shape,k,s,p,d", [((2, 64, 112, 112), 3, 2, 1, 1), ((3, 3, 30, 30), 5, 1, 2, 2),
-                                           ((2, 7, 9, 17), 3, 2, 1, 1), ((1, 4, 1, 1), 1, 1, 0, 1)])
+                                           ((2, 7, 9, 17), 3, 2, 1, 1), ((1, 4, 1, 1), 1, 1, 0, 1),
+                                           ((2, 16, 9, 17), 3, 2, 1, 1), ((1, 8, 2, 2), 3, 2, 1, 1), ((2, 24, 10, 12), 3, 2, 0, 1)])
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
 def test_maxpool_bit_exact(shape, k, s, p, d, dtype):
     x = _rand(*shape, dtype=dtype)
@@ -276,6 +277,19 @@ def test_nchw_to_nhwc_bit_exact_with_zero_padding(n, c, h, w, cp, dtype):
     C.check(f(X.data_ptr(), out.data_ptr(), 4 if dtype == torch.float32 else 8, n, c, h * w, cp, torch.cuda.current_stream().cuda_stream))
     want = torch.zeros(n, h, w, cp, dtype=dtype)
     want[..., :c] = x.permute(0, 2, 3, 1)
+    assert torch.equal(out.cpu(), want)
+
+
+@pytest.mark.parametrize("n,c,h,w,left,total", [(2, 3, 12, 224, 3, 232), (3, 3, 9, 40, 3, 46), (2, 3, 7, 41, 3, 48), (1, 2, 5, 16, 0, 16), (5, 3, 3, 8, 2, 11)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_nchw_to_nhwc_wide_bit_exact_with_zero_columns(n, c, h, w, left, total, dtype):
+    # rows that start on a 4-element boundary take the vector kernel, the others (w = 41) the row kernel
+    cp = 4 if dtype == torch.float32 else 8
+    x = _rand(n, c, h, w, dtype=dtype)
+    out = torch.full((n, h, total, cp), float("nan"), device=DEV, dtype=dtype)
+    G.nchw_to_nhwc_wide(x.to(DEV), out, cp, left, total)
+    want = torch.zeros(n, h, total, cp, dtype=dtype)
+    want[:, :, left:left + w, :c] = x.permute(0, 2, 3, 1)
     assert torch.equal(out.cpu(), want)
 
 
