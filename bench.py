@@ -190,6 +190,7 @@ def main():
     ap.add_argument("--config", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--precision", default=None)
+    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: this library's peer-store gather, or NCCL's all_gather")
     ap.add_argument("--steps-out", default=None, help="write the per-plan-step CUDA-event table here")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -235,7 +236,17 @@ def main():
     torch.cuda.synchronize()
     eng = comp.compiled[0].engine
     launches_per_step = eng.executor.last_launch_count()
-    runner = BatchShardedRunner(lambda *a: eng.run(*a), device=dev, host_result_ranks=(0,))
+    # N > 1: the gather is this library's own kernel (every rank stores its slice into every rank's buffer over NVLink);
+    # it is checked against NCCL's all_gather once, on this step's real output, before anything is timed
+    runner = BatchShardedRunner(lambda *a: eng.run(*a), device=dev, host_result_ranks=(0,), gather=args.gather if world > 1 else "nccl")
+    if world > 1 and args.gather == "peer":
+        from llcompiler_b200.executor.sharded import gather_batch
+        with torch.no_grad():
+            local_out = eng.run(*(i[lo:hi] for i in dev_inputs))[0]
+        want_full = gather_batch(local_out, batch)
+        got_full, _ = runner.gather(local_out, batch)
+        torch.cuda.synchronize()
+        assert torch.equal(got_full, want_full), "the peer-store gather differs from NCCL's all_gather"
     flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)   # > 126 MB L2
 
     for _ in range(args.warmup):                # the executor captures its CUDA graph on the second of these calls
@@ -335,7 +346,11 @@ def main():
             "e2e": {"value": batch * args.steps / (e2e_ms * 1e-3), "unit": "samples/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,
                     "call": "BatchShardedRunner.pipelined(depth=2): two batches in flight",
                     "one_batch_at_a_time": batch * args.steps / (e2e_sync_ms * 1e-3)},
-            "gpu_launches": int(launches_per_step * args.steps),
+            # this library's kernels inside the timed region: the plan's launches, plus the gather's push kernel at N > 1
+            "gpu_launches": int((launches_per_step + (1 if world > 1 and runner.gather_mode == "peer" else 0)) * args.steps),
+            "gather": ("none (one GPU)" if world == 1 else
+                       "llc_cuda_push_rows: peer stores over NVLink into symmetric memory, checked against NCCL all_gather" if runner.gather_mode == "peer"
+                       else "NCCL all_gather_into_tensor" + (f" (peer gather unavailable: {runner.gather_fallback})" if runner.gather_fallback else "")),
             "roofline": roof,
             "cpu_baseline": cpu,
         }

@@ -158,6 +158,14 @@ int llc_cuda_nchw_to_nhwc(const void* x, void* out, int32_t dtype, int64_t n, in
 int llc_cuda_nchw_to_nhwc_wide(const void* x, void* out, int32_t dtype, int64_t n, int64_t c, int64_t h, int64_t w, int64_t c_pad, int64_t w_left,
                                int64_t w_total, void* stream);
 
+/* Multi-destination copy: `bytes` bytes at `src` are stored at byte offset `dst_offset_bytes` of each of the `n_dst`
+ * (at most 8) buffers in `dst` (a host array of device pointers); each source vector is read once.  The destinations may
+ * be peer memory of other GPUs (plain stores over NVLink): this is the gather step of batch-sharded inference, every rank
+ * pushing its slice of the output into every rank's copy of the full batch; the caller synchronises the ranks before
+ * (the destinations are free) and after (every slice has arrived).  No counterpart in the reference, which runs on one
+ * device; it stands where its Execution::run results (src/Compiler/Execution.cpp:21-66) of several GPUs are put together. */
+int llc_cuda_push_rows(const void* src, void* const* dst, int32_t n_dst, int64_t dst_offset_bytes, int64_t bytes, void* stream);
+
 /* Fused elementwise chain: one coalesced pass that evaluates a small register program per
  * output element.  Replaces chains of llh.add/sub/mul/div/max/min/abs/sqrt/exp/where/compare/
  * convert_to/broadcast_to (-> stablehlo elementwise ops, LLHToHLO.cpp:479-490) and strided

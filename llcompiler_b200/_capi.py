@@ -38,6 +38,7 @@ def lib() -> ctypes.CDLL:
         _lib.llc_version.restype = c_char_p
         _lib.llc_compile.argtypes = [c_char_p, POINTER(LlcOptions), c_char_p, c_size_t]
         _lib.llc_run_pass.argtypes = [c_char_p, c_char_p, POINTER(LlcOptions), POINTER(c_char_p)]
+        _lib.llc_cuda_push_rows.argtypes = [ctypes.c_void_p, POINTER(ctypes.c_void_p), ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p]
     return _lib
 
 
@@ -136,4 +137,5 @@ EXPORTED_SYMBOLS = [
     "llc_output_shape", "llc_run", "llc_profile", "llc_status", "llc_last_launch_count", "llc_arena_bytes", "llc_free", "llc_last_error",
     "llc_version", "llc_cuda_gemm", "llc_cuda_conv2d", "llc_cuda_maxpool2d", "llc_cuda_reduce",
     "llc_cuda_softmax", "llc_cuda_layernorm", "llc_cuda_gather", "llc_cuda_eltwise", "llc_cuda_status", "llc_cuda_nchw_to_nhwc", "llc_cuda_gemm_static_scratch", "llc_cuda_attention", "llc_cuda_nchw_to_nhwc_wide",
+    "llc_cuda_push_rows",
 ]

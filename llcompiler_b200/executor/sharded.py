@@ -53,10 +53,22 @@ class BatchShardedRunner:
     With ``device`` set (GPU ranks over NCCL) host inputs are accepted too: the rank's slice is copied to the
     device (asynchronously when the host tensor is page-locked), the gather runs over the device tensors, and the
     gathered batch is copied back to page-locked host memory on the ranks listed in ``host_result_ranks``
-    (default: every rank); the other ranks copy back their own slice only."""
+    (default: every rank); the other ranks copy back their own slice only.
 
-    def __init__(self, fn: Callable, group=None, device: Optional[torch.device] = None, host_result_ranks: Optional[Sequence[int]] = None):
+    ``gather="peer"`` (GPU ranks of one node) replaces the NCCL all-gather by this library's own kernel: the gathered
+    batch lives in symmetric memory (two buffers per result shape, used in turn), every rank stores its slice straight
+    into every rank's buffer over NVLink (``llc_cuda_push_rows``), with a barrier before (the buffer is free everywhere)
+    and after (every slice has arrived).  The tensor returned is one of those two buffers: it is overwritten by the
+    next-but-one call.  If symmetric memory cannot be set up the runner falls back to NCCL and says so in
+    ``gather_fallback``."""
+
+    def __init__(self, fn: Callable, group=None, device: Optional[torch.device] = None, host_result_ranks: Optional[Sequence[int]] = None,
+                 gather: str = "nccl"):
+        if gather not in ("nccl", "peer"):
+            raise ValueError("gather must be 'nccl' or 'peer'")
         self.fn, self.group, self.device = fn, group, device
+        self.gather_mode, self.gather_fallback = gather, None
+        self._peer = {}
         self.host_result_ranks = None if host_result_ranks is None else set(host_result_ranks)
         self._host_out = {}
         self._copy_stream = None
@@ -72,6 +84,46 @@ class BatchShardedRunner:
         torch.cuda.current_stream(t.device).synchronize()
         return buf
 
+    def _peer_state(self, local: torch.Tensor, total: int):
+        key = (total, tuple(local.shape[1:]), local.dtype)
+        st = self._peer.get(key)
+        if st is None:
+            import ctypes
+            import torch.distributed._symmetric_memory as symm_mem
+            buf = symm_mem.empty((2, total) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+            hdl = symm_mem.rendezvous(buf, group=self.group if self.group is not None else dist.group.WORLD)
+            ptrs = (ctypes.c_void_p * hdl.world_size)(*[int(p) for p in hdl.buffer_ptrs])
+            st = self._peer[key] = {"buf": buf, "hdl": hdl, "ptrs": ptrs, "next": 0, "guard": [None, None]}
+        return st
+
+    def gather(self, local: torch.Tensor, total: int):
+        """The full batch from every rank's slice: (tensor, token).  With the peer gather the token names the buffer
+        used, so that ``pipelined`` can keep it from being overwritten while a copy still reads it."""
+        world, rank = _world_and_rank(self.group)
+        if self.gather_mode != "peer" or world == 1 or not local.is_cuda or total % world or world > 8:
+            return gather_batch(local, total, self.group), None
+        try:
+            st = self._peer_state(local, total)
+        except Exception as e:  # symmetric memory is not available here: the NCCL path is always there
+            self.gather_mode, self.gather_fallback = "nccl", f"{type(e).__name__}: {e}"
+            return gather_batch(local, total, self.group), None
+        from .. import _capi as C
+        local = local.contiguous()
+        k = st["next"] & 1
+        st["next"] += 1
+        main = torch.cuda.current_stream(local.device)
+        if st["guard"][k] is not None:                 # a read-back of this buffer's previous contents is still in flight
+            main.wait_event(st["guard"][k])
+            st["guard"][k] = None
+        hdl = st["hdl"]
+        hdl.barrier(channel=0)                         # every rank is done with buffer k: it may be overwritten
+        lo, _ = shard_bounds(total, world, rank)
+        row_bytes = local[0].numel() * local.element_size() if local.shape[0] else 0
+        C.check(C.lib().llc_cuda_push_rows(local.data_ptr(), st["ptrs"], world, (k * total + lo) * row_bytes,
+                                           local.numel() * local.element_size(), main.cuda_stream))
+        hdl.barrier(channel=1)                         # every slice has arrived everywhere
+        return st["buf"][k], (st, k)
+
     def __call__(self, *inputs: torch.Tensor) -> torch.Tensor:
         world, rank = _world_and_rank(self.group)
         total = inputs[0].shape[0]
@@ -83,7 +135,7 @@ class BatchShardedRunner:
         out = self.fn(*local)
         if isinstance(out, (list, tuple)):
             out = out[0]
-        full = gather_batch(out, total, self.group)
+        full, _ = self.gather(out, total)
         if from_host:
             wants_full = self.host_result_ranks is None or rank in self.host_result_ranks
             return self._to_host(full if wants_full else out)
@@ -123,7 +175,7 @@ class BatchShardedRunner:
             out = self.fn(*local)
             if isinstance(out, (list, tuple)):
                 out = out[0]
-            full = gather_batch(out, total, self.group)
+            full, token = self.gather(out, total)
             wants_full = self.host_result_ranks is None or rank in self.host_result_ranks
             src = full if wants_full else out
             key = (tuple(src.shape), src.dtype)
@@ -139,6 +191,8 @@ class BatchShardedRunner:
                 host.copy_(src, non_blocking=True)
                 done.record(copy)
             src.record_stream(copy)          # the allocator must not hand the result's memory out again before the copy has read it
+            if token is not None and wants_full:
+                token[0]["guard"][token[1]] = done   # ... nor may the peers overwrite the gather buffer before that
             pending.append((done, host))
             if len(pending) >= depth:
                 d, h = pending.popleft()

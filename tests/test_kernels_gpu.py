@@ -308,3 +308,18 @@ def test_empty_problems_launch_nothing_and_succeed():
     torch.cuda.synchronize()
     from llcompiler_b200 import _capi as C
     assert C.lib().llc_cuda_status() == 0
+
+
+@pytest.mark.parametrize("nbytes,ndst,offset", [(16 * 1000, 3, 0), (16 * 4096 + 7, 2, 160), (5, 1, 16), (151 * 1024 * 1024 // 8, 8, 0)])
+def test_push_rows_copies_into_every_destination(nbytes, ndst, offset):
+    # the gather kernel with all destinations on this GPU: every destination gets the bytes at the offset, nothing else moves
+    import ctypes
+    from llcompiler_b200 import _capi as C
+    src = torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device=DEV)
+    dsts = [torch.full((offset + nbytes + 32,), 7, dtype=torch.uint8, device=DEV) for _ in range(ndst)]
+    ptrs = (ctypes.c_void_p * ndst)(*[d.data_ptr() for d in dsts])
+    C.check(C.lib().llc_cuda_push_rows(src.data_ptr(), ptrs, ndst, offset, nbytes, torch.cuda.current_stream().cuda_stream))
+    torch.cuda.synchronize()
+    for d in dsts:
+        assert torch.equal(d[offset:offset + nbytes], src)
+        assert bool((d[:offset] == 7).all()) and bool((d[offset + nbytes:] == 7).all())
