@@ -248,11 +248,22 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
       if (rowMask && ok && !mbarWait(&barMaskFull[it & 1], (it >> 1) & 1, abortWord)) { atomicExch(&g_attnStatus, 7); ok = false; }
       // the mask row is all zeros and covers every column: logits are scale * score
       const bool plain = rowMask && sMaskSet[it & 1] == 0 && p.scaleLog2e > 0.f;
-      const long long mRow = zb0 * p.m_s0 + zb1 * p.m_s1 + gm * p.m_sm;
-      auto logit = [&](float s, int col) -> float {    // scaled score plus mask, in units of log2
-        if constexpr (rowMask) return fmaf(s, p.scaleLog2e, sMaskCur[col]);
-        if (col >= p.N || gm >= p.M) return col < p.N ? s * p.scaleLog2e : -INFINITY;
-        return fmaf(s, p.scaleLog2e, loadAs(p.mask, mRow + col, p.mask_dtype) * kLog2e);
+      // per-row mask: eight neighbouring mask values of this thread's query row (times log2 e; -inf past the last key;
+      // rows past the last query read the last row's and are clipped by the store), the element type decided once
+      const long long mRow = zb0 * p.m_s0 + zb1 * p.m_s1 + (gm < p.M ? gm : p.M - 1) * p.m_sm;
+      auto mask8 = [&](int col0, float* mk) {
+        const int last = (int)p.N - 1;
+        if (p.mask_dtype == LLC_FLOAT32) {
+          const float* m = static_cast<const float*>(p.mask) + mRow;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) mk[e] = __ldg(m + min(col0 + e, last));
+        } else {
+          const __nv_bfloat16* m = static_cast<const __nv_bfloat16*>(p.mask) + mRow;
+#pragma unroll
+          for (int e = 0; e < 8; ++e) mk[e] = __bfloat162float(m[min(col0 + e, last)]);
+        }
+#pragma unroll
+        for (int e = 0; e < 8; ++e) mk[e] = col0 + e <= last ? mk[e] * kLog2e : -INFINITY;
       };
       // ---- pass 1: row maximum.  Chunk r of the thread lives in sc[r & 1]; the load of the next chunk is in flight while
       // this one is worked on.  Tensor memory delivers about 128 bytes per clock to the SM, which is what bounds this pass.
@@ -272,7 +283,12 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
           }
         } else {
 #pragma unroll
-          for (int j = 0; j < 32; ++j) mx = fmaxf(mx, logit(__uint_as_float(v[j]), c * 32 + j));
+          for (int j = 0; j < 4; ++j) {
+            float mk[8];
+            mask8(c * 32 + j * 8, mk);
+#pragma unroll
+            for (int e = 0; e < 8; ++e) mx = fmaxf(mx, fmaf(__uint_as_float(v[j * 8 + e]), p.scaleLog2e, mk[e]));
+          }
         }
         return mx;
       };
@@ -325,8 +341,10 @@ attention_kernel(const __grid_constant__ CUtensorMap mapQ, const __grid_constant
 #pragma unroll
               for (int e = 0; e < 8; ++e) e8[e] = fmaf(__uint_as_float(v[j * 8 + e]), p.scaleLog2e, mk[e]) - mx;
             } else {
+              float mk[8];
+              mask8(c * 32 + j * 8, mk);
 #pragma unroll
-              for (int e = 0; e < 8; ++e) e8[e] = logit(__uint_as_float(v[j * 8 + e]), c * 32 + j * 8 + e) - mx;
+              for (int e = 0; e < 8; ++e) e8[e] = fmaf(__uint_as_float(v[j * 8 + e]), p.scaleLog2e, mk[e]) - mx;
             }
 #pragma unroll
             for (int e = 0; e < 8; ++e) { e8[e] = fastExp2(e8[e]); sum4[e & 3] += e8[e]; }
