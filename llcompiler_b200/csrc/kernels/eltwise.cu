@@ -166,19 +166,8 @@ __device__ __forceinline__ float pick4(const float (*r)[8], int which, int v) {
   const float lo = which & 1 ? r[1][v] : r[0][v], hi = which & 1 ? r[3][v] : r[2][v];
   return which & 2 ? hi : lo;
 }
-template <typename IDX>
-__global__ void __launch_bounds__(256) eltwise_small_kernel(const __grid_constant__ EltArgs p) {
-  const IDX t = (IDX)blockIdx.x * blockDim.x + threadIdx.x;
-  if ((long long)t * 8 >= p.total) return;
-  IDX rem = t * 8;
-  long long oOff = 0, iOff[kSmallProg] = {0, 0, 0, 0};
-  for (int d = p.rank - 1; d >= 0; --d) {
-    const IDX ext = (IDX)p.shape[d];
-    const IDX c = rem % ext; rem /= ext;
-    oOff += (long long)c * p.ostr[d];
-#pragma unroll
-    for (int k = 0; k < kSmallProg; ++k) if (k < p.nin) iOff[k] += (long long)c * p.istr[k][d];
-  }
+// Eight neighbouring elements of the innermost dim: the operands' element offsets are given, the program is run on registers.
+__device__ __forceinline__ void eltwiseSmallBody(const EltArgs& p, long long oOff, const long long* iOff) {
   const int last = p.rank - 1;
   auto loadOperand = [&](int k, float* dst) {
     const void* base = k == 0 ? p.in[0] : k == 1 ? p.in[1] : k == 2 ? p.in[2] : p.in[3];
@@ -251,6 +240,39 @@ __global__ void __launch_bounds__(256) eltwise_small_kernel(const __grid_constan
     h = __floats2bfloat162_rn(o[4], o[5]); q.z = *reinterpret_cast<unsigned*>(&h); h = __floats2bfloat162_rn(o[6], o[7]); q.w = *reinterpret_cast<unsigned*>(&h);
     *reinterpret_cast<uint4*>(reinterpret_cast<__nv_bfloat16*>(p.out) + oOff) = q;
   }
+}
+
+template <typename IDX>
+__global__ void __launch_bounds__(256) eltwise_small_kernel(const __grid_constant__ EltArgs p) {
+  const IDX t = (IDX)blockIdx.x * blockDim.x + threadIdx.x;
+  if ((long long)t * 8 >= p.total) return;
+  IDX rem = t * 8;
+  long long oOff = 0, iOff[kSmallProg] = {0, 0, 0, 0};
+  for (int d = p.rank - 1; d >= 0; --d) {
+    const IDX ext = (IDX)p.shape[d];
+    const IDX c = rem % ext; rem /= ext;
+    oOff += (long long)c * p.ostr[d];
+#pragma unroll
+    for (int k = 0; k < kSmallProg; ++k) if (k < p.nin) iOff[k] += (long long)c * p.istr[k][d];
+  }
+  eltwiseSmallBody(p, oOff, iOff);
+}
+
+// The same for at most two dims (rows x inner, which is what is left of most steps once dense dims are merged): a block
+// is blockDim.y rows by blockDim.x eight-element pieces of one row part, so no thread divides.
+__global__ void __launch_bounds__(256) eltwise_small_rows_kernel(const __grid_constant__ EltArgs p, int partsPerRow, long long rows, int pieces) {
+  const long long rowBlock = blockIdx.x / partsPerRow;
+  const int part = (int)(blockIdx.x - rowBlock * partsPerRow);
+  const long long row = rowBlock * blockDim.y + threadIdx.y;
+  const int piece = part * (int)blockDim.x + (int)threadIdx.x;
+  if (row >= rows || piece >= pieces) return;
+  const bool two = p.rank == 2;
+  const int last = p.rank - 1;
+  const long long col = (long long)piece * 8;
+  long long oOff = col + (two ? row * p.ostr[0] : 0), iOff[kSmallProg] = {0, 0, 0, 0};
+#pragma unroll
+  for (int k = 0; k < kSmallProg; ++k) if (k < p.nin) iOff[k] = col * p.istr[k][last] + (two ? row * p.istr[k][0] : 0);
+  eltwiseSmallBody(p, oOff, iOff);
 }
 
 int parseProgram(const char* text, EltProgram& prog, int nin) {
@@ -575,6 +597,19 @@ extern "C" int llc_cuda_eltwise(const LlcEltwiseParams* q, void* stream) {
     if (a.istr[k][r - 1] == 0) continue;
     if (reinterpret_cast<uintptr_t>(a.in[k]) & 15) small = false;
     for (int d = 0; d + 1 < r && small; ++d) if (a.istr[k][d] % 8) small = false;
+  }
+  if (small && r <= 2) {
+    const long long rows = r == 2 ? a.shape[0] : 1, pieces = inner / 8;
+    // threads along a row: the row's pieces split into equal parts of at most 256, rounded up to whole warps
+    const long long parts = (pieces + 255) / 256;
+    const int tx = (int)((((pieces + parts - 1) / parts) + 31) / 32 * 32);
+    const int ty = (int)std::max<long long>(1, std::min<long long>(256 / tx, rows));
+    const long long blocks = ((rows + ty - 1) / ty) * parts;
+    if (pieces <= 0x7FFFFFFFLL / 8 && blocks <= 0x7FFFFFFFLL) {
+      eltwise_small_rows_kernel<<<(unsigned)blocks, dim3((unsigned)tx, (unsigned)ty), 0, st>>>(a, (int)parts, rows, (int)pieces);
+      LLC_LAUNCH_CHECK("eltwise_small_rows_kernel");
+      return LLC_OK;
+    }
   }
   if (small) {
     const long long threads = total / 8;
