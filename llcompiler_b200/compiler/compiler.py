@@ -73,13 +73,11 @@ class CompiledFunction:
         h = hashlib.blake2b(digest_size=16)
         for pos, _ in self.imported.weight_files:
             _tensor_digest(h, args[pos])
-        self.weight_dir = os.path.join(self.cache_entry, "v_" + h.hexdigest())
-        marker = os.path.join(self.weight_dir, ".complete")
-        if not os.path.exists(marker):
-            os.makedirs(self.weight_dir, exist_ok=True)
+        def write_set(directory: str) -> None:
             for pos, path in self.imported.weight_files:
-                save_weight(os.path.join(self.weight_dir, os.path.basename(path)), args[pos])
-            open(marker, "w").close()
+                save_weight(os.path.join(directory, os.path.basename(path)), args[pos])
+
+        self.weight_dir = publish_weight_set(self.cache_entry, "v_" + h.hexdigest(), write_set)
         self.engine = self._engine_factory(self.plan_path, self.weight_dir)
 
     def __call__(self, args):
@@ -93,6 +91,28 @@ class CompiledFunction:
         if not isinstance(outs, (list, tuple)):
             outs = [outs]
         return tuple(outs) if im.output_is_tuple else outs[0]
+
+
+def publish_weight_set(entry: str, name: str, write_set) -> str:
+    """Directory ``entry/name`` holding a complete weight set, written at most once however many processes ask for it at
+    the same time (the ranks of a multi-GPU job all compile the same graph).  A writer fills a directory of its own and
+    renames it into place, so a reader never sees a file that is still being written; the loser of that race throws its
+    copy away.  Returns the directory to load from."""
+    final = os.path.join(entry, name)
+    marker = os.path.join(final, ".complete")
+    if os.path.exists(marker):
+        return final
+    tmp = tempfile.mkdtemp(prefix=name + ".tmp", dir=entry)
+    write_set(tmp)
+    open(os.path.join(tmp, ".complete"), "w").close()
+    try:
+        os.rename(tmp, final)
+        return final
+    except OSError:
+        if os.path.exists(marker):                     # another process published the same set first
+            shutil.rmtree(tmp, ignore_errors=True)
+            return final
+        return tmp                                     # something unfinished sits under that name: keep the private copy
 
 
 class LLCompiler(Importer):

@@ -79,3 +79,43 @@ def test_cache_is_shared_between_processes_and_can_be_switched_off(tmp_path, mon
     assert outs[0].stdout.split()[-1] == outs[1].stdout.split()[-1]
     off = subprocess.run([sys.executable, "-c", script], env=dict(env, LLC_CACHE_DIR="off"), capture_output=True, text=True, timeout=300)
     assert off.returncode == 0 and "hits 0" in off.stdout
+
+
+def _publish_worker(args):
+    entry, n_files, size = args
+    import numpy as np
+    from llcompiler_b200.compiler.compiler import publish_weight_set
+
+    def write_set(directory):
+        for i in range(n_files):
+            np.save(os.path.join(directory, f"w{i}.npy"), np.full(size, i, dtype=np.float32))
+
+    d = publish_weight_set(entry, "v_test", write_set)
+    # whatever directory came back must be complete the moment it is returned: every file whole and right
+    for i in range(n_files):
+        a = np.load(os.path.join(d, f"w{i}.npy"))
+        if a.shape != (size,) or not (a == i).all():
+            return False
+    return os.path.exists(os.path.join(d, ".complete"))
+
+
+def test_weight_set_is_published_once_by_racing_processes(tmp_path):
+    """The ranks of a multi-GPU job compile the same graph at the same time: none of them may read a weight file that
+    another one is still writing."""
+    import multiprocessing as mp
+    entry = str(tmp_path / "g_race")
+    os.makedirs(entry)
+    with mp.get_context("spawn").Pool(6) as pool:
+        ok = pool.map(_publish_worker, [(entry, 12, 200_000)] * 6)
+    assert all(ok)
+    left = sorted(os.listdir(entry))
+    assert left == ["v_test"], left                      # the losers of the race removed their copies
+
+
+def test_weight_set_beside_an_unfinished_directory(tmp_path):
+    from llcompiler_b200.compiler.compiler import publish_weight_set
+    entry = str(tmp_path / "g_old")
+    os.makedirs(os.path.join(entry, "v_x"))              # a directory without its marker: a writer that died
+    open(os.path.join(entry, "v_x", "stale.npy"), "w").close()
+    d = publish_weight_set(entry, "v_x", lambda directory: open(os.path.join(directory, "w.npy"), "w").close())
+    assert d != os.path.join(entry, "v_x") and os.path.exists(os.path.join(d, "w.npy")) and os.path.exists(os.path.join(d, ".complete"))
