@@ -190,7 +190,9 @@ def main():
     ap.add_argument("--config", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--cpu-budget", type=float, default=15.0)
     ap.add_argument("--precision", default=None)
-    ap.add_argument("--gather", default="peer", choices=["peer", "nccl"], help="N > 1: this library's peer-store gather, or NCCL's all_gather")
+    ap.add_argument("--gather", default="auto", choices=["auto", "peer", "nccl"],
+                    help="N > 1: this library's peer-store gather or NCCL's all_gather; auto = peer up to 4 GPUs (the sizes it was "
+                         "measured at), NCCL above")
     ap.add_argument("--steps-out", default=None, help="write the per-plan-step CUDA-event table here")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
@@ -236,10 +238,11 @@ def main():
     torch.cuda.synchronize()
     eng = comp.compiled[0].engine
     launches_per_step = eng.executor.last_launch_count()
+    gather_mode = "nccl" if world == 1 else (("peer" if world <= 4 else "nccl") if args.gather == "auto" else args.gather)
     # N > 1: the gather is this library's own kernel (every rank stores its slice into every rank's buffer over NVLink);
     # it is checked against NCCL's all_gather once, on this step's real output, before anything is timed
-    runner = BatchShardedRunner(lambda *a: eng.run(*a), device=dev, host_result_ranks=(0,), gather=args.gather if world > 1 else "nccl")
-    if world > 1 and args.gather == "peer":
+    runner = BatchShardedRunner(lambda *a: eng.run(*a), device=dev, host_result_ranks=(0,), gather=gather_mode)
+    if gather_mode == "peer":
         from llcompiler_b200.executor.sharded import gather_batch
         with torch.no_grad():
             local_out = eng.run(*(i[lo:hi] for i in dev_inputs))[0]
