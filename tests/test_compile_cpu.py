@@ -115,3 +115,55 @@ def test_resnet18_stem_without_row_merging(monkeypatch):
     assert max_rel_err(got, want) < 1e-4
     plan = comp.compiled[0].engine.text
     assert "[64,7,7,4;" in plan and "wide:" not in plan
+
+
+class _Siblings(torch.nn.Module):
+    """Linear layers over one activation in the forms the sibling-GEMM fusion has to tell apart."""
+
+    def __init__(self, form):
+        super().__init__()
+        self.form = form
+        self.a, self.b, self.c = (torch.nn.Linear(128, 64) for _ in range(3))
+        self.wide = torch.nn.Linear(128, 128)
+        self.register_buffer("mix", torch.linspace(-1, 1, 4 * 64).view(4, 64))
+
+    def forward(self, x):
+        if self.form == "three":                # two of them read through reshapes before the third is computed: those two fuse
+            q, k, v = self.a(x), self.b(x), self.c(x)
+            return (q.view(-1, 4, 16) * k.view(-1, 4, 16)).sum(-1) @ self.mix + v
+        if self.form == "activation":           # the sums are absorbed as residual epilogues, so each GEMM has a reader of the one before: none fuses
+            return self.a(x) + torch.relu(self.b(x)) + self.c(x)
+        if self.form == "widths":               # a different width is not a sibling
+            return self.a(x).sum(-1, keepdim=True) + self.wide(x)
+        if self.form == "flat":                 # a reader that flattens rows and columns cannot be restated: no fusion
+            return self.a(x).reshape(4, 128).abs(), self.b(x).abs()
+        raise ValueError(self.form)
+
+
+@pytest.mark.parametrize("form,gemms,fused", [("three", 3, 1), ("activation", 3, 0), ("widths", 2, 0), ("flat", 2, 0)])
+def test_sibling_gemms_fuse_only_where_every_reader_can_follow(form, gemms, fused):
+    torch.manual_seed(0)
+    m = _Siblings(form)
+    comp, got, want = _run(m, (torch.randn(8, 128),))
+    for g, w in zip(got, want) if isinstance(want, tuple) else [(got, want)]:
+        assert max_rel_err(g, w) < 1e-4
+    plan = comp.compiled[0].engine.text
+    assert plan.count("step gemm") == gemms, plan
+    # a fused GEMM reads the stacked weights: a B operand of 2 or 3 x 64 columns with batch strides of its own
+    n_fused = sum(1 for line in plan.splitlines() if line.startswith("step gemm") and (";16384,16384,1,128]" in line or ";24576,24576,1,128]" in line))
+    assert n_fused == fused, plan
+
+
+def test_sibling_gemms_that_are_graph_outputs_stay_apart():
+    class Two(torch.nn.Module):
+        def __init__(self):
+            super().__init__()
+            self.a, self.b = torch.nn.Linear(128, 64), torch.nn.Linear(128, 64)
+
+        def forward(self, x):
+            return self.a(x), self.b(x)
+
+    torch.manual_seed(0)
+    m = Two()
+    comp, got, want = _run(m, (torch.randn(8, 128),))
+    assert max_rel_err(got[0], want[0]) < 1e-4 and max_rel_err(got[1], want[1]) < 1e-4
