@@ -217,7 +217,7 @@ std::string Module::str() const {
     }
     o << "  }\n";
   }
-  if (!symbolRelations.empty()) {   // the relations live in a module of their own, as in the reference's output
+  if (!symbolRelations.empty() || hasSymbolModule) {   // the relations live in a module of their own, as in the reference's output
     o << "  module @__symbol__ {\n";
     for (auto& l : symbolRelations) o << "    " << l << "\n";
     o << "  }\n";
@@ -570,18 +570,41 @@ struct Parser {
     m->funcs.push_back(std::move(f));
   }
 
+  void keepRelation(Op* op, std::string text) {
+    if (op->name != "llh.symbol_relation" && op->name != "llh.symbol_relation_map" && op->name != "llh.symbol_binary_relation") return;
+    Module::ParsedRelation r;
+    while (!text.empty() && isspace((unsigned char)text.front())) text.erase(text.begin());
+    while (!text.empty() && isspace((unsigned char)text.back())) text.pop_back();
+    r.text = text;
+    if (const Attr* a = op->attr("relation_kind")) { size_t lt = a->s.find('<'), gt = a->s.rfind('>'); r.kind = lt != std::string::npos && gt != std::string::npos ? a->s.substr(lt + 1, gt - lt - 1) : a->s; }
+    if (const Attr* a = op->attr("symbol")) r.symbol = a->s;
+    if (const Attr* a = op->attr("relation")) r.relation = a->s;
+    if (op->name != "llh.symbol_relation") r.kind = op->name;
+    m->parsedRelations.push_back(r);
+  }
+
   void moduleBody() {
     for (;;) {
       if (eof() || peek("}")) return;
       if (eatWord("func.func")) { function(); continue; }
-      if (peekWord("module") || peekWord("builtin.module")) {  // nested module (e.g. @__symbol__): skipped
+      if (peekWord("module") || peekWord("builtin.module")) {  // nested module (@__symbol__ and the like): only its symbol relations are kept
         ident(); if (eat("@")) ident();
         if (eatWord("attributes")) attrDict("{", "}");
-        balanced('{', '}');
+        expect("{");
+        m->hasSymbolModule = true;
+        while (!peek("}")) {
+          if (eof()) fail("unterminated nested module");
+          const size_t b = p;
+          Func dummy; operation(dummy);
+          if (!dummy.ops.empty()) keepRelation(dummy.ops.back(), s.substr(b, p - b));
+        }
+        expect("}");
         continue;
       }
       if (peek("\"llh.symbolic_int\"") || peek("\"llh.")) {  // module-level symbol declarations: kept, in order, for printing
+        const size_t opBegin = p;
         Func dummy; operation(dummy);
+        if (!dummy.ops.empty()) keepRelation(dummy.ops.back(), s.substr(opBegin, p - opBegin));
         if (!dummy.ops.empty() && dummy.ops.back()->name == "llh.symbolic_int")
           if (const Attr* n = dummy.ops.back()->attr("sym_name")) {
             bool known = false;

@@ -100,6 +100,11 @@ struct Module {
   std::vector<std::string> leadingLines;  // "#map = ..." aliases kept verbatim
   std::vector<std::string> symbolRelations;   // generic-form "llh.symbol_relation" lines printed after the functions
   std::vector<std::string> symbolDecls;   // names declared as "llh.symbolic_int" ops at the head of the module body
+  // relations read from the input (module level or the nested module @__symbol__): kind ("EQ", "GE", ...), the two
+  // symbols, and the op as written
+  struct ParsedRelation { std::string kind, symbol, relation, text; };
+  std::vector<ParsedRelation> parsedRelations;
+  bool hasSymbolModule = false;           // print `module @__symbol__ { ... }` even when it holds no relation
   Value* newValue(const Type& t, const std::string& name = "");
   Op* newOp(const std::string& name);
   Func* entrance();

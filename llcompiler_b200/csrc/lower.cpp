@@ -1315,7 +1315,15 @@ struct Lowering {
         const Attr* s = findAttr(attrs, "func.input_symbol_" + std::to_string(d));
         std::string name = s ? s->s : "";
         if (a->type.dims[d] != kDynamic) { shape.push_back(Expr(a->type.dims[d])); continue; }
-        if (name.empty()) name = "s" + std::to_string(fresh++);
+        // an encoding the argument's type already carries names the extent (text that went through infer-symbol-shape before)
+        if (name.empty() && d < a->type.encoding.size()) {
+          const std::string& e = a->type.encoding[d];
+          bool plain = !e.empty() && (isalpha((unsigned char)e[0]) || e[0] == '_');
+          for (char ch : e) if (!isalnum((unsigned char)ch) && ch != '_') plain = false;
+          if (plain) name = e;
+        }
+        if (name.empty()) { do name = "s" + std::to_string(fresh++); while (seen.count(name)); }
+        seen.insert(name);
         if (name[0] == 'c' && name.size() > 1 && std::isdigit((unsigned char)name[1])) { shape.push_back(Expr(std::stoll(name.substr(1)))); continue; }
         // a torch symbol expression such as "2*s0" cannot name an input extent; plain names only
         shape.push_back(Expr::sym(name));
@@ -1667,7 +1675,52 @@ namespace llc {
 // (the reference pass: src/Dialect/LLH/SymbolInfer/InferSymbolShape.cpp:61-175).  Constant
 // extents are named c<value>, input symbols keep their names, derived extents are printed as
 // expressions where the reference would mint a fresh symbol plus a relation.
+// Symbols that the input declares equal (`llh.symbol_relation` of kind EQ, usually in the nested module @__symbol__) become
+// one symbol: the `relation` side is renamed to the `symbol` side wherever it occurs - encodings of types, `symbol`
+// attributes, encoding attributes of bind ops, argument attributes - and its declaration is dropped (the reference folds
+// such relations in its canonicalisation of the symbol ops, LLHCanonicalize of SymbolRelationOp).
+static void unifyEqualSymbols(Module& m) {
+  std::map<std::string, std::string> to;
+  auto find = [&](std::string n) { for (auto it = to.find(n); it != to.end(); it = to.find(n)) n = it->second; return n; };
+  for (auto& r : m.parsedRelations)
+    if (r.kind == "EQ" && !r.symbol.empty() && !r.relation.empty()) {
+      const std::string a = find(r.symbol), b = find(r.relation);
+      if (a != b) to[b] = a;
+    }
+  if (to.empty()) return;
+  auto renameText = [&](std::string& text) {           // "@name" tokens inside attribute text
+    std::string out;
+    for (size_t i = 0; i < text.size();) {
+      if (text[i] == '@') {
+        size_t j = i + 1;
+        while (j < text.size() && (isalnum((unsigned char)text[j]) || text[j] == '_')) ++j;
+        out += "@" + find(text.substr(i + 1, j - i - 1));
+        i = j;
+      } else out += text[i++];
+    }
+    text = out;
+  };
+  std::function<void(Attr&)> renameAttr = [&](Attr& a) {
+    if (a.kind == Attr::SymRef) a.s = find(a.s);
+    else if (a.kind == Attr::Enum || a.kind == Attr::Raw) renameText(a.s);
+    else if (a.kind == Attr::Str && to.count(a.s)) a.s = find(a.s);
+    for (auto& e : a.elems) renameAttr(e);
+    for (auto& kv : a.dict) renameAttr(kv.second);
+  };
+  for (auto& v : m.valueStore) for (auto& n : v->type.encoding) n = find(n);
+  for (auto& op : m.opStore) { for (auto& kv : op->props) renameAttr(kv.second); for (auto& kv : op->attrs) renameAttr(kv.second); }
+  for (auto& f : m.funcs) {
+    for (auto& al : f.argAttrs) for (auto& kv : al) renameAttr(kv.second);
+    for (auto& t : f.resultTypes) for (auto& n : t.encoding) n = find(n);
+  }
+  std::vector<std::string> decls;
+  for (auto& d : m.symbolDecls) if (!to.count(d)) decls.push_back(d);
+  m.symbolDecls = decls;
+}
+
 void runInferSymbolShape(Module& m) {
+  unifyEqualSymbols(m);
+  const std::set<std::string> declaredBefore(m.symbolDecls.begin(), m.symbolDecls.end());
   runOperationLegalization(m);
   CompileOptionsData opts;
   Lowering L(m, opts);
@@ -1771,12 +1824,21 @@ void runInferSymbolShape(Module& m) {
   for (auto& n : m.symbolDecls) {
     bool plain = !n.empty() && n[0] == 's';
     for (char c : n) if (!isalnum((unsigned char)c) && c != '_') plain = false;
-    if (!plain) continue;
+    if (!plain || declaredBefore.count(n)) continue;     // the relation is recorded when a symbol is created, not for one the input declares
     anyDynamic = true;
     m.symbolRelations.push_back("\"llh.symbol_relation\"() <{relation = @c1, relation_kind = #llh.SymbolRelation<GE>, symbol = @" + n + "}> : () -> ()");
   }
   if (anyDynamic && declared.insert("c1").second) m.symbolDecls.push_back("c1");
   for (auto& l : relationMaps) m.symbolRelations.push_back(l);
+  // relations the input came with stay, except the equalities folded above and those between constants only
+  for (auto& r : m.parsedRelations) {
+    auto isConstName = [](const std::string& n) { return n.size() > 1 && n[0] == 'c' && isdigit((unsigned char)n[1]); };
+    if (r.kind == "EQ") continue;
+    if ((r.symbol.empty() || isConstName(r.symbol)) && (r.relation.empty() || isConstName(r.relation))) continue;
+    m.symbolRelations.push_back(r.text);
+  }
+  m.parsedRelations.clear();
+  m.hasSymbolModule = true;
   if (f) {
     f->resultTypes.clear();
     for (Op* op : f->ops) if (op->name == "func.return") for (Value* v : op->operands) f->resultTypes.push_back(v->type);

@@ -16,12 +16,11 @@ PASSES = {"--infer-symbol-shape": "infer-symbol-shape", "-infer-symbol-shape": "
           "--remove-redundant-ops": "remove-redundant-ops", "--decompose-ops": "decompose-ops", "--transform-layout": "transform-layout",
           "--canonicalize": "canonicalize", "-canonicalize": "canonicalize", "--inline": "inline", "--cse": "cse",
           "--unload-and-bind-encoding": "unload-and-bind-encoding"}
-# functions of each file whose CHECK lines hold on this implementation's output (None: all of them); the one left out
-# needs symbols unified through EQ relations read from a nested module
+# functions of each file whose CHECK lines hold on this implementation's output (None: all of them)
 EXPECTED = {
     "infer_symbol_shape.mlir": None,
     "extra_symbol_infer_shape.mlir": None,
-    "canonicalize_symbol.mlir": {"sink_symbol_bind", "main"},
+    "canonicalize_symbol.mlir": None,
     "remove_redundant_ops.mlir": None,      # all of them
     "operation-legalization.mlir": None,
     "decompose_ops.mlir": None,
