@@ -1239,6 +1239,40 @@ struct Lowering {
     }
     tvs[op->results[0]] = makeView(o, raw(xv).isConst);
   }
+  // llh.cat (LLHOps.td: CatOp, `dim` attribute): the result is one buffer, every operand is written into its range of it
+  // along `dim` by an elementwise step of its own (a lazy operand is evaluated straight into its range).
+  void cat(Op* op) {
+    if (op->operands.empty()) fail("llh.cat without operands");
+    const Attr* da = op->attr("dim");
+    std::vector<TV*> ts;
+    for (Value* v : op->operands) { TV& t = get(v); settle(t); ts.push_back(&t); }
+    const size_t r = ts[0]->shape.size();
+    int64_t dim = da ? da->i : 0;
+    if (dim < 0) dim += (int64_t)r;
+    if (dim < 0 || dim >= (int64_t)r) fail("llh.cat: dim out of range");
+    std::vector<Expr> shape = ts[0]->shape;
+    Expr along(0);
+    for (TV* t : ts) {
+      if (t->shape.size() != r) fail("llh.cat: operands of different rank");
+      for (size_t d = 0; d < r; ++d) if ((int64_t)d != dim && !(t->shape[d] == shape[d])) fail("llh.cat: operands differ outside the concatenated dim");
+      along = along + t->shape[dim];
+    }
+    shape[dim] = along;
+    DType dt = op->results[0]->type.elt == DType::None ? ts[0]->dtype : op->results[0]->type.elt;
+    bool allConst = true;
+    for (TV* t : ts) allConst = allConst && t->isConst;
+    if (shapesOnly) { TV t; t.kind = TV::ViewK; t.dtype = dt; t.shape = shape; tvs[op->results[0]] = t; return; }
+    View out = freshView(dt, shape, allConst);
+    Expr at(0);
+    for (TV* t : ts) {
+      View part = out;
+      part.offset = out.offset + at * out.strides[dim];
+      part.shape = t->shape;
+      emitEltwise(operandNode(*t, t->shape), part, allConst && numelOf(shape).isConst());
+      at = at + t->shape[dim];
+    }
+    tvs[op->results[0]] = makeView(out, allConst);
+  }
   void extract(Op* op) {
     View x = viewOf(op->operands[0]);
     Expr idx = scalarOf(op->operands[1]);
@@ -1513,6 +1547,7 @@ struct Lowering {
       else if (s == "transpose") transpose(op);
       else if (s == "broadcast_to" || s == "expand") broadcastTo(op);
       else if (s == "stride_slice") strideSlice(op);
+      else if (s == "cat") cat(op);
       else if (s == "extract") extract(op);
       else if (s == "symbolic_bind" || s == "encoding_bind" || s == "symbol_bind" || s == "print" || s == "aot" ||
                s == "symbol_relation" || s == "symbol_relation_map" || s == "symbol_binary_relation") continue;

@@ -28,7 +28,7 @@ import torch
 import torch.fx
 from torch.fx.passes.shape_prop import TensorMetadata
 
-from ..dialect.llh import (DYNAMIC, Block, Op, TensorType, Value, array_i64, bool_attr, enum_attr,
+from ..dialect.llh import (DYNAMIC, Block, Op, TensorType, Value, array_i64, bool_attr, dense_attr, enum_attr,
                            f64_attr, i64_attr, print_module, str_attr)
 
 INT64_MAX = 9223372036854775807
@@ -320,6 +320,63 @@ def _expand(ctx, node):
     rank_in, rank_out = x.type.rank, len(fake.shape)
     return ctx.block.op("llh.broadcast_to", [x] + _dims_of(ctx, fake), [tensor_type_of(fake)],
                         {"cast_dims": array_i64(range(rank_out - rank_in, rank_out))})
+
+
+def _filled(ctx, node, value):
+    """A tensor of the node's shape holding one value: a one-element constant broadcast to the shape, which the lowering
+    keeps as a constant of the expression it is used in (llcompiler/importer/fx_op_translate/alloc_ops.py:83-100)."""
+    fake = _meta(node)
+    rt = tensor_type_of(fake)
+    const_op = ctx.block.op("llh.constant", [], [TensorType([1], rt.elt)], {"value": dense_attr(value, TensorType([1], rt.elt))})
+    if len(fake.shape) == 0:
+        return const_op
+    const = const_op.result
+    x = ctx.block.op("llh.reshape", [const] + [ctx.block.constant_i64(1)] * len(fake.shape), [TensorType([1] * len(fake.shape), rt.elt)]).result
+    return ctx.block.op("llh.broadcast_to", [x] + _dims_of(ctx, fake), [rt], {"cast_dims": array_i64(range(len(fake.shape)))})
+
+
+@translator("aten::full")
+def _full(ctx, node):
+    return _filled(ctx, node, node.args[1])
+
+
+@translator("aten::zeros", "aten::zeros_like", "aten::new_zeros")
+def _zeros(ctx, node):
+    return _filled(ctx, node, 0)
+
+
+@translator("aten::ones", "aten::ones_like", "aten::new_ones")
+def _ones(ctx, node):
+    return _filled(ctx, node, 1)
+
+
+@translator("aten::full_like")
+def _full_like(ctx, node):
+    return _filled(ctx, node, node.args[1])
+
+
+@translator("aten::scalar_tensor")
+def _scalar_tensor(ctx, node):
+    # llcompiler/importer/fx_op_translate/alloc_ops.py:72-80
+    t = TensorType([1], tensor_type_of(_meta(node)).elt)
+    return ctx.block.op("llh.constant", [], [t], {"value": dense_attr(node.args[0], t)})
+
+
+@translator("aten::empty.memory_format", "aten::empty", "aten::empty_like", "aten::new_empty")
+def _empty(ctx, node):
+    # uninitialised storage of the node's extents (llcompiler/importer/fx_op_translate/alloc_ops.py:46-69)
+    fake = _meta(node)
+    return ctx.block.op("llh.empty", _dims_of(ctx, fake), [tensor_type_of(fake)])
+
+
+@translator("aten::cat")
+def _cat(ctx, node):
+    # llh.cat with the dim as an attribute (llcompiler/importer/fx_op_translate/cat.py:39-57)
+    dim = node.kwargs["dim"] if "dim" in node.kwargs else (node.args[1] if len(node.args) > 1 else 0)
+    fake = _meta(node)
+    if dim < 0:
+        dim += len(fake.shape)
+    return ctx.block.op("llh.cat", [_arg(ctx, a) for a in node.args[0]], [tensor_type_of(fake)], {"dim": i64_attr(dim)})
 
 
 @translator("aten::convolution")

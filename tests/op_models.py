@@ -190,6 +190,22 @@ class SliceClamped(nn.Module):
         return x[:, 2:100] + x[:, -3:]           # an end past the extent is clamped, a negative start counts from the end
 
 
+class CatAlongDims(nn.Module):
+    def forward(self, x):
+        a = torch.cat([x, torch.relu(x), x * 2.0], dim=1)        # a view, a lazy expression and another one, along a middle dim
+        b = torch.cat((a, a[..., :5]), dim=-1)                  # along the last dim, ragged extents
+        return torch.cat([b, b], 0)
+
+
+class Allocations(nn.Module):
+    def forward(self, x):
+        z = torch.zeros(3, 24, 20)
+        o = torch.ones_like(x)
+        f = torch.full((24, 20), 0.5)
+        e = torch.empty(3, 3, 24, 20)                            # uninitialised: only its shape may matter
+        return (x + z) * o + f + torch.zeros_like(e) + torch.scalar_tensor(2.0)
+
+
 def _g(seed):
     return torch.Generator().manual_seed(seed)
 
@@ -224,6 +240,8 @@ OP_CASES = {
     "addmm_beta_alpha": (AddmmBetaAlpha, lambda: (torch.randn(10, 24, generator=_g(28)),), False),
     "slice_clamped": (SliceClamped, lambda: (torch.randn(6, 5, 7, generator=_g(29)),), True),
     "layer_norm_gelu": (LayerNormGelu, lambda: (torch.randn(4, 6, 48, generator=_g(26)),), False),
+    "cat": (CatAlongDims, lambda: (torch.randn(3, 4, 6, 7, generator=_g(30)),), True),
+    "allocations": (Allocations, lambda: (torch.randn(3, 3, 24, 20, generator=_g(31)),), False),
 }
 
 
