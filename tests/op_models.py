@@ -199,11 +199,12 @@ class CatAlongDims(nn.Module):
 
 class Allocations(nn.Module):
     def forward(self, x):
-        z = torch.zeros(3, 24, 20)
+        d = x.device
+        z = torch.zeros(3, 24, 20, device=d)
         o = torch.ones_like(x)
-        f = torch.full((24, 20), 0.5)
-        e = torch.empty(3, 3, 24, 20)                            # uninitialised: only its shape may matter
-        return (x + z) * o + f + torch.zeros_like(e) + torch.scalar_tensor(2.0)
+        f = torch.full((24, 20), 0.5, device=d)
+        e = torch.empty(3, 3, 24, 20, device=d)                  # uninitialised: only its shape may matter
+        return (x + z) * o + f + torch.zeros_like(e) + torch.scalar_tensor(2.0, device=d)
 
 
 def _g(seed):
