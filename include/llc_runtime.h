@@ -76,8 +76,8 @@ int llc_compile(const char* mlir_text, const LlcOptions* options, char* out_path
  * a buffer owned by the library (valid until the next call on this thread).  This is what the
  * reference's llc-opt driver does for its lit tests (tools/llc-opt/llc-opt.cpp:37-60).
  * Passes: "parse", "operation-legalization", "remove-redundant-ops", "fuse-softmax", "infer-symbol-shape",
- * "decompose-ops", "transform-layout", "canonicalize", "inline" (the folders), "cse", "unload-and-bind-encoding",
- * "lower" (prints the kernel plan); a comma-separated list is applied in order. */
+ * "decompose-ops", "transform-layout", "canonicalize", "inline" (the folders), "cse", "symbol-cse",
+ * "unload-and-bind-encoding", "lower" (prints the kernel plan); a comma-separated list is applied in order. */
 int llc_run_pass(const char* mlir_text, const char* pass, const LlcOptions* options, const char** out_text);
 
 /* Replaces llc::compiler::Execution::load (src/Compiler/Execution.cpp:10-19): reads the plan,

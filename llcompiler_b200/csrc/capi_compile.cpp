@@ -85,6 +85,7 @@ extern "C" int llc_run_pass(const char* text, const char* pass, const LlcOptions
         else if (one == "canonicalize") runCanonicalize(*m);
         else if (one == "inline") runFold(*m);
         else if (one == "cse") runCse(*m);
+        else if (one == "symbol-cse") runSymbolCse(*m);
         else if (one == "unload-and-bind-encoding") runUnloadAndBindEncoding(*m);
         else if (one == "lower") { checkOptions(d); result += lowerToPlan(*m, d).str(); result += "// -----\n"; printedPlan = true; break; }
         else return setError(LLC_ERR_ARGUMENT, "unknown pass '" + one + "'");

@@ -202,7 +202,11 @@ std::string Module::str() const {
       }
       for (size_t i = 0; i < op->results.size(); ++i) o << (i ? ", " : "") << nm(op->results[i]);
       if (!op->results.empty()) o << " = ";
-      o << "\"" << op->name << "\"(";
+      if (op->written == "arith.constant" && op->attrs.empty() && op->props.size() == 1 && op->props[0].first == "value") {
+        o << "arith.constant " << op->props[0].second.str() << "\n";      // MLIR's custom form: `arith.constant 0 : index`
+        continue;
+      }
+      o << "\"" << (op->written.empty() ? op->name : op->written) << "\"(";
       for (size_t i = 0; i < op->operands.size(); ++i) o << (i ? ", " : "") << nm(op->operands[i]);
       o << ")";
       if (!op->props.empty()) o << " <{" << attrListStr(op->props) << "}>";
@@ -505,6 +509,7 @@ struct Parser {
         }
       } else if (name == "arith.constant") {
         op = m->newOp("llh.constant");
+        op->written = name;
         if (peek("{")) op->attrs = attrDict("{", "}");
         Attr v = attrValue();
         op->props.emplace_back("value", v);
@@ -520,6 +525,7 @@ struct Parser {
         static const std::map<std::string, std::string> same = {{"tensor.dim", "llh.dim"}, {"arith.addi", "llh.add"}, {"arith.subi", "llh.sub"},
                                                                 {"arith.muli", "llh.mul"}, {"arith.divsi", "llh.div"}, {"arith.index_cast", "llh.scalar_cast"}};
         op = m->newOp(same.at(name));
+        op->written = name;
         if (peek("{")) op->attrs = attrDict("{", "}");
         for (;;) { op->operands.push_back(use(valueName())); if (!eat(",")) break; }
         expect(":");

@@ -78,6 +78,7 @@ struct Op {
   AttrList attrs;    // {...}
   std::vector<Value*> results;
   bool erased = false;
+  std::string written;   // the op's name in the input when it was read from another dialect's custom form ("tensor.dim", "arith.subi", ...)
   const Attr* attr(const std::string& n) const { const Attr* a = findAttr(props, n); return a ? a : findAttr(attrs, n); }
   void setProp(const std::string& n, const Attr& a);
 };

@@ -392,4 +392,45 @@ void runUnloadAndBindEncoding(Module& m) {
   m.recomputeUsers();
 }
 
+// symbol-cse (the reference: src/Dialect/LLH/Transforms/SymbolCSE.cpp, driven by test/Dialect/LLH/symbol_infer/symbol_cse.mlir):
+// after infer-symbol-shape every integer scalar carries `symbol = @...`.  Two values with the same symbol are the same
+// number, so the later one is replaced by the earlier; a value whose symbol is a constant c<N> is replaced by that
+// constant (written `arith.constant N : index` when the value came from the arith / tensor dialects).
+void runSymbolCse(Module& m) {
+  for (auto& f : m.funcs) {
+    std::map<std::string, Value*> first;
+    std::vector<Op*> out;
+    auto replaceUses = [&](Value* from, Value* to) {
+      for (Op* u : f.ops) for (auto& v : u->operands) if (v == from) v = to;
+    };
+    for (Op* op : f.ops) {
+      if (op->erased) continue;
+      const Attr* sym = op->results.size() == 1 && !op->results[0]->type.isTensor() ? op->attr("symbol") : nullptr;
+      if (!sym || sym->kind != Attr::SymRef) { out.push_back(op); continue; }
+      const std::string& name = sym->s;
+      const bool isConstSym = name.size() > 1 && name[0] == 'c' && isdigit((unsigned char)name[1]);
+      const bool isConstOp = op->name == "llh.constant";
+      if (isConstSym && !isConstOp) {
+        Op* c = m.newOp("llh.constant");
+        if (!op->written.empty()) c->written = "arith.constant";
+        Attr v = Attr::integer(std::stoll(name.substr(1)));
+        if (!op->written.empty()) v.type = Type::scalar(DType::Index);
+        c->props.emplace_back("value", v);
+        Value* r = m.newValue(op->results[0]->type);
+        r->def = c; c->results.push_back(r);
+        out.push_back(c);
+        replaceUses(op->results[0], r);
+        op->erased = true;
+        continue;
+      }
+      auto it = first.find(name);
+      if (it != first.end() && !isConstOp) { replaceUses(op->results[0], it->second); op->erased = true; continue; }
+      if (it == first.end()) first[name] = op->results[0];
+      out.push_back(op);
+    }
+    f.ops = out;
+  }
+  m.recomputeUsers();
+}
+
 }  // namespace llc

@@ -79,6 +79,7 @@ Plan lowerToPlan(Module& m, const CompileOptionsData& opts);
 
 // LLH-level passes that are useful on their own (and are what the structure tests drive).
 void runOperationLegalization(Module& m);
+void runSymbolCse(Module& m);   // integer scalars that carry the same symbol become one value; a constant symbol becomes a constant
 void runRemoveRedundantOps(Module& m);
 void runFuseSoftmax(Module& m);
 void runInferSymbolShape(Module& m);   // writes #llh.encoding onto every tensor type

@@ -13,7 +13,8 @@ import sys
 
 from . import _capi
 
-PASSES = ("parse", "operation-legalization", "remove-redundant-ops", "fuse-softmax", "infer-symbol-shape", "lower")
+PASSES = ("parse", "operation-legalization", "remove-redundant-ops", "fuse-softmax", "infer-symbol-shape", "decompose-ops", "transform-layout",
+          "canonicalize", "inline", "cse", "symbol-cse", "unload-and-bind-encoding", "lower")
 
 
 def main(argv=None) -> int:
@@ -30,9 +31,8 @@ def main(argv=None) -> int:
     outs = []
     for piece in pieces:
         try:
-            cur = piece
-            for n in names or ["parse"]:
-                cur = _capi.run_pass(cur, n).split("// -----")[0]
+            # the passes run as one pipeline over the parsed module, as llc-opt's do
+            cur = _capi.run_pass(piece, ",".join(names or ["parse"])).split("// -----")[0]
             outs.append(cur.rstrip("\n"))
         except _capi.LlcError as e:
             sys.stderr.write(f"error: {e}\n")

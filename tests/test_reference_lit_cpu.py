@@ -15,12 +15,13 @@ REF = reference_path("test", "Dialect", "LLH") or ""
 PASSES = {"--infer-symbol-shape": "infer-symbol-shape", "-infer-symbol-shape": "infer-symbol-shape", "--operation-legalization": "operation-legalization",
           "--remove-redundant-ops": "remove-redundant-ops", "--decompose-ops": "decompose-ops", "--transform-layout": "transform-layout",
           "--canonicalize": "canonicalize", "-canonicalize": "canonicalize", "--inline": "inline", "--cse": "cse",
-          "--unload-and-bind-encoding": "unload-and-bind-encoding"}
+          "--unload-and-bind-encoding": "unload-and-bind-encoding", "--symbol-cse": "symbol-cse"}
 # functions of each file whose CHECK lines hold on this implementation's output (None: all of them)
 EXPECTED = {
     "infer_symbol_shape.mlir": None,
     "extra_symbol_infer_shape.mlir": None,
     "canonicalize_symbol.mlir": None,
+    "symbol_cse.mlir": None,
     "remove_redundant_ops.mlir": None,      # all of them
     "operation-legalization.mlir": None,
     "decompose_ops.mlir": None,
