@@ -204,6 +204,13 @@ def _translate(ctx: _Ctx, n: OnnxNode) -> None:
                                     _window(x.type.shape[3], k[1], stride[1], pads[1], pads[3], dil[1], ceil)]
         emit("llh.max_pool", [x], shape, {"dilation": array_i64(dil), "pad": array_i64(pads), "kernel_shape": array_i64(k),
                                           "stride": array_i64(stride), "ceil_mode": bool_attr(ceil)})
+    elif op == "Concat":
+        xs = [ctx.get(i) for i in n.inputs]
+        axis = int(a.get("axis", 0)) % x.type.rank
+        along = [v.type.shape[axis] for v in xs]
+        shape = list(x.type.shape)
+        shape[axis] = DYNAMIC if DYNAMIC in along else sum(along)
+        emit("llh.cat", xs, shape, {"dim": i64_attr(axis)})
     elif op == "GlobalAveragePool":
         emit("llh.adaptive_average_pool", [x], x.type.shape[:2] + [1, 1], {"out_size": array_i64([1, 1])})
     elif op in ("Flatten", "Reshape"):

@@ -118,3 +118,19 @@ def test_onnx_transformer_encoder_layer():
         got = fn(ids)
         assert tuple(got.shape) == (batch, seq, d) and max_rel_err(got, want) < 1e-4
     assert len(comp.compiled) == 1
+
+
+def test_onnx_concat():
+    w = _np(6, 8, scale=0.3)
+    nodes = [("Relu", ["x"], ["r"], {}), ("Concat", ["x", "r", "x"], ["c"], {"axis": 1}), ("Concat", ["c", "c"], ["d"], {"axis": 0}),
+             ("Gemm", ["d", "w"], ["y"], {"transB": 1})]
+    data = W.build_model(nodes, {"w": w}, [("x", [4, 2])], [("y", [8, 8])])
+    with pytest.raises(Exception):
+        InterpreterCompiler().compile_onnx(data)(torch.randn(4, 2))           # 3 * 2 = 6 columns against a weight of 8: refused
+    w = _np(8, 6, scale=0.3)
+    data = W.build_model(nodes, {"w": w}, [("x", [4, 2])], [("y", [8, 8])])
+    fn = InterpreterCompiler().compile_onnx(data)
+    x = torch.randn(4, 2)
+    c = torch.cat([x, torch.relu(x), x], 1)
+    want = F.linear(torch.cat([c, c], 0), torch.from_numpy(w))
+    assert max_rel_err(fn(x), want) < 1e-5
