@@ -47,12 +47,13 @@ def _worker(rank, world, port, total, q):
         dist.destroy_process_group()
 
 
-@pytest.mark.parametrize("total", [64, 7])
-def test_two_ranks_gather_the_full_batch(total):
+@pytest.mark.parametrize("world,total", [(2, 64), (2, 7), (8, 64), (8, 20)])
+def test_ranks_gather_the_full_batch(world, total):
+    # eight ranks also compile the same graph at the same time through one cache directory, as the ranks of an 8-GPU job do
     ctx = mp.get_context("spawn")
     q = ctx.Queue()
-    port = 29500 + (os.getpid() % 1000) + total
-    procs = [ctx.Process(target=_worker, args=(r, 2, port, total, q)) for r in range(2)]
+    port = 29500 + (os.getpid() % 1000) + total + 100 * world
+    procs = [ctx.Process(target=_worker, args=(r, world, port, total, q)) for r in range(world)]
     for p in procs:
         p.start()
     results = [q.get(timeout=300) for _ in procs]
