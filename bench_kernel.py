@@ -10,6 +10,7 @@ command that profiler captures are taken on, and the per-kernel timing tool behi
   python bench_kernel.py gather     ROWS D VOCAB DTYPE [REPS]
   python bench_kernel.py eltwise    ROWS D DTYPE [REPS]         (out = a + b[broadcast row])
   python bench_kernel.py nchw2nhwc  N C H W DTYPE [REPS]        (input re-layout with channel padding and halo)
+  python bench_kernel.py push       BYTES NDST [REPS]           (the gather's multi-destination copy, destinations on this GPU)
 PREC: bf16 | tf32 | tf32x3 | fp32      DTYPE: bf16 | f32
 Every repetition is timed with CUDA events on the launching stream after an L2 flush (a 256 MB write); the line
 printed is the median: `<kind> ... ms <t> TFLOP/s <x> GB/s <y> status <word>` with the algorithmic FLOPs and bytes.
@@ -146,6 +147,17 @@ def main(argv):
         out = torch.empty(n, h, w + 8, cpad, device="cuda", dtype=dt)
         ms = timed(lambda: G.nchw_to_nhwc_wide(x, out, cpad, 3, w + 8), reps)
         report(" ".join(argv), ms, 0.0, (x.numel() + out.numel()) * x.element_size())
+    elif kind == "push":
+        import ctypes
+        nbytes, ndst = int(argv[1]), int(argv[2])
+        reps = int(argv[3]) if len(argv) > 3 else 7
+        src = torch.randint(0, 256, (nbytes,), dtype=torch.uint8, device="cuda")
+        dsts = [torch.empty(nbytes, dtype=torch.uint8, device="cuda") for _ in range(ndst)]
+        ptrs = (ctypes.c_void_p * ndst)(*[d.data_ptr() for d in dsts])
+        st = torch.cuda.current_stream().cuda_stream
+        ms = timed(lambda: C.check(C.lib().llc_cuda_push_rows(src.data_ptr(), ptrs, ndst, 0, nbytes, st)), reps)
+        assert all(torch.equal(d, src) for d in dsts)
+        report(" ".join(argv), ms, 0.0, (1 + ndst) * nbytes)
     else:
         raise SystemExit(__doc__)
     torch.cuda.synchronize()
