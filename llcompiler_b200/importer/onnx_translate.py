@@ -204,6 +204,69 @@ def _translate(ctx: _Ctx, n: OnnxNode) -> None:
                                     _window(x.type.shape[3], k[1], stride[1], pads[1], pads[3], dil[1], ceil)]
         emit("llh.max_pool", [x], shape, {"dilation": array_i64(dil), "pad": array_i64(pads), "kernel_shape": array_i64(k),
                                           "stride": array_i64(stride), "ceil_mode": bool_attr(ceil)})
+    elif op in ("ReduceMean", "ReduceSum", "ReduceMax", "ReduceMin"):
+        # axes: an attribute up to opset 12 (17 for the others), a constant input after that
+        axes = a.get("axes")
+        if axes is None and len(n.inputs) > 1 and n.inputs[1]:
+            axes = ctx.const_ints(n.inputs[1])
+        axes = sorted(int(v) % x.type.rank for v in (axes if axes is not None else range(x.type.rank)))
+        keep = int(a.get("keepdims", 1))
+        red_shape = [d for i, d in enumerate(x.type.shape) if i not in axes]
+        name = {"ReduceMean": "llh.reduce_mean", "ReduceSum": "llh.reduce_sum", "ReduceMax": "llh.reduce_max", "ReduceMin": "llh.reduce_min"}[op]
+        if not keep:
+            emit(name, [x], red_shape or [1], {"axis": array_i64(axes)})
+        else:                                   # keepdims = reduce + reshape, as the FX importer writes it
+            red = b.op(name, [x], [TensorType(red_shape or [1], x.type.elt)], {"axis": array_i64(axes)}).result
+            shape = [1 if i in axes else d for i, d in enumerate(x.type.shape)]
+            dims = [b.constant_i64(1) if i in axes else (b.dim(x, i) if d == DYNAMIC else b.constant_i64(d)) for i, d in enumerate(x.type.shape)]
+            emit("llh.reshape", [red] + dims, shape)
+    elif op == "Pow":
+        if n.inputs[1] not in ctx.g.initializers or ctx.g.initializers[n.inputs[1]].size != 1:
+            raise NotImplementedError("Pow with an exponent that is not a constant scalar")
+        e = float(ctx.g.initializers[n.inputs[1]].reshape(-1)[0])
+        emit("llh.pow", [x, b.scalar_tensor(e, x.type.elt)], x.type.shape)
+    elif op == "Cast":
+        to = {FLOAT: "f32", INT64: "i64", 16: "bf16", 10: "f16", 6: "i32", 9: "i1"}.get(int(a.get("to", FLOAT)))
+        if to is None:
+            raise NotImplementedError(f"Cast to ONNX element type {a.get('to')}")
+        emit("llh.convert_to", [x], x.type.shape, elt=to)
+    elif op == "Where":
+        y, z = ctx.get(n.inputs[1]), ctx.get(n.inputs[2])
+        shape = _bcast(_bcast(x.type.shape, y.type.shape), z.type.shape)
+        ctx.values[n.outputs[0]] = b.op("llh.where", [x, y, z], [TensorType(shape, y.type.elt)]).result
+    elif op in ("Unsqueeze", "Squeeze"):
+        axes = a.get("axes")
+        if axes is None and len(n.inputs) > 1 and n.inputs[1]:
+            axes = ctx.const_ints(n.inputs[1])
+        if op == "Unsqueeze":
+            rank = x.type.rank + len(axes)
+            axes = sorted(int(v) % rank for v in axes)
+            src = iter(range(x.type.rank))
+            pairs = [(1, None) if i in axes else (lambda j: (x.type.shape[j], j))(next(src)) for i in range(rank)]
+        else:
+            axes = sorted(int(v) % x.type.rank for v in axes) if axes is not None else [i for i, d in enumerate(x.type.shape) if d == 1]
+            pairs = [(d, i) for i, d in enumerate(x.type.shape) if i not in axes]
+        shape = [d for d, _ in pairs] or [1]
+        dims = [b.constant_i64(1) if j is None else (b.dim(x, j) if d == DYNAMIC else b.constant_i64(d)) for d, j in pairs] or [b.constant_i64(1)]
+        emit("llh.reshape", [x] + dims, shape)
+    elif op == "Slice":
+        starts, ends = ctx.const_ints(n.inputs[1]), ctx.const_ints(n.inputs[2])
+        axes = ctx.const_ints(n.inputs[3]) if len(n.inputs) > 3 and n.inputs[3] else list(range(len(starts)))
+        steps = ctx.const_ints(n.inputs[4]) if len(n.inputs) > 4 and n.inputs[4] else [1] * len(starts)
+        rank = x.type.rank
+        lo, hi, st = [0] * rank, list(x.type.shape), [1] * rank
+        for s0, e0, ax, sp in zip(starts, ends, axes, steps):
+            ax %= rank
+            ext = x.type.shape[ax]
+            if ext == DYNAMIC or sp < 1:
+                raise NotImplementedError("Slice along a symbolic extent or with a negative step")
+            s0 = max(0, min(ext, s0 + ext if s0 < 0 else s0))
+            e0 = max(0, min(ext, e0 + ext if e0 < 0 else e0))
+            lo[ax], hi[ax], st[ax] = s0, max(s0, e0), sp
+        shape = [x.type.shape[i] if x.type.shape[i] == DYNAMIC else -(-(hi[i] - lo[i]) // st[i]) for i in range(rank)]
+        ends_v = [b.dim(x, i) if x.type.shape[i] == DYNAMIC else b.constant_i64(hi[i]) for i in range(rank)]
+        emit("llh.stride_slice", [x] + [b.constant_i64(v) for v in lo] + ends_v + [b.constant_i64(v) for v in st], shape,
+             {"operandSegmentSizes": "array<i32: 1, %d, %d, %d>" % (rank, rank, rank)})
     elif op == "Concat":
         xs = [ctx.get(i) for i in n.inputs]
         axis = int(a.get("axis", 0)) % x.type.rank

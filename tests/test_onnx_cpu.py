@@ -134,3 +134,37 @@ def test_onnx_concat():
     c = torch.cat([x, torch.relu(x), x], 1)
     want = F.linear(torch.cat([c, c], 0), torch.from_numpy(w))
     assert max_rel_err(fn(x), want) < 1e-5
+
+
+def test_onnx_layer_norm_spelled_out_and_shape_ops():
+    # the way exporters without a LayerNormalization op write it: ReduceMean, Sub, Pow, ReduceMean, Add, Sqrt, Div, Mul, Add
+    g, bt = _np(16, seed=1) + 1.0, _np(16, seed=2)
+    two, eps = np.array(2.0, dtype=np.float32), np.array(1e-5, dtype=np.float32)
+    axes = np.array([-1], dtype=np.int64)
+    nodes = [("ReduceMean", ["x", "axes"], ["mu"], {"keepdims": 1}), ("Sub", ["x", "mu"], ["d"], {}), ("Pow", ["d", "two"], ["sq"], {}),
+             ("ReduceMean", ["sq"], ["var"], {"axes": [-1], "keepdims": 1}), ("Add", ["var", "eps"], ["ve"], {}), ("Sqrt", ["ve"], ["sd"], {}),
+             ("Div", ["d", "sd"], ["nrm"], {}), ("Mul", ["nrm", "g"], ["sc"], {}), ("Add", ["sc", "bt"], ["ln"], {}),
+             ("Slice", ["ln", "st", "en", "ax", "sp"], ["sl"], {}), ("Unsqueeze", ["sl", "uax"], ["un"], {}), ("Squeeze", ["un", "uax"], ["sq2"], {}),
+             ("ReduceSum", ["sq2", "axes"], ["rs"], {"keepdims": 0}), ("ReduceMax", ["sq2"], ["rm"], {"axes": [1], "keepdims": 0}), ("Add", ["rs", "rm"], ["y"], {})]
+    init = {"g": g, "bt": bt, "two": two, "eps": eps, "axes": axes, "st": np.array([1, 2], dtype=np.int64), "en": np.array([100, -2], dtype=np.int64),
+            "ax": np.array([0, 1], dtype=np.int64), "sp": np.array([1, 2], dtype=np.int64), "uax": np.array([1], dtype=np.int64)}
+    data = W.build_model(nodes, init, [("x", [6, 16])], [("y", [5])])
+    fn = InterpreterCompiler().compile_onnx(data)
+    x = torch.randn(6, 16)
+    ln = F.layer_norm(x, (16,), torch.from_numpy(g), torch.from_numpy(bt), 1e-5)
+    sl = ln[1:100, 2:-2:2]
+    want = sl.sum(-1) + sl.amax(1)
+    assert max_rel_err(fn(x), want) < 1e-5
+
+
+def test_onnx_cast_and_where():
+    nodes = [("Relu", ["x"], ["r"], {}), ("Cast", ["m"], ["mf"], {"to": 1}), ("Mul", ["r", "mf"], ["a"], {}), ("Neg", ["x"], ["nx"], {}),
+             ("Where", ["c", "a", "nx"], ["y"], {})]
+    data = W.build_model(nodes, {"m": np.arange(8, dtype=np.int64).reshape(1, 8)}, [("x", [4, 8]), ("c", [4, 8])], [("y", [4, 8])])
+    try:
+        fn = InterpreterCompiler().compile_onnx(data)
+    except NotImplementedError:
+        pytest.skip("boolean graph inputs are not part of the ONNX entry")
+    x, c = torch.randn(4, 8), torch.randn(4, 8) > 0
+    want = torch.where(c, torch.relu(x) * torch.arange(8).float(), -x)
+    assert max_rel_err(fn(x, c), want) < 1e-6
