@@ -1,11 +1,12 @@
-"""`llc-opt` for the textual LLH surface: runs one pass of the C++ compile library over a file and prints the result,
+"""`llc-opt` for the textual LLH surface: runs passes of the C++ compile library over a file and prints the result,
 the way the reference's lit files drive its tool (`// RUN: llc-opt --split-input-file --<pass> %s | FileCheck %s`,
 test/lit.cfg.py:49-61; tools/llc-opt/llc-opt.cpp:37-60).
 
     python -m llcompiler_b200.llc_opt --infer-symbol-shape [--split-input-file] file.mlir
 
-Passes: --parse, --operation-legalization, --remove-redundant-ops, --fuse-softmax, --infer-symbol-shape, --lower
-(the kernel plan).  `-` reads standard input.
+Passes (several are applied in the order given, as one pipeline): --parse, --operation-legalization,
+--remove-redundant-ops, --fuse-softmax, --infer-symbol-shape, --decompose-ops, --transform-layout, --canonicalize,
+--inline, --cse, --symbol-cse, --unload-and-bind-encoding, --lower (the kernel plan).  `-` reads standard input.
 """
 from __future__ import annotations
 

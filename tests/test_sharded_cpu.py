@@ -62,3 +62,16 @@ def test_ranks_gather_the_full_batch(world, total):
         assert p.exitcode == 0
     for rank, shape, err in results:
         assert shape == (total, 10) and err < 1e-4
+
+
+def test_pipelined_refuses_what_it_cannot_do():
+    from llcompiler_b200.executor import BatchShardedRunner
+    r = BatchShardedRunner(lambda x: x)
+    with pytest.raises(ValueError):
+        next(r.pipelined([(torch.zeros(2, 2),)]))          # no device: the pipelined call needs CUDA streams
+    with pytest.raises(ValueError):
+        BatchShardedRunner(lambda x: x, gather="ring")      # only "nccl" and "peer"
+    # without a process group the gather of a one-rank "group" is the local tensor itself, whatever the mode asked for
+    t = torch.arange(6.0).view(3, 2)
+    got, token = BatchShardedRunner(lambda x: x, gather="peer").gather(t, 3)
+    assert got is t and token is None
